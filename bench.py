@@ -1,0 +1,517 @@
+#!/usr/bin/env python
+"""Benchmark of the THC apply / reduceDim / reduceAll path on B200.
+
+Workload (config "c5" of the baseline): two fp32 tensors of 524288 x 8192 (2^32 elements,
+16 GiB each), N(0,1), split by rows over the ranks.  One step, per rank, through the THC C API:
+    THCudaTensor_cmul(z, x, y); THCudaTensor_add(z, z, 1); THCudaTensor_max(v, i, z, 1, 1);
+    sum-all of z left on the device; NCCL all-reduce of the per-rank partials (N > 1).
+metric = algorithmic HBM bytes of those four calls per second, summed over all ranks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Under torchrun every rank runs this file; rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS_TOTAL = 524288
+COLS = 8192
+# algorithmic bytes per element of one step (compulsory reads + writes of the logical elements):
+# cmul 3*4, add in place 2*4, max read 4, sumall read 4; plus 12 bytes per row of max outputs
+BYTES_PER_ELEM = 12 + 8 + 4 + 4
+BYTES_PER_ROW_EXTRA = 12
+METRIC = "thc_apply_reduce_algorithmic_hbm_throughput"
+UNIT = "GB/s"
+
+
+def step_bytes(rows: int) -> int:
+    return rows * COLS * BYTES_PER_ELEM + rows * BYTES_PER_ROW_EXTRA
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device_index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the TH CPU restatement (oracle port) on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_step(oracle, np, x, y, z, v, i, OP, RED):
+    """One step of the workload on host arrays through the oracle (all of its threads)."""
+    oracle.pointwise(OP["MUL"], z, [x, y])
+    oracle.pointwise(OP["ADD_S"], z, [z], 1.0)
+    vv, ii = oracle.reduce_dim(RED["MAX"], 0, 0, z, 1, with_index=True)
+    s = oracle.reduce_all(RED["SUM"], 0, 0, z)
+    return vv, ii, s
+
+
+def run_cpu(rows: int, steps: int, warmup: int, threads: int | None):
+    import numpy as np
+    from oracle import Oracle
+    from cutorch_b200._lib import OP, RED
+    o = Oracle()
+    nthreads = threads or o.max_threads()
+    o.set_threads(nthreads)
+    rng = np.random.default_rng(1234)
+    x = rng.standard_normal((rows, COLS), dtype=np.float32)
+    y = rng.standard_normal((rows, COLS), dtype=np.float32)
+    z = np.empty_like(x)
+    for _ in range(warmup):
+        cpu_step(o, np, x, y, z, None, None, OP, RED)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(o, np, x, y, z, None, None, OP, RED)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return step_bytes(rows) / dt / 1e9, dt, nthreads
+
+
+def reference_main(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    rows = 4096  # bounded sample: 1/128 of the rows per step, 128 MiB per tensor
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    gbs, dt, nthreads = run_cpu(rows, steps, warmup, None)
+    sample = f"{rows} of {ROWS_TOTAL} rows x {COLS} per step ({steps} steps), scaled by bytes"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt * 1e3 * (ROWS_TOTAL / rows), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c5: cmul, add 1, row max+argmax, sum-all on fp32 524288x8192 (row sample on the host)",
+                   "impl_note": "TH CPU semantics restated in oracle/th_oracle.cpp (torch7's TH is not in the cutorch tree)"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------------------------
+# our arm
+# --------------------------------------------------------------------------------------------
+def ours_main(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from cutorch_b200 import thc, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert ROWS_TOTAL % world == 0
+    rows = ROWS_TOTAL // world
+    if args.rows:
+        rows = args.rows
+    n = rows * COLS
+
+    state = thc.State()
+    stream = torch.cuda.current_stream()
+    state.set_stream(stream.cuda_stream, local)
+    lib = _lib.load_library()
+
+    # synthetic inputs, generated on the device per shard from seed + rank
+    g = torch.Generator(device=dev)
+    g.manual_seed(1000 + rank)
+    x = torch.empty(rows, COLS, dtype=torch.float32, device=dev)
+    y = torch.empty(rows, COLS, dtype=torch.float32, device=dev)
+    z = torch.empty(rows, COLS, dtype=torch.float32, device=dev)
+    chunk = 8192
+    for r0 in range(0, rows, chunk):
+        x[r0:r0 + chunk].normal_(generator=g)
+        y[r0:r0 + chunk].normal_(generator=g)
+    v = torch.empty(rows, 1, dtype=torch.float32, device=dev)
+    idx = torch.empty(rows, 1, dtype=torch.int64, device=dev)
+    partial = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    tx = thc.Tensor.wrap(state, "Float", x.data_ptr(), (rows, COLS))
+    ty = thc.Tensor.wrap(state, "Float", y.data_ptr(), (rows, COLS))
+    tz = thc.Tensor.wrap(state, "Float", z.data_ptr(), (rows, COLS))
+    tv = thc.Tensor.wrap(state, "Float", v.data_ptr(), (rows, 1))
+    ti = thc.Tensor.wrap(state, "Long", idx.data_ptr(), (rows, 1))
+
+    def step():
+        tz.cmul(tx, ty)
+        tz.add(tz, 1.0)
+        tv.max(ti, tz, 1, 1)
+        tz.sumall_to_device(partial.data_ptr())
+        if world > 1:
+            dist.all_reduce(partial)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.thcb200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    launches = lib.thcb200_launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    total_sum = float(partial.item())
+    ms_per_step = ms / args.steps
+    total_bytes = step_bytes(rows) * world
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # per-kernel durations (CUDA events on the launching stream), for the roofline of the dominant kernel
+    def time_call(fn, reps):
+        evs = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            evs.append((a, b))
+        torch.cuda.synchronize()
+        ts = sorted(a.elapsed_time(b) for a, b in evs)
+        return sum(ts) / len(ts), ts[0]
+
+    reps = max(3, min(args.steps, 10))
+    kernels = {}
+    for name, fn, nbytes in (
+        ("cmul contig_vec", lambda: tz.cmul(tx, ty), 12 * n),
+        ("add_scalar contig_vec (in place)", lambda: tz.add(tz, 1.0), 8 * n),
+        ("max+argmax dim1 row_warp", lambda: tv.max(ti, tz, 1, 1), 4 * n + 12 * rows),
+        ("sumall reduce_all", lambda: tz.sumall_to_device(partial.data_ptr()), 4 * n),
+    ):
+        avg, best = time_call(fn, reps)
+        kernels[name] = {"avg_ms": avg, "best_ms": best, "bytes": nbytes, "gbs": nbytes / (avg * 1e-3) / 1e9}
+    peak, peak_src = measured_peaks()
+    dom = kernels["cmul contig_vec"]
+    roofline = {"bound": "hbm", "kernel": "apply_contig_vec_kernel<MUL,float,2> (THCudaTensor_cmul)",
+                "achieved": dom["gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
+                "frac": dom["gbs"] / peak, "frac_of_nominal_8000": dom["gbs"] / 8000.0, "traffic": None,
+                "per_kernel": {k: {"gbs": round(vv["gbs"], 1), "frac": round(vv["gbs"] / peak, 4), "avg_ms": round(vv["avg_ms"], 4)}
+                               for k, vv in kernels.items()}}
+
+    # end to end: host (pinned) inputs -> device -> THC calls -> results back on the host
+    e2e = run_e2e(args, torch, thc, state, stream, dev, rows, world, rank)
+
+    extra = {}
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        srows = 2048
+        gbs, dt, nthreads = run_cpu(srows, 2, 1, None)
+        cpu_baseline = {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port",
+                        "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (2 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
+        if args.configs:
+            extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "c5: THCudaTensor_cmul, _add(1), _max(dim 1, indices), sum-all + all-reduce of partials on fp32 "
+                                   f"{ROWS_TOTAL}x{COLS} split by rows over {world} GPU(s)",
+                       "rows_per_gpu": rows, "cols": COLS, "bytes_per_step": total_bytes,
+                       "l2": "inputs (16 GiB per tensor at N=1) are far larger than the 126 MB L2; no flush needed",
+                       "elements_per_s": rows * COLS * world / (ms_per_step * 1e-3)},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks, "checksum": total_sum,
+        }
+        line.update(extra)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
+    """Same step with HOST inputs: per row chunk, pinned host -> device copies, the four THC
+    calls, and the row results plus the sum copied back, all inside the timed region."""
+    import torch.distributed as dist
+    chunk = min(8192, rows)
+    nchunks = rows // chunk
+    # host side: one pinned chunk pair per slot, refilled from a host array standing for the
+    # caller's data.  The host array is `host_rows` rows, cycled when the shard is larger than
+    # what the box can pin.
+    avail = 0
+    try:
+        for ln in open("/proc/meminfo"):
+            if ln.startswith("MemAvailable"):
+                avail = int(ln.split()[1]) * 1024
+    except OSError:
+        pass
+    need = 2 * rows * COLS * 4
+    budget = max(avail // (3 * max(world, 1)), 2 * chunk * COLS * 4)
+    host_rows = rows if need <= budget else max(chunk, (budget // (2 * COLS * 4)) // chunk * chunk)
+    hx = torch.empty(host_rows, COLS, dtype=torch.float32, pin_memory=True)
+    hy = torch.empty(host_rows, COLS, dtype=torch.float32, pin_memory=True)
+    g = torch.Generator(device=dev)
+    g.manual_seed(2000 + rank)
+    tmp = torch.empty(chunk, COLS, dtype=torch.float32, device=dev)
+    for r0 in range(0, host_rows, chunk):
+        tmp.normal_(generator=g)
+        hx[r0:r0 + chunk].copy_(tmp)
+        tmp.normal_(generator=g)
+        hy[r0:r0 + chunk].copy_(tmp)
+    hv = torch.empty(rows, 1, dtype=torch.float32, pin_memory=True)
+    hi = torch.empty(rows, 1, dtype=torch.int64, pin_memory=True)
+    hs = torch.empty(1, dtype=torch.float64, pin_memory=True)
+    nslots = 2
+    dx = [torch.empty(chunk, COLS, dtype=torch.float32, device=dev) for _ in range(nslots)]
+    dy = [torch.empty(chunk, COLS, dtype=torch.float32, device=dev) for _ in range(nslots)]
+    dz = [torch.empty(chunk, COLS, dtype=torch.float32, device=dev) for _ in range(nslots)]
+    dv = torch.empty(rows, 1, dtype=torch.float32, device=dev)
+    di = torch.empty(rows, 1, dtype=torch.int64, device=dev)
+    parts = torch.zeros(nchunks, dtype=torch.float64, device=dev)
+    total = torch.zeros(1, dtype=torch.float64, device=dev)
+    W = lambda t, kind, shape: thc.Tensor.wrap(state, kind, t.data_ptr(), shape)
+    tx = [W(t, "Float", (chunk, COLS)) for t in dx]
+    ty = [W(t, "Float", (chunk, COLS)) for t in dy]
+    tz = [W(t, "Float", (chunk, COLS)) for t in dz]
+    tparts = W(parts, "Double", (nchunks,))
+    copy_stream = torch.cuda.Stream(device=dev)
+    ready = [torch.cuda.Event() for _ in range(nslots)]
+    freed = [torch.cuda.Event() for _ in range(nslots)]
+
+    def e2e_step():
+        for c in range(nchunks):
+            s = c % nslots
+            h0 = (c * chunk) % host_rows
+            with torch.cuda.stream(copy_stream):
+                if c >= nslots:
+                    copy_stream.wait_event(freed[s])
+                dx[s].copy_(hx[h0:h0 + chunk], non_blocking=True)
+                dy[s].copy_(hy[h0:h0 + chunk], non_blocking=True)
+                ready[s].record(copy_stream)
+            stream.wait_event(ready[s])
+            tz[s].cmul(tx[s], ty[s])
+            tz[s].add(tz[s], 1.0)
+            tv = thc.Tensor.wrap(state, "Float", dv[c * chunk:].data_ptr(), (chunk, 1))
+            ti = thc.Tensor.wrap(state, "Long", di[c * chunk:].data_ptr(), (chunk, 1))
+            tv.max(ti, tz[s], 1, 1)
+            tz[s].sumall_to_device(parts[c:].data_ptr())
+            freed[s].record(stream)
+            tv.free()
+            ti.free()
+        tparts.sumall_to_device(total.data_ptr())
+        if world > 1:
+            dist.all_reduce(total)
+        hv.copy_(dv, non_blocking=True)
+        hi.copy_(di, non_blocking=True)
+        hs.copy_(total, non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = max(1, min(args.steps, 3))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    h2d = 2 * rows * COLS * 4
+    d2h = rows * 12 + 8
+    return {"value": step_bytes(rows) * world / (ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+            "d2h_bytes_per_step": d2h * world, "ms_per_step": ms, "steps": steps,
+            "host_rows_resident": host_rows, "note": "pinned host chunks of 8192 rows, double-buffered H2D overlapped with the kernels"
+            + ("" if host_rows == rows else f"; host array of {host_rows} rows cycled (box cannot pin {need >> 30} GiB)")}
+
+
+def run_small_configs(torch, thc, state, stream, dev, peak):
+    """Device-time GB/s of the other baseline configs (c1-c4) at full size, N = 1.  An L2 flush
+    (512 MiB memset) runs between timed iterations because several of these tensors fit L2."""
+    import numpy as np
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    W = lambda t, kind: thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+
+    def timed(fn, nbytes, reps=10):
+        ts = []
+        for _ in range(3):
+            fn()
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        med = ts[len(ts) // 2]
+        return {"gbs": round(nbytes / (med * 1e-3) / 1e9, 1), "frac": round(nbytes / (med * 1e-3) / 1e9 / peak, 4),
+                "median_us": round(med * 1e3, 2), "best_us": round(ts[0] * 1e3, 2), "bytes": nbytes}
+
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    # c1
+    n = 16777216
+    x = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
+    y = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
+    z = torch.empty(n, device=dev)
+    res = torch.zeros(1, dtype=torch.float64, device=dev)
+    tx, ty, tz = W(x, "Float"), W(y, "Float"), W(z, "Float")
+    out["c1_cadd_f32_16M"] = timed(lambda: tz.cadd(tx, 2.5, ty), 12 * n)
+    out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n)
+    del x, y, z
+    # c2
+    shape = (64, 256, 56, 56)
+    n = 64 * 256 * 56 * 56
+    x = torch.empty(shape, device=dev).normal_(generator=g)
+    ybase = torch.empty(64, 56, 56, 256, device=dev).normal_(generator=g)
+    yv = ybase.transpose(1, 3)
+    wbase = torch.empty(64, 256, 56, 112, device=dev).normal_(generator=g)
+    wv = wbase[..., ::2]
+    o = torch.empty(shape, device=dev)
+    to, tx, ty, tw = W(o, "Float"), W(x, "Float"), W(yv, "Float"), W(wv, "Float")
+    out["c2_addcmul_f32_transposed_strided"] = timed(lambda: to.addcmul(tx, 0.5, ty, tw), 16 * n)
+    del x, ybase, wbase, o
+    # c3
+    m = (torch.randint(-1000, 1001, (32768, 8192), device=dev, generator=g).float() / 8)
+    tm = W(m, "Float")
+    n = m.numel()
+    r1, r0 = torch.empty(32768, 1, device=dev), torch.empty(1, 8192, device=dev)
+    i1, i0 = torch.empty(32768, 1, dtype=torch.int64, device=dev), torch.empty(1, 8192, dtype=torch.int64, device=dev)
+    tr1, tr0, ti1, ti0 = W(r1, "Float"), W(r0, "Float"), W(i1, "Long"), W(i0, "Long")
+    out["c3_sum_dim1"] = timed(lambda: tr1.sum(tm, 1, 1), 4 * n + 4 * 32768)
+    out["c3_sum_dim0"] = timed(lambda: tr0.sum(tm, 0, 1), 4 * n + 4 * 8192)
+    out["c3_max_dim1"] = timed(lambda: tr1.max(ti1, tm, 1, 1), 4 * n + 12 * 32768)
+    out["c3_max_dim0"] = timed(lambda: tr0.max(ti0, tm, 0, 1), 4 * n + 12 * 8192)
+    del m
+    # c4.1
+    h = (torch.empty(8192, 8192, device=dev).normal_(0, 2, generator=g)).half()
+    h2 = torch.empty_like(h)
+    rh = torch.empty(1, 8192, dtype=torch.float16, device=dev)
+    th, th2, trh = W(h, "Half"), W(h2, "Half"), W(rh, "Half")
+    n = h.numel()
+    out["c4_sigmoid_f16"] = timed(lambda: th2.sigmoid(th), 4 * n)
+    out["c4_mean_dim0_f16"] = timed(lambda: trh.mean(th2, 0, 1), 2 * n + 2 * 8192)
+    out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192)
+    del h, h2
+    # c4.2
+    n = 134217728
+    a = torch.randint(-2**20, 2**20 + 1, (n,), dtype=torch.int32, device=dev, generator=g)
+    b = torch.randint(-7, 8, (n,), dtype=torch.int32, device=dev, generator=g)
+    c = torch.empty_like(a)
+    ta, tb, tc = W(a, "Int"), W(b, "Int"), W(c, "Int")
+    out["c4_cmul_i32_128M"] = timed(lambda: tc.cmul(ta, tb), 12 * n, reps=5)
+    out["c4_sumall_i32_128M"] = timed(lambda: tc.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
+    del a, b, c
+    # c4.3
+    d = torch.empty(n, dtype=torch.float64, device=dev).uniform_(0, 1, generator=g)
+    td = W(d, "Double")
+    out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=0, help="rows per GPU (default: 524288 / world size)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--configs", action="store_true", default=True, help="also time the c1-c4 configs at N=1")
+    ap.add_argument("--no-configs", dest="configs", action="store_false")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        return reference_main(args)
+    return ours_main(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,231 @@
+// Pointwise apply kernels for sm_100a and the per-call planner that picks one of them.
+//
+//   contig_vec : every operand collapses to one unit-stride run and is 16-byte aligned.
+//                Each thread owns kUnroll 16-byte vectors per operand, all loads issued
+//                before the first use; one tile per CTA, the tail handled by scalars.
+//   tiled      : some operands have their unit stride in a different dimension than the
+//                others (a transposed view).  A CTA stages a [TC x TJ] tile of those
+//                operands through shared memory so that both the global reads (along the
+//                operand's own unit-stride dim) and the global writes (along the output's)
+//                move whole 32-byte sectors.
+//   generic    : anything else: each operand individually collapsed
+//                (TensorInfo::collapseDims rule), linear index -> offset by multiply-high
+//                division, four independent elements in flight per thread.
+//
+// Replaces kernelPointwiseApply1/2/3 and THC_pointwiseApply1/2/3
+// (lib/THC/THCApply.cuh:19-98,124-640).
+#pragma once
+
+#include "core.cuh"
+#include "ops.cuh"
+
+namespace thcb {
+
+constexpr int kApplyThreads = 256;
+constexpr int kApplyUnroll = 4;
+
+// ----------------------------------------------------------------------------------
+// contig_vec
+// ----------------------------------------------------------------------------------
+template <int OP, typename T, int NIN>
+__global__ void __launch_bounds__(kApplyThreads)
+apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
+                        OpParams<T> p) {
+  constexpr int V = 16 / sizeof(T);                       // elements per 16-byte vector
+  constexpr uint64_t kTile = (uint64_t)kApplyThreads * kApplyUnroll * V;
+  const uint64_t base = (uint64_t)blockIdx.x * kTile;
+  if (base + kTile <= n) {
+    Bytes16 va[kApplyUnroll], vb[kApplyUnroll], vc[kApplyUnroll];
+#pragma unroll
+    for (int u = 0; u < kApplyUnroll; ++u) {
+      const uint64_t i = base + ((uint64_t)u * kApplyThreads + threadIdx.x) * V;
+      if constexpr (NIN >= 1) va[u] = ld16_stream(a + i);
+      if constexpr (NIN >= 2) vb[u] = ld16_stream(b + i);
+      if constexpr (NIN >= 3) vc[u] = ld16_stream(c + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kApplyUnroll; ++u) {
+      const uint64_t i = base + ((uint64_t)u * kApplyThreads + threadIdx.x) * V;
+      Bytes16 vo;
+      T *eo = reinterpret_cast<T *>(&vo);
+      const T *ea = reinterpret_cast<const T *>(&va[u]);
+      const T *eb = reinterpret_cast<const T *>(&vb[u]);
+      const T *ec = reinterpret_cast<const T *>(&vc[u]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        T x = NIN >= 1 ? ea[k] : T();
+        T y = NIN >= 2 ? eb[k] : T();
+        T z = NIN >= 3 ? ec[k] : T();
+        eo[k] = pw_apply<OP, T>(p, x, y, z);
+      }
+      st16(out + i, vo);
+    }
+  } else {
+    for (uint64_t i = base + threadIdx.x; i < n; i += kApplyThreads) {
+      T x = T(), y = T(), z = T();
+      if constexpr (NIN >= 1) x = a[i];
+      if constexpr (NIN >= 2) y = b[i];
+      if constexpr (NIN >= 3) z = c[i];
+      out[i] = pw_apply<OP, T>(p, x, y, z);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// generic
+// ----------------------------------------------------------------------------------
+template <int OP, typename T, int NIN, typename IndexT>
+__global__ void __launch_bounds__(kApplyThreads)
+apply_generic_kernel(T *out, StridedView<IndexT> vo, const T *a, StridedView<IndexT> va,
+                     const T *b, StridedView<IndexT> vb, const T *c, StridedView<IndexT> vc,
+                     IndexT n, OpParams<T> p) {
+  constexpr int U = kApplyUnroll;
+  const IndexT tile = (IndexT)kApplyThreads * U;
+  // grid is sized so that blockIdx.x * tile never wraps; one tile per CTA
+  const IndexT base = (IndexT)blockIdx.x * tile + threadIdx.x;
+  T x[U], y[U], z[U];
+  IndexT oo[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const IndexT i = base + (IndexT)u * kApplyThreads;
+    x[u] = T(); y[u] = T(); z[u] = T();
+    if (i < n) {
+      oo[u] = vo.offset(i);
+      if constexpr (NIN >= 1) x[u] = a[va.offset(i)];
+      if constexpr (NIN >= 2) y[u] = b[vb.offset(i)];
+      if constexpr (NIN >= 3) z[u] = c[vc.offset(i)];
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const IndexT i = base + (IndexT)u * kApplyThreads;
+    if (i < n) out[oo[u]] = pw_apply<OP, T>(p, x[u], y[u], z[u]);
+  }
+}
+
+// ----------------------------------------------------------------------------------
+// tiled (transposed operands)
+//
+// Iteration space as seen by the kernel: [outer] x [C] x [J] in the output's logical
+// order restricted to the dims that matter:
+//   J  the trailing group of logical dims (row-major linear index j within the group),
+//   C  one earlier logical dim in which the "staged" operands have stride 1,
+//   outer: all remaining dims, decoded from blockIdx.
+// "Direct" operands are addressed as base(outer) + c*strideC + j*strideJ (the J group
+// collapses for them).  "Staged" operands are addressed as base(outer) + c + offJ(j),
+// where offJ walks the (at most kTiledJDims) dims of the group with the operand's own
+// strides.  A CTA handles TC consecutive c and TJ consecutive j.
+// ----------------------------------------------------------------------------------
+constexpr int kTiledJDims = 3;
+constexpr int kTiledOuterDims = 6;
+constexpr int kTiledThreads = 256;
+constexpr int kTJ = 64;   // j extent of a tile
+
+struct TiledOperand {
+  int staged;                        // 1: unit stride along C, goes through shared memory
+  int slot;                          // shared-memory slot of a staged operand
+  int64_t strideC;                   // element stride along C (1 when staged)
+  int64_t strideJ;                   // direct operands: stride of the collapsed J group
+  int64_t jstrides[kTiledJDims];     // staged operands: per-dim strides inside the J group
+  int64_t ostrides[kTiledOuterDims]; // strides of the outer dims
+};
+
+struct TiledPlan {
+  int nouter;
+  int njd;                           // dims in the J group (staged-operand walk)
+  uint32_t sizeC, sizeJ;
+  uint32_t tilesC, tilesJ;
+  FastDiv32 outerSizes[kTiledOuterDims];
+  FastDiv32 jSizes[kTiledJDims];
+  FastDiv32 tilesCdiv, tilesJdiv;
+  TiledOperand op[4];                // 0 = out, 1..3 = inputs
+};
+
+template <int OP, typename T, int NIN>
+__global__ void __launch_bounds__(kTiledThreads)
+apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpParams<T> p) {
+  constexpr int TC = (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128);  // 128-byte runs
+  constexpr int PAD = (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4);
+  constexpr int NW = kTiledThreads / 32;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T *tile = reinterpret_cast<T *>(smem_raw);  // [slots][kTJ][TC + PAD]
+  constexpr int kSlot = kTJ * (TC + PAD);
+
+  // decode blockIdx -> (outer, tile_c, tile_j)
+  uint32_t bid = blockIdx.x, tj, tc, rest;
+  P.tilesJdiv.divmod(bid, rest, tj);
+  P.tilesCdiv.divmod(rest, rest, tc);
+  int64_t base[4] = {0, 0, 0, 0};
+#pragma unroll
+  for (int d = kTiledOuterDims - 1; d >= 0; --d) {
+    if (d < P.nouter) {
+      uint32_t q, r;
+      P.outerSizes[d].divmod(rest, q, r);
+      rest = q;
+#pragma unroll
+      for (int o = 0; o <= NIN; ++o) base[o] += (int64_t)r * P.op[o].ostrides[d];
+    }
+  }
+  const uint32_t c0 = tc * TC, j0 = tj * kTJ;
+  const uint32_t nc = min((uint32_t)TC, P.sizeC - c0), nj = min((uint32_t)kTJ, P.sizeJ - j0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T *in[4] = {nullptr, a, b, c};
+
+  // phase 1: staged inputs -> shared memory, lanes along C (the operand's unit stride)
+#pragma unroll
+  for (int o = 1; o <= NIN; ++o) {
+    if (P.op[o].staged) {
+      for (uint32_t jj = warp; jj < nj; jj += NW) {
+        uint32_t j = j0 + jj, q = j, r;
+        int64_t off = base[o];
+#pragma unroll
+        for (int d = kTiledJDims - 1; d >= 0; --d) {
+          if (d < P.njd) {
+            P.jSizes[d].divmod(q, q, r);
+            off += (int64_t)r * P.op[o].jstrides[d];
+          }
+        }
+        for (uint32_t cc = lane; cc < nc; cc += 32)
+          tile[P.op[o].slot * kSlot + jj * (TC + PAD) + cc] = in[o][off + c0 + cc];
+      }
+    }
+  }
+  __syncthreads();
+
+  // phase 2: compute with lanes along J (unit stride of the direct operands)
+  const bool out_staged = P.op[0].staged;
+  for (uint32_t cc = warp; cc < nc; cc += NW) {
+    for (uint32_t jj = lane; jj < nj; jj += 32) {
+      T v[4];
+#pragma unroll
+      for (int o = 1; o <= NIN; ++o) {
+        if (P.op[o].staged) v[o] = tile[P.op[o].slot * kSlot + jj * (TC + PAD) + cc];
+        else v[o] = in[o][base[o] + (int64_t)(c0 + cc) * P.op[o].strideC + (int64_t)(j0 + jj) * P.op[o].strideJ];
+      }
+      T r = pw_apply<OP, T>(p, NIN >= 1 ? v[1] : T(), NIN >= 2 ? v[2] : T(), NIN >= 3 ? v[3] : T());
+      if (out_staged) tile[P.op[0].slot * kSlot + jj * (TC + PAD) + cc] = r;
+      else out[base[0] + (int64_t)(c0 + cc) * P.op[0].strideC + (int64_t)(j0 + jj) * P.op[0].strideJ] = r;
+    }
+  }
+  if (out_staged) {
+    __syncthreads();
+    for (uint32_t jj = warp; jj < nj; jj += NW) {
+      uint32_t q = j0 + jj, r;
+      int64_t off = base[0];
+#pragma unroll
+      for (int d = kTiledJDims - 1; d >= 0; --d) {
+        if (d < P.njd) {
+          P.jSizes[d].divmod(q, q, r);
+          off += (int64_t)r * P.op[0].jstrides[d];
+        }
+      }
+      for (uint32_t cc = lane; cc < nc; cc += 32) out[off + c0 + cc] = tile[P.op[0].slot * kSlot + jj * (TC + PAD) + cc];
+    }
+  }
+}
+
+template <typename T> constexpr int tiled_tc() { return (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128); }
+template <typename T> constexpr int tiled_pad() { return (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4); }
+template <typename T> constexpr size_t tiled_slot_bytes() { return (size_t)kTJ * (tiled_tc<T>() + tiled_pad<T>()) * sizeof(T); }
+
+}  // namespace thcb

@@ -1,0 +1,41 @@
+// Per-device context: reduction workspace, ticket counters, pinned result slot.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/thcb200.h"
+
+namespace thcb {
+constexpr int kNumTickets = 4096;
+}
+
+struct thcb200_ctx {
+  int device;
+  int num_sms;
+  int max_smem_optin;
+  void *ws;               // device workspace for partial results, grown on demand
+  size_t ws_bytes;
+  unsigned int *tickets;  // kNumTickets counters, zero between launches (kernels reset them)
+  int *status;            // device word: kernels record bounded-wait failures here
+  void *host_slot;        // pinned, 64 bytes
+  void *dev_slot;         // device, 64 bytes: result of reduce_all_host
+};
+
+namespace thcb {
+
+// Returns a device buffer of at least `bytes` (256-byte aligned), valid until the next call
+// that asks for more.  Growing synchronises the device; nullptr on allocation failure.
+void *ctx_workspace(thcb200_ctx *ctx, size_t bytes);
+
+#define THCB_CUDA_TRY(expr)                                                              \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess) {                                                             \
+      ::thcb::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return THCB200_ERR_CUDA;                                                           \
+    }                                                                                    \
+  } while (0)
+
+}  // namespace thcb

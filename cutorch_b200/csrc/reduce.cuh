@@ -1,0 +1,602 @@
+// Reduction kernels for sm_100a: full reduction (one launch, fixed order, last-block
+// finalize) and dimension reductions over inner-contiguous rows, outer-strided columns and
+// arbitrary layouts, each with a plain-value and a (value, first position) form.
+//
+// Replaces kernelReduceAll/Pass1/Pass2 (lib/THC/THCReduceAll.cuh:21-123),
+// kernelReduceContigDim / kernelReduceNoncontigDim(_shared) (lib/THC/THCReduce.cuh:25-214) and
+// kernelTransformReduceInnermostDimIndex / OuterDimIndex
+// (lib/THC/THCTensorMathReduce.cuh:453-585).
+#pragma once
+
+#include <math.h>
+
+#include <type_traits>
+
+#include "core.cuh"
+
+namespace thcb {
+
+// Fold modes: the (reduce op, pre-transform) pairs that exist in the C API.
+enum ReduceMode {
+  kSum = 0, kSumAbs, kSumSquare, kSumPowAbs, kSumNonZero, kSumSqDev,
+  kProd, kMin, kMax, kAll, kAny, kNumReduceModes
+};
+
+inline int reduce_mode(int rop, int pre) {
+  if (rop == THCB200_RED_SUM) {
+    switch (pre) {
+      case THCB200_PRE_IDENTITY: return kSum;
+      case THCB200_PRE_ABS: return kSumAbs;
+      case THCB200_PRE_SQUARE: return kSumSquare;
+      case THCB200_PRE_POWABS: return kSumPowAbs;
+      case THCB200_PRE_NONZERO: return kSumNonZero;
+      case THCB200_PRE_SQDEV: return kSumSqDev;
+    }
+    return -1;
+  }
+  if (pre != THCB200_PRE_IDENTITY) return -1;
+  switch (rop) {
+    case THCB200_RED_PROD: return kProd;
+    case THCB200_RED_MIN: return kMin;
+    case THCB200_RED_MAX: return kMax;
+    case THCB200_RED_ALL: return kAll;
+    case THCB200_RED_ANY: return kAny;
+  }
+  return -1;
+}
+
+template <typename M> __device__ __forceinline__ bool is_nan(M v) { return v != v; }
+
+// ---------------------------------------------------------------------------------
+// Folder<T, MODE>: accumulator type, element transform and combine of one fold mode.
+//   Sum-like modes accumulate in TypeTraits<T>::Acc (double for float/double, float for
+//   half, int64 for integers) -- the accumulate types of TH's CPU reductions, with the
+//   transform applied in that type as TH does.
+//   Min/Max compare in the element's math type; a NaN wins, as in TH's scans.
+// ---------------------------------------------------------------------------------
+template <typename T, int MODE>
+struct Folder {
+  static constexpr bool kMinMax = (MODE == kMin || MODE == kMax);
+  static constexpr bool kLogical = (MODE == kAll || MODE == kAny);
+  using SumAcc = typename TypeTraits<T>::Acc;
+  using M = typename TypeTraits<T>::Math;
+  using Acc = typename std::conditional<kMinMax, M, typename std::conditional<kLogical, int, SumAcc>::type>::type;
+  struct Params { Acc s; };
+
+  __host__ __device__ static Acc init() {
+    if constexpr (MODE == kProd) return (Acc)1;
+    else if constexpr (MODE == kAll) return 1;
+    else if constexpr (kMinMax) return Acc();  // unused: min/max folds start from an element
+    else return (Acc)0;
+  }
+  __device__ __forceinline__ static Acc pre(T x, const Params &p) {
+    if constexpr (kMinMax) return to_math<T>(x);
+    else if constexpr (kLogical) return to_math<T>(x) != (M)0 ? 1 : 0;
+    else {
+      const Acc v = (Acc)to_math<T>(x);
+      if constexpr (MODE == kSumAbs) return v < 0 ? -v : v;
+      else if constexpr (MODE == kSumSquare) return v * v;
+      else if constexpr (MODE == kSumPowAbs) {
+        if constexpr (std::is_same<Acc, float>::value) return powf(fabsf(v), p.s);
+        else return (Acc)pow(fabs((double)v), (double)p.s);
+      }
+      else if constexpr (MODE == kSumNonZero) return v != 0 ? (Acc)1 : (Acc)0;
+      else if constexpr (MODE == kSumSqDev) return (v - p.s) * (v - p.s);
+      else return v;
+    }
+  }
+  __device__ __forceinline__ static Acc combine(Acc a, Acc b) {
+    if constexpr (MODE == kProd) {
+      if constexpr (TypeTraits<T>::is_fp) return a * b;
+      else return (Acc)((uint64_t)a * (uint64_t)b);
+    }
+    else if constexpr (MODE == kAll) return a && b;
+    else if constexpr (MODE == kAny) return a || b;
+    else if constexpr (MODE == kMax) {
+      if constexpr (TypeTraits<T>::is_fp) { if (is_nan(a)) return a; if (is_nan(b)) return b; }
+      return a > b ? a : b;
+    }
+    else if constexpr (MODE == kMin) {
+      if constexpr (TypeTraits<T>::is_fp) { if (is_nan(a)) return a; if (is_nan(b)) return b; }
+      return a < b ? a : b;
+    }
+    else {
+      if constexpr (TypeTraits<T>::is_fp) return a + b;
+      else return (Acc)((uint64_t)a + (uint64_t)b);
+    }
+  }
+};
+
+// (value, position) accumulator of max/min along a dim.  `better(a, b)`: a is kept over b.
+// Total order: NaN beats numbers, then the larger (smaller) value, then the lower position,
+// which makes the combine associative and commutative: any tree gives the first occurrence.
+template <typename M>
+struct ValIdx {
+  M v;
+  int64_t i;  // 0-based position along the reduced dim; -1 = empty
+};
+
+template <typename T, bool IS_MAX>
+struct IndexFolder {
+  using M = typename TypeTraits<T>::Math;
+  using Acc = ValIdx<M>;
+  __device__ __forceinline__ static Acc empty() { Acc a; a.v = M(); a.i = -1; return a; }
+  __device__ __forceinline__ static bool better(const Acc &a, const Acc &b) {
+    if (b.i < 0) return true;
+    if (a.i < 0) return false;
+    if constexpr (TypeTraits<T>::is_fp) {
+      const bool an = is_nan(a.v), bn = is_nan(b.v);
+      if (an || bn) return an && (!bn || a.i < b.i);
+    }
+    if (a.v == b.v) return a.i < b.i;
+    return IS_MAX ? (a.v > b.v) : (a.v < b.v);
+  }
+  __device__ __forceinline__ static Acc combine(const Acc &a, const Acc &b) { return better(a, b) ? a : b; }
+  __device__ __forceinline__ static void feed(Acc &acc, T x, int64_t pos) {
+    Acc e; e.v = to_math<T>(x); e.i = pos;
+    if (!better(acc, e)) acc = e;
+  }
+};
+
+// ---- warp / block combine in a fixed order -------------------------------------------
+template <typename A> __device__ __forceinline__ A shfl_xor(A v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
+template <> __device__ __forceinline__ int64_t shfl_xor<int64_t>(int64_t v, int m) { return (int64_t)__shfl_xor_sync(0xffffffffu, (long long)v, m); }
+template <> __device__ __forceinline__ int16_t shfl_xor<int16_t>(int16_t v, int m) { return (int16_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
+template <> __device__ __forceinline__ int8_t shfl_xor<int8_t>(int8_t v, int m) { return (int8_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
+template <> __device__ __forceinline__ uint8_t shfl_xor<uint8_t>(uint8_t v, int m) { return (uint8_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
+template <typename M> __device__ __forceinline__ ValIdx<M> shfl_xor_vi(ValIdx<M> a, int m) {
+  ValIdx<M> r;
+  r.v = shfl_xor<M>(a.v, m);
+  r.i = shfl_xor<int64_t>(a.i, m);
+  return r;
+}
+
+// Butterfly over the 32 lanes; every lane ends with the same value.  For the min/max value
+// folds an "empty" flag travels with the value (lanes that saw no element).
+template <typename F> __device__ __forceinline__ typename F::Acc warp_fold(typename F::Acc v) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) v = F::combine(v, shfl_xor<typename F::Acc>(v, m));
+  return v;
+}
+template <typename F> __device__ __forceinline__ typename F::Acc warp_fold_vi(typename F::Acc v) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) v = F::combine(v, shfl_xor_vi(v, m));
+  return v;
+}
+
+// Value accumulator with validity, so that min/max need no sentinel start value.
+template <typename F>
+struct Opt {
+  typename F::Acc v;
+  int has;
+  __device__ __forceinline__ void feed(typename F::Acc x) {
+    if constexpr (F::kMinMax) { v = has ? F::combine(v, x) : x; has = 1; }
+    else v = F::combine(v, x);
+  }
+  __device__ __forceinline__ void merge(const Opt &o) {
+    if constexpr (F::kMinMax) { if (o.has) { v = has ? F::combine(v, o.v) : o.v; has = 1; } }
+    else v = F::combine(v, o.v);
+  }
+  __device__ __forceinline__ static Opt start() { Opt o; o.v = F::init(); o.has = 0; return o; }
+};
+template <typename F> __device__ __forceinline__ Opt<F> warp_fold_opt(Opt<F> a) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) {
+    Opt<F> o;
+    o.v = shfl_xor<typename F::Acc>(a.v, m);
+    o.has = __shfl_xor_sync(0xffffffffu, a.has, m);
+    // keep the operand order independent of the lane so both partners compute the same
+    const bool low = (threadIdx.x & m) == 0;
+    Opt<F> x = low ? a : o, y = low ? o : a;
+    x.merge(y);
+    a = x;
+  }
+  return a;
+}
+
+// Decodes a slice number into element offsets of the input and output(s); the dims are the
+// non-reduced ones.  Evaluated once per slice, so plain 64-bit division is acceptable.
+struct SliceMap {
+  int n;
+  uint64_t size[kMaxDims];
+  int64_t in_stride[kMaxDims];
+  int64_t out_stride[kMaxDims];
+  int64_t idx_stride[kMaxDims];
+  __device__ __forceinline__ void decode(uint64_t lin, int64_t &in_off, int64_t &out_off, int64_t &idx_off) const {
+    in_off = 0; out_off = 0; idx_off = 0;
+    for (int d = n - 1; d >= 0; --d) {
+      uint64_t q = lin / size[d], r = lin - q * size[d];
+      in_off += (int64_t)r * in_stride[d];
+      out_off += (int64_t)r * out_stride[d];
+      idx_off += (int64_t)r * idx_stride[d];
+      lin = q;
+    }
+  }
+};
+
+constexpr int kRedThreads = 256;
+constexpr int kRedWarps = kRedThreads / 32;
+constexpr int kRedUnroll = 4;
+
+// ====================================================================================
+// reduce_all: persistent CTAs walk 16 KiB tiles block-cyclically; partial per CTA; the CTA
+// that draws the last ticket folds the partials in index order and writes the result.
+// ====================================================================================
+template <typename T, int MODE, bool VEC>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
+                  void *partials_raw, unsigned int *ticket, void *result) {
+  using F = Folder<T, MODE>;
+  using Acc = typename F::Acc;
+  struct Partial { Acc v; int has; };
+  Partial *partials = reinterpret_cast<Partial *>(partials_raw);
+  constexpr int V = 16 / sizeof(T);
+  constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * (VEC ? V : 1);
+  Opt<F> acc = Opt<F>::start();
+  const uint64_t ntiles = (n + kTile - 1) / kTile;
+  for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t base = t * kTile;
+    if constexpr (VEC) {
+      if (base + kTile <= n) {
+        Bytes16 v[kRedUnroll];
+#pragma unroll
+        for (int u = 0; u < kRedUnroll; ++u) v[u] = ld16_stream(in + base + ((uint64_t)u * kRedThreads + threadIdx.x) * V);
+#pragma unroll
+        for (int u = 0; u < kRedUnroll; ++u) {
+          const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+          for (int k = 0; k < V; ++k) acc.feed(F::pre(e[k], prm));
+        }
+      } else {
+        for (uint64_t i = base + threadIdx.x; i < n; i += kRedThreads) acc.feed(F::pre(in[i], prm));
+      }
+    } else {
+      T x[kRedUnroll];
+      bool ok[kRedUnroll];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const uint64_t i = base + (uint64_t)u * kRedThreads + threadIdx.x;
+        ok[u] = i < n;
+        if (ok[u]) x[u] = in[view.offset(i)];
+      }
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) if (ok[u]) acc.feed(F::pre(x[u], prm));
+    }
+  }
+  __shared__ Partial sm[kRedWarps];
+  __shared__ bool is_last;
+  acc = warp_fold_opt<F>(acc);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sm[warp].v = acc.v; sm[warp].has = acc.has; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Opt<F> b = Opt<F>::start();
+    for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = sm[w].v; o.has = sm[w].has; b.merge(o); }
+    partials[blockIdx.x].v = b.v;
+    partials[blockIdx.x].has = b.has;
+    __threadfence();
+    const unsigned int done = atomicAdd(ticket, 1u);
+    is_last = (done == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  Opt<F> f = Opt<F>::start();
+  for (unsigned int i = threadIdx.x; i < gridDim.x; i += kRedThreads) {
+    Opt<F> o;
+    o.v = partials[i].v; o.has = partials[i].has;
+    f.merge(o);
+  }
+  f = warp_fold_opt<F>(f);
+  __syncthreads();
+  if (lane == 0) { sm[warp].v = f.v; sm[warp].has = f.has; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Opt<F> b = Opt<F>::start();
+    for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = sm[w].v; o.has = sm[w].has; b.merge(o); }
+    // result slot: double for floating element types, int64 for integer ones
+    if constexpr (TypeTraits<T>::is_fp) *reinterpret_cast<double *>(result) = (double)b.v;
+    else *reinterpret_cast<int64_t *>(result) = (int64_t)b.v;
+    *ticket = 0;  // ready for the next launch on this stream
+  }
+}
+
+// ====================================================================================
+// Output conversion of the dimension reductions: accumulator -> element type.
+// ====================================================================================
+template <typename T, typename Acc> __device__ __forceinline__ T acc_to_elem(Acc a) {
+  if constexpr (std::is_same<T, __half>::value) return __float2half_rn((float)a);
+  else return (T)a;
+}
+
+// Partial accumulators of split reductions, kept in the workspace between the two stages.
+template <typename Acc> struct PartialVal { Acc v; int has; };
+
+// ====================================================================================
+// ROW: the reduced dim has stride 1.  A unit of work is (slice, split); WARP_PER_UNIT picks
+// one warp per unit (8 units per CTA) or the whole CTA per unit.  With nsplit > 1 the unit's
+// partial goes to the workspace [slice][split] and finish_kernel completes the fold.
+// ====================================================================================
+template <typename T, int MODE, bool INDEX, bool IS_MAX, bool VEC, bool WARP_PER_UNIT>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
+                  uint32_t nsplit, uint64_t split_len, typename Folder<T, MODE>::Params prm, void *partials_raw) {
+  using F = Folder<T, MODE>;
+  using IF = IndexFolder<T, IS_MAX>;
+  constexpr int V = 16 / sizeof(T);
+  constexpr int GROUP = WARP_PER_UNIT ? 32 : kRedThreads;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gt = WARP_PER_UNIT ? lane : threadIdx.x;  // thread index inside the group
+  const uint64_t unit = WARP_PER_UNIT ? (uint64_t)blockIdx.x * kRedWarps + warp : blockIdx.x;
+  const uint64_t nunits = nslices * nsplit;
+  const bool active = unit < nunits;
+  const uint64_t slice = active ? unit / nsplit : 0;
+  const uint32_t split = active ? (uint32_t)(unit - slice * nsplit) : 0;
+  int64_t in_off = 0, out_off = 0, idx_off = 0;
+  if (active) map.decode(slice, in_off, out_off, idx_off);
+  const T *row = in + in_off;
+  const uint64_t k0 = (uint64_t)split * split_len;
+  const uint64_t k1 = active ? (k0 + split_len < K ? k0 + split_len : K) : k0;
+
+  Opt<F> acc = Opt<F>::start();
+  typename IF::Acc best = IF::empty();
+  uint64_t k = k0;
+  if constexpr (VEC) {
+    // whole 16-byte vectors, kRedUnroll of them in flight per thread (split_len is a multiple of V)
+    constexpr uint64_t kStep = (uint64_t)GROUP * V * kRedUnroll;
+    for (; k + kStep <= k1; k += kStep) {
+      Bytes16 v[kRedUnroll];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) v[u] = ld16_stream(row + k + ((uint64_t)u * GROUP + gt) * V);
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          if constexpr (INDEX) IF::feed(best, e[j], (int64_t)(k + ((uint64_t)u * GROUP + gt) * V + j));
+          else acc.feed(F::pre(e[j], prm));
+        }
+      }
+    }
+    for (; k + (uint64_t)GROUP * V <= k1; k += (uint64_t)GROUP * V) {
+      Bytes16 v = ld16_stream(row + k + (uint64_t)gt * V);
+      const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        if constexpr (INDEX) IF::feed(best, e[j], (int64_t)(k + (uint64_t)gt * V + j));
+        else acc.feed(F::pre(e[j], prm));
+      }
+    }
+  }
+  for (uint64_t i = k + gt; i < k1; i += GROUP) {
+    if constexpr (INDEX) IF::feed(best, row[i], (int64_t)i);
+    else acc.feed(F::pre(row[i], prm));
+  }
+
+  // fold inside the group
+  if constexpr (INDEX) best = warp_fold_vi<IF>(best);
+  else acc = warp_fold_opt<F>(acc);
+  if constexpr (!WARP_PER_UNIT) {
+    __shared__ PartialVal<typename F::Acc> smv[kRedWarps];
+    __shared__ typename IF::Acc smi[kRedWarps];
+    if (lane == 0) {
+      if constexpr (INDEX) smi[warp] = best;
+      else { smv[warp].v = acc.v; smv[warp].has = acc.has; }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if constexpr (INDEX) {
+        best = smi[0];
+        for (int w = 1; w < kRedWarps; ++w) best = IF::combine(best, smi[w]);
+      } else {
+        acc = Opt<F>::start();
+        for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = smv[w].v; o.has = smv[w].has; acc.merge(o); }
+      }
+    }
+  }
+  if (!active || gt != 0) return;
+  if (nsplit > 1) {
+    if constexpr (INDEX) reinterpret_cast<typename IF::Acc *>(partials_raw)[unit] = best;
+    else {
+      PartialVal<typename F::Acc> *pp = reinterpret_cast<PartialVal<typename F::Acc> *>(partials_raw);
+      pp[unit].v = acc.v; pp[unit].has = acc.has;
+    }
+  } else {
+    if constexpr (INDEX) {
+      out[out_off] = from_math<T>(best.v);
+      idx_out[idx_off] = best.i + 1;  // TH_INDEX_BASE
+    } else {
+      out[out_off] = acc_to_elem<T, typename F::Acc>(acc.v);
+    }
+  }
+}
+
+// Column loads: 16-byte vectors where the layout allows, 4-byte words for the 1-byte types
+// (their accumulators would not fit shared memory at 16 columns per lane), else one element.
+template <int BYTES, typename T> struct ColVec {
+  using type = T;
+  __device__ __forceinline__ static T load(const T *p) { return *p; }
+};
+template <typename T> struct ColVec<16, T> {
+  using type = Bytes16;
+  __device__ __forceinline__ static Bytes16 load(const T *p) { return ld16_stream(p); }
+};
+template <> struct ColVec<4, uint8_t> {
+  using type = uint32_t;
+  __device__ __forceinline__ static uint32_t load(const uint8_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
+};
+template <> struct ColVec<4, int8_t> {
+  using type = uint32_t;
+  __device__ __forceinline__ static uint32_t load(const int8_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
+};
+// elements per lane of the vector form of reduce_col_kernel
+template <typename T> constexpr int col_vec_elems() { return sizeof(T) == 1 ? 4 : 16 / (int)sizeof(T); }
+
+// ====================================================================================
+// COL: some non-reduced dim ("inner", size I) has stride 1 in the input and the reduced dim
+// is strided.  A CTA owns 32 lanes x V adjacent inner positions and one K split; its 8 warps
+// take the rows of the split round-robin, kRedUnroll row loads in flight per thread, and are
+// merged through shared memory in warp order.
+// ====================================================================================
+template <typename T, int MODE, bool INDEX, bool IS_MAX, int V>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims other than K and inner */,
+                  uint64_t nouter, uint64_t K, int64_t strideK, uint64_t I, int64_t out_inner_stride,
+                  int64_t idx_inner_stride, uint32_t nsplit, uint64_t split_len, uint32_t tiles_i,
+                  typename Folder<T, MODE>::Params prm, void *partials_raw) {
+  using F = Folder<T, MODE>;
+  using IF = IndexFolder<T, IS_MAX>;
+  using VecT = typename ColVec<V * sizeof(T), T>::type;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // blockIdx.x -> (outer, split, inner tile)
+  uint64_t b = blockIdx.x;
+  const uint32_t ti = (uint32_t)(b % tiles_i); b /= tiles_i;
+  const uint32_t split = (uint32_t)(b % nsplit); b /= nsplit;
+  const uint64_t outer = b;
+  int64_t in_off, out_off, idx_off;
+  map.decode(outer, in_off, out_off, idx_off);
+  const uint64_t i0 = ((uint64_t)ti * 32 + lane) * V;
+  const bool col_ok = i0 < I;  // I is a multiple of V on the vector path
+  const uint64_t k0 = (uint64_t)split * split_len;
+  const uint64_t k1 = k0 + split_len < K ? k0 + split_len : K;
+  const T *col = in + in_off + (int64_t)i0;
+
+  Opt<F> acc[V];
+  typename IF::Acc best[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) { acc[j] = Opt<F>::start(); best[j] = IF::empty(); }
+  if (col_ok) {
+    uint64_t k = k0 + warp;
+    for (; k + (uint64_t)(kRedUnroll - 1) * kRedWarps < k1; k += (uint64_t)kRedUnroll * kRedWarps) {
+      VecT v[kRedUnroll];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const T *p = col + (int64_t)(k + (uint64_t)u * kRedWarps) * strideK;
+        v[u] = ColVec<V * sizeof(T), T>::load(p);
+      }
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          if constexpr (INDEX) IF::feed(best[j], e[j], (int64_t)(k + (uint64_t)u * kRedWarps));
+          else acc[j].feed(F::pre(e[j], prm));
+        }
+      }
+    }
+    for (; k < k1; k += kRedWarps) {
+      VecT v;
+      const T *p = col + (int64_t)k * strideK;
+      v = ColVec<V * sizeof(T), T>::load(p);
+      const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        if constexpr (INDEX) IF::feed(best[j], e[j], (int64_t)k);
+        else acc[j].feed(F::pre(e[j], prm));
+      }
+    }
+  }
+  // merge the 8 warps in warp order through shared memory
+  __shared__ PartialVal<typename F::Acc> smv[INDEX ? 1 : kRedWarps][32 * V + 1];
+  __shared__ typename IF::Acc smi[INDEX ? kRedWarps : 1][32 * V + 1];
+#pragma unroll
+  for (int j = 0; j < V; ++j) {
+    if constexpr (INDEX) smi[warp][lane * V + j] = best[j];
+    else { smv[warp][lane * V + j].v = acc[j].v; smv[warp][lane * V + j].has = acc[j].has; }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 32 * V; c += kRedThreads) {
+    const uint64_t i = (uint64_t)ti * 32 * V + c;
+    if (i >= I) continue;
+    const uint64_t slot = (outer * I + i) * nsplit + split;  // [outer][inner][split]
+    if constexpr (INDEX) {
+      typename IF::Acc r = smi[0][c];
+      for (int w = 1; w < kRedWarps; ++w) r = IF::combine(r, smi[w][c]);
+      if (nsplit > 1) reinterpret_cast<typename IF::Acc *>(partials_raw)[slot] = r;
+      else {
+        out[out_off + (int64_t)i * out_inner_stride] = from_math<T>(r.v);
+        idx_out[idx_off + (int64_t)i * idx_inner_stride] = r.i + 1;
+      }
+    } else {
+      Opt<F> r = Opt<F>::start();
+      for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = smv[w][c].v; o.has = smv[w][c].has; r.merge(o); }
+      if (nsplit > 1) {
+        PartialVal<typename F::Acc> *pp = reinterpret_cast<PartialVal<typename F::Acc> *>(partials_raw);
+        pp[slot].v = r.v; pp[slot].has = r.has;
+      } else {
+        out[out_off + (int64_t)i * out_inner_stride] = acc_to_elem<T, typename F::Acc>(r.v);
+      }
+    }
+  }
+}
+
+// ====================================================================================
+// finish: folds the nsplit partials of every output in split order (one thread per output).
+// Output o = outer * I + inner for COL (I = 1 for ROW, where outer is the slice).
+// ====================================================================================
+template <typename T, int MODE, bool INDEX, bool IS_MAX>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_finish_kernel(T *out, int64_t *idx_out, SliceMap map, uint64_t nouter, uint64_t I,
+                     int64_t out_inner_stride, int64_t idx_inner_stride, uint32_t nsplit,
+                     const void *partials_raw) {
+  using F = Folder<T, MODE>;
+  using IF = IndexFolder<T, IS_MAX>;
+  const uint64_t o = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
+  if (o >= nouter * I) return;
+  const uint64_t outer = o / I, i = o - outer * I;
+  int64_t in_off, out_off, idx_off;
+  map.decode(outer, in_off, out_off, idx_off);
+  if constexpr (INDEX) {
+    const typename IF::Acc *pp = reinterpret_cast<const typename IF::Acc *>(partials_raw) + o * nsplit;
+    typename IF::Acc r = pp[0];
+    for (uint32_t s = 1; s < nsplit; ++s) r = IF::combine(r, pp[s]);
+    out[out_off + (int64_t)i * out_inner_stride] = from_math<T>(r.v);
+    idx_out[idx_off + (int64_t)i * idx_inner_stride] = r.i + 1;
+  } else {
+    const PartialVal<typename F::Acc> *pp = reinterpret_cast<const PartialVal<typename F::Acc> *>(partials_raw) + o * nsplit;
+    Opt<F> r = Opt<F>::start();
+    for (uint32_t s = 0; s < nsplit; ++s) { Opt<F> x; x.v = pp[s].v; x.has = pp[s].has; r.merge(x); }
+    out[out_off + (int64_t)i * out_inner_stride] = acc_to_elem<T, typename F::Acc>(r.v);
+  }
+}
+
+// ====================================================================================
+// STRIDED (fallback): one thread per output slice walks the reduced dim with its stride.
+// ====================================================================================
+template <typename T, int MODE, bool INDEX, bool IS_MAX>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_strided_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
+                      int64_t strideK, typename Folder<T, MODE>::Params prm) {
+  using F = Folder<T, MODE>;
+  using IF = IndexFolder<T, IS_MAX>;
+  const uint64_t s = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
+  if (s >= nslices) return;
+  int64_t in_off, out_off, idx_off;
+  map.decode(s, in_off, out_off, idx_off);
+  const T *p = in + in_off;
+  Opt<F> acc = Opt<F>::start();
+  typename IF::Acc best = IF::empty();
+  uint64_t k = 0;
+  for (; k + kRedUnroll <= K; k += kRedUnroll) {
+    T x[kRedUnroll];
+#pragma unroll
+    for (int u = 0; u < kRedUnroll; ++u) x[u] = p[(int64_t)(k + u) * strideK];
+#pragma unroll
+    for (int u = 0; u < kRedUnroll; ++u) {
+      if constexpr (INDEX) IF::feed(best, x[u], (int64_t)(k + u));
+      else acc.feed(F::pre(x[u], prm));
+    }
+  }
+  for (; k < K; ++k) {
+    if constexpr (INDEX) IF::feed(best, p[(int64_t)k * strideK], (int64_t)k);
+    else acc.feed(F::pre(p[(int64_t)k * strideK], prm));
+  }
+  if constexpr (INDEX) {
+    out[out_off] = from_math<T>(best.v);
+    idx_out[idx_off] = best.i + 1;
+  } else {
+    out[out_off] = acc_to_elem<T, typename F::Acc>(acc.v);
+  }
+}
+
+}  // namespace thcb

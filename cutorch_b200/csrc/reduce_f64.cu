@@ -1,0 +1,16 @@
+// Reduction kernels instantiated for double.
+#include "reduce_launch.cuh"
+
+namespace thcb {
+int reduce_all_f64(thcb200_ctx *ctx, int mode, const HostView &in, thcb200_scalar s, void *result, cudaStream_t st) {
+  return reduce_all_typed<double>(ctx, mode, in, s, result, st);
+}
+int reduce_dim_f64(thcb200_ctx *ctx, int mode, const HostView &in, const HostView &out, int dim, thcb200_scalar s,
+                  cudaStream_t st) {
+  return reduce_dim_typed<double>(ctx, mode, in, out, dim, s, st);
+}
+int reduce_dim_index_f64(thcb200_ctx *ctx, bool is_max, const HostView &in, const HostView &values,
+                        const HostView &indices, int dim, cudaStream_t st) {
+  return reduce_dim_index_typed<double>(ctx, is_max, in, values, indices, dim, st);
+}
+}  // namespace thcb

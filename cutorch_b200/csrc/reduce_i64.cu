@@ -1,0 +1,16 @@
+// Reduction kernels instantiated for int64_t.
+#include "reduce_launch.cuh"
+
+namespace thcb {
+int reduce_all_i64(thcb200_ctx *ctx, int mode, const HostView &in, thcb200_scalar s, void *result, cudaStream_t st) {
+  return reduce_all_typed<int64_t>(ctx, mode, in, s, result, st);
+}
+int reduce_dim_i64(thcb200_ctx *ctx, int mode, const HostView &in, const HostView &out, int dim, thcb200_scalar s,
+                  cudaStream_t st) {
+  return reduce_dim_typed<int64_t>(ctx, mode, in, out, dim, s, st);
+}
+int reduce_dim_index_i64(thcb200_ctx *ctx, bool is_max, const HostView &in, const HostView &values,
+                        const HostView &indices, int dim, cudaStream_t st) {
+  return reduce_dim_index_typed<int64_t>(ctx, is_max, in, values, indices, dim, st);
+}
+}  // namespace thcb

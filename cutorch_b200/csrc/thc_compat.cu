@@ -1,0 +1,850 @@
+// The THC C API of the apply / reduce path (include/THC/THC.h) on top of the descriptor-level
+// core (include/thcb200.h): tensor/storage metadata, output resizing, argument checks and the
+// composition rules of the THCTensor_(op) entry points
+// (lib/THC/generic/THCTensorMathPointwise.cu, THCTensorMathPairwise.cu, THCTensorMathReduce.cu,
+// THCTensorCopy.cu, THCTensor.c, THCStorage.c).  Host code only; every kernel launch goes
+// through thcb200_*.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+#include <string>
+
+#include "../../include/THC/THC.h"
+#include "../../include/thcb200.h"
+
+// ======================================================================================
+// Errors
+// ======================================================================================
+namespace {
+
+struct THFailure {
+  std::string msg;
+  int arg;
+};
+
+THErrorHandlerFunction g_error_handler = nullptr;
+void *g_error_handler_data = nullptr;
+THArgErrorHandlerFunction g_arg_error_handler = nullptr;
+void *g_arg_error_handler_data = nullptr;
+thread_local bool g_failed = false;
+thread_local char g_failure_msg[1024] = "";
+
+[[noreturn]] void th_error(const char *fmt, ...) {
+  char buf[900];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (g_error_handler) {
+    g_error_handler(buf, g_error_handler_data);  // does not return by contract
+    abort();
+  }
+  throw THFailure{buf, 0};
+}
+
+[[noreturn]] void th_arg_error(int arg, const char *fmt, ...) {
+  char buf[900];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (g_arg_error_handler) {
+    g_arg_error_handler(arg, buf, g_arg_error_handler_data);
+    abort();
+  }
+  char full[1000];
+  snprintf(full, sizeof(full), "invalid argument %d: %s", arg, buf);
+  throw THFailure{full, arg};
+}
+
+void record_failure(const THFailure &f) {
+  g_failed = true;
+  snprintf(g_failure_msg, sizeof(g_failure_msg), "%s", f.msg.c_str());
+}
+
+#define THArgCheck(cond, arg, ...) do { if (!(cond)) th_arg_error(arg, __VA_ARGS__); } while (0)
+#define THCudaCheck(expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) th_error("cuda runtime error (%d) : %s at %s:%d", (int)_e, cudaGetErrorString(_e), __FILE__, __LINE__); } while (0)
+#define CUTORCH_DIM_WARNING "tensor too large or too many (>25) dimensions"
+
+#define API_BEGIN try {
+#define API_END } catch (const THFailure &f) { record_failure(f); }
+#define API_END_RET(v) } catch (const THFailure &f) { record_failure(f); return v; }
+
+}  // namespace
+
+// ======================================================================================
+// State
+// ======================================================================================
+struct THCState {
+  int numDevices;
+  thcb200_ctx **ctx;          // one per device, created on first use
+  THCStream **current;        // current stream per device (null = default stream)
+  THCDeviceAllocator *allocator;
+  THCDeviceAllocator defaultAllocator;
+  int initialised;
+};
+
+namespace {
+
+cudaError_t default_malloc(void *, void **p, size_t n, cudaStream_t) { return cudaMalloc(p, n); }
+cudaError_t default_free(void *, void *p) { return cudaFree(p); }
+
+int current_device() {
+  int d = 0;
+  THCudaCheck(cudaGetDevice(&d));
+  return d;
+}
+
+thcb200_ctx *state_ctx(THCState *state) {
+  if (!state || !state->initialised) th_error("THCState is not initialised (call THCudaInit)");
+  const int d = current_device();
+  if (d >= state->numDevices) th_error("current device %d out of range", d);
+  if (!state->ctx[d]) {
+    if (thcb200_ctx_create(&state->ctx[d], d) != 0) th_error("%s", thcb200_last_error());
+  }
+  return state->ctx[d];
+}
+
+cudaStream_t state_stream(THCState *state) {
+  const int d = current_device();
+  if (state && state->initialised && d < state->numDevices && state->current[d]) return state->current[d]->stream;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+void THSetErrorHandler(THErrorHandlerFunction f, void *data) { g_error_handler = f; g_error_handler_data = data; }
+void THSetArgErrorHandler(THArgErrorHandlerFunction f, void *data) { g_arg_error_handler = f; g_arg_error_handler_data = data; }
+int THCB200_errorOccurred(void) { return g_failed ? 1 : 0; }
+const char *THCB200_errorMessage(void) { return g_failure_msg; }
+void THCB200_clearError(void) { g_failed = false; g_failure_msg[0] = 0; }
+
+THLongStorage *THLongStorage_newWithSize(ptrdiff_t size) {
+  THLongStorage *s = (THLongStorage *)calloc(1, sizeof(THLongStorage));
+  s->data = size > 0 ? (long *)calloc((size_t)size, sizeof(long)) : nullptr;
+  s->size = size;
+  s->refcount = 1;
+  s->flag = TH_STORAGE_REFCOUNTED | TH_STORAGE_RESIZABLE | TH_STORAGE_FREEMEM;
+  return s;
+}
+THLongStorage *THLongStorage_newWithSize1(long a) {
+  THLongStorage *s = THLongStorage_newWithSize(1);
+  s->data[0] = a;
+  return s;
+}
+void THLongStorage_set(THLongStorage *s, ptrdiff_t i, long v) {
+  API_BEGIN
+  THArgCheck(i >= 0 && i < s->size, 2, "out of bounds");
+  s->data[i] = v;
+  API_END
+}
+long THLongStorage_get(const THLongStorage *s, ptrdiff_t i) {
+  API_BEGIN
+  THArgCheck(i >= 0 && i < s->size, 2, "out of bounds");
+  return s->data[i];
+  API_END_RET(0)
+}
+void THLongStorage_free(THLongStorage *s) {
+  if (!s) return;
+  if (--s->refcount > 0) return;
+  free(s->data);
+  free(s);
+}
+
+THCState *THCState_alloc(void) { return (THCState *)calloc(1, sizeof(THCState)); }
+void THCState_free(THCState *state) { free(state); }
+
+void THCudaInit(THCState *state) {
+  API_BEGIN
+  if (!state) th_error("THCudaInit: null state");
+  int n = 0;
+  THCudaCheck(cudaGetDeviceCount(&n));
+  state->numDevices = n;
+  state->ctx = (thcb200_ctx **)calloc((size_t)(n > 0 ? n : 1), sizeof(thcb200_ctx *));
+  state->current = (THCStream **)calloc((size_t)(n > 0 ? n : 1), sizeof(THCStream *));
+  state->defaultAllocator.malloc = default_malloc;
+  state->defaultAllocator.realloc = nullptr;
+  state->defaultAllocator.free = default_free;
+  state->defaultAllocator.emptyCache = nullptr;
+  state->defaultAllocator.cacheInfo = nullptr;
+  state->defaultAllocator.state = nullptr;
+  state->allocator = &state->defaultAllocator;
+  state->initialised = 1;
+  API_END
+}
+
+void THCudaShutdown(THCState *state) {
+  if (!state || !state->initialised) return;
+  for (int d = 0; d < state->numDevices; ++d) {
+    if (state->ctx[d]) thcb200_ctx_destroy(state->ctx[d]);
+    if (state->current[d]) THCStream_free(state->current[d]);
+  }
+  free(state->ctx);
+  free(state->current);
+  state->ctx = nullptr;
+  state->current = nullptr;
+  state->initialised = 0;
+}
+
+int THCState_getNumDevices(THCState *state) { return state->numDevices; }
+cudaStream_t THCState_getCurrentStream(THCState *state) {
+  API_BEGIN
+  return state_stream(state);
+  API_END_RET(0)
+}
+cudaStream_t THCState_getCurrentStreamOnDevice(THCState *state, int device) {
+  if (state && state->initialised && device >= 0 && device < state->numDevices && state->current[device])
+    return state->current[device]->stream;
+  return 0;
+}
+THCStream *THCState_getStream(THCState *state) {
+  API_BEGIN
+  const int d = current_device();
+  return state->current[d];
+  API_END_RET(nullptr)
+}
+void THCState_setStream(THCState *state, THCStream *stream) {
+  API_BEGIN
+  const int d = current_device();
+  if (stream) {
+    THArgCheck(stream->device == d, 2, "stream belongs to another device");
+    THCStream_retain(stream);
+  }
+  if (state->current[d]) THCStream_free(state->current[d]);
+  state->current[d] = stream;
+  API_END
+}
+THCDeviceAllocator *THCState_getDeviceAllocator(THCState *state) { return state->allocator; }
+void THCState_setDeviceAllocator(THCState *state, THCDeviceAllocator *allocator) { state->allocator = allocator; }
+cudaError_t THCudaMalloc(THCState *state, void **ptr, size_t size) {
+  return state->allocator->malloc(state->allocator->state, ptr, size, state_stream(state));
+}
+cudaError_t THCudaFree(THCState *state, void *ptr) { return state->allocator->free(state->allocator->state, ptr); }
+
+struct THCB200StreamOwned {
+  THCStream s;
+  int owns;
+};
+THCStream *THCStream_new(int flags) {
+  API_BEGIN
+  THCB200StreamOwned *o = (THCB200StreamOwned *)calloc(1, sizeof(THCB200StreamOwned));
+  o->s.device = current_device();
+  THCudaCheck(cudaStreamCreateWithFlags(&o->s.stream, (unsigned)flags));
+  o->s.refcount = 1;
+  o->owns = 1;
+  return &o->s;
+  API_END_RET(nullptr)
+}
+THCStream *THCStream_defaultStream(int device) {
+  THCB200StreamOwned *o = (THCB200StreamOwned *)calloc(1, sizeof(THCB200StreamOwned));
+  o->s.device = device;
+  o->s.stream = 0;
+  o->s.refcount = 1;
+  o->owns = 0;
+  return &o->s;
+}
+THCStream *THCB200_streamFromRaw(cudaStream_t stream, int device) {
+  THCB200StreamOwned *o = (THCB200StreamOwned *)calloc(1, sizeof(THCB200StreamOwned));
+  o->s.device = device;
+  o->s.stream = stream;
+  o->s.refcount = 1;
+  o->owns = 0;
+  return &o->s;
+}
+void THCStream_retain(THCStream *self) { if (self) __sync_fetch_and_add(&self->refcount, 1); }
+void THCStream_free(THCStream *self) {
+  if (!self) return;
+  if (__sync_sub_and_fetch(&self->refcount, 1) > 0) return;
+  THCB200StreamOwned *o = (THCB200StreamOwned *)self;
+  if (o->owns && self->stream) cudaStreamDestroy(self->stream);
+  free(o);
+}
+struct thcb200_ctx *THCB200_currentContext(THCState *state) {
+  API_BEGIN
+  return state_ctx(state);
+  API_END_RET(nullptr)
+}
+
+half THC_float2half(float a) {
+  __half h = __float2half_rn(a);
+  half r;
+  memcpy(&r, &h, sizeof(r));
+  return r;
+}
+float THC_half2float(half a) {
+  __half h;
+  memcpy(&h, &a, sizeof(h));
+  return __half2float(h);
+}
+
+}  // extern "C"
+
+// ======================================================================================
+// Typed storage / tensor templates.  StorageT<R> and TensorT<R> have the layout of the C
+// structs declared per type in THC.h.
+// ======================================================================================
+namespace {
+
+template <typename R> struct StorageT {
+  R *data;
+  ptrdiff_t size;
+  int refcount;
+  char flag;
+  THCDeviceAllocator *allocator;
+  void *allocatorContext;
+  StorageT *view;
+  int device;
+};
+
+template <typename R> struct TensorT {
+  long *size;
+  long *stride;
+  int nDimension;
+  StorageT<R> *storage;
+  ptrdiff_t storageOffset;
+  int refcount;
+  char flag;
+};
+
+template <typename R> struct RealTraits;
+template <> struct RealTraits<unsigned char> { static constexpr int dtype = THCB200_U8; static constexpr bool fp = false; using acc = long; };
+template <> struct RealTraits<char> { static constexpr int dtype = THCB200_I8; static constexpr bool fp = false; using acc = long; };
+template <> struct RealTraits<short> { static constexpr int dtype = THCB200_I16; static constexpr bool fp = false; using acc = long; };
+template <> struct RealTraits<int> { static constexpr int dtype = THCB200_I32; static constexpr bool fp = false; using acc = long; };
+template <> struct RealTraits<long> { static constexpr int dtype = THCB200_I64; static constexpr bool fp = false; using acc = long; };
+template <> struct RealTraits<half> { static constexpr int dtype = THCB200_F16; static constexpr bool fp = true; using acc = float; };
+template <> struct RealTraits<float> { static constexpr int dtype = THCB200_F32; static constexpr bool fp = true; using acc = float; };
+template <> struct RealTraits<double> { static constexpr int dtype = THCB200_F64; static constexpr bool fp = true; using acc = double; };
+
+template <typename R> thcb200_scalar to_scalar(R v) { thcb200_scalar s; s.f = (double)v; s.i = (int64_t)v; return s; }
+template <> thcb200_scalar to_scalar<half>(half v) { thcb200_scalar s; s.f = (double)THC_half2float(v); s.i = (int64_t)s.f; return s; }
+thcb200_scalar scalar_f(double v) { thcb200_scalar s; s.f = v; s.i = (int64_t)v; return s; }
+thcb200_scalar scalar_i(int64_t v) { thcb200_scalar s; s.f = (double)v; s.i = v; return s; }
+template <typename R> R from_double(double v) { return (R)v; }
+template <> half from_double<half>(double v) { return THC_float2half((float)v); }
+template <typename R> double real_to_double(R v) { return (double)v; }
+template <> double real_to_double<half>(half v) { return (double)THC_half2float(v); }
+
+// ---- storage -------------------------------------------------------------------------
+template <typename R> StorageT<R> *storage_new(THCState *state, ptrdiff_t size) {
+  THArgCheck(size >= 0, 2, "invalid size");
+  StorageT<R> *s = (StorageT<R> *)calloc(1, sizeof(StorageT<R>));
+  s->allocator = state->allocator;
+  s->allocatorContext = state->allocator->state;
+  s->refcount = 1;
+  s->flag = TH_STORAGE_REFCOUNTED | TH_STORAGE_RESIZABLE | TH_STORAGE_FREEMEM;
+  s->device = current_device();
+  s->size = size;
+  if (size > 0) {
+    cudaError_t e = s->allocator->malloc(s->allocatorContext, (void **)&s->data, (size_t)size * sizeof(R), state_stream(state));
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      free(s);
+      th_error("cuda runtime error (%d) : %s (allocating %zu bytes)", (int)e, cudaGetErrorString(e), (size_t)size * sizeof(R));
+    }
+  }
+  return s;
+}
+
+template <typename R> void storage_free(THCState *, StorageT<R> *s) {
+  if (!s) return;
+  if (!(s->flag & TH_STORAGE_REFCOUNTED)) return;
+  if (__sync_sub_and_fetch(&s->refcount, 1) > 0) return;
+  if ((s->flag & TH_STORAGE_FREEMEM) && s->data) s->allocator->free(s->allocatorContext, s->data);
+  if ((s->flag & TH_STORAGE_FREEMEM) == 0 && s->view) storage_free<R>(nullptr, s->view);
+  free(s);
+}
+
+template <typename R> void storage_resize(THCState *state, StorageT<R> *s, ptrdiff_t size) {
+  THArgCheck(size >= 0, 2, "invalid size");
+  if (!(s->flag & TH_STORAGE_RESIZABLE)) th_error("Trying to resize storage that is not resizable");
+  if (size == s->size) return;
+  R *nd = nullptr;
+  if (size > 0) {
+    cudaError_t e = s->allocator->malloc(s->allocatorContext, (void **)&nd, (size_t)size * sizeof(R), state_stream(state));
+    if (e != cudaSuccess) { cudaGetLastError(); th_error("cuda runtime error (%d) : %s", (int)e, cudaGetErrorString(e)); }
+    if (s->data && s->size > 0) {
+      const ptrdiff_t keep = size < s->size ? size : s->size;
+      THCudaCheck(cudaMemcpyAsync(nd, s->data, (size_t)keep * sizeof(R), cudaMemcpyDeviceToDevice, state_stream(state)));
+    }
+  }
+  if (s->data && (s->flag & TH_STORAGE_FREEMEM)) {
+    // the old block may still be read by work queued on the stream
+    THCudaCheck(cudaStreamSynchronize(state_stream(state)));
+    s->allocator->free(s->allocatorContext, s->data);
+  }
+  s->data = nd;
+  s->size = size;
+  s->flag |= TH_STORAGE_FREEMEM;
+}
+
+// ---- tensor --------------------------------------------------------------------------
+template <typename R> TensorT<R> *tensor_alloc() {
+  TensorT<R> *t = (TensorT<R> *)calloc(1, sizeof(TensorT<R>));
+  t->refcount = 1;
+  t->flag = TH_TENSOR_REFCOUNTED;
+  return t;
+}
+
+template <typename R> ptrdiff_t tensor_nelement(const TensorT<R> *t) {
+  if (t->nDimension == 0) return 0;
+  ptrdiff_t n = 1;
+  for (int d = 0; d < t->nDimension; ++d) n *= t->size[d];
+  return n;
+}
+
+template <typename R> bool tensor_is_contiguous(const TensorT<R> *t) {
+  long z = 1;
+  for (int d = t->nDimension - 1; d >= 0; --d) {
+    if (t->size[d] != 1) {
+      if (t->stride[d] != z) return false;
+      z *= t->size[d];
+    }
+  }
+  return true;
+}
+
+template <typename R> bool tensor_same_size(const TensorT<R> *a, const TensorT<R> *b) {
+  if (a->nDimension != b->nDimension) return false;
+  for (int d = 0; d < a->nDimension; ++d)
+    if (a->size[d] != b->size[d]) return false;
+  return true;
+}
+
+// Gives the tensor nd dims of the given sizes; strides default to row-major when `stride`
+// is null or an entry is negative.  The storage only ever grows.
+template <typename R> void tensor_raw_resize(THCState *state, TensorT<R> *t, int nd, const long *size, const long *stride) {
+  bool same = (nd == t->nDimension);
+  for (int d = 0; same && d < nd; ++d) {
+    if (size[d] != t->size[d]) same = false;
+    if (stride && stride[d] >= 0 && stride[d] != t->stride[d]) same = false;
+  }
+  if (same) return;
+  if (nd <= 0) { t->nDimension = 0; return; }
+  if (nd != t->nDimension) {
+    t->size = (long *)realloc(t->size, sizeof(long) * nd);
+    t->stride = (long *)realloc(t->stride, sizeof(long) * nd);
+    t->nDimension = nd;
+  }
+  ptrdiff_t extent = 1;
+  for (int d = nd - 1; d >= 0; --d) {
+    t->size[d] = size[d];
+    if (stride && stride[d] >= 0) t->stride[d] = stride[d];
+    else t->stride[d] = (d == nd - 1) ? 1 : t->size[d + 1] * t->stride[d + 1];
+    extent += (ptrdiff_t)(t->size[d] - 1) * t->stride[d];
+  }
+  if (extent + t->storageOffset > 0) {
+    if (!t->storage) t->storage = storage_new<R>(state, 0);
+    if (extent + t->storageOffset > t->storage->size) storage_resize<R>(state, t->storage, extent + t->storageOffset);
+  }
+}
+
+template <typename R> void tensor_raw_set(THCState *state, TensorT<R> *t, StorageT<R> *storage, ptrdiff_t offset, int nd,
+                                          const long *size, const long *stride) {
+  THArgCheck(offset >= 0, 3, "Tensor: invalid storage offset");
+  if (t->storage != storage) {
+    if (t->storage) storage_free<R>(state, t->storage);
+    t->storage = storage;
+    if (storage) __sync_fetch_and_add(&storage->refcount, 1);
+  }
+  t->storageOffset = offset;
+  tensor_raw_resize<R>(state, t, nd, size, stride);
+}
+
+template <typename R> void tensor_free(THCState *state, TensorT<R> *t) {
+  if (!t) return;
+  if (!(t->flag & TH_TENSOR_REFCOUNTED)) return;
+  if (__sync_sub_and_fetch(&t->refcount, 1) > 0) return;
+  free(t->size);
+  free(t->stride);
+  if (t->storage) storage_free<R>(state, t->storage);
+  free(t);
+}
+
+template <typename R> TensorT<R> *tensor_new_with_tensor(THCState *state, TensorT<R> *src) {
+  TensorT<R> *t = tensor_alloc<R>();
+  tensor_raw_set<R>(state, t, src->storage, src->storageOffset, src->nDimension, src->size, src->stride);
+  return t;
+}
+
+template <typename R> void tensor_narrow(THCState *state, TensorT<R> *self, TensorT<R> *src, int dim, long first, long size) {
+  if (!src) src = self;
+  THArgCheck(dim >= 0 && dim < src->nDimension, 3, "out of range");
+  THArgCheck(first >= 0 && first < src->size[dim], 4, "out of range");
+  THArgCheck(size > 0 && first + size <= src->size[dim], 5, "out of range");
+  if (self != src) tensor_raw_set<R>(state, self, src->storage, src->storageOffset, src->nDimension, src->size, src->stride);
+  if (first > 0) self->storageOffset += first * self->stride[dim];
+  self->size[dim] = size;
+}
+
+template <typename R> void tensor_select(THCState *state, TensorT<R> *self, TensorT<R> *src, int dim, long index) {
+  if (!src) src = self;
+  THArgCheck(src->nDimension > 1, 1, "cannot select on a vector");
+  THArgCheck(dim >= 0 && dim < src->nDimension, 3, "out of range");
+  THArgCheck(index >= 0 && index < src->size[dim], 4, "out of range");
+  if (self != src) tensor_raw_set<R>(state, self, src->storage, src->storageOffset, src->nDimension, src->size, src->stride);
+  tensor_narrow<R>(state, self, nullptr, dim, index, 1);
+  for (int d = dim; d < self->nDimension - 1; ++d) {
+    self->size[d] = self->size[d + 1];
+    self->stride[d] = self->stride[d + 1];
+  }
+  self->nDimension--;
+}
+
+template <typename R> void tensor_transpose(THCState *state, TensorT<R> *self, TensorT<R> *src, int d1, int d2) {
+  if (!src) src = self;
+  THArgCheck(d1 >= 0 && d1 < src->nDimension, 1, "out of range");
+  THArgCheck(d2 >= 0 && d2 < src->nDimension, 2, "out of range");
+  if (self != src) tensor_raw_set<R>(state, self, src->storage, src->storageOffset, src->nDimension, src->size, src->stride);
+  if (d1 == d2) return;
+  long z = self->stride[d1]; self->stride[d1] = self->stride[d2]; self->stride[d2] = z;
+  z = self->size[d1]; self->size[d1] = self->size[d2]; self->size[d2] = z;
+}
+
+template <typename R> void tensor_squeeze1d(THCState *state, TensorT<R> *self, TensorT<R> *src, int dim) {
+  if (!src) src = self;
+  THArgCheck(dim >= 0 && dim < src->nDimension, 3, "dimension out of range");
+  if (self != src) tensor_raw_set<R>(state, self, src->storage, src->storageOffset, src->nDimension, src->size, src->stride);
+  if (src->size[dim] == 1 && src->nDimension > 1) {
+    for (int d = dim; d < self->nDimension - 1; ++d) {
+      self->size[d] = self->size[d + 1];
+      self->stride[d] = self->stride[d + 1];
+    }
+    self->nDimension--;
+  }
+}
+
+template <typename R> void tensor_resize_as(THCState *state, TensorT<R> *self, TensorT<R> *src) {
+  if (!tensor_same_size<R>(self, src)) tensor_raw_resize<R>(state, self, src->nDimension, src->size, nullptr);
+}
+
+// ---- descriptors and the math layer ----------------------------------------------------
+template <typename R> thcb200_tensor describe(const TensorT<R> *t) {
+  thcb200_tensor d;
+  memset(&d, 0, sizeof(d));
+  d.dtype = RealTraits<R>::dtype;
+  d.ndim = t->nDimension;
+  if (t->nDimension > THCB200_MAX_DIMS) th_arg_error(2, CUTORCH_DIM_WARNING);
+  for (int i = 0; i < t->nDimension; ++i) { d.sizes[i] = t->size[i]; d.strides[i] = t->stride[i]; }
+  d.data = (t->storage && t->storage->data) ? (void *)(t->storage->data + t->storageOffset) : nullptr;
+  return d;
+}
+
+void check_core(int rc, int arg = 2) {
+  if (rc == 0) return;
+  if (rc == THCB200_ERR_DIMS) th_arg_error(arg, CUTORCH_DIM_WARNING);
+  if (rc == THCB200_ERR_SIZE) th_arg_error(arg, "sizes do not match");
+  th_error("%s", thcb200_last_error());
+}
+
+template <typename R> void check_gpu1(THCState *, const TensorT<R> *t, int cur) {
+  if (t && t->storage && t->storage->data && t->storage->device != cur) th_error("arguments are located on different GPUs");
+}
+template <typename R> void check_gpu(THCState *state, std::initializer_list<const TensorT<R> *> ts) {
+  const int cur = current_device();
+  for (const TensorT<R> *t : ts) check_gpu1<R>(state, t, cur);
+}
+
+template <typename R>
+void pointwise(THCState *state, int op, TensorT<R> *out, TensorT<R> *a, TensorT<R> *b, TensorT<R> *c, thcb200_scalar s0,
+               thcb200_scalar s1, int flags = 0) {
+  thcb200_tensor dout = describe<R>(out), da, db, dc;
+  int nin = 0;
+  if (a) { da = describe<R>(a); nin = 1; }
+  if (b) { db = describe<R>(b); nin = 2; }
+  if (c) { dc = describe<R>(c); nin = 3; }
+  check_core(thcb200_pointwise_ex(state_ctx(state), op, &dout, a ? &da : nullptr, b ? &db : nullptr, c ? &dc : nullptr, nin,
+                                  s0, s1, (void *)state_stream(state), flags));
+}
+
+const thcb200_scalar kZero = {0.0, 0};
+
+// self = op(src) (in place when self == src)
+template <typename R> void unary(THCState *state, int op, TensorT<R> *self, TensorT<R> *src, thcb200_scalar s0 = kZero,
+                                 thcb200_scalar s1 = kZero) {
+  check_gpu<R>(state, {self, src});
+  if (self != src) tensor_resize_as<R>(state, self, src);
+  pointwise<R>(state, op, self, src, nullptr, nullptr, s0, s1);
+}
+
+// self = op(src1, src2) (in place when self == src1)
+template <typename R> void binary(THCState *state, int op, TensorT<R> *self, TensorT<R> *src1, TensorT<R> *src2,
+                                  thcb200_scalar s0 = kZero) {
+  check_gpu<R>(state, {self, src1, src2});
+  THArgCheck(tensor_nelement<R>(src1) == tensor_nelement<R>(src2), 3, "sizes do not match");
+  if (self != src1) tensor_resize_as<R>(state, self, src1);
+  pointwise<R>(state, op, self, src1, src2, nullptr, s0, kZero);
+}
+
+// byte ranges [lo, hi) of the elements a view can touch
+template <typename R> bool may_alias(const TensorT<R> *a, const TensorT<R> *b) {
+  if (!a->storage || !b->storage || !a->storage->data || !b->storage->data) return false;
+  auto range = [](const TensorT<R> *t, const R *&lo, const R *&hi) {
+    ptrdiff_t mn = 0, mx = 0;
+    for (int d = 0; d < t->nDimension; ++d) {
+      if (t->size[d] == 0) { lo = hi = nullptr; return; }
+      const ptrdiff_t span = (ptrdiff_t)(t->size[d] - 1) * t->stride[d];
+      if (span > 0) mx += span; else mn += span;
+    }
+    lo = t->storage->data + t->storageOffset + mn;
+    hi = t->storage->data + t->storageOffset + mx + 1;
+  };
+  const R *alo, *ahi, *blo, *bhi;
+  range(a, alo, ahi);
+  range(b, blo, bhi);
+  if (!alo || !blo) return false;
+  return alo < bhi && blo < ahi;
+}
+
+template <typename R> void tensor_copy(THCState *state, TensorT<R> *self, TensorT<R> *src, int flags = 0) {
+  if (self == src) return;
+  THArgCheck(tensor_nelement<R>(self) == tensor_nelement<R>(src), 2, "sizes do not match");
+  const ptrdiff_t n = tensor_nelement<R>(self);
+  if (n == 0) return;
+  check_gpu<R>(state, {self, src});
+  if (tensor_is_contiguous<R>(self) && tensor_is_contiguous<R>(src)) {
+    THCudaCheck(cudaMemcpyAsync(self->storage->data + self->storageOffset, src->storage->data + src->storageOffset,
+                                (size_t)n * sizeof(R), cudaMemcpyDeviceToDevice, state_stream(state)));
+    return;
+  }
+  pointwise<R>(state, THCB200_OP_COPY, self, src, nullptr, nullptr, kZero, kZero, flags);
+}
+
+template <typename RD, typename RS> void tensor_copy_convert(THCState *state, TensorT<RD> *dst, TensorT<RS> *src) {
+  THArgCheck(tensor_nelement<RD>(dst) == tensor_nelement<RS>(src), 2, "sizes do not match");
+  if (tensor_nelement<RD>(dst) == 0) return;
+  thcb200_tensor dd = describe<RD>(dst), ds = describe<RS>(src);
+  check_core(thcb200_copy_convert(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
+}
+
+template <typename R> TensorT<R> *tensor_new_contiguous(THCState *state, TensorT<R> *t) {
+  if (tensor_is_contiguous<R>(t)) { __sync_fetch_and_add(&t->refcount, 1); return t; }
+  TensorT<R> *c = tensor_alloc<R>();
+  tensor_raw_resize<R>(state, c, t->nDimension, t->size, nullptr);
+  tensor_copy<R>(state, c, t);
+  return c;
+}
+
+template <typename R> TensorT<R> *tensor_new_clone(THCState *state, TensorT<R> *t) {
+  TensorT<R> *c = tensor_alloc<R>();
+  tensor_raw_resize<R>(state, c, t->nDimension, t->size, nullptr);
+  tensor_copy<R>(state, c, t);
+  return c;
+}
+
+// out = t + value * (src1 (*|/) src2).  cutorch copies t into self and then updates self in
+// place (lib/THC/generic/THCTensorMathPointwise.cu:582-629); when self shares no memory with
+// src1/src2 the copy is folded into one four-operand kernel, which computes the same values.
+template <typename R> void addc(THCState *state, int op, TensorT<R> *self, TensorT<R> *t, R value, TensorT<R> *src1,
+                                TensorT<R> *src2) {
+  check_gpu<R>(state, {self, t, src1, src2});
+  THArgCheck(tensor_nelement<R>(src1) == tensor_nelement<R>(src2), 3, "sizes do not match");
+  if (self != t) {
+    tensor_resize_as<R>(state, self, t);
+    if (!may_alias<R>(self, src1) && !may_alias<R>(self, src2) && !may_alias<R>(self, t)) {
+      pointwise<R>(state, op, self, t, src1, src2, to_scalar<R>(value), kZero);
+      return;
+    }
+    tensor_copy<R>(state, self, t);
+  }
+  pointwise<R>(state, op, self, self, src1, src2, to_scalar<R>(value), kZero);
+}
+
+template <typename R> R negate(R v) { return (R)(-v); }
+template <> half negate<half>(half v) { return THC_float2half(-THC_half2float(v)); }
+template <typename R> bool is_one(R v) { return v == (R)1; }
+template <> bool is_one<half>(half v) { return THC_half2float(v) == 1.0f; }
+
+// cross product along `dimension` of two tensors holding 3-vectors there
+// (lib/THC/generic/THCTensorMathPointwise.cu:111-144): out_i = x_j * y_k - x_k * y_j.
+template <typename R> void cross(THCState *state, TensorT<R> *self, TensorT<R> *x, TensorT<R> *y, int dimension) {
+  check_gpu<R>(state, {self, x, y});
+  THArgCheck(x->nDimension == y->nDimension, 2, "inconsistent tensor dimension");
+  for (int i = 0; i < x->nDimension; ++i) THArgCheck(x->size[i] == y->size[i], 2, "inconsistent tensor sizes");
+  THArgCheck(dimension >= 0 && dimension < x->nDimension, 3, "dimension out of range");
+  THArgCheck(x->size[dimension] == 3, 3, "dimension must have size 3");
+  TensorT<R> *xs = x, *ys = y;
+  bool ox = false, oy = false;
+  if (self == x || may_alias<R>(self, x)) { xs = tensor_new_clone<R>(state, x); ox = true; }
+  if (self == y || may_alias<R>(self, y)) { ys = tensor_new_clone<R>(state, y); oy = true; }
+  tensor_resize_as<R>(state, self, xs);
+  for (int i = 0; i < 3; ++i) {
+    const int j = (i + 1) % 3, k = (i + 2) % 3;
+    TensorT<R> *o = tensor_new_with_tensor<R>(state, self), *xj = tensor_new_with_tensor<R>(state, xs),
+               *xk = tensor_new_with_tensor<R>(state, xs), *yj = tensor_new_with_tensor<R>(state, ys),
+               *yk = tensor_new_with_tensor<R>(state, ys);
+    tensor_narrow<R>(state, o, nullptr, dimension, i, 1);
+    tensor_narrow<R>(state, xj, nullptr, dimension, j, 1);
+    tensor_narrow<R>(state, xk, nullptr, dimension, k, 1);
+    tensor_narrow<R>(state, yj, nullptr, dimension, j, 1);
+    tensor_narrow<R>(state, yk, nullptr, dimension, k, 1);
+    pointwise<R>(state, THCB200_OP_MUL, o, xj, yk, nullptr, kZero, kZero);
+    pointwise<R>(state, THCB200_OP_ADDCMUL, o, o, xk, yj, scalar_i(-1), kZero);
+    tensor_free<R>(state, o); tensor_free<R>(state, xj); tensor_free<R>(state, xk);
+    tensor_free<R>(state, yj); tensor_free<R>(state, yk);
+  }
+  if (ox) tensor_free<R>(state, xs);
+  if (oy) tensor_free<R>(state, ys);
+}
+
+// ---- reductions ----------------------------------------------------------------------
+template <typename R> void resize_reduced(THCState *state, TensorT<R> *out, const long *src_size, int nd, long dim) {
+  long sz[THCB200_MAX_DIMS];
+  for (int i = 0; i < nd; ++i) sz[i] = src_size[i];
+  sz[dim] = 1;
+  tensor_raw_resize<R>(state, out, nd, sz, nullptr);
+}
+
+template <typename R>
+void reduce_dim(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self, TensorT<R> *src, long dim, int keepdim) {
+  check_gpu<R>(state, {self, src});
+  THArgCheck(src->nDimension <= THCB200_MAX_DIMS, 2, CUTORCH_DIM_WARNING);
+  THArgCheck(dim >= 0 && dim < src->nDimension, 3, "dimension out of range");
+  THArgCheck(self != src, 1, "output must differ from the input");
+  resize_reduced<R>(state, self, src->size, src->nDimension, dim);
+  thcb200_tensor dout = describe<R>(self), din = describe<R>(src);
+  check_core(thcb200_reduce_dim(state_ctx(state), rop, pre, s, &dout, &din, (int)dim, (void *)state_stream(state)));
+  if (!keepdim) tensor_squeeze1d<R>(state, self, nullptr, (int)dim);
+}
+
+template <typename R>
+void reduce_dim_index(THCState *state, int rop, TensorT<R> *values, TensorT<long> *indices, TensorT<R> *src, long dim, int keepdim) {
+  check_gpu<R>(state, {values, src});
+  check_gpu<long>(state, {indices});
+  THArgCheck(src->nDimension <= THCB200_MAX_DIMS, 4, CUTORCH_DIM_WARNING);
+  THArgCheck(dim >= 0 && dim < src->nDimension, 5, "dimension out of range");
+  THArgCheck(values != src, 1, "output must differ from the input");
+  resize_reduced<R>(state, values, src->size, src->nDimension, dim);
+  resize_reduced<long>(state, indices, src->size, src->nDimension, dim);
+  thcb200_tensor dv = describe<R>(values), di = describe<long>(indices), din = describe<R>(src);
+  check_core(thcb200_reduce_dim_index(state_ctx(state), rop, &dv, &di, &din, (int)dim, (void *)state_stream(state)), 4);
+  if (!keepdim) {
+    tensor_squeeze1d<R>(state, values, nullptr, (int)dim);
+    tensor_squeeze1d<long>(state, indices, nullptr, (int)dim);
+  }
+}
+
+// Full reduction to the host.  The core returns a double (floating types) or int64.
+template <typename R> double reduce_all_f(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self) {
+  check_gpu<R>(state, {self});
+  thcb200_tensor d = describe<R>(self);
+  union { double f; int64_t i; } r;
+  r.i = 0;
+  check_core(thcb200_reduce_all_host(state_ctx(state), rop, pre, s, &d, &r, (void *)state_stream(state)), 1);
+  return RealTraits<R>::fp ? r.f : (double)r.i;
+}
+template <typename R> int64_t reduce_all_i(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self) {
+  check_gpu<R>(state, {self});
+  thcb200_tensor d = describe<R>(self);
+  union { double f; int64_t i; } r;
+  r.i = 0;
+  check_core(thcb200_reduce_all_host(state_ctx(state), rop, pre, s, &d, &r, (void *)state_stream(state)), 1);
+  return RealTraits<R>::fp ? (int64_t)r.f : r.i;
+}
+template <typename R> typename RealTraits<R>::acc reduce_all_acc(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self) {
+  using A = typename RealTraits<R>::acc;
+  if (RealTraits<R>::fp) return (A)reduce_all_f<R>(state, rop, pre, s, self);
+  return (A)reduce_all_i<R>(state, rop, pre, s, self);
+}
+
+}  // namespace
+
+// ======================================================================================
+// Per-type extern "C" wrappers
+// ======================================================================================
+#define real unsigned char
+#define accreal long
+#define CReal CudaByte
+#define THC_T_FLOATING 0
+#define THC_T_SIGNED 0
+#define THC_T_HALF 0
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+#undef THC_T_SIGNED
+
+#define real char
+#define accreal long
+#define CReal CudaChar
+#define THC_T_SIGNED 0
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+#undef THC_T_SIGNED
+#define THC_T_SIGNED 1
+
+#define real short
+#define accreal long
+#define CReal CudaShort
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+
+#define real int
+#define accreal long
+#define CReal CudaInt
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+
+#define real long
+#define accreal long
+#define CReal CudaLong
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+
+#undef THC_T_FLOATING
+#define THC_T_FLOATING 1
+
+#define real half
+#define accreal float
+#define CReal CudaHalf
+#undef THC_T_HALF
+#define THC_T_HALF 1
+#include "thc_compat_type.inc"
+#undef THC_T_HALF
+#define THC_T_HALF 0
+#undef real
+#undef accreal
+#undef CReal
+
+#define real float
+#define accreal float
+#define CReal Cuda
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+
+#define real double
+#define accreal double
+#define CReal CudaDouble
+#include "thc_compat_type.inc"
+#undef real
+#undef accreal
+#undef CReal
+
+extern "C" {
+int THCudaByteTensor_logicalall(THCState *state, THCudaByteTensor *self) {
+  API_BEGIN
+  return (int)reduce_all_i<unsigned char>(state, THCB200_RED_ALL, THCB200_PRE_IDENTITY, kZero, (TensorT<unsigned char> *)self);
+  API_END_RET(0)
+}
+int THCudaByteTensor_logicalany(THCState *state, THCudaByteTensor *self) {
+  API_BEGIN
+  return (int)reduce_all_i<unsigned char>(state, THCB200_RED_ANY, THCB200_PRE_IDENTITY, kZero, (TensorT<unsigned char> *)self);
+  API_END_RET(0)
+}
+}

@@ -1,0 +1,220 @@
+/* Per-type declarations, expanded by THCForEachType.h with `real`, `accreal`, `CReal`,
+ * THC_T_FLOATING, THC_T_SIGNED and THC_T_HALF defined.  Not include-guarded on purpose. */
+#define THCTensor TH_CONCAT_3(TH, CReal, Tensor)
+#define THCStorage TH_CONCAT_3(TH, CReal, Storage)
+#define THCTensor_(NAME) TH_CONCAT_4(TH, CReal, Tensor_, NAME)
+#define THCStorage_(NAME) TH_CONCAT_4(TH, CReal, Storage_, NAME)
+
+#ifdef THC_B200_DECLARE_STRUCTS
+
+/* lib/THC/generic/THCStorage.h:9-19 */
+typedef struct THCStorage {
+  real *data;
+  ptrdiff_t size;
+  int refcount;
+  char flag;
+  THCDeviceAllocator *allocator;
+  void *allocatorContext;
+  struct THCStorage *view;
+  int device;
+} THCStorage;
+
+/* lib/THC/generic/THCTensor.h:7-19 */
+typedef struct THCTensor {
+  long *size;
+  long *stride;
+  int nDimension;
+  THCStorage *storage;
+  ptrdiff_t storageOffset;
+  int refcount;
+  char flag;
+} THCTensor;
+
+#endif /* THC_B200_DECLARE_STRUCTS */
+
+#ifdef THC_B200_DECLARE_API
+
+/* ---- storage (lib/THC/generic/THCStorage.h) ---- */
+THC_API real *THCStorage_(data)(THCState *state, const THCStorage *self);
+THC_API ptrdiff_t THCStorage_(size)(THCState *state, const THCStorage *self);
+THC_API int THCStorage_(elementSize)(THCState *state);
+THC_API THCStorage *THCStorage_(new)(THCState *state);
+THC_API THCStorage *THCStorage_(newWithSize)(THCState *state, ptrdiff_t size);
+/* takes ownership of data (cudaMalloc'ed); clear TH_STORAGE_FREEMEM to only borrow it */
+THC_API THCStorage *THCStorage_(newWithData)(THCState *state, real *data, ptrdiff_t size);
+THC_API void THCStorage_(setFlag)(THCState *state, THCStorage *storage, const char flag);
+THC_API void THCStorage_(clearFlag)(THCState *state, THCStorage *storage, const char flag);
+THC_API void THCStorage_(retain)(THCState *state, THCStorage *storage);
+THC_API void THCStorage_(free)(THCState *state, THCStorage *storage);
+THC_API void THCStorage_(resize)(THCState *state, THCStorage *storage, ptrdiff_t size);
+THC_API int THCStorage_(getDevice)(THCState *state, const THCStorage *storage);
+
+/* ---- tensor (lib/THC/generic/THCTensor.h) ---- */
+THC_API THCStorage *THCTensor_(storage)(THCState *state, const THCTensor *self);
+THC_API ptrdiff_t THCTensor_(storageOffset)(THCState *state, const THCTensor *self);
+THC_API int THCTensor_(nDimension)(THCState *state, const THCTensor *self);
+THC_API long THCTensor_(size)(THCState *state, const THCTensor *self, int dim);
+THC_API long THCTensor_(stride)(THCState *state, const THCTensor *self, int dim);
+THC_API THLongStorage *THCTensor_(newSizeOf)(THCState *state, THCTensor *self);
+THC_API THLongStorage *THCTensor_(newStrideOf)(THCState *state, THCTensor *self);
+THC_API real *THCTensor_(data)(THCState *state, const THCTensor *self);
+
+THC_API THCTensor *THCTensor_(new)(THCState *state);
+THC_API THCTensor *THCTensor_(newWithTensor)(THCState *state, THCTensor *tensor);
+THC_API THCTensor *THCTensor_(newWithStorage)(THCState *state, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                              THLongStorage *size_, THLongStorage *stride_);
+THC_API THCTensor *THCTensor_(newWithStorage1d)(THCState *state, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                                long size0_, long stride0_);
+THC_API THCTensor *THCTensor_(newWithStorage2d)(THCState *state, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                                long size0_, long stride0_, long size1_, long stride1_);
+THC_API THCTensor *THCTensor_(newWithStorage3d)(THCState *state, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                                long size0_, long stride0_, long size1_, long stride1_,
+                                                long size2_, long stride2_);
+THC_API THCTensor *THCTensor_(newWithStorage4d)(THCState *state, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                                long size0_, long stride0_, long size1_, long stride1_,
+                                                long size2_, long stride2_, long size3_, long stride3_);
+THC_API THCTensor *THCTensor_(newWithSize)(THCState *state, THLongStorage *size_, THLongStorage *stride_);
+THC_API THCTensor *THCTensor_(newWithSize1d)(THCState *state, long size0_);
+THC_API THCTensor *THCTensor_(newWithSize2d)(THCState *state, long size0_, long size1_);
+THC_API THCTensor *THCTensor_(newWithSize3d)(THCState *state, long size0_, long size1_, long size2_);
+THC_API THCTensor *THCTensor_(newWithSize4d)(THCState *state, long size0_, long size1_, long size2_, long size3_);
+THC_API THCTensor *THCTensor_(newClone)(THCState *state, THCTensor *self);
+THC_API THCTensor *THCTensor_(newContiguous)(THCState *state, THCTensor *tensor);
+THC_API THCTensor *THCTensor_(newSelect)(THCState *state, THCTensor *tensor, int dimension_, long sliceIndex_);
+THC_API THCTensor *THCTensor_(newNarrow)(THCState *state, THCTensor *tensor, int dimension_, long firstIndex_, long size_);
+THC_API THCTensor *THCTensor_(newTranspose)(THCState *state, THCTensor *tensor, int dimension1_, int dimension2_);
+
+THC_API void THCTensor_(resize)(THCState *state, THCTensor *tensor, THLongStorage *size, THLongStorage *stride);
+THC_API void THCTensor_(resizeAs)(THCState *state, THCTensor *tensor, THCTensor *src);
+THC_API void THCTensor_(resize1d)(THCState *state, THCTensor *tensor, long size0_);
+THC_API void THCTensor_(resize2d)(THCState *state, THCTensor *tensor, long size0_, long size1_);
+THC_API void THCTensor_(resize3d)(THCState *state, THCTensor *tensor, long size0_, long size1_, long size2_);
+THC_API void THCTensor_(resize4d)(THCState *state, THCTensor *tensor, long size0_, long size1_, long size2_, long size3_);
+THC_API void THCTensor_(set)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(setStorage)(THCState *state, THCTensor *self, THCStorage *storage_, ptrdiff_t storageOffset_,
+                                    THLongStorage *size_, THLongStorage *stride_);
+THC_API void THCTensor_(narrow)(THCState *state, THCTensor *self, THCTensor *src, int dimension_, long firstIndex_, long size_);
+THC_API void THCTensor_(select)(THCState *state, THCTensor *self, THCTensor *src, int dimension_, long sliceIndex_);
+THC_API void THCTensor_(transpose)(THCState *state, THCTensor *self, THCTensor *src, int dimension1_, int dimension2_);
+THC_API void THCTensor_(squeeze1d)(THCState *state, THCTensor *self, THCTensor *src, int dimension_);
+THC_API int THCTensor_(isContiguous)(THCState *state, const THCTensor *self);
+THC_API int THCTensor_(isSameSizeAs)(THCState *state, const THCTensor *self, const THCTensor *src);
+THC_API ptrdiff_t THCTensor_(nElement)(THCState *state, const THCTensor *self);
+THC_API void THCTensor_(retain)(THCState *state, THCTensor *self);
+THC_API void THCTensor_(free)(THCState *state, THCTensor *self);
+THC_API void THCTensor_(freeCopyTo)(THCState *state, THCTensor *self, THCTensor *dst);
+THC_API int THCTensor_(getDevice)(THCState *state, const THCTensor *self);
+THC_API int THCTensor_(checkGPU)(THCState *state, unsigned int nTensors, ...);
+
+/* ---- fill / copy (lib/THC/generic/THCTensorMath.h:5-6, THCTensorCopy.h) ---- */
+THC_API void THCTensor_(fill)(THCState *state, THCTensor *self, real value);
+THC_API void THCTensor_(zero)(THCState *state, THCTensor *self);
+THC_API void THCTensor_(copy)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(copyIgnoringOverlaps)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(copyCudaByte)(THCState *state, THCTensor *dst, struct THCudaByteTensor *src);
+THC_API void THCTensor_(copyCudaChar)(THCState *state, THCTensor *dst, struct THCudaCharTensor *src);
+THC_API void THCTensor_(copyCudaShort)(THCState *state, THCTensor *dst, struct THCudaShortTensor *src);
+THC_API void THCTensor_(copyCudaInt)(THCState *state, THCTensor *dst, struct THCudaIntTensor *src);
+THC_API void THCTensor_(copyCudaLong)(THCState *state, THCTensor *dst, struct THCudaLongTensor *src);
+THC_API void THCTensor_(copyCudaHalf)(THCState *state, THCTensor *dst, struct THCudaHalfTensor *src);
+THC_API void THCTensor_(copyCuda)(THCState *state, THCTensor *dst, struct THCudaTensor *src);
+THC_API void THCTensor_(copyCudaDouble)(THCState *state, THCTensor *dst, struct THCudaDoubleTensor *src);
+
+/* ---- pointwise math (lib/THC/generic/THCTensorMathPointwise.h) ---- */
+#if THC_T_FLOATING
+THC_API void THCTensor_(sigmoid)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(log)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(lgamma)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(log1p)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(exp)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(cos)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(acos)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(cosh)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(sin)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(asin)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(sinh)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(tan)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(atan)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(atan2)(THCState *state, THCTensor *r_, THCTensor *tx, THCTensor *ty);
+THC_API void THCTensor_(tanh)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(pow)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(tpow)(THCState *state, THCTensor *self, real value, THCTensor *src);
+THC_API void THCTensor_(sqrt)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(rsqrt)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(ceil)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(floor)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(round)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(trunc)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(frac)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(lerp)(THCState *state, THCTensor *result, THCTensor *a, THCTensor *b, real w);
+THC_API void THCTensor_(cinv)(THCState *state, THCTensor *self, THCTensor *src);
+#endif
+#if THC_T_FLOATING || THC_T_SIGNED
+THC_API void THCTensor_(neg)(THCState *state, THCTensor *self, THCTensor *src);
+#endif
+THC_API void THCTensor_(abs)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(sign)(THCState *state, THCTensor *self, THCTensor *src);
+THC_API void THCTensor_(clamp)(THCState *state, THCTensor *self, THCTensor *src, real min_value, real max_value);
+THC_API void THCTensor_(cross)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2, int dimension);
+THC_API void THCTensor_(cadd)(THCState *state, THCTensor *self, THCTensor *src1, real value, THCTensor *src2);
+THC_API void THCTensor_(csub)(THCState *state, THCTensor *self, THCTensor *src1, real value, THCTensor *src2);
+THC_API void THCTensor_(cmul)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cpow)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cdiv)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(clshift)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(crshift)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cmax)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cmin)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cfmod)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cremainder)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cmaxValue)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(cminValue)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(cbitand)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cbitor)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(cbitxor)(THCState *state, THCTensor *self, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(addcmul)(THCState *state, THCTensor *self, THCTensor *t, real value, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(addcdiv)(THCState *state, THCTensor *self, THCTensor *t, real value, THCTensor *src1, THCTensor *src2);
+
+/* ---- tensor (op) scalar (lib/THC/generic/THCTensorMathPairwise.h) ---- */
+THC_API void THCTensor_(add)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(sub)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(mul)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(div)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(lshift)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(rshift)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(fmod)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(remainder)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(bitand)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(bitor)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(bitxor)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API int THCTensor_(equal)(THCState *state, THCTensor *self, THCTensor *src);
+
+/* ---- reductions (lib/THC/generic/THCTensorMathReduce.h) ---- */
+#if THC_T_FLOATING
+THC_API void THCTensor_(norm)(THCState *state, THCTensor *self, THCTensor *src, real value, long dimension, int keepdim);
+THC_API accreal THCTensor_(normall)(THCState *state, THCTensor *self, real value);
+THC_API accreal THCTensor_(varall)(THCState *state, THCTensor *self, int biased);
+THC_API accreal THCTensor_(stdall)(THCState *state, THCTensor *self, int biased);
+#endif
+THC_API void THCTensor_(sum)(THCState *state, THCTensor *self, THCTensor *src, long dim, int keepdim);
+THC_API void THCTensor_(prod)(THCState *state, THCTensor *self, THCTensor *src, long dim, int keepdim);
+THC_API void THCTensor_(mean)(THCState *state, THCTensor *self, THCTensor *src, long dim, int keepdim);
+THC_API accreal THCTensor_(sumall)(THCState *state, THCTensor *self);
+THC_API accreal THCTensor_(prodall)(THCState *state, THCTensor *self);
+THC_API accreal THCTensor_(meanall)(THCState *state, THCTensor *self);
+THC_API void THCTensor_(min)(THCState *state, THCTensor *values, struct THCudaLongTensor *indices, THCTensor *src, long dim, int keepdim);
+THC_API void THCTensor_(max)(THCState *state, THCTensor *values, struct THCudaLongTensor *indices, THCTensor *src, long dim, int keepdim);
+THC_API real THCTensor_(minall)(THCState *state, THCTensor *self);
+THC_API real THCTensor_(maxall)(THCState *state, THCTensor *self);
+
+/* Extensions with no counterpart in cutorch: the full-reduction result stays on the device
+ * as a double (floating types) or int64 (integer types) so that a collective can consume
+ * it without a host round trip. */
+THC_API void THCTensor_(sumallToDevice)(THCState *state, THCTensor *self, void *result_dev);
+
+#endif /* THC_B200_DECLARE_API */
+
+#undef THCTensor
+#undef THCStorage
+#undef THCTensor_
+#undef THCStorage_

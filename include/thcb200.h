@@ -1,0 +1,222 @@
+/*
+ * thcb200.h -- descriptor-level C ABI of the B200 strided-tensor apply / reduce core.
+ *
+ * This is the thin boundary between host code (C, C++, Lua FFI, ctypes ...) and the
+ * hand-written sm_100a kernels.  Every entry point takes plain pointers and sizes; no
+ * C++ or framework types cross it.  The THC-compatible C API (include/THC/THC.h:
+ * THCudaTensor_cadd, THCudaTensor_sumall, ...) is implemented on top of these calls.
+ *
+ * Reference interfaces replaced (paths inside the cutorch tree):
+ *   thcb200_pointwise        <- THC_pointwiseApply1/2/3      lib/THC/THCApply.cuh:124-640
+ *   thcb200_reduce_dim       <- THC_reduceDim                lib/THC/THCReduce.cuh:258-453
+ *   thcb200_reduce_dim_index <- THC_reduceDimIndex           lib/THC/THCTensorMathReduce.cuh:619-661
+ *   thcb200_reduce_all       <- THC_reduceAll                lib/THC/THCReduceAll.cuh:234-342
+ *   thcb200_collapse_dims    <- TensorInfo::collapseDims     lib/THC/THCTensorInfo.cuh:74-224
+ *   thcb200_overlapping      <- TensorUtils::overlappingIndices  lib/THC/THCTensorTypeUtils.cu:163-218
+ *   thcb200_can_use_32bit    <- TensorUtils::canUse32BitIndexMath lib/THC/THCTensorTypeUtils.cu:220-245
+ *
+ * All functions return 0 on success or a negative thcb200_status; the message of the
+ * last failure on the calling thread is available from thcb200_last_error().
+ * Kernels are launched asynchronously on the given stream unless stated otherwise.
+ */
+#ifndef THCB200_H
+#define THCB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define THCB200_API __attribute__((visibility("default")))
+#else
+#define THCB200_API
+#endif
+
+#define THCB200_MAX_DIMS 25 /* MAX_CUTORCH_DIMS, lib/THC/THCTensorInfo.cuh:10 */
+
+typedef enum thcb200_status {
+  THCB200_OK = 0,
+  THCB200_ERR_ARG = -1,        /* bad argument (dtype/op combination, null pointer ...) */
+  THCB200_ERR_DIMS = -2,       /* more than THCB200_MAX_DIMS dimensions */
+  THCB200_ERR_SIZE = -3,       /* element counts of the operands differ */
+  THCB200_ERR_CUDA = -4,       /* a CUDA runtime call failed */
+  THCB200_ERR_UNSUPPORTED = -5,/* op is not defined for this dtype (e.g. bit ops on float) */
+  THCB200_ERR_NOMEM = -6,      /* workspace allocation failed */
+  THCB200_ERR_LIMIT = -7       /* size beyond a documented fixed limit */
+} thcb200_status;
+
+/* Element types, in the order of cutorch's eight tensor types. */
+typedef enum thcb200_dtype {
+  THCB200_U8 = 0,  /* THCudaByteTensor   */
+  THCB200_I8 = 1,  /* THCudaCharTensor   */
+  THCB200_I16 = 2, /* THCudaShortTensor  */
+  THCB200_I32 = 3, /* THCudaIntTensor    */
+  THCB200_I64 = 4, /* THCudaLongTensor   */
+  THCB200_F16 = 5, /* THCudaHalfTensor   */
+  THCB200_F32 = 6, /* THCudaTensor       */
+  THCB200_F64 = 7  /* THCudaDoubleTensor */
+} thcb200_dtype;
+
+/* A strided view: `data` already includes the storage offset; strides are in elements. */
+typedef struct thcb200_tensor {
+  void *data;
+  int32_t dtype;
+  int32_t ndim;
+  int64_t sizes[THCB200_MAX_DIMS];
+  int64_t strides[THCB200_MAX_DIMS];
+} thcb200_tensor;
+
+/* A scalar argument: the caller fills both views of the value (f is used by the
+ * floating-point element types, i by the integer ones). */
+typedef struct thcb200_scalar {
+  double f;
+  int64_t i;
+} thcb200_scalar;
+
+/* Pointwise operations.  out = f(in0[, in1[, in2]]; s0, s1).  In-place use passes the
+ * same view as `out` and `in0`. */
+typedef enum thcb200_op {
+  /* no input */
+  THCB200_OP_FILL = 0,       /* out = s0 */
+  /* one input, no scalar */
+  THCB200_OP_COPY,           /* out = in0 (same dtype) */
+  THCB200_OP_LOG, THCB200_OP_LGAMMA, THCB200_OP_LOG1P, THCB200_OP_EXP, THCB200_OP_COS,
+  THCB200_OP_SIN, THCB200_OP_SQRT, THCB200_OP_RSQRT, THCB200_OP_CEIL, THCB200_OP_FLOOR,
+  THCB200_OP_TRUNC, THCB200_OP_ACOS, THCB200_OP_COSH, THCB200_OP_ASIN, THCB200_OP_SINH,
+  THCB200_OP_TAN, THCB200_OP_ATAN, THCB200_OP_TANH, THCB200_OP_ROUND, THCB200_OP_FRAC,
+  THCB200_OP_CINV, THCB200_OP_NEG, THCB200_OP_ABS, THCB200_OP_SIGN, THCB200_OP_SIGMOID,
+  /* one input, scalar(s) */
+  THCB200_OP_CLAMP,          /* s0 = min, s1 = max */
+  THCB200_OP_POW,            /* in0 ** s0 (special cases 1, 2, 3, -1, -2) */
+  THCB200_OP_TPOW,           /* s0 ** in0 */
+  THCB200_OP_ADD_S, THCB200_OP_SUB_S, THCB200_OP_MUL_S,
+  THCB200_OP_DIV_S,          /* in0 / s0: a true division as in TH (cutorch multiplies by 1/s0) */
+  THCB200_OP_LSHIFT_S, THCB200_OP_RSHIFT_S, THCB200_OP_FMOD_S, THCB200_OP_REMAINDER_S,
+  THCB200_OP_BITAND_S, THCB200_OP_BITOR_S, THCB200_OP_BITXOR_S,
+  THCB200_OP_MAX_S, THCB200_OP_MIN_S,
+  /* comparisons with s0, result 1 or 0 in the element type (lib/THC/THCTensorMathCompare.cuh) */
+  THCB200_OP_LT_S, THCB200_OP_GT_S, THCB200_OP_LE_S, THCB200_OP_GE_S, THCB200_OP_EQ_S, THCB200_OP_NE_S,
+  /* two inputs */
+  THCB200_OP_ADD,            /* in0 + in1 */
+  THCB200_OP_SUB,            /* in0 - in1 */
+  THCB200_OP_CADD,           /* in0 + s0 * in1 (not contracted to an FMA) */
+  THCB200_OP_MUL, THCB200_OP_DIV, THCB200_OP_CPOW, THCB200_OP_CLSHIFT, THCB200_OP_CRSHIFT,
+  THCB200_OP_CMAX, THCB200_OP_CMIN, THCB200_OP_CFMOD, THCB200_OP_CREMAINDER,
+  THCB200_OP_CBITAND, THCB200_OP_CBITOR, THCB200_OP_CBITXOR, THCB200_OP_ATAN2,
+  THCB200_OP_LERP,           /* in0 + s0 * (in1 - in0) */
+  /* element-wise comparisons, result 1 or 0 in the element type (lib/THC/THCTensorMathCompareT.cuh) */
+  THCB200_OP_LT, THCB200_OP_GT, THCB200_OP_LE, THCB200_OP_GE, THCB200_OP_EQ, THCB200_OP_NE,
+  /* three inputs */
+  THCB200_OP_ADDCMUL,        /* in0 + (s0 * in1) * in2, TH's association */
+  THCB200_OP_ADDCDIV,        /* in0 + (s0 * in1) / in2 */
+  THCB200_OP_COUNT
+} thcb200_op;
+
+/* Fold operators of the reductions. */
+typedef enum thcb200_reduce_op {
+  THCB200_RED_SUM = 0,
+  THCB200_RED_PROD = 1,
+  THCB200_RED_MIN = 2,  /* TH rule: a NaN element wins */
+  THCB200_RED_MAX = 3,
+  THCB200_RED_ALL = 4,  /* logical and of (x != 0), result 0/1 */
+  THCB200_RED_ANY = 5,
+  THCB200_RED_COUNT
+} thcb200_reduce_op;
+
+/* Per-element transform applied before the fold (modifyOp of THC_reduceDim). */
+typedef enum thcb200_pre_op {
+  THCB200_PRE_IDENTITY = 0,
+  THCB200_PRE_ABS = 1,      /* norm p = 1 */
+  THCB200_PRE_SQUARE = 2,   /* norm p = 2 */
+  THCB200_PRE_POWABS = 3,   /* |x| ** s   (norm p) */
+  THCB200_PRE_NONZERO = 4,  /* x != 0 ? 1 : 0 (norm p = 0) */
+  THCB200_PRE_SQDEV = 5,    /* (x - s) ** 2 (varall) */
+  THCB200_PRE_COUNT
+} thcb200_pre_op;
+
+/* Opaque per-device context: the reduction workspace (per-block partials, tickets),
+ * a pinned host slot for results and cached device properties.  It replaces the
+ * scratch-space services of THCState (lib/THC/THCGeneral.c:677-712).  A context may be
+ * used from one stream at a time. */
+typedef struct thcb200_ctx thcb200_ctx;
+
+THCB200_API int thcb200_ctx_create(thcb200_ctx **out, int device);
+THCB200_API void thcb200_ctx_destroy(thcb200_ctx *ctx);
+THCB200_API const char *thcb200_last_error(void);
+/* Number of kernels this library has launched in this process (all contexts). */
+THCB200_API int64_t thcb200_launch_count(void);
+/* Name of the kernel family picked by the most recent pointwise / reduce call of this
+ * thread ("contig_vec", "tiled", "generic", "row_warp", "col_tile", ...). */
+THCB200_API const char *thcb200_last_plan(void);
+
+/* Plain synchronous copies between host and device memory (cudaMemcpyAsync on `stream`
+ * followed by a stream synchronize); for hosts that have no CUDA binding of their own. */
+THCB200_API int thcb200_memcpy_h2d(void *dst_dev, const void *src_host, size_t bytes, void *stream);
+THCB200_API int thcb200_memcpy_d2h(void *dst_host, const void *src_dev, size_t bytes, void *stream);
+THCB200_API int thcb200_stream_synchronize(void *stream);
+
+/* ---- host-side layout helpers (no GPU work) -------------------------------------- */
+
+/* In-place TensorInfo::collapseDims.  Returns the new index of exclude_dim (or -1). */
+THCB200_API int thcb200_collapse_dims(int64_t *sizes, int64_t *strides, int *ndim, int exclude_dim);
+/* 1 if two distinct index tuples of the view address the same element. */
+THCB200_API int thcb200_overlapping(const thcb200_tensor *t);
+/* 1 if element count and largest offset both fit 32-bit unsigned arithmetic. */
+THCB200_API int thcb200_can_use_32bit(const thcb200_tensor *t);
+/* Element offset of logical (row-major) index `linear` in the view. */
+THCB200_API int64_t thcb200_index_to_offset(const thcb200_tensor *t, int64_t linear);
+
+/* ---- device work ----------------------------------------------------------------- */
+
+/* out = op(in...).  Operands need equal element counts, not equal shapes; each is
+ * walked in its own row-major order.  nin must match the op's arity. */
+THCB200_API int thcb200_pointwise(thcb200_ctx *ctx, int op, const thcb200_tensor *out,
+                      const thcb200_tensor *in0, const thcb200_tensor *in1,
+                      const thcb200_tensor *in2, int nin, thcb200_scalar s0,
+                      thcb200_scalar s1, void *stream);
+
+/* Same with flags.  THCB200_FLAG_IGNORE_OVERLAP writes through an output view whose index
+ * tuples alias without the dense temporary (copyIgnoringOverlaps,
+ * lib/THC/THCTensorCopy.cu:24-205). */
+#define THCB200_FLAG_IGNORE_OVERLAP 1
+THCB200_API int thcb200_pointwise_ex(thcb200_ctx *ctx, int op, const thcb200_tensor *out,
+                         const thcb200_tensor *in0, const thcb200_tensor *in1,
+                         const thcb200_tensor *in2, int nin, thcb200_scalar s0,
+                         thcb200_scalar s1, void *stream, int flags);
+
+/* out = convert(in): element-wise copy between any two dtypes (C cast semantics; half
+ * goes through float).  lib/THC/THCTensorCopy.cu:12-21,114-121. */
+THCB200_API int thcb200_copy_convert(thcb200_ctx *ctx, const thcb200_tensor *out,
+                         const thcb200_tensor *in, void *stream);
+
+/* Fold `in` along `dim`.  `out` has in's sizes with sizes[dim] == 1 and in's dtype;
+ * accumulation is in double (f32, f64), float (f16) or int64 (integers). */
+THCB200_API int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
+                       const thcb200_tensor *out, const thcb200_tensor *in, int dim,
+                       void *stream);
+
+/* max / min along `dim` with 1-based int64 positions of the first occurrence (a NaN
+ * counts as the extreme value).  `indices` is an I64 view shaped like `values`. */
+THCB200_API int thcb200_reduce_dim_index(thcb200_ctx *ctx, int rop, const thcb200_tensor *values,
+                             const thcb200_tensor *indices, const thcb200_tensor *in,
+                             int dim, void *stream);
+
+/* Fold every element of `in`.  The result is written to `result_dev` (8-byte aligned
+ * device memory, 8 bytes) as a double for the floating element types and as an int64 for
+ * the integer ones, whatever the fold.  Accumulation is in double (f32, f64), float (f16)
+ * or int64.  One launch, fixed combine order, no atomics on data: repeatable bit for bit. */
+THCB200_API int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
+                       const thcb200_tensor *in, void *result_dev, void *stream);
+
+/* Same, then waits for the stream and stores the accumulator in *result_host (8 bytes,
+ * same typing as above). */
+THCB200_API int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
+                            const thcb200_tensor *in, void *result_host, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THCB200_H */
