@@ -190,6 +190,27 @@ __device__ __forceinline__ M fp_apply(M s0, M s1, M a, M b, M c) {
 }
 
 // ---- integer element types ------------------------------------------------------------
+// a ** b on integers.  TH evaluates pow() in double and converts back, which is exact for every
+// result a double holds; repeated squaring gives those same values without depending on the
+// last bits of a device pow().  Negative exponents follow 1 / a**|b| truncated toward zero.
+template <typename I> __device__ __forceinline__ I int_pow(I a, I b) {
+  using P = typename Promoted<I>::type;
+  using U = typename WideU<P>::type;
+  if (b < 0) {
+    if (a == (I)1) return (I)1;
+    if ((I)-1 < (I)0 && a == (I)-1) return (b & 1) ? (I)-1 : (I)1;
+    return (I)0;
+  }
+  U base = (U)(P)a, r = 1;
+  uint64_t e = (uint64_t)b;
+  while (e) {
+    if (e & 1) r *= base;
+    base *= base;
+    e >>= 1;
+  }
+  return (I)(P)r;
+}
+
 template <int OP, typename I>
 __device__ __forceinline__ I int_apply(I s0, I s1, I a, I b, I c) {
   using P = typename Promoted<I>::type;  // arithmetic happens in P, the store truncates to I
@@ -227,7 +248,7 @@ __device__ __forceinline__ I int_apply(I s0, I s1, I a, I b, I c) {
   else if constexpr (OP == THCB200_OP_CADD) return (I)w_add<P>((P)a, w_mul<P>((P)s0, (P)b));
   else if constexpr (OP == THCB200_OP_MUL) return (I)w_mul<P>((P)a, (P)b);
   else if constexpr (OP == THCB200_OP_DIV) return (I)((P)a / (P)b);
-  else if constexpr (OP == THCB200_OP_CPOW) return (I)pow((double)a, (double)b);
+  else if constexpr (OP == THCB200_OP_CPOW) return int_pow<I>(a, b);
   else if constexpr (OP == THCB200_OP_CLSHIFT) return (I)((P)a << (P)b);
   else if constexpr (OP == THCB200_OP_CRSHIFT) return (I)((P)a >> (P)b);
   else if constexpr (OP == THCB200_OP_CMAX) return (a > b) ? a : b;

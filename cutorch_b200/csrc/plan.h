@@ -52,6 +52,11 @@ void make_apply_plan(const HostView *ops, int nops, size_t elem_size, ApplyPlan 
 template <typename IndexT>
 inline StridedView<IndexT> to_strided_view(const ApplyPlan &p, int o) {
   StridedView<IndexT> v;
+  if (o >= p.nops) {  // operand not used by this op: a trivial view (the plan holds nothing for it)
+    v.dims = 1;
+    for (int i = 0; i < kGenericDims; ++i) { v.sizes[i] = DivHelper<IndexT>(1); v.strides[i] = 0; }
+    return v;
+  }
   v.dims = p.gdims[o];
   for (int i = 0; i < kGenericDims; ++i) {
     if (i < v.dims) {

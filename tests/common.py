@@ -77,10 +77,10 @@ def ulp_diff(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     it = {2: np.int16, 4: np.int32, 8: np.int64}[a.dtype.itemsize]
     ai = a.view(it).astype(np.int64)
     bi = b.view(it).astype(np.int64)
-    sign = np.int64(1) << (8 * a.dtype.itemsize - 1)
+    mask = np.int64((1 << (8 * a.dtype.itemsize - 1)) - 1)
     # sign-magnitude bit patterns -> integers that are monotonic in the float value
-    ai = np.where(ai < 0, -(ai & (sign - 1)), ai)
-    bi = np.where(bi < 0, -(bi & (sign - 1)), bi)
+    ai = np.where(ai < 0, -(ai & mask), ai)
+    bi = np.where(bi < 0, -(bi & mask), bi)
     d = np.abs(ai - bi)
     both_nan = np.isnan(a) & np.isnan(b)
     d = np.where(both_nan, 0, d)

@@ -27,11 +27,25 @@ UNARY_FP = {
 }
 
 
-def check(kind, got, want, exact, what):
+def as_real(kind, v):
+    """The value a `real` argument of this tensor type actually carries (a half scalar is rounded
+    to half before the call, exactly as cutorch's Lua layer converts it)."""
+    if kind in INT_KINDS:
+        return int(v)
+    return float(NP_OF_KIND[kind].type(v))
+
+
+# Double-precision CUDA math functions documented at up to 2 ulp (tanh) / 4 ulp (lgamma) from the
+# true value, against a libm that is itself up to 1 ulp off: the distance between the two exceeds
+# the 2-ulp bar for these two functions only.
+ULP_EXCEPTIONS = {("Double", "lgamma"): 5, ("Double", "tanh"): 3}
+
+
+def check(kind, got, want, exact, what, ulp=2):
     if NP_OF_KIND[kind].kind != "f" or exact:
         assert_bit_equal(got, want, what)
     else:
-        assert_ulp(got, want, 1 if kind == "Half" else 2, what)
+        assert_ulp(got, want, 1 if kind == "Half" else ulp, what)
 
 
 @pytest.mark.parametrize("kind", FP_KINDS)
@@ -46,10 +60,11 @@ def test_unary_math(state, oracle, kind, name):
         dx = to_device(state, x)
         out = thc.Tensor.new(state, kind)
         out.call(name, out, dx)
-        check(kind, out.numpy(), want, exact, f"{kind}.{name} {layout}")
+        ulp = ULP_EXCEPTIONS.get((kind, name), 2)
+        check(kind, out.numpy(), want, exact, f"{kind}.{name} {layout}", ulp)
         # in place
         dx.call(name, dx, dx)
-        check(kind, dx.numpy(), want, exact, f"{kind}.{name} in place {layout}")
+        check(kind, dx.numpy(), want, exact, f"{kind}.{name} in place {layout}", ulp)
 
 
 @pytest.mark.parametrize("kind", ALL_KINDS)
@@ -103,7 +118,7 @@ def test_cadd_csub(state, oracle, kind, value):
     csub negates the scalar (lib/THC/generic/THCTensorMathPointwise.cu:264-342)."""
     if kind == "Byte" and value < 0:
         value = 3
-    v = int(value) if kind in INT_KINDS else value
+    v = as_real(kind, value)
     r = rng(5)
     for la, lb, shape in [("contiguous", "contiguous", (20011,)), ("transposed", "strided", (8, 5, 12))]:
         a, b = make_view(r, kind, shape, la), make_view(r, kind, shape, lb)
@@ -112,7 +127,7 @@ def test_cadd_csub(state, oracle, kind, value):
                 want = oracle.pointwise(OP["ADD" if name == "cadd" else "SUB"], np.zeros(shape, a.dtype), [a, b])
             else:
                 if kind == "Byte":
-                    sv = int(np.uint8(sv))
+                    sv = sv & 0xFF
                 want = oracle.pointwise(OP["CADD"], np.zeros(shape, a.dtype), [a, b], sv)
             out = thc.Tensor.new(state, kind)
             out.call(name, out, to_device(state, a), v, to_device(state, b))
@@ -132,6 +147,7 @@ def test_scalar_ops(state, oracle, kind):
     if isint:
         cases += [("bitand", "BITAND_S", 5), ("bitor", "BITOR_S", 9), ("bitxor", "BITXOR_S", 6)]
     for name, op, v in cases:
+        v = as_real(kind, v)
         for layout in ("contiguous", "transposed", "strided"):
             x = make_view(r, kind, (6, 10, 7), layout)
             if name in ("lshift", "rshift") and isint:
@@ -159,6 +175,7 @@ def test_pow_family(state, oracle, kind):
     x = make_view(r, kind, (12, 9), "strided")
     x[...] = r.uniform(0.2, 3, size=x.shape).astype(x.dtype)
     for v in (1, 2, 3, -1, -2, 0.5, 2.7):
+        v = as_real(kind, v)
         want = oracle.pointwise(OP["POW"], np.zeros(x.shape, x.dtype), [x], v)
         out = thc.Tensor.new(state, kind)
         out.call("pow", out, to_device(state, x), v)
@@ -172,9 +189,10 @@ def test_pow_family(state, oracle, kind):
     out = thc.Tensor.new(state, kind)
     out.call("atan2", out, to_device(state, x), to_device(state, y))
     check(kind, out.numpy(), want, False, f"{kind}.atan2")
-    want = oracle.pointwise(OP["LERP"], np.zeros(x.shape, x.dtype), [x, y], 0.3)
+    w = as_real(kind, 0.3)
+    want = oracle.pointwise(OP["LERP"], np.zeros(x.shape, x.dtype), [x, y], w)
     out = thc.Tensor.new(state, kind)
-    out.call("lerp", out, to_device(state, x), to_device(state, y), 0.3)
+    out.call("lerp", out, to_device(state, x), to_device(state, y), w)
     assert_bit_equal(out.numpy(), want, f"{kind}.lerp")
 
 
