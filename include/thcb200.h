@@ -198,6 +198,21 @@ THCB200_API int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_s
                        const thcb200_tensor *out, const thcb200_tensor *in, int dim,
                        void *stream);
 
+/* thcb200_reduce_dim for callers that cannot allocate device memory when they call it (their
+ * memory pool owns the whole device, their plug-in contract forbids allocations after start-up,
+ * or they cannot take the synchronisation an allocation may imply).  It has no counterpart in
+ * cutorch.  Same arguments minus the context, same kernels and results; the partials of split
+ * reductions live in a static device array of THCB200_STATIC_SCRATCH_BYTES that every GPU
+ * holding this library keeps until the process exits, and the call performs no cudaMalloc,
+ * cudaFree or other allocating call.  A reduction whose partials exceed the array returns
+ * THCB200_ERR_LIMIT.  The first call on each device resolves the array's device address: make
+ * it outside any stream capture.  All calls on a device share the array: do not let two of them
+ * overlap on the GPU. */
+#define THCB200_STATIC_SCRATCH_BYTES (2u << 20)
+THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_scalar s,
+                              const thcb200_tensor *out, const thcb200_tensor *in, int dim,
+                              void *stream);
+
 /* max / min along `dim` with 1-based int64 positions of the first occurrence (a NaN
  * counts as the extreme value).  `indices` is an I64 view shaped like `values`. */
 THCB200_API int thcb200_reduce_dim_index(thcb200_ctx *ctx, int rop, const thcb200_tensor *values,
