@@ -283,7 +283,7 @@ def ours_main(args):
                                for k, vv in kernels.items()}}
 
     # end to end: host (pinned) inputs -> device -> THC calls -> results back on the host
-    e2e = run_e2e(args, torch, thc, state, stream, dev, rows, world, rank)
+    e2e = None if args.no_e2e else run_e2e(args, torch, thc, state, stream, dev, rows, world, rank)
 
     extra = {}
     cpu_baseline = None
@@ -293,6 +293,7 @@ def ours_main(args):
         cpu_baseline = {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port",
                         "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (2 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
         if args.configs:
+            from bench_configs import run_small_configs
             extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
 
     if rank == 0:
@@ -416,91 +417,20 @@ def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
             + ("" if host_rows == rows else f"; host array of {host_rows} rows cycled (box cannot pin {need >> 30} GiB)")}
 
 
-def run_small_configs(torch, thc, state, stream, dev, peak):
-    """Device-time GB/s of the other baseline configs (c1-c4) at full size, N = 1.  An L2 flush
-    (512 MiB memset) runs between timed iterations because several of these tensors fit L2."""
-    import numpy as np
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-    W = lambda t, kind: thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
-
-    def timed(fn, nbytes, reps=10):
-        ts = []
-        for _ in range(3):
-            fn()
-        for _ in range(reps):
-            flush.zero_()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            fn()
-            b.record(stream)
-            torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
-        ts.sort()
-        med = ts[len(ts) // 2]
-        return {"gbs": round(nbytes / (med * 1e-3) / 1e9, 1), "frac": round(nbytes / (med * 1e-3) / 1e9 / peak, 4),
-                "median_us": round(med * 1e3, 2), "best_us": round(ts[0] * 1e3, 2), "bytes": nbytes}
-
-    out = {}
-    g = torch.Generator(device=dev)
-    g.manual_seed(7)
-    # c1
-    n = 16777216
-    x = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
-    y = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
-    z = torch.empty(n, device=dev)
-    res = torch.zeros(1, dtype=torch.float64, device=dev)
-    tx, ty, tz = W(x, "Float"), W(y, "Float"), W(z, "Float")
-    out["c1_cadd_f32_16M"] = timed(lambda: tz.cadd(tx, 2.5, ty), 12 * n)
-    out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n)
-    del x, y, z
-    # c2
-    shape = (64, 256, 56, 56)
-    n = 64 * 256 * 56 * 56
-    x = torch.empty(shape, device=dev).normal_(generator=g)
-    ybase = torch.empty(64, 56, 56, 256, device=dev).normal_(generator=g)
-    yv = ybase.transpose(1, 3)
-    wbase = torch.empty(64, 256, 56, 112, device=dev).normal_(generator=g)
-    wv = wbase[..., ::2]
-    o = torch.empty(shape, device=dev)
-    to, tx, ty, tw = W(o, "Float"), W(x, "Float"), W(yv, "Float"), W(wv, "Float")
-    out["c2_addcmul_f32_transposed_strided"] = timed(lambda: to.addcmul(tx, 0.5, ty, tw), 16 * n)
-    del x, ybase, wbase, o
-    # c3
-    m = (torch.randint(-1000, 1001, (32768, 8192), device=dev, generator=g).float() / 8)
-    tm = W(m, "Float")
-    n = m.numel()
-    r1, r0 = torch.empty(32768, 1, device=dev), torch.empty(1, 8192, device=dev)
-    i1, i0 = torch.empty(32768, 1, dtype=torch.int64, device=dev), torch.empty(1, 8192, dtype=torch.int64, device=dev)
-    tr1, tr0, ti1, ti0 = W(r1, "Float"), W(r0, "Float"), W(i1, "Long"), W(i0, "Long")
-    out["c3_sum_dim1"] = timed(lambda: tr1.sum(tm, 1, 1), 4 * n + 4 * 32768)
-    out["c3_sum_dim0"] = timed(lambda: tr0.sum(tm, 0, 1), 4 * n + 4 * 8192)
-    out["c3_max_dim1"] = timed(lambda: tr1.max(ti1, tm, 1, 1), 4 * n + 12 * 32768)
-    out["c3_max_dim0"] = timed(lambda: tr0.max(ti0, tm, 0, 1), 4 * n + 12 * 8192)
-    del m
-    # c4.1
-    h = (torch.empty(8192, 8192, device=dev).normal_(0, 2, generator=g)).half()
-    h2 = torch.empty_like(h)
-    rh = torch.empty(1, 8192, dtype=torch.float16, device=dev)
-    th, th2, trh = W(h, "Half"), W(h2, "Half"), W(rh, "Half")
-    n = h.numel()
-    out["c4_sigmoid_f16"] = timed(lambda: th2.sigmoid(th), 4 * n)
-    out["c4_mean_dim0_f16"] = timed(lambda: trh.mean(th2, 0, 1), 2 * n + 2 * 8192)
-    out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192)
-    del h, h2
-    # c4.2
-    n = 134217728
-    a = torch.randint(-2**20, 2**20 + 1, (n,), dtype=torch.int32, device=dev, generator=g)
-    b = torch.randint(-7, 8, (n,), dtype=torch.int32, device=dev, generator=g)
-    c = torch.empty_like(a)
-    ta, tb, tc = W(a, "Int"), W(b, "Int"), W(c, "Int")
-    out["c4_cmul_i32_128M"] = timed(lambda: tc.cmul(ta, tb), 12 * n, reps=5)
-    out["c4_sumall_i32_128M"] = timed(lambda: tc.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
-    del a, b, c
-    # c4.3
-    d = torch.empty(n, dtype=torch.float64, device=dev).uniform_(0, 1, generator=g)
-    td = W(d, "Double")
-    out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5)
-    return out
+def only_main(args):
+    """Times a subset of the c1-c4 configs on cuda:0 (the small case used for ncu captures)."""
+    import torch
+    from cutorch_b200 import thc
+    from bench_configs import run_small_configs
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    state = thc.State()
+    stream = torch.cuda.current_stream()
+    state.set_stream(stream.cuda_stream, 0)
+    peak, src = measured_peaks()
+    res = run_small_configs(torch, thc, state, stream, dev, peak, only=set(args.only.split(",")), reps_override=args.reps or None)
+    print(json.dumps({"per_config": res, "peak": peak, "peak_source": src}))
+    return 0
 
 
 def main():
@@ -513,11 +443,16 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--configs", action="store_true", default=True, help="also time the c1-c4 configs at N=1")
     ap.add_argument("--no-configs", dest="configs", action="store_false")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--only", default="", help="comma list of c1..c4: time just those configs on one GPU and print them")
+    ap.add_argument("--reps", type=int, default=0, help="timed repetitions per entry with --only")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
         return reference_main(args)
+    if args.only:
+        return only_main(args)
     return ours_main(args)
 
 

@@ -1,0 +1,101 @@
+"""Device-time measurements of the baseline configs c1-c4 (full size, one GPU), used by bench.py.
+
+Each entry is one THC call timed with CUDA events on the launching stream; a 512 MiB memset runs
+between timed iterations so that tensors that would fit the 126 MB L2 are read from HBM.
+`python bench.py --only c2,c3` runs a subset (that is also the small case the ncu captures use).
+"""
+from __future__ import annotations
+
+
+def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_override=None):
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+
+    def W(t, kind):
+        return thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+
+    def timed(fn, nbytes, reps=10):
+        reps = reps_override or reps
+        ts = []
+        for _ in range(3):
+            fn()
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        med = ts[len(ts) // 2]
+        gbs = nbytes / (med * 1e-3) / 1e9
+        return {"gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "frac_of_nominal_8000": round(gbs / 8000.0, 4),
+                "median_us": round(med * 1e3, 2), "best_us": round(ts[0] * 1e3, 2), "bytes": nbytes}
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    res = torch.zeros(1, dtype=torch.float64, device=dev)
+    out = {}
+
+    def c1():
+        n = 16777216
+        x = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
+        y = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
+        z = torch.empty(n, device=dev)
+        tx, ty, tz = W(x, "Float"), W(y, "Float"), W(z, "Float")
+        out["c1_cadd_f32_16M"] = timed(lambda: tz.cadd(tx, 2.5, ty), 12 * n)
+        out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n)
+
+    def c2():
+        shape = (64, 256, 56, 56)
+        n = 64 * 256 * 56 * 56
+        x = torch.empty(shape, device=dev).normal_(generator=g)
+        ybase = torch.empty(64, 56, 56, 256, device=dev).normal_(generator=g)
+        yv = ybase.transpose(1, 3)
+        wbase = torch.empty(64, 256, 56, 112, device=dev).normal_(generator=g)
+        wv = wbase[..., ::2]
+        o = torch.empty(shape, device=dev)
+        to, tx, ty, tw = W(o, "Float"), W(x, "Float"), W(yv, "Float"), W(wv, "Float")
+        out["c2_addcmul_f32_transposed_strided"] = timed(lambda: to.addcmul(tx, 0.5, ty, tw), 16 * n)
+
+    def c3():
+        m = (torch.randint(-1000, 1001, (32768, 8192), device=dev, generator=g).float() / 8)
+        tm = W(m, "Float")
+        n = m.numel()
+        r1, r0 = torch.empty(32768, 1, device=dev), torch.empty(1, 8192, device=dev)
+        i1 = torch.empty(32768, 1, dtype=torch.int64, device=dev)
+        i0 = torch.empty(1, 8192, dtype=torch.int64, device=dev)
+        tr1, tr0, ti1, ti0 = W(r1, "Float"), W(r0, "Float"), W(i1, "Long"), W(i0, "Long")
+        out["c3_sum_dim1"] = timed(lambda: tr1.sum(tm, 1, 1), 4 * n + 4 * 32768)
+        out["c3_sum_dim0"] = timed(lambda: tr0.sum(tm, 0, 1), 4 * n + 4 * 8192)
+        out["c3_max_dim1"] = timed(lambda: tr1.max(ti1, tm, 1, 1), 4 * n + 12 * 32768)
+        out["c3_max_dim0"] = timed(lambda: tr0.max(ti0, tm, 0, 1), 4 * n + 12 * 8192)
+
+    def c4():
+        h = (torch.empty(8192, 8192, device=dev).normal_(0, 2, generator=g)).half()
+        h2 = torch.empty_like(h)
+        rh = torch.empty(1, 8192, dtype=torch.float16, device=dev)
+        th, th2, trh = W(h, "Half"), W(h2, "Half"), W(rh, "Half")
+        n = h.numel()
+        out["c4_sigmoid_f16"] = timed(lambda: th2.sigmoid(th), 4 * n)
+        out["c4_mean_dim0_f16"] = timed(lambda: trh.mean(th2, 0, 1), 2 * n + 2 * 8192)
+        out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192)
+        del h, h2
+        n = 134217728
+        a = torch.randint(-2**20, 2**20 + 1, (n,), dtype=torch.int32, device=dev, generator=g)
+        b = torch.randint(-7, 8, (n,), dtype=torch.int32, device=dev, generator=g)
+        c = torch.empty_like(a)
+        ta, tb, tc = W(a, "Int"), W(b, "Int"), W(c, "Int")
+        out["c4_cmul_i32_128M"] = timed(lambda: tc.cmul(ta, tb), 12 * n, reps=5)
+        out["c4_sumall_i32_128M"] = timed(lambda: tc.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
+        del a, b, c
+        d = torch.empty(n, dtype=torch.float64, device=dev).uniform_(0, 1, generator=g)
+        td = W(d, "Double")
+        out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5)
+
+    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4)):
+        if only is None or name in only:
+            fn()
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+    return out

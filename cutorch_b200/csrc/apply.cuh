@@ -115,6 +115,12 @@ apply_generic_kernel(T *out, StridedView<IndexT> vo, const T *a, StridedView<Ind
 // collapses for them).  "Staged" operands are addressed as base(outer) + c + offJ(j),
 // where offJ walks the (at most kTiledJDims) dims of the group with the operand's own
 // strides.  A CTA handles TC consecutive c and TJ consecutive j.
+//
+// Phase 1 brings the staged tiles in with lanes along C: a warp instruction reads 128
+// contiguous bytes of the staged operand, and each thread issues all of its row loads
+// before the first shared-memory store.  Phase 2 runs with lanes along J: direct operands
+// and the output move in contiguous runs, the staged values come transposed out of padded
+// shared memory (conflict-free both ways), all global loads of a thread again first.
 // ----------------------------------------------------------------------------------
 constexpr int kTiledJDims = 3;
 constexpr int kTiledOuterDims = 6;
@@ -141,15 +147,37 @@ struct TiledPlan {
   TiledOperand op[4];                // 0 = out, 1..3 = inputs
 };
 
+template <typename T> constexpr int tiled_tc() { return (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128); }
+template <typename T> constexpr int tiled_pad() { return (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4); }
+template <typename T> constexpr size_t tiled_slot_bytes() { return (size_t)kTJ * (tiled_tc<T>() + tiled_pad<T>()) * sizeof(T); }
+
+// element offset of position j of the J group for a staged operand
+__device__ __forceinline__ int64_t tiled_joff(const TiledPlan &P, const TiledOperand &o, uint32_t j) {
+  int64_t off = 0;
+  uint32_t q = j, r;
+#pragma unroll
+  for (int d = kTiledJDims - 1; d >= 0; --d) {
+    if (d < P.njd) {
+      P.jSizes[d].divmod(q, q, r);
+      off += (int64_t)r * o.jstrides[d];
+    }
+  }
+  return off;
+}
+
 template <int OP, typename T, int NIN>
 __global__ void __launch_bounds__(kTiledThreads)
 apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpParams<T> p) {
-  constexpr int TC = (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128);  // 128-byte runs
-  constexpr int PAD = (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4);
+  constexpr int TC = tiled_tc<T>();          // 128-byte runs of the staged operand
+  constexpr int LD = TC + tiled_pad<T>();    // padded row length in shared memory
   constexpr int NW = kTiledThreads / 32;
+  constexpr int RPW = kTJ / NW;              // phase 1: rows (j) per warp
+  constexpr int CPL = TC / 32;               // phase 1: c per lane
+  constexpr int CPW = TC / NW;               // phase 2: c per warp
+  constexpr int JPL = kTJ / 32;              // phase 2: j per lane
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T *tile = reinterpret_cast<T *>(smem_raw);  // [slots][kTJ][TC + PAD]
-  constexpr int kSlot = kTJ * (TC + PAD);
+  T *tile = reinterpret_cast<T *>(smem_raw);  // [slots][kTJ][LD]
+  constexpr int kSlot = kTJ * LD;
 
   // decode blockIdx -> (outer, tile_c, tile_j)
   uint32_t bid = blockIdx.x, tj, tc, rest;
@@ -170,62 +198,92 @@ apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpPa
   const uint32_t nc = min((uint32_t)TC, P.sizeC - c0), nj = min((uint32_t)kTJ, P.sizeJ - j0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T *in[4] = {nullptr, a, b, c};
+  const bool full = (nc == (uint32_t)TC) && (nj == (uint32_t)kTJ);
+  const bool out_staged = P.op[0].staged;
 
-  // phase 1: staged inputs -> shared memory, lanes along C (the operand's unit stride)
+  // ---- phase 1: staged inputs -> shared memory, lanes along C
 #pragma unroll
   for (int o = 1; o <= NIN; ++o) {
-    if (P.op[o].staged) {
-      for (uint32_t jj = warp; jj < nj; jj += NW) {
-        uint32_t j = j0 + jj, q = j, r;
-        int64_t off = base[o];
+    if (!P.op[o].staged) continue;
+    T *slot = tile + P.op[o].slot * kSlot;
+    const T *src = in[o] + base[o] + c0;
+    if (full) {
+      T v[RPW][CPL];
 #pragma unroll
-        for (int d = kTiledJDims - 1; d >= 0; --d) {
-          if (d < P.njd) {
-            P.jSizes[d].divmod(q, q, r);
-            off += (int64_t)r * P.op[o].jstrides[d];
-          }
-        }
-        for (uint32_t cc = lane; cc < nc; cc += 32)
-          tile[P.op[o].slot * kSlot + jj * (TC + PAD) + cc] = in[o][off + c0 + cc];
+      for (int r = 0; r < RPW; ++r) {
+        const int64_t off = tiled_joff(P, P.op[o], j0 + warp + r * NW);
+#pragma unroll
+        for (int q = 0; q < CPL; ++q) v[r][q] = src[off + lane + 32 * q];
+      }
+#pragma unroll
+      for (int r = 0; r < RPW; ++r)
+#pragma unroll
+        for (int q = 0; q < CPL; ++q) slot[(warp + r * NW) * LD + lane + 32 * q] = v[r][q];
+    } else {
+      for (uint32_t jj = warp; jj < nj; jj += NW) {
+        const int64_t off = tiled_joff(P, P.op[o], j0 + jj);
+        for (uint32_t cc = lane; cc < nc; cc += 32) slot[jj * LD + cc] = src[off + cc];
       }
     }
   }
   __syncthreads();
 
-  // phase 2: compute with lanes along J (unit stride of the direct operands)
-  const bool out_staged = P.op[0].staged;
-  for (uint32_t cc = warp; cc < nc; cc += NW) {
-    for (uint32_t jj = lane; jj < nj; jj += 32) {
-      T v[4];
+  // ---- phase 2: compute with lanes along J
+  if (full) {
 #pragma unroll
-      for (int o = 1; o <= NIN; ++o) {
-        if (P.op[o].staged) v[o] = tile[P.op[o].slot * kSlot + jj * (TC + PAD) + cc];
-        else v[o] = in[o][base[o] + (int64_t)(c0 + cc) * P.op[o].strideC + (int64_t)(j0 + jj) * P.op[o].strideJ];
-      }
-      T r = pw_apply<OP, T>(p, NIN >= 1 ? v[1] : T(), NIN >= 2 ? v[2] : T(), NIN >= 3 ? v[3] : T());
-      if (out_staged) tile[P.op[0].slot * kSlot + jj * (TC + PAD) + cc] = r;
-      else out[base[0] + (int64_t)(c0 + cc) * P.op[0].strideC + (int64_t)(j0 + jj) * P.op[0].strideJ] = r;
-    }
-  }
-  if (out_staged) {
-    __syncthreads();
-    for (uint32_t jj = warp; jj < nj; jj += NW) {
-      uint32_t q = j0 + jj, r;
-      int64_t off = base[0];
+    for (int r0 = 0; r0 < CPW; r0 += 4) {   // 4 c per pass keeps the register count in check
+      T v[4][JPL][4];
 #pragma unroll
-      for (int d = kTiledJDims - 1; d >= 0; --d) {
-        if (d < P.njd) {
-          P.jSizes[d].divmod(q, q, r);
-          off += (int64_t)r * P.op[0].jstrides[d];
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t cc = warp + (r0 + r) * NW;
+#pragma unroll
+        for (int h = 0; h < JPL; ++h) {
+          const uint32_t jj = lane + 32 * h;
+#pragma unroll
+          for (int o = 1; o <= NIN; ++o) {
+            if (P.op[o].staged) v[r][h][o] = tile[P.op[o].slot * kSlot + jj * LD + cc];
+            else v[r][h][o] = in[o][base[o] + (int64_t)(c0 + cc) * P.op[o].strideC + (int64_t)(j0 + jj) * P.op[o].strideJ];
+          }
         }
       }
-      for (uint32_t cc = lane; cc < nc; cc += 32) out[off + c0 + cc] = tile[P.op[0].slot * kSlot + jj * (TC + PAD) + cc];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t cc = warp + (r0 + r) * NW;
+#pragma unroll
+        for (int h = 0; h < JPL; ++h) {
+          const uint32_t jj = lane + 32 * h;
+          const T res = pw_apply<OP, T>(p, NIN >= 1 ? v[r][h][1] : T(), NIN >= 2 ? v[r][h][2] : T(), NIN >= 3 ? v[r][h][3] : T());
+          if (out_staged) tile[P.op[0].slot * kSlot + jj * LD + cc] = res;
+          else out[base[0] + (int64_t)(c0 + cc) * P.op[0].strideC + (int64_t)(j0 + jj) * P.op[0].strideJ] = res;
+        }
+      }
+    }
+  } else {
+    for (uint32_t cc = warp; cc < nc; cc += NW) {
+      for (uint32_t jj = lane; jj < nj; jj += 32) {
+        T v[4];
+#pragma unroll
+        for (int o = 1; o <= NIN; ++o) {
+          if (P.op[o].staged) v[o] = tile[P.op[o].slot * kSlot + jj * LD + cc];
+          else v[o] = in[o][base[o] + (int64_t)(c0 + cc) * P.op[o].strideC + (int64_t)(j0 + jj) * P.op[o].strideJ];
+        }
+        const T res = pw_apply<OP, T>(p, NIN >= 1 ? v[1] : T(), NIN >= 2 ? v[2] : T(), NIN >= 3 ? v[3] : T());
+        if (out_staged) tile[P.op[0].slot * kSlot + jj * LD + cc] = res;
+        else out[base[0] + (int64_t)(c0 + cc) * P.op[0].strideC + (int64_t)(j0 + jj) * P.op[0].strideJ] = res;
+      }
+    }
+  }
+
+  // ---- phase 3: a staged output leaves through shared memory, lanes along C again
+  if (out_staged) {
+    __syncthreads();
+    const T *slot = tile + P.op[0].slot * kSlot;
+    T *dst = out + base[0] + c0;
+    for (uint32_t jj = warp; jj < nj; jj += NW) {
+      const int64_t off = tiled_joff(P, P.op[0], j0 + jj);
+      for (uint32_t cc = lane; cc < nc; cc += 32) dst[off + cc] = slot[jj * LD + cc];
     }
   }
 }
-
-template <typename T> constexpr int tiled_tc() { return (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128); }
-template <typename T> constexpr int tiled_pad() { return (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4); }
-template <typename T> constexpr size_t tiled_slot_bytes() { return (size_t)kTJ * (tiled_tc<T>() + tiled_pad<T>()) * sizeof(T); }
 
 }  // namespace thcb

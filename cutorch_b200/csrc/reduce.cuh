@@ -138,6 +138,56 @@ struct IndexFolder {
   }
 };
 
+// Per-thread running extreme for the value+position reductions.  A thread meets its elements
+// in increasing position, so a strict comparison keeps the first occurrence and the only
+// other rule needed is "the first NaN wins and ends the contest".  It starts from a sentinel
+// (lowest / highest value) instead of a validity flag: a thread that only ever saw the
+// sentinel reports "empty", which the final write resolves to (sentinel, first position) --
+// correct, because in that case every element of the slice equals the sentinel.
+// Positions are 32-bit offsets from `origin` (a unit never spans more than 2^32 - 2 elements).
+template <typename M, bool FP> struct Sentinel;
+template <typename M> struct Sentinel<M, true> {
+  __device__ __forceinline__ static M lowest() { return (M)-INFINITY; }
+  __device__ __forceinline__ static M highest() { return (M)INFINITY; }
+};
+template <typename M> struct Sentinel<M, false> {
+  __device__ __forceinline__ static M lowest() { return ((M)-1 > (M)0) ? (M)0 : (M)((uint64_t)1 << (sizeof(M) * 8 - 1)); }
+  __device__ __forceinline__ static M highest() { return (M)~lowest(); }
+};
+
+template <typename T, bool IS_MAX>
+struct FastIdx {
+  using M = typename TypeTraits<T>::Math;
+  static constexpr bool FP = TypeTraits<T>::is_fp;
+  static constexpr uint32_t kEmpty = 0xFFFFFFFFu;
+  M bv;
+  uint32_t bi;
+  bool bnan;
+  __device__ __forceinline__ static M sentinel() { return IS_MAX ? Sentinel<M, FP>::lowest() : Sentinel<M, FP>::highest(); }
+  __device__ __forceinline__ void reset() { bv = sentinel(); bi = kEmpty; bnan = false; }
+  __device__ __forceinline__ void feed(T xe, uint32_t rel) {
+    const M x = to_math<T>(xe);
+    bool take = IS_MAX ? (x > bv) : (x < bv);
+    if constexpr (FP) {
+      const bool xn = (x != x);
+      take = take || (xn && !bnan);
+      bnan = bnan || xn;
+    }
+    if (take) { bv = x; bi = rel; }
+  }
+  __device__ __forceinline__ ValIdx<M> result(uint64_t origin) const {
+    ValIdx<M> r;
+    r.v = bv;
+    r.i = (bi == kEmpty) ? (int64_t)-1 : (int64_t)(origin + bi);
+    return r;
+  }
+  // final value of an output whose merged result is still "empty": all elements equal the sentinel
+  __device__ __forceinline__ static ValIdx<M> resolve(ValIdx<M> r) {
+    if (r.i < 0) { r.v = sentinel(); r.i = 0; }
+    return r;
+  }
+};
+
 // ---- warp / block combine in a fixed order -------------------------------------------
 template <typename A> __device__ __forceinline__ A shfl_xor(A v, int m) { return __shfl_xor_sync(0xffffffffu, v, m); }
 template <> __device__ __forceinline__ int64_t shfl_xor<int64_t>(int64_t v, int m) { return (int64_t)__shfl_xor_sync(0xffffffffu, (long long)v, m); }
@@ -339,7 +389,8 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
   const uint64_t k1 = active ? (k0 + split_len < K ? k0 + split_len : K) : k0;
 
   Opt<F> acc = Opt<F>::start();
-  typename IF::Acc best = IF::empty();
+  FastIdx<T, IS_MAX> fast;
+  fast.reset();
   uint64_t k = k0;
   if constexpr (VEC) {
     // whole 16-byte vectors, kRedUnroll of them in flight per thread (split_len is a multiple of V)
@@ -353,7 +404,7 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
         const T *e = reinterpret_cast<const T *>(&v[u]);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          if constexpr (INDEX) IF::feed(best, e[j], (int64_t)(k + ((uint64_t)u * GROUP + gt) * V + j));
+          if constexpr (INDEX) fast.feed(e[j], (uint32_t)(k - k0) + (uint32_t)((u * GROUP + gt) * V + j));
           else acc.feed(F::pre(e[j], prm));
         }
       }
@@ -363,17 +414,18 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
       const T *e = reinterpret_cast<const T *>(&v);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        if constexpr (INDEX) IF::feed(best, e[j], (int64_t)(k + (uint64_t)gt * V + j));
+        if constexpr (INDEX) fast.feed(e[j], (uint32_t)(k - k0) + (uint32_t)(gt * V + j));
         else acc.feed(F::pre(e[j], prm));
       }
     }
   }
   for (uint64_t i = k + gt; i < k1; i += GROUP) {
-    if constexpr (INDEX) IF::feed(best, row[i], (int64_t)i);
+    if constexpr (INDEX) fast.feed(row[i], (uint32_t)(i - k0));
     else acc.feed(F::pre(row[i], prm));
   }
 
   // fold inside the group
+  typename IF::Acc best = fast.result(k0);
   if constexpr (INDEX) best = warp_fold_vi<IF>(best);
   else acc = warp_fold_opt<F>(acc);
   if constexpr (!WARP_PER_UNIT) {
@@ -403,6 +455,7 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
     }
   } else {
     if constexpr (INDEX) {
+      best = FastIdx<T, IS_MAX>::resolve(best);
       out[out_off] = from_math<T>(best.v);
       idx_out[idx_off] = best.i + 1;  // TH_INDEX_BASE
     } else {
@@ -462,9 +515,9 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
   const T *col = in + in_off + (int64_t)i0;
 
   Opt<F> acc[V];
-  typename IF::Acc best[V];
+  FastIdx<T, IS_MAX> fast[V];
 #pragma unroll
-  for (int j = 0; j < V; ++j) { acc[j] = Opt<F>::start(); best[j] = IF::empty(); }
+  for (int j = 0; j < V; ++j) { acc[j] = Opt<F>::start(); fast[j].reset(); }
   if (col_ok) {
     uint64_t k = k0 + warp;
     for (; k + (uint64_t)(kRedUnroll - 1) * kRedWarps < k1; k += (uint64_t)kRedUnroll * kRedWarps) {
@@ -479,7 +532,7 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
         const T *e = reinterpret_cast<const T *>(&v[u]);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-          if constexpr (INDEX) IF::feed(best[j], e[j], (int64_t)(k + (uint64_t)u * kRedWarps));
+          if constexpr (INDEX) fast[j].feed(e[j], (uint32_t)(k - k0) + (uint32_t)(u * kRedWarps));
           else acc[j].feed(F::pre(e[j], prm));
         }
       }
@@ -491,7 +544,7 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
       const T *e = reinterpret_cast<const T *>(&v);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
-        if constexpr (INDEX) IF::feed(best[j], e[j], (int64_t)k);
+        if constexpr (INDEX) fast[j].feed(e[j], (uint32_t)(k - k0));
         else acc[j].feed(F::pre(e[j], prm));
       }
     }
@@ -501,7 +554,7 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
   __shared__ typename IF::Acc smi[INDEX ? kRedWarps : 1][32 * V + 1];
 #pragma unroll
   for (int j = 0; j < V; ++j) {
-    if constexpr (INDEX) smi[warp][lane * V + j] = best[j];
+    if constexpr (INDEX) smi[warp][lane * V + j] = fast[j].result(k0);
     else { smv[warp][lane * V + j].v = acc[j].v; smv[warp][lane * V + j].has = acc[j].has; }
   }
   __syncthreads();
@@ -514,6 +567,7 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
       for (int w = 1; w < kRedWarps; ++w) r = IF::combine(r, smi[w][c]);
       if (nsplit > 1) reinterpret_cast<typename IF::Acc *>(partials_raw)[slot] = r;
       else {
+        r = FastIdx<T, IS_MAX>::resolve(r);
         out[out_off + (int64_t)i * out_inner_stride] = from_math<T>(r.v);
         idx_out[idx_off + (int64_t)i * idx_inner_stride] = r.i + 1;
       }
@@ -550,6 +604,7 @@ reduce_finish_kernel(T *out, int64_t *idx_out, SliceMap map, uint64_t nouter, ui
     const typename IF::Acc *pp = reinterpret_cast<const typename IF::Acc *>(partials_raw) + o * nsplit;
     typename IF::Acc r = pp[0];
     for (uint32_t s = 1; s < nsplit; ++s) r = IF::combine(r, pp[s]);
+    r = FastIdx<T, IS_MAX>::resolve(r);
     out[out_off + (int64_t)i * out_inner_stride] = from_math<T>(r.v);
     idx_out[idx_off + (int64_t)i * idx_inner_stride] = r.i + 1;
   } else {

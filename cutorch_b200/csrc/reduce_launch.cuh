@@ -118,8 +118,10 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
   const uint64_t target_ctas = (uint64_t)ctx->num_sms * 4;
 
   int inner = -1;
-  const bool row = (pl->strideK == 1 || pl->K <= 1);
-  if (!row) {
+  // the row / column kernels track positions as 32-bit offsets inside a unit of work
+  const bool huge_k = pl->K > 0xFFFFFFF0ull;
+  const bool row = (pl->strideK == 1 || pl->K <= 1) && !huge_k;
+  if (!row && !huge_k) {
     for (int i = nd - 1; i >= 0; --i)
       if (is[i] == 1 && size[i] >= 32) { inner = i; break; }
   }
