@@ -116,7 +116,7 @@ apply_generic_kernel(T *out, StridedView<IndexT> vo, const T *a, StridedView<Ind
 // where offJ walks the (at most kTiledJDims) dims of the group with the operand's own
 // strides.  A CTA handles TC consecutive c and TJ consecutive j.
 //
-// Phase 1 brings the staged tiles in with lanes along C: a warp instruction reads 128
+// Phase 1 brings the staged tiles in with lanes along C: a warp instruction reads 256
 // contiguous bytes of the staged operand, and each thread issues all of its row loads
 // before the first shared-memory store.  Phase 2 runs with lanes along J: direct operands
 // and the output move in contiguous runs, the staged values come transposed out of padded
@@ -125,7 +125,8 @@ apply_generic_kernel(T *out, StridedView<IndexT> vo, const T *a, StridedView<Ind
 constexpr int kTiledJDims = 3;
 constexpr int kTiledOuterDims = 6;
 constexpr int kTiledThreads = 256;
-constexpr int kTJ = 64;   // j extent of a tile
+constexpr int kTJ = 64;            // j extent of a tile
+constexpr int kTiledRunBytes = 256; // bytes of the staged operand's unit-stride run per tile row
 
 struct TiledOperand {
   int staged;                        // 1: unit stride along C, goes through shared memory
@@ -139,6 +140,7 @@ struct TiledOperand {
 struct TiledPlan {
   int nouter;
   int njd;                           // dims in the J group (staged-operand walk)
+  int c_fastest;                     // 1: consecutive CTAs walk C first (neighbours share the staged operand's lines)
   uint32_t sizeC, sizeJ;
   uint32_t tilesC, tilesJ;
   FastDiv32 outerSizes[kTiledOuterDims];
@@ -147,42 +149,41 @@ struct TiledPlan {
   TiledOperand op[4];                // 0 = out, 1..3 = inputs
 };
 
-template <typename T> constexpr int tiled_tc() { return (sizeof(T) >= 4) ? 32 : (sizeof(T) == 2 ? 64 : 128); }
-template <typename T> constexpr int tiled_pad() { return (sizeof(T) >= 4) ? 1 : (sizeof(T) == 2 ? 2 : 4); }
+inline int tiled_tc_for(size_t elem_size) { return (int)(kTiledRunBytes / elem_size); }
+template <typename T> constexpr int tiled_tc() { return kTiledRunBytes / (int)sizeof(T); }
+// padding that makes the row pitch an odd number of 32-bit words (64-bit words for 8-byte types)
+template <typename T> constexpr int tiled_pad() { return sizeof(T) >= 4 ? 1 : (sizeof(T) == 2 ? 2 : 4); }
 template <typename T> constexpr size_t tiled_slot_bytes() { return (size_t)kTJ * (tiled_tc<T>() + tiled_pad<T>()) * sizeof(T); }
-
-// element offset of position j of the J group for a staged operand
-__device__ __forceinline__ int64_t tiled_joff(const TiledPlan &P, const TiledOperand &o, uint32_t j) {
-  int64_t off = 0;
-  uint32_t q = j, r;
-#pragma unroll
-  for (int d = kTiledJDims - 1; d >= 0; --d) {
-    if (d < P.njd) {
-      P.jSizes[d].divmod(q, q, r);
-      off += (int64_t)r * o.jstrides[d];
-    }
-  }
-  return off;
+// dynamic shared memory: the staged tiles, then one row-offset table per slot
+template <typename T> constexpr size_t tiled_smem_bytes(int slots) {
+  return (((size_t)slots * tiled_slot_bytes<T>() + 15) / 16) * 16 + (size_t)slots * kTJ * sizeof(int64_t);
 }
 
 template <int OP, typename T, int NIN>
 __global__ void __launch_bounds__(kTiledThreads)
-apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpParams<T> p) {
-  constexpr int TC = tiled_tc<T>();          // 128-byte runs of the staged operand
+apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpParams<T> p, int slots) {
+  constexpr int TC = tiled_tc<T>();
   constexpr int LD = TC + tiled_pad<T>();    // padded row length in shared memory
   constexpr int NW = kTiledThreads / 32;
   constexpr int RPW = kTJ / NW;              // phase 1: rows (j) per warp
   constexpr int CPL = TC / 32;               // phase 1: c per lane
   constexpr int CPW = TC / NW;               // phase 2: c per warp
   constexpr int JPL = kTJ / 32;              // phase 2: j per lane
+  constexpr int CPP = (CPW > 4) ? 4 : CPW;   // c per pass of phase 2 (bounds the registers)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T *tile = reinterpret_cast<T *>(smem_raw);  // [slots][kTJ][LD]
   constexpr int kSlot = kTJ * LD;
+  int64_t *joffs = reinterpret_cast<int64_t *>(smem_raw + (((size_t)slots * tiled_slot_bytes<T>() + 15) / 16) * 16);
 
   // decode blockIdx -> (outer, tile_c, tile_j)
   uint32_t bid = blockIdx.x, tj, tc, rest;
-  P.tilesJdiv.divmod(bid, rest, tj);
-  P.tilesCdiv.divmod(rest, rest, tc);
+  if (P.c_fastest) {
+    P.tilesCdiv.divmod(bid, rest, tc);
+    P.tilesJdiv.divmod(rest, rest, tj);
+  } else {
+    P.tilesJdiv.divmod(bid, rest, tj);
+    P.tilesCdiv.divmod(rest, rest, tc);
+  }
   int64_t base[4] = {0, 0, 0, 0};
 #pragma unroll
   for (int d = kTiledOuterDims - 1; d >= 0; --d) {
@@ -201,19 +202,40 @@ apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpPa
   const bool full = (nc == (uint32_t)TC) && (nj == (uint32_t)kTJ);
   const bool out_staged = P.op[0].staged;
 
+  // ---- prologue: one thread per tile row walks the J group once for every staged operand
+  if (threadIdx.x < kTJ && threadIdx.x < nj) {
+    uint32_t q = j0 + threadIdx.x, r;
+    uint32_t idx[kTiledJDims] = {0, 0, 0};
+#pragma unroll
+    for (int d = kTiledJDims - 1; d >= 0; --d) {
+      if (d < P.njd) { P.jSizes[d].divmod(q, q, r); idx[d] = r; }
+    }
+#pragma unroll
+    for (int o = 0; o <= NIN; ++o) {
+      if (P.op[o].staged) {
+        int64_t off = 0;
+#pragma unroll
+        for (int d = 0; d < kTiledJDims; ++d) off += (int64_t)idx[d] * P.op[o].jstrides[d];
+        joffs[P.op[o].slot * kTJ + threadIdx.x] = off;
+      }
+    }
+  }
+  __syncthreads();
+
   // ---- phase 1: staged inputs -> shared memory, lanes along C
 #pragma unroll
   for (int o = 1; o <= NIN; ++o) {
     if (!P.op[o].staged) continue;
     T *slot = tile + P.op[o].slot * kSlot;
+    const int64_t *jo = joffs + P.op[o].slot * kTJ;
     const T *src = in[o] + base[o] + c0;
     if (full) {
       T v[RPW][CPL];
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        const int64_t off = tiled_joff(P, P.op[o], j0 + warp + r * NW);
+        const T *row = src + jo[warp + r * NW] + lane;
 #pragma unroll
-        for (int q = 0; q < CPL; ++q) v[r][q] = src[off + lane + 32 * q];
+        for (int q = 0; q < CPL; ++q) v[r][q] = row[32 * q];
       }
 #pragma unroll
       for (int r = 0; r < RPW; ++r)
@@ -221,8 +243,8 @@ apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpPa
         for (int q = 0; q < CPL; ++q) slot[(warp + r * NW) * LD + lane + 32 * q] = v[r][q];
     } else {
       for (uint32_t jj = warp; jj < nj; jj += NW) {
-        const int64_t off = tiled_joff(P, P.op[o], j0 + jj);
-        for (uint32_t cc = lane; cc < nc; cc += 32) slot[jj * LD + cc] = src[off + cc];
+        const T *row = src + jo[jj];
+        for (uint32_t cc = lane; cc < nc; cc += 32) slot[jj * LD + cc] = row[cc];
       }
     }
   }
@@ -230,32 +252,50 @@ apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpPa
 
   // ---- phase 2: compute with lanes along J
   if (full) {
+    // per-operand pointer of this thread's first element; later ones are whole multiples of incC / incJ away
+    const T *ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+    int64_t incC[4] = {0, 0, 0, 0}, incJ[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int r0 = 0; r0 < CPW; r0 += 4) {   // 4 c per pass keeps the register count in check
-      T v[4][JPL][4];
+    for (int o = 1; o <= NIN; ++o) {
+      if (!P.op[o].staged) {
+        ptr[o] = in[o] + base[o] + (int64_t)(c0 + warp) * P.op[o].strideC + (int64_t)(j0 + lane) * P.op[o].strideJ;
+        incC[o] = (int64_t)NW * P.op[o].strideC;
+        incJ[o] = 32 * P.op[o].strideJ;
+      }
+    }
+    T *optr = out + base[0] + (int64_t)(c0 + warp) * P.op[0].strideC + (int64_t)(j0 + lane) * P.op[0].strideJ;
+    const int64_t oincC = (int64_t)NW * P.op[0].strideC, oincJ = 32 * P.op[0].strideJ;
+#pragma unroll 1
+    for (int r0 = 0; r0 < CPW; r0 += CPP) {
+      T v[CPP][JPL][4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint32_t cc = warp + (r0 + r) * NW;
+      for (int o = 1; o <= NIN; ++o) {
+        if (P.op[o].staged) {
+          const T *slot = tile + P.op[o].slot * kSlot + lane * LD + warp + r0 * NW;
 #pragma unroll
-        for (int h = 0; h < JPL; ++h) {
-          const uint32_t jj = lane + 32 * h;
+          for (int r = 0; r < CPP; ++r)
 #pragma unroll
-          for (int o = 1; o <= NIN; ++o) {
-            if (P.op[o].staged) v[r][h][o] = tile[P.op[o].slot * kSlot + jj * LD + cc];
-            else v[r][h][o] = in[o][base[o] + (int64_t)(c0 + cc) * P.op[o].strideC + (int64_t)(j0 + jj) * P.op[o].strideJ];
+            for (int h = 0; h < JPL; ++h) v[r][h][o] = slot[h * 32 * LD + r * NW];
+        } else {
+          const T *pr = ptr[o] + (int64_t)r0 * P.op[o].strideC * NW;
+#pragma unroll
+          for (int r = 0; r < CPP; ++r) {
+#pragma unroll
+            for (int h = 0; h < JPL; ++h) v[r][h][o] = pr[h * incJ[o]];
+            pr += incC[o];
           }
         }
       }
+      T *po = optr + (int64_t)r0 * oincC;
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint32_t cc = warp + (r0 + r) * NW;
+      for (int r = 0; r < CPP; ++r) {
 #pragma unroll
         for (int h = 0; h < JPL; ++h) {
-          const uint32_t jj = lane + 32 * h;
           const T res = pw_apply<OP, T>(p, NIN >= 1 ? v[r][h][1] : T(), NIN >= 2 ? v[r][h][2] : T(), NIN >= 3 ? v[r][h][3] : T());
-          if (out_staged) tile[P.op[0].slot * kSlot + jj * LD + cc] = res;
-          else out[base[0] + (int64_t)(c0 + cc) * P.op[0].strideC + (int64_t)(j0 + jj) * P.op[0].strideJ] = res;
+          if (out_staged) tile[P.op[0].slot * kSlot + (lane + 32 * h) * LD + warp + (r0 + r) * NW] = res;
+          else po[h * oincJ] = res;
         }
+        po += oincC;
       }
     }
   } else {
@@ -278,10 +318,11 @@ apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpPa
   if (out_staged) {
     __syncthreads();
     const T *slot = tile + P.op[0].slot * kSlot;
+    const int64_t *jo = joffs + P.op[0].slot * kTJ;
     T *dst = out + base[0] + c0;
     for (uint32_t jj = warp; jj < nj; jj += NW) {
-      const int64_t off = tiled_joff(P, P.op[0], j0 + jj);
-      for (uint32_t cc = lane; cc < nc; cc += 32) dst[off + cc] = slot[jj * LD + cc];
+      T *row = dst + jo[jj];
+      for (uint32_t cc = lane; cc < nc; cc += 32) row[cc] = slot[jj * LD + cc];
     }
   }
 }

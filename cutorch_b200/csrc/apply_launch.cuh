@@ -46,16 +46,16 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       const TiledPlan &t = plan.tiled;
       uint64_t blocks = (uint64_t)t.tilesC * t.tilesJ;
       for (int i = 0; i < t.nouter; ++i) blocks *= t.outerSizes[i].d;
-      const size_t smem = plan.tiled_slots * tiled_slot_bytes<T>();
+      const size_t smem = tiled_smem_bytes<T>(plan.tiled_slots);
       static thread_local int smem_set_for_device = -1;
       if (smem > 48 * 1024 && smem_set_for_device != ctx->device) {
         THCB_CUDA_TRY(cudaFuncSetAttribute(apply_tiled_kernel<OP, T, NIN>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)(4 * tiled_slot_bytes<T>())));
+                                           (int)tiled_smem_bytes<T>(4)));
         smem_set_for_device = ctx->device;
       }
       set_plan_name("tiled");
-      apply_tiled_kernel<OP, T, NIN><<<(unsigned)blocks, kTiledThreads, smem, st>>>(out, a, b, c, t, p);
+      apply_tiled_kernel<OP, T, NIN><<<(unsigned)blocks, kTiledThreads, smem, st>>>(out, a, b, c, t, p, plan.tiled_slots);
       break;
     }
     case kApplyGeneric: {

@@ -3,6 +3,7 @@
 
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -167,7 +168,7 @@ bool same_squeezed_shape(const HostView *ops, int nops, Dims *out) {
 bool try_tiled(const Dims &d, int nops, size_t elem_size, ApplyPlan *plan) {
   const int k = d.n;
   if (k < 2) return false;
-  const int tc = elem_size >= 4 ? 32 : (elem_size == 2 ? 64 : 128);
+  const int tc = tiled_tc_for(elem_size);
   // classify operands: direct = smallest |stride| sits in the last dim
   int p = -1;
   bool staged[4] = {false, false, false, false};
@@ -200,6 +201,7 @@ bool try_tiled(const Dims &d, int nops, size_t elem_size, ApplyPlan *plan) {
   memset(&t, 0, sizeof(t));
   t.nouter = p;
   t.njd = njd;
+  t.c_fastest = 1;  // measured on B200: either CTA order gives the same bandwidth
   t.sizeC = (uint32_t)sizeC;
   t.sizeJ = (uint32_t)sizeJ;
   t.tilesC = (uint32_t)((sizeC + tc - 1) / tc);

@@ -368,7 +368,7 @@ template <typename Acc> struct PartialVal { Acc v; int has; };
 // partial goes to the workspace [slice][split] and finish_kernel completes the fold.
 // ====================================================================================
 template <typename T, int MODE, bool INDEX, bool IS_MAX, bool VEC, bool WARP_PER_UNIT>
-__global__ void __launch_bounds__(kRedThreads)
+__global__ void __launch_bounds__(kRedThreads, 4)
 reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
                   uint32_t nsplit, uint64_t split_len, typename Folder<T, MODE>::Params prm, void *partials_raw) {
   using F = Folder<T, MODE>;
@@ -492,7 +492,7 @@ template <typename T> constexpr int col_vec_elems() { return sizeof(T) == 1 ? 4 
 // merged through shared memory in warp order.
 // ====================================================================================
 template <typename T, int MODE, bool INDEX, bool IS_MAX, int V>
-__global__ void __launch_bounds__(kRedThreads)
+__global__ void __launch_bounds__(kRedThreads, 4)
 reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims other than K and inner */,
                   uint64_t nouter, uint64_t K, int64_t strideK, uint64_t I, int64_t out_inner_stride,
                   int64_t idx_inner_stride, uint32_t nsplit, uint64_t split_len, uint32_t tiles_i,

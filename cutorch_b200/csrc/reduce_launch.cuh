@@ -167,7 +167,7 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
     } else {
       pl->kind = kRedRowBlock;
       if (nout < target_ctas / 2 && pl->K >= 4 * block_step) {
-        uint64_t want = (target_ctas + nout - 1) / nout;
+        uint64_t want = target_ctas / nout;  // all units resident at once (one wave, 4 CTAs per SM)
         uint64_t maxs = pl->K / (2 * block_step);
         if (want > maxs) want = maxs;
         if (want > 1) {
@@ -196,7 +196,7 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
     const uint64_t ctas = nouter * pl->tiles_i;
     const uint64_t step = (uint64_t)kRedWarps * kRedUnroll;  // rows per CTA iteration
     if (ctas < target_ctas && pl->K >= 4 * step) {
-      uint64_t want = (target_ctas + ctas - 1) / ctas;
+      uint64_t want = target_ctas / ctas;  // all CTAs resident at once (one wave, 4 CTAs per SM)
       uint64_t maxs = pl->K / (2 * step);
       if (want > maxs) want = maxs;
       if (want > 1) {
