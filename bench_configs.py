@@ -2,6 +2,7 @@
 
 Each entry is one THC call timed with CUDA events on the launching stream; a 512 MiB memset runs
 between timed iterations so that tensors that would fit the 126 MB L2 are read from HBM.
+The flush writes 512 MiB and then reads 256 MiB so no dirty lines are left.
 `python bench.py --only c2,c3` runs a subset (that is also the small case the ncu captures use).
 """
 from __future__ import annotations
@@ -13,13 +14,20 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
     def W(t, kind):
         return thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
 
+    clean = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    res_flush = torch.zeros(1, dtype=torch.int64, device=dev)
+    tclean = W(clean, "Byte")
+
     def timed(fn, nbytes, reps=10):
         reps = reps_override or reps
         ts = []
         for _ in range(3):
             fn()
         for _ in range(reps):
+            # write 512 MiB (evicts the operands), then read 256 MiB so that the lines left in L2 are
+            # clean: otherwise the timed kernel would also pay for writing back the flush's dirty lines
             flush.zero_()
+            tclean.sumall_to_device(res_flush.data_ptr())
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             fn()

@@ -102,7 +102,7 @@ const PointwiseFn kPointwise[8] = {pointwise_u8, pointwise_i8, pointwise_i16, po
 typedef int (*ReduceAllFn)(thcb200_ctx *, int, const HostView &, thcb200_scalar, void *, cudaStream_t);
 const ReduceAllFn kReduceAll[8] = {reduce_all_u8, reduce_all_i8, reduce_all_i16, reduce_all_i32,
                                    reduce_all_i64, reduce_all_f16, reduce_all_f32, reduce_all_f64};
-typedef int (*ReduceDimFn)(thcb200_ctx *, int, const HostView &, const HostView &, int, thcb200_scalar, cudaStream_t);
+typedef int (*ReduceDimFn)(thcb200_ctx *, int, const HostView &, const HostView &, int, thcb200_scalar, PostOp, cudaStream_t);
 const ReduceDimFn kReduceDim[8] = {reduce_dim_u8, reduce_dim_i8, reduce_dim_i16, reduce_dim_i32,
                                    reduce_dim_i64, reduce_dim_f16, reduce_dim_f32, reduce_dim_f64};
 typedef int (*ReduceDimIndexFn)(thcb200_ctx *, bool, const HostView &, const HostView &, const HostView &, int, cudaStream_t);
@@ -349,7 +349,16 @@ static int check_reduce_dim(const HostView &vin, const HostView &vout, int dim, 
 
 int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, const thcb200_tensor *out,
                        const thcb200_tensor *in, int dim, void *stream) {
+  thcb200_scalar none = {0.0, 0};
+  return thcb200_reduce_dim_post(ctx, rop, pre, s, THCB200_POST_NONE, none, out, in, dim, stream);
+}
+
+int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, int post_kind, thcb200_scalar post_value,
+                            const thcb200_tensor *out, const thcb200_tensor *in, int dim, void *stream) {
   HostView vin, vout;
+  if (post_kind < THCB200_POST_NONE || post_kind > THCB200_POST_POW) { set_error("reduce_dim: unknown post op %d", post_kind); return THCB200_ERR_ARG; }
+  if (post_kind == THCB200_POST_DIV && post_value.f == 0.0 && post_value.i == 0) { set_error("reduce_dim: division by zero"); return THCB200_ERR_ARG; }
+  PostOp post = {post_kind, post_value.f, post_value.i};
   int rc = check_reduce_common(ctx, in, &vin, "reduce_dim input");
   if (rc) return rc;
   rc = to_host_view(out, &vout, "reduce_dim output");
@@ -360,7 +369,7 @@ int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, con
   rc = check_reduce_dim(vin, vout, dim, "reduce_dim");
   if (rc) return rc;
   if (vout.numel == 0) return THCB200_OK;
-  return kReduceDim[vin.dtype](ctx, mode, vin, vout, dim, s, (cudaStream_t)stream);
+  return kReduceDim[vin.dtype](ctx, mode, vin, vout, dim, s, post, (cudaStream_t)stream);
 }
 
 int thcb200_reduce_dim_index(thcb200_ctx *ctx, int rop, const thcb200_tensor *values, const thcb200_tensor *indices,

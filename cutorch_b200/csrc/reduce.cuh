@@ -13,6 +13,7 @@
 #include <type_traits>
 
 #include "core.cuh"
+#include "ops.cuh"
 
 namespace thcb {
 
@@ -359,8 +360,68 @@ template <typename T, typename Acc> __device__ __forceinline__ T acc_to_elem(Acc
   else return (T)a;
 }
 
+// Optional step applied to each output after the fold, for the entry points cutorch composes
+// from two calls: mean = sum then div by the length (lib/THC/generic/THCTensorMathReduce.cu:37-43),
+// norm = fold then pow (:160-187).  The fold result is first rounded to the element type, then
+// the step runs in the element's math type and rounds again -- the values of the two-call form.
+enum PostKind { kPostNone = 0, kPostDiv = 1, kPostPow = 2 };
+struct PostOp {
+  int kind;
+  double f;     // operand for floating element types
+  int64_t i;    // operand for integer element types
+};
+
+template <typename T, typename Acc> __device__ __forceinline__ T finalize_out(Acc a, const PostOp &post) {
+  T r = acc_to_elem<T, Acc>(a);
+  if (post.kind == kPostNone) return r;
+  using M = typename TypeTraits<T>::Math;
+  if constexpr (TypeTraits<T>::is_fp) {
+    const M x = to_math<T>(r);
+    if (post.kind == kPostDiv) return from_math<T>(x / (M)post.f);
+    return from_math<T>(fp_apply<THCB200_OP_POW, M>((M)post.f, (M)0, x, (M)0, (M)0));
+  } else {
+    using P = typename Promoted<T>::type;
+    if (post.kind == kPostDiv) return (T)((P)r / (P)post.i);
+    return r;
+  }
+}
+
 // Partial accumulators of split reductions, kept in the workspace between the two stages.
 template <typename Acc> struct PartialVal { Acc v; int has; };
+
+// Folds the nsplit partials of output `o` in split order and writes the result: the second
+// stage of a split reduction, run either by reduce_finish_kernel or by the last CTA of a tile.
+template <typename T, int MODE, bool INDEX, bool IS_MAX>
+__device__ __forceinline__ void finish_output(T *out_elem, int64_t *idx_elem, uint64_t o, uint32_t nsplit,
+                                              const void *partials_raw, const PostOp &post) {
+  using F = Folder<T, MODE>;
+  using IF = IndexFolder<T, IS_MAX>;
+  if constexpr (INDEX) {
+    const typename IF::Acc *pp = reinterpret_cast<const typename IF::Acc *>(partials_raw) + o * nsplit;
+    typename IF::Acc r = pp[0];
+    for (uint32_t s = 1; s < nsplit; ++s) r = IF::combine(r, pp[s]);
+    r = FastIdx<T, IS_MAX>::resolve(r);
+    *out_elem = from_math<T>(r.v);
+    *idx_elem = r.i + 1;  // TH_INDEX_BASE
+  } else {
+    const PartialVal<typename F::Acc> *pp = reinterpret_cast<const PartialVal<typename F::Acc> *>(partials_raw) + o * nsplit;
+    Opt<F> r = Opt<F>::start();
+    for (uint32_t s = 0; s < nsplit; ++s) { Opt<F> x; x.v = pp[s].v; x.has = pp[s].has; r.merge(x); }
+    *out_elem = finalize_out<T, typename F::Acc>(r.v, post);
+  }
+}
+
+// Draws a ticket for `tile`; true in the CTA that drew the last of `count` (all partials of
+// the tile are then visible to it).  Call with every thread of the CTA, after the partial stores.
+__device__ __forceinline__ bool last_cta_of_tile(unsigned int *tickets, uint64_t tile, uint32_t count) {
+  __shared__ bool s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&tickets[tile], 1u) == count - 1);
+  __syncthreads();
+  if (s_last) __threadfence();
+  return s_last;
+}
 
 // ====================================================================================
 // ROW: the reduced dim has stride 1.  A unit of work is (slice, split); WARP_PER_UNIT picks
@@ -370,7 +431,8 @@ template <typename Acc> struct PartialVal { Acc v; int has; };
 template <typename T, int MODE, bool INDEX, bool IS_MAX, bool VEC, bool WARP_PER_UNIT>
 __global__ void __launch_bounds__(kRedThreads, 4)
 reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
-                  uint32_t nsplit, uint64_t split_len, typename Folder<T, MODE>::Params prm, void *partials_raw) {
+                  uint32_t nsplit, uint64_t split_len, typename Folder<T, MODE>::Params prm, void *partials_raw,
+                  unsigned int *tickets, PostOp post) {
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   constexpr int V = 16 / sizeof(T);
@@ -446,21 +508,32 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
       }
     }
   }
-  if (!active || gt != 0) return;
   if (nsplit > 1) {
-    if constexpr (INDEX) reinterpret_cast<typename IF::Acc *>(partials_raw)[unit] = best;
-    else {
-      PartialVal<typename F::Acc> *pp = reinterpret_cast<PartialVal<typename F::Acc> *>(partials_raw);
-      pp[unit].v = acc.v; pp[unit].has = acc.has;
+    // only the CTA-per-unit form splits
+    if (active && gt == 0) {
+      if constexpr (INDEX) reinterpret_cast<typename IF::Acc *>(partials_raw)[unit] = best;
+      else {
+        PartialVal<typename F::Acc> *pp = reinterpret_cast<PartialVal<typename F::Acc> *>(partials_raw);
+        pp[unit].v = acc.v; pp[unit].has = acc.has;
+      }
     }
+    if constexpr (!WARP_PER_UNIT) {
+      if (tickets && last_cta_of_tile(tickets, slice, nsplit)) {
+        if (threadIdx.x == 0) {
+          finish_output<T, MODE, INDEX, IS_MAX>(out + out_off, idx_out + idx_off, slice, nsplit, partials_raw, post);
+          tickets[slice] = 0;
+        }
+      }
+    }
+    return;
+  }
+  if (!active || gt != 0) return;
+  if constexpr (INDEX) {
+    best = FastIdx<T, IS_MAX>::resolve(best);
+    out[out_off] = from_math<T>(best.v);
+    idx_out[idx_off] = best.i + 1;  // TH_INDEX_BASE
   } else {
-    if constexpr (INDEX) {
-      best = FastIdx<T, IS_MAX>::resolve(best);
-      out[out_off] = from_math<T>(best.v);
-      idx_out[idx_off] = best.i + 1;  // TH_INDEX_BASE
-    } else {
-      out[out_off] = acc_to_elem<T, typename F::Acc>(acc.v);
-    }
+    out[out_off] = finalize_out<T, typename F::Acc>(acc.v, post);
   }
 }
 
@@ -496,7 +569,7 @@ __global__ void __launch_bounds__(kRedThreads, 4)
 reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims other than K and inner */,
                   uint64_t nouter, uint64_t K, int64_t strideK, uint64_t I, int64_t out_inner_stride,
                   int64_t idx_inner_stride, uint32_t nsplit, uint64_t split_len, uint32_t tiles_i,
-                  typename Folder<T, MODE>::Params prm, void *partials_raw) {
+                  typename Folder<T, MODE>::Params prm, void *partials_raw, unsigned int *tickets, PostOp post) {
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   using VecT = typename ColVec<V * sizeof(T), T>::type;
@@ -578,8 +651,22 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
         PartialVal<typename F::Acc> *pp = reinterpret_cast<PartialVal<typename F::Acc> *>(partials_raw);
         pp[slot].v = r.v; pp[slot].has = r.has;
       } else {
-        out[out_off + (int64_t)i * out_inner_stride] = acc_to_elem<T, typename F::Acc>(r.v);
+        out[out_off + (int64_t)i * out_inner_stride] = finalize_out<T, typename F::Acc>(r.v, post);
       }
+    }
+  }
+  // the CTA that completes a column tile folds its partials right away (no second launch)
+  if (nsplit > 1 && tickets) {
+    const uint64_t tile = outer * tiles_i + ti;
+    if (last_cta_of_tile(tickets, tile, nsplit)) {
+      for (int c = threadIdx.x; c < 32 * V; c += kRedThreads) {
+        const uint64_t i = (uint64_t)ti * 32 * V + c;
+        if (i >= I) continue;
+        finish_output<T, MODE, INDEX, IS_MAX>(out + out_off + (int64_t)i * out_inner_stride,
+                                              idx_out + idx_off + (int64_t)i * idx_inner_stride, outer * I + i, nsplit,
+                                              partials_raw, post);
+      }
+      if (threadIdx.x == 0) tickets[tile] = 0;
     }
   }
 }
@@ -592,27 +679,14 @@ template <typename T, int MODE, bool INDEX, bool IS_MAX>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_finish_kernel(T *out, int64_t *idx_out, SliceMap map, uint64_t nouter, uint64_t I,
                      int64_t out_inner_stride, int64_t idx_inner_stride, uint32_t nsplit,
-                     const void *partials_raw) {
-  using F = Folder<T, MODE>;
-  using IF = IndexFolder<T, IS_MAX>;
+                     const void *partials_raw, PostOp post) {
   const uint64_t o = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
   if (o >= nouter * I) return;
   const uint64_t outer = o / I, i = o - outer * I;
   int64_t in_off, out_off, idx_off;
   map.decode(outer, in_off, out_off, idx_off);
-  if constexpr (INDEX) {
-    const typename IF::Acc *pp = reinterpret_cast<const typename IF::Acc *>(partials_raw) + o * nsplit;
-    typename IF::Acc r = pp[0];
-    for (uint32_t s = 1; s < nsplit; ++s) r = IF::combine(r, pp[s]);
-    r = FastIdx<T, IS_MAX>::resolve(r);
-    out[out_off + (int64_t)i * out_inner_stride] = from_math<T>(r.v);
-    idx_out[idx_off + (int64_t)i * idx_inner_stride] = r.i + 1;
-  } else {
-    const PartialVal<typename F::Acc> *pp = reinterpret_cast<const PartialVal<typename F::Acc> *>(partials_raw) + o * nsplit;
-    Opt<F> r = Opt<F>::start();
-    for (uint32_t s = 0; s < nsplit; ++s) { Opt<F> x; x.v = pp[s].v; x.has = pp[s].has; r.merge(x); }
-    out[out_off + (int64_t)i * out_inner_stride] = acc_to_elem<T, typename F::Acc>(r.v);
-  }
+  finish_output<T, MODE, INDEX, IS_MAX>(out + out_off + (int64_t)i * out_inner_stride,
+                                        idx_out + idx_off + (int64_t)i * idx_inner_stride, o, nsplit, partials_raw, post);
 }
 
 // ====================================================================================
@@ -621,7 +695,7 @@ reduce_finish_kernel(T *out, int64_t *idx_out, SliceMap map, uint64_t nouter, ui
 template <typename T, int MODE, bool INDEX, bool IS_MAX>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_strided_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
-                      int64_t strideK, typename Folder<T, MODE>::Params prm) {
+                      int64_t strideK, typename Folder<T, MODE>::Params prm, PostOp post) {
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   const uint64_t s = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
@@ -650,7 +724,7 @@ reduce_strided_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint6
     out[out_off] = from_math<T>(best.v);
     idx_out[idx_off] = best.i + 1;
   } else {
-    out[out_off] = acc_to_elem<T, typename F::Acc>(acc.v);
+    out[out_off] = finalize_out<T, typename F::Acc>(acc.v, post);
   }
 }
 

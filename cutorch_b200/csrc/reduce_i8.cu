@@ -6,8 +6,8 @@ int reduce_all_i8(thcb200_ctx *ctx, int mode, const HostView &in, thcb200_scalar
   return reduce_all_typed<int8_t>(ctx, mode, in, s, result, st);
 }
 int reduce_dim_i8(thcb200_ctx *ctx, int mode, const HostView &in, const HostView &out, int dim, thcb200_scalar s,
-                  cudaStream_t st) {
-  return reduce_dim_typed<int8_t>(ctx, mode, in, out, dim, s, st);
+                  PostOp post, cudaStream_t st) {
+  return reduce_dim_typed<int8_t>(ctx, mode, in, out, dim, s, post, st);
 }
 int reduce_dim_index_i8(thcb200_ctx *ctx, bool is_max, const HostView &in, const HostView &values,
                         const HostView &indices, int dim, cudaStream_t st) {

@@ -224,7 +224,7 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
 
 template <typename T, int MODE, bool INDEX, bool IS_MAX>
 int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out, const HostView *idx, int dim,
-                      thcb200_scalar s, cudaStream_t st) {
+                      thcb200_scalar s, PostOp post, cudaStream_t st) {
   using F = Folder<T, MODE>;
   typename F::Params prm;
   if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Acc)s.f; else prm.s = (typename F::Acc)s.i;
@@ -242,45 +242,52 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
     partials = ctx_workspace(ctx, noutputs * pl.nsplit * 16);
     if (!partials) return THCB200_ERR_NOMEM;
   }
+  // With few enough tiles the CTA that completes a tile folds its partials itself (ticket per
+  // tile); otherwise, or without ticket counters, a second small launch does.
+  unsigned int *tickets = nullptr;
+  if (pl.nsplit > 1 && ctx->tickets) {
+    const uint64_t ntiles = (pl.kind == kRedCol) ? pl.nslices * pl.tiles_i : pl.nslices;
+    if (ntiles <= (uint64_t)kNumTickets) tickets = ctx->tickets;
+  }
   int launches = 1;
   switch (pl.kind) {
     case kRedRowWarp: {
       const uint64_t blocks = (pl.nslices + kRedWarps - 1) / kRedWarps;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name(pl.vec ? "row_warp_vec" : "row_warp");
-      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr);
-      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr);
+      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
+      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
       break;
     }
     case kRedRowBlock: {
       const uint64_t blocks = pl.nslices * pl.nsplit;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name(pl.nsplit > 1 ? "row_block_split" : "row_block");
-      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials);
-      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials);
+      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
+      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
       break;
     }
     case kRedCol: {
       const uint64_t blocks = pl.nslices * pl.tiles_i * pl.nsplit;
       set_plan_name(pl.nsplit > 1 ? "col_tile_split" : "col_tile");
-      if (pl.vec) reduce_col_kernel<T, MODE, INDEX, IS_MAX, CV><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials);
-      else reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials);
+      if (pl.vec) reduce_col_kernel<T, MODE, INDEX, IS_MAX, CV><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
+      else reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
       break;
     }
     case kRedStrided: {
       const uint64_t blocks = (pl.nslices + kRedThreads - 1) / kRedThreads;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name("strided");
-      reduce_strided_kernel<T, MODE, INDEX, IS_MAX><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, prm);
+      reduce_strided_kernel<T, MODE, INDEX, IS_MAX><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, prm, post);
       break;
     }
   }
   THCB_CUDA_TRY(cudaGetLastError());
-  if (pl.nsplit > 1) {
+  if (pl.nsplit > 1 && !tickets) {
     const uint64_t blocks = (noutputs + kRedThreads - 1) / kRedThreads;
     const uint64_t I = pl.kind == kRedCol ? pl.I : 1;
     reduce_finish_kernel<T, MODE, INDEX, IS_MAX><<<(unsigned)blocks, kRedThreads, 0, st>>>(
-        op, xp, pl.map, pl.nslices, I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, partials);
+        op, xp, pl.map, pl.nslices, I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, partials, post);
     THCB_CUDA_TRY(cudaGetLastError());
     ++launches;
   }
@@ -290,20 +297,20 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
 
 template <typename T>
 int reduce_dim_typed(thcb200_ctx *ctx, int mode, const HostView &in, const HostView &out, int dim, thcb200_scalar s,
-                     cudaStream_t st) {
+                     PostOp post, cudaStream_t st) {
   switch (mode) {
-    case kSum: return launch_reduce_dim<T, kSum, false, false>(ctx, in, out, nullptr, dim, s, st);
-    case kProd: return launch_reduce_dim<T, kProd, false, false>(ctx, in, out, nullptr, dim, s, st);
-    case kMin: return launch_reduce_dim<T, kMin, false, false>(ctx, in, out, nullptr, dim, s, st);
-    case kMax: return launch_reduce_dim<T, kMax, false, false>(ctx, in, out, nullptr, dim, s, st);
+    case kSum: return launch_reduce_dim<T, kSum, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+    case kProd: return launch_reduce_dim<T, kProd, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+    case kMin: return launch_reduce_dim<T, kMin, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+    case kMax: return launch_reduce_dim<T, kMax, false, false>(ctx, in, out, nullptr, dim, s, post, st);
     default: break;
   }
   if constexpr (TypeTraits<T>::is_fp) {
     switch (mode) {
-      case kSumAbs: return launch_reduce_dim<T, kSumAbs, false, false>(ctx, in, out, nullptr, dim, s, st);
-      case kSumSquare: return launch_reduce_dim<T, kSumSquare, false, false>(ctx, in, out, nullptr, dim, s, st);
-      case kSumPowAbs: return launch_reduce_dim<T, kSumPowAbs, false, false>(ctx, in, out, nullptr, dim, s, st);
-      case kSumNonZero: return launch_reduce_dim<T, kSumNonZero, false, false>(ctx, in, out, nullptr, dim, s, st);
+      case kSumAbs: return launch_reduce_dim<T, kSumAbs, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+      case kSumSquare: return launch_reduce_dim<T, kSumSquare, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+      case kSumPowAbs: return launch_reduce_dim<T, kSumPowAbs, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+      case kSumNonZero: return launch_reduce_dim<T, kSumNonZero, false, false>(ctx, in, out, nullptr, dim, s, post, st);
       default: break;
     }
   }
@@ -315,13 +322,13 @@ template <typename T>
 int reduce_dim_index_typed(thcb200_ctx *ctx, bool is_max, const HostView &in, const HostView &values,
                            const HostView &indices, int dim, cudaStream_t st) {
   thcb200_scalar s = {0.0, 0};
-  if (is_max) return launch_reduce_dim<T, kMax, true, true>(ctx, in, values, &indices, dim, s, st);
-  return launch_reduce_dim<T, kMin, true, false>(ctx, in, values, &indices, dim, s, st);
+  if (is_max) return launch_reduce_dim<T, kMax, true, true>(ctx, in, values, &indices, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+  return launch_reduce_dim<T, kMin, true, false>(ctx, in, values, &indices, dim, s, PostOp{kPostNone, 0.0, 0}, st);
 }
 
 #define THCB_DECLARE_REDUCE(SUFFIX)                                                                                    \
   int reduce_all_##SUFFIX(thcb200_ctx *, int, const HostView &, thcb200_scalar, void *, cudaStream_t);                  \
-  int reduce_dim_##SUFFIX(thcb200_ctx *, int, const HostView &, const HostView &, int, thcb200_scalar, cudaStream_t);   \
+  int reduce_dim_##SUFFIX(thcb200_ctx *, int, const HostView &, const HostView &, int, thcb200_scalar, PostOp, cudaStream_t);   \
   int reduce_dim_index_##SUFFIX(thcb200_ctx *, bool, const HostView &, const HostView &, const HostView &, int, cudaStream_t);
 THCB_DECLARE_REDUCE(u8)
 THCB_DECLARE_REDUCE(i8)

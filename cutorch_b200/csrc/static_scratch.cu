@@ -118,13 +118,13 @@ extern "C" THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_s
   }
   cudaStream_t st = (cudaStream_t)stream;
   switch (vin.dtype) {
-    case THCB200_U8: return reduce_dim_u8(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_I8: return reduce_dim_i8(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_I16: return reduce_dim_i16(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_I32: return reduce_dim_i32(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_I64: return reduce_dim_i64(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_F16: return reduce_dim_f16(&view_ctx, mode, vin, vout, dim, s, st);
-    case THCB200_F32: return reduce_dim_f32(&view_ctx, mode, vin, vout, dim, s, st);
-    default: return reduce_dim_f64(&view_ctx, mode, vin, vout, dim, s, st);
+    case THCB200_U8: return reduce_dim_u8(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_I8: return reduce_dim_i8(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_I16: return reduce_dim_i16(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_I32: return reduce_dim_i32(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_I64: return reduce_dim_i64(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_F16: return reduce_dim_f16(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    case THCB200_F32: return reduce_dim_f32(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
+    default: return reduce_dim_f64(&view_ctx, mode, vin, vout, dim, s, PostOp{kPostNone, 0.0, 0}, st);
   }
 }

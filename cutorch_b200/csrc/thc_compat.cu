@@ -702,14 +702,16 @@ template <typename R> void resize_reduced(THCState *state, TensorT<R> *out, cons
 }
 
 template <typename R>
-void reduce_dim(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self, TensorT<R> *src, long dim, int keepdim) {
+void reduce_dim(THCState *state, int rop, int pre, thcb200_scalar s, TensorT<R> *self, TensorT<R> *src, long dim, int keepdim,
+                int post_kind = THCB200_POST_NONE, thcb200_scalar post_value = kZero) {
   check_gpu<R>(state, {self, src});
   THArgCheck(src->nDimension <= THCB200_MAX_DIMS, 2, CUTORCH_DIM_WARNING);
   THArgCheck(dim >= 0 && dim < src->nDimension, 3, "dimension out of range");
   THArgCheck(self != src, 1, "output must differ from the input");
   resize_reduced<R>(state, self, src->size, src->nDimension, dim);
   thcb200_tensor dout = describe<R>(self), din = describe<R>(src);
-  check_core(thcb200_reduce_dim(state_ctx(state), rop, pre, s, &dout, &din, (int)dim, (void *)state_stream(state)));
+  check_core(thcb200_reduce_dim_post(state_ctx(state), rop, pre, s, post_kind, post_value, &dout, &din, (int)dim,
+                                     (void *)state_stream(state)));
   if (!keepdim) tensor_squeeze1d<R>(state, self, nullptr, (int)dim);
 }
 

@@ -198,6 +198,20 @@ THCB200_API int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_s
                        const thcb200_tensor *out, const thcb200_tensor *in, int dim,
                        void *stream);
 
+/* thcb200_reduce_dim followed, inside the same kernel, by the second call cutorch composes
+ * some entry points from: mean = sum then div by the length of the dim
+ * (lib/THC/generic/THCTensorMathReduce.cu:37-43), norm = fold then pow (:160-187).  The fold is
+ * rounded to the element type first, then the step is applied in the element's math type and
+ * rounded again, so the values are those of the two-call form. */
+typedef enum thcb200_post_op {
+  THCB200_POST_NONE = 0,
+  THCB200_POST_DIV = 1,   /* out = fold / post_value */
+  THCB200_POST_POW = 2    /* out = fold ** post_value (floating types) */
+} thcb200_post_op;
+THCB200_API int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
+                            int post_kind, thcb200_scalar post_value, const thcb200_tensor *out,
+                            const thcb200_tensor *in, int dim, void *stream);
+
 /* thcb200_reduce_dim for callers that cannot allocate device memory when they call it (their
  * memory pool owns the whole device, their plug-in contract forbids allocations after start-up,
  * or they cannot take the synchronisation an allocation may imply).  It has no counterpart in
