@@ -168,6 +168,7 @@ def ours_main(args):
     import torch
     import torch.distributed as dist
     from cutorch_b200 import thc, _lib
+    from cutorch_b200.shard import combine_partials, shard_rows
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -178,8 +179,7 @@ def ours_main(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    assert ROWS_TOTAL % world == 0
-    rows = ROWS_TOTAL // world
+    row_start, rows = shard_rows(ROWS_TOTAL, world, rank)
     if args.rows:
         rows = args.rows
     n = rows * COLS
@@ -214,8 +214,7 @@ def ours_main(args):
         tz.add(tz, 1.0)
         tv.max(ti, tz, 1, 1)
         tz.sumall_to_device(partial.data_ptr())
-        if world > 1:
-            dist.all_reduce(partial)
+        combine_partials(partial, "sum")   # NCCL all-reduce of the 8-byte partials (no-op at N=1)
 
     def barrier():
         if world > 1:
@@ -240,6 +239,10 @@ def ours_main(args):
     e1.record(stream)
     barrier()
     launches = lib.thcb200_launch_count() - launches0
+    lt = torch.tensor([launches], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(lt)
+    launches = int(lt.item())
     ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
