@@ -27,8 +27,11 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   constexpr int V = 16 / sizeof(T);
   const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vec ? V : 1);
   const uint64_t ntiles = (n + tile - 1) / tile;
-  uint64_t grid = (uint64_t)ctx->num_sms * 8;
-  if (grid > ntiles) grid = ntiles;
+  // at most 8 CTAs per SM (all resident at once), sized so that every CTA gets the same
+  // number of tiles (to within one): a function of n and the SM count only
+  const uint64_t max_grid = (uint64_t)ctx->num_sms * 8;
+  const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;
+  uint64_t grid = per_cta ? (ntiles + per_cta - 1) / per_cta : 1;
   if (grid < 1) grid = 1;
   void *partials = ctx_workspace(ctx, grid * 16);
   if (!partials) return THCB200_ERR_NOMEM;
