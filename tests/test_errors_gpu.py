@@ -1,0 +1,139 @@
+"""Error behaviour of the THC entry points (THArgCheck / THError in cutorch): bad calls are
+reported with cutorch's messages and leave the library usable; nothing faults the GPU."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from cutorch_b200 import _lib, thc
+from cutorch_b200._lib import OP, PRE, RED
+from common import rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+def test_size_mismatch_is_an_argument_error(state):
+    a = to_device(state, np.zeros((4, 5), np.float32))
+    b = to_device(state, np.zeros((4, 6), np.float32))
+    out = thc.Tensor.new(state, "Float")
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        out.cmul(a, b)
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        out.cadd(a, 2.0, b)
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        out.copy(b) if out.nelement else a.copy(b)
+    # still usable afterwards
+    out.cmul(a, a)
+    assert out.sizes == [4, 5]
+
+
+def test_ops_undefined_for_a_type(state):
+    f = to_device(state, np.ones(8, np.float32))
+    with pytest.raises(thc.THCError, match="integer type"):
+        f.bitand(f, 3)
+    with pytest.raises(thc.THCError, match="integer type"):
+        f.cbitxor(f, f)
+    h = to_device(state, np.ones(8, np.float16))
+    with pytest.raises(thc.THCError, match="not supported for torch.CudaHalfTensor"):
+        h.lshift(h, 1)
+    i = to_device(state, np.ones(8, np.int32))
+    with pytest.raises(AttributeError):
+        state.fn("Int", "sigmoid")   # fp-only entry points are not exported for integer types
+
+
+def test_division_by_zero_scalar(state):
+    i = to_device(state, np.arange(8, dtype=np.int32))
+    with pytest.raises(thc.THCError, match="divide by zero"):
+        i.div(i, 0)
+
+
+def test_dimension_checks(state):
+    m = to_device(state, np.zeros((3, 4), np.float32))
+    out = thc.Tensor.new(state, "Float")
+    with pytest.raises(thc.THCError, match="dimension out of range"):
+        out.sum(m, 2, 1)
+    idx = thc.Tensor.new(state, "Long")
+    with pytest.raises(thc.THCError, match="dimension out of range"):
+        out.max(idx, m, -1, 1)
+    with pytest.raises(thc.THCError, match="output must differ"):
+        m.sum(m, 0, 1)
+
+
+def test_more_than_25_dims_is_refused(state):
+    """cutorch's 'tensor too large or too many (>25) dimensions' (lib/THC/THCTensorInfo.cuh:14-16)."""
+    lib = _lib.load_library()
+    d = _lib.TensorDesc()
+    d.data = 4096
+    d.dtype = _lib.F32
+    d.ndim = 26
+    rc = lib.thcb200_pointwise(C.c_void_p(state.context), OP["FILL"], C.byref(d), None, None, None, 0, _lib.scalar(1), _lib.scalar(0),
+                               C.c_void_p(state.stream))
+    assert rc == -2 and b"too many (>25) dimensions" in lib.thcb200_last_error()
+    # 25 dims are fine
+    shape = [2] * 3 + [1] * 22
+    t = thc.Tensor.new(state, "Float", *shape)
+    t.fill(2.0)
+    assert t.sumall() == 16.0
+
+
+def test_descriptor_level_argument_checks(state):
+    lib = _lib.load_library()
+    ctx, st = C.c_void_p(state.context), C.c_void_p(state.stream)
+    a = to_device(state, np.zeros(16, np.float32))
+    b = to_device(state, np.zeros(16, np.int32))
+    da, db = a.descriptor(), b.descriptor()
+    z = _lib.scalar(0)
+    assert lib.thcb200_pointwise(ctx, OP["MUL"], C.byref(da), C.byref(da), C.byref(db), None, 2, z, z, st) == -1   # mixed dtypes
+    assert lib.thcb200_pointwise(ctx, OP["MUL"], C.byref(da), C.byref(da), None, None, 1, z, z, st) == -1          # wrong arity
+    assert lib.thcb200_pointwise(ctx, 9999, C.byref(da), C.byref(da), None, None, 1, z, z, st) == -1                # unknown op
+    assert lib.thcb200_pointwise(ctx, OP["CBITAND"], C.byref(da), C.byref(da), C.byref(da), None, 2, z, z, st) == -5  # undefined for float
+    assert lib.thcb200_reduce_all(ctx, RED["SUM"], PRE["SQUARE"], z, C.byref(db), C.c_void_p(a.data_ptr), st) == -5  # norm on ints
+    assert lib.thcb200_reduce_all(ctx, RED["MAX"], PRE["ABS"], z, C.byref(da), C.c_void_p(a.data_ptr), st) == -1     # pre-op only with sum
+    out = to_device(state, np.zeros((1, 4), np.float32))
+    src = to_device(state, np.zeros((3, 5), np.float32))
+    do, ds = out.descriptor(), src.descriptor()
+    assert lib.thcb200_reduce_dim(ctx, RED["SUM"], 0, z, C.byref(do), C.byref(ds), 0, st) == -3                      # output shape
+
+
+def test_empty_tensors_are_no_ops(state):
+    e = thc.Tensor.new(state, "Float")
+    out = thc.Tensor.new(state, "Float")
+    out.cmul(e, e)
+    assert out.nelement == 0
+    assert e.sumall() == 0.0
+    assert e.prodall() == 1.0
+
+
+def test_scalar_tensor_and_size_one_dims(state, oracle):
+    r = rng("ones")
+    x = r.standard_normal((1, 1, 1)).astype(np.float32)
+    dx = to_device(state, x)
+    out = thc.Tensor.new(state, "Float")
+    out.add(dx, 2.0)
+    assert np.array_equal(out.numpy(), x + np.float32(2.0))
+    assert dx.sumall() == float(x.sum())
+    v, i = thc.Tensor.new(state, "Float"), thc.Tensor.new(state, "Long")
+    v.max(i, dx, 1, 1)
+    assert i.numpy().tolist() == [[[1]]]
+
+
+def test_int64_indexing_path(state):
+    """A view whose offsets exceed 32 bits runs the 64-bit index kernels (no 4 GiB tensor needed:
+    the view skips through a 5 GiB byte buffer with a huge stride)."""
+    torch = pytest.importorskip("torch")
+    dev = torch.device("cuda", 0)
+    buf = torch.zeros(5 * 2**30, dtype=torch.uint8, device=dev)
+    stride = 2**32 + 16
+    buf[0] = 3
+    buf[stride] = 4
+    t = thc.Tensor.wrap(state, "Byte", buf.data_ptr(), (2, 8), (stride, 1), storage_elems=5 * 2**30)
+    assert _lib.load_library().thcb200_can_use_32bit(C.byref(t.descriptor())) == 0
+    out = thc.Tensor.new(state, "Byte")
+    out.add(t, 1)
+    assert _lib.load_library().thcb200_last_plan() == b"generic64"
+    assert out.numpy().tolist() == [[4, 1, 1, 1, 1, 1, 1, 1], [5, 1, 1, 1, 1, 1, 1, 1]]
+    t.fill(7)
+    torch.cuda.synchronize()
+    assert int(buf[stride + 7]) == 7 and int(buf[8]) == 0
+    del buf
+    torch.cuda.empty_cache()
