@@ -23,7 +23,8 @@ OPS = [
 ]
 OP = {name: i for i, name in enumerate(OPS)}
 RED = {"SUM": 0, "PROD": 1, "MIN": 2, "MAX": 3, "ALL": 4, "ANY": 5}
-PRE = {"IDENTITY": 0, "ABS": 1, "SQUARE": 2, "POWABS": 3, "NONZERO": 4, "SQDEV": 5}
+PRE = {"IDENTITY": 0, "ABS": 1, "SQUARE": 2, "POWABS": 3, "NONZERO": 4, "SQDEV": 5, "MOMENTS": 6}
+POST = {"NONE": 0, "DIV": 1, "POW": 2, "VAR_BIASED": 3, "VAR_UNBIASED": 4, "STD_BIASED": 5, "STD_UNBIASED": 6}
 FLAG_IGNORE_OVERLAP = 1
 
 
@@ -114,6 +115,7 @@ def load_library() -> C.CDLL:
     lib.thcb200_pointwise_ex.argtypes = lib.thcb200_pointwise.argtypes + [C.c_int]
     lib.thcb200_copy_convert.argtypes = [vp, P(TensorDesc), P(TensorDesc), vp]
     lib.thcb200_reduce_dim.argtypes = [vp, C.c_int, C.c_int, Scalar, P(TensorDesc), P(TensorDesc), C.c_int, vp]
+    lib.thcb200_reduce_dim_post.argtypes = [vp, C.c_int, C.c_int, Scalar, C.c_int, Scalar, P(TensorDesc), P(TensorDesc), C.c_int, vp]
     lib.thcb200_reduce_dim_index.argtypes = [vp, C.c_int, P(TensorDesc), P(TensorDesc), P(TensorDesc), C.c_int, vp]
     lib.thcb200_reduce_all.argtypes = [vp, C.c_int, C.c_int, Scalar, P(TensorDesc), vp, vp]
     lib.thcb200_reduce_all_host.argtypes = [vp, C.c_int, C.c_int, Scalar, P(TensorDesc), vp, vp]

@@ -79,5 +79,28 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     return LIB
 
 
+USERTEST_SRC = PKG.parent / "tests" / "csrc" / "user_apply_test.cu"
+USERTEST_LIB = PKG / "lib" / "libthcb200_usertest.so"
+
+
+def build_user_test() -> Path:
+    """Compiles tests/csrc/user_apply_test.cu (user functors through include/THC/THCApply.cuh) against
+    the library, the way a downstream CUDA project would."""
+    if not USERTEST_SRC.exists():
+        return USERTEST_LIB
+    newest = max(USERTEST_SRC.stat().st_mtime, _newest_header(), LIB.stat().st_mtime if LIB.exists() else 0)
+    if USERTEST_LIB.exists() and USERTEST_LIB.stat().st_mtime >= newest:
+        return USERTEST_LIB
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
+           "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-cudart", "shared", "-shared", "-I", str(INCLUDE),
+           str(USERTEST_SRC), "-o", str(USERTEST_LIB), "-L", str(LIB.parent), "-lthcb200", "-Xlinker", "-rpath,$ORIGIN",
+           "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the user-functor test library failed:\n{r.stdout}\n{r.stderr}")
+    return USERTEST_LIB
+
+
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv))
+    print(build_user_test())

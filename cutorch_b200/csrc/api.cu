@@ -356,7 +356,11 @@ int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, con
 int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, int post_kind, thcb200_scalar post_value,
                             const thcb200_tensor *out, const thcb200_tensor *in, int dim, void *stream) {
   HostView vin, vout;
-  if (post_kind < THCB200_POST_NONE || post_kind > THCB200_POST_POW) { set_error("reduce_dim: unknown post op %d", post_kind); return THCB200_ERR_ARG; }
+  if (post_kind < THCB200_POST_NONE || post_kind > THCB200_POST_STD_UNBIASED) { set_error("reduce_dim: unknown post op %d", post_kind); return THCB200_ERR_ARG; }
+  if ((pre == THCB200_PRE_MOMENTS) != (post_kind >= THCB200_POST_VAR_BIASED)) {
+    set_error("reduce_dim: THCB200_PRE_MOMENTS and the var/std post steps go together");
+    return THCB200_ERR_ARG;
+  }
   if (post_kind == THCB200_POST_DIV && post_value.f == 0.0 && post_value.i == 0) { set_error("reduce_dim: division by zero"); return THCB200_ERR_ARG; }
   PostOp post = {post_kind, post_value.f, post_value.i};
   int rc = check_reduce_common(ctx, in, &vin, "reduce_dim input");
@@ -369,6 +373,7 @@ int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s
   rc = check_reduce_dim(vin, vout, dim, "reduce_dim");
   if (rc) return rc;
   if (vout.numel == 0) return THCB200_OK;
+  if (post_kind >= THCB200_POST_VAR_BIASED) post.f = (double)vin.sizes[dim];  // n of the var/std formulas
   return kReduceDim[vin.dtype](ctx, mode, vin, vout, dim, s, post, (cudaStream_t)stream);
 }
 

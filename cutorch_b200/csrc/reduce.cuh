@@ -20,7 +20,7 @@ namespace thcb {
 // Fold modes: the (reduce op, pre-transform) pairs that exist in the C API.
 enum ReduceMode {
   kSum = 0, kSumAbs, kSumSquare, kSumPowAbs, kSumNonZero, kSumSqDev,
-  kProd, kMin, kMax, kAll, kAny, kNumReduceModes
+  kProd, kMin, kMax, kAll, kAny, kSumMoments, kNumReduceModes
 };
 
 inline int reduce_mode(int rop, int pre) {
@@ -32,6 +32,7 @@ inline int reduce_mode(int rop, int pre) {
       case THCB200_PRE_POWABS: return kSumPowAbs;
       case THCB200_PRE_NONZERO: return kSumNonZero;
       case THCB200_PRE_SQDEV: return kSumSqDev;
+      case THCB200_PRE_MOMENTS: return kSumMoments;
     }
     return -1;
   }
@@ -55,17 +56,23 @@ template <typename M> __device__ __forceinline__ bool is_nan(M v) { return v != 
 //   transform applied in that type as TH does.
 //   Min/Max compare in the element's math type; a NaN wins, as in TH's scans.
 // ---------------------------------------------------------------------------------
+// running sums of x and x*x (var / std along a dim)
+template <typename A> struct Moments { A s, s2; };
+
 template <typename T, int MODE>
 struct Folder {
   static constexpr bool kMinMax = (MODE == kMin || MODE == kMax);
   static constexpr bool kLogical = (MODE == kAll || MODE == kAny);
+  static constexpr bool kMoments = (MODE == kSumMoments);
   using SumAcc = typename TypeTraits<T>::Acc;
   using M = typename TypeTraits<T>::Math;
-  using Acc = typename std::conditional<kMinMax, M, typename std::conditional<kLogical, int, SumAcc>::type>::type;
-  struct Params { Acc s; };
+  using Scalar = typename std::conditional<kMinMax, M, typename std::conditional<kLogical, int, SumAcc>::type>::type;
+  using Acc = typename std::conditional<kMoments, Moments<SumAcc>, Scalar>::type;
+  struct Params { Scalar s; };
 
   __host__ __device__ static Acc init() {
-    if constexpr (MODE == kProd) return (Acc)1;
+    if constexpr (kMoments) { Acc a; a.s = 0; a.s2 = 0; return a; }
+    else if constexpr (MODE == kProd) return (Acc)1;
     else if constexpr (MODE == kAll) return 1;
     else if constexpr (kMinMax) return Acc();  // unused: min/max folds start from an element
     else return (Acc)0;
@@ -73,7 +80,11 @@ struct Folder {
   __device__ __forceinline__ static Acc pre(T x, const Params &p) {
     if constexpr (kMinMax) return to_math<T>(x);
     else if constexpr (kLogical) return to_math<T>(x) != (M)0 ? 1 : 0;
-    else {
+    else if constexpr (kMoments) {
+      const SumAcc v = (SumAcc)to_math<T>(x);
+      Acc a; a.s = v; a.s2 = v * v;
+      return a;
+    } else {
       const Acc v = (Acc)to_math<T>(x);
       if constexpr (MODE == kSumAbs) return v < 0 ? -v : v;
       else if constexpr (MODE == kSumSquare) return v * v;
@@ -87,7 +98,8 @@ struct Folder {
     }
   }
   __device__ __forceinline__ static Acc combine(Acc a, Acc b) {
-    if constexpr (MODE == kProd) {
+    if constexpr (kMoments) { Acc r; r.s = a.s + b.s; r.s2 = a.s2 + b.s2; return r; }
+    else if constexpr (MODE == kProd) {
       if constexpr (TypeTraits<T>::is_fp) return a * b;
       else return (Acc)((uint64_t)a * (uint64_t)b);
     }
@@ -195,6 +207,18 @@ template <> __device__ __forceinline__ int64_t shfl_xor<int64_t>(int64_t v, int 
 template <> __device__ __forceinline__ int16_t shfl_xor<int16_t>(int16_t v, int m) { return (int16_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
 template <> __device__ __forceinline__ int8_t shfl_xor<int8_t>(int8_t v, int m) { return (int8_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
 template <> __device__ __forceinline__ uint8_t shfl_xor<uint8_t>(uint8_t v, int m) { return (uint8_t)__shfl_xor_sync(0xffffffffu, (int)v, m); }
+template <> __device__ __forceinline__ Moments<double> shfl_xor<Moments<double>>(Moments<double> v, int m) {
+  Moments<double> r;
+  r.s = __shfl_xor_sync(0xffffffffu, v.s, m);
+  r.s2 = __shfl_xor_sync(0xffffffffu, v.s2, m);
+  return r;
+}
+template <> __device__ __forceinline__ Moments<float> shfl_xor<Moments<float>>(Moments<float> v, int m) {
+  Moments<float> r;
+  r.s = __shfl_xor_sync(0xffffffffu, v.s, m);
+  r.s2 = __shfl_xor_sync(0xffffffffu, v.s2, m);
+  return r;
+}
 template <typename M> __device__ __forceinline__ ValIdx<M> shfl_xor_vi(ValIdx<M> a, int m) {
   ValIdx<M> r;
   r.v = shfl_xor<M>(a.v, m);
@@ -364,25 +388,44 @@ template <typename T, typename Acc> __device__ __forceinline__ T acc_to_elem(Acc
 // from two calls: mean = sum then div by the length (lib/THC/generic/THCTensorMathReduce.cu:37-43),
 // norm = fold then pow (:160-187).  The fold result is first rounded to the element type, then
 // the step runs in the element's math type and rounds again -- the values of the two-call form.
-enum PostKind { kPostNone = 0, kPostDiv = 1, kPostPow = 2 };
+enum PostKind { kPostNone = 0, kPostDiv = 1, kPostPow = 2, kPostVarBiased = 3, kPostVarUnbiased = 4, kPostStdBiased = 5, kPostStdUnbiased = 6 };
 struct PostOp {
   int kind;
   double f;     // operand for floating element types
   int64_t i;    // operand for integer element types
 };
 
+// var / std from the running sums, in the accumulate type (TH: sum and sum of squares over the
+// slice, E[x^2] - E[x]^2 with the n/(n-1) correction when unbiased, clamped at zero); post.f = n.
+template <typename T, typename A> __device__ __forceinline__ T finalize_moments(Moments<A> a, const PostOp &post) {
+  const A n = (A)post.f;
+  const A mean = a.s / n;
+  const bool unbiased = (post.kind == kPostVarUnbiased || post.kind == kPostStdUnbiased);
+  A v = unbiased ? a.s2 / (n - (A)1) - (n / (n - (A)1)) * mean * mean : a.s2 / n - mean * mean;
+  v = v < (A)0 ? (A)0 : v;
+  if (post.kind == kPostStdBiased || post.kind == kPostStdUnbiased) v = (A)sqrt((double)v);
+  return acc_to_elem<T, A>(v);
+}
+
+template <typename A> struct IsMoments : std::false_type {};
+template <typename A> struct IsMoments<Moments<A>> : std::true_type {};
+
 template <typename T, typename Acc> __device__ __forceinline__ T finalize_out(Acc a, const PostOp &post) {
-  T r = acc_to_elem<T, Acc>(a);
-  if (post.kind == kPostNone) return r;
-  using M = typename TypeTraits<T>::Math;
-  if constexpr (TypeTraits<T>::is_fp) {
-    const M x = to_math<T>(r);
-    if (post.kind == kPostDiv) return from_math<T>(x / (M)post.f);
-    return from_math<T>(fp_apply<THCB200_OP_POW, M>((M)post.f, (M)0, x, (M)0, (M)0));
+  if constexpr (IsMoments<Acc>::value) {
+    return finalize_moments<T>(a, post);
   } else {
-    using P = typename Promoted<T>::type;
-    if (post.kind == kPostDiv) return (T)((P)r / (P)post.i);
-    return r;
+    T r = acc_to_elem<T, Acc>(a);
+    if (post.kind == kPostNone) return r;
+    using M = typename TypeTraits<T>::Math;
+    if constexpr (TypeTraits<T>::is_fp) {
+      const M x = to_math<T>(r);
+      if (post.kind == kPostDiv) return from_math<T>(x / (M)post.f);
+      return from_math<T>(fp_apply<THCB200_OP_POW, M>((M)post.f, (M)0, x, (M)0, (M)0));
+    } else {
+      using P = typename Promoted<T>::type;
+      if (post.kind == kPostDiv) return (T)((P)r / (P)post.i);
+      return r;
+    }
   }
 }
 

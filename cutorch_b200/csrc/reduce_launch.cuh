@@ -15,7 +15,7 @@ template <typename T, int MODE>
 int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, void *result, cudaStream_t st) {
   using F = Folder<T, MODE>;
   typename F::Params prm;
-  if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Acc)s.f; else prm.s = (typename F::Acc)s.i;
+  if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Scalar)s.f; else prm.s = (typename F::Scalar)s.i;
   // collapsed view of the input
   int64_t sizes[kMaxDims], strides[kMaxDims];
   int nd = in.ndim;
@@ -86,6 +86,9 @@ int reduce_all_typed(thcb200_ctx *ctx, int mode, const HostView &in, thcb200_sca
 // ------------------------------------------------------------------------------------
 // reduce_dim planning (shared by the value and the value+index forms)
 // ------------------------------------------------------------------------------------
+// workspace bytes per partial accumulator (the largest is two doubles and a flag)
+constexpr size_t kPartialSlotBytes = 32;
+
 enum RedDimKind { kRedRowWarp, kRedRowBlock, kRedCol, kRedStrided };
 
 struct RedDimPlan {
@@ -230,7 +233,7 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
                       thcb200_scalar s, PostOp post, cudaStream_t st) {
   using F = Folder<T, MODE>;
   typename F::Params prm;
-  if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Acc)s.f; else prm.s = (typename F::Acc)s.i;
+  if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Scalar)s.f; else prm.s = (typename F::Scalar)s.i;
   constexpr int V = 16 / sizeof(T);
   constexpr int CV = col_vec_elems<T>();
   RedDimPlan pl;
@@ -242,7 +245,7 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
   void *partials = nullptr;
   const uint64_t noutputs = (pl.kind == kRedCol) ? pl.nslices * pl.I : pl.nslices;
   if (pl.nsplit > 1) {
-    partials = ctx_workspace(ctx, noutputs * pl.nsplit * 16);
+    partials = ctx_workspace(ctx, noutputs * pl.nsplit * kPartialSlotBytes);
     if (!partials) return THCB200_ERR_NOMEM;
   }
   // With few enough tiles the CTA that completes a tile folds its partials itself (ticket per
@@ -314,6 +317,7 @@ int reduce_dim_typed(thcb200_ctx *ctx, int mode, const HostView &in, const HostV
       case kSumSquare: return launch_reduce_dim<T, kSumSquare, false, false>(ctx, in, out, nullptr, dim, s, post, st);
       case kSumPowAbs: return launch_reduce_dim<T, kSumPowAbs, false, false>(ctx, in, out, nullptr, dim, s, post, st);
       case kSumNonZero: return launch_reduce_dim<T, kSumNonZero, false, false>(ctx, in, out, nullptr, dim, s, post, st);
+      case kSumMoments: return launch_reduce_dim<T, kSumMoments, false, false>(ctx, in, out, nullptr, dim, s, post, st);
       default: break;
     }
   }

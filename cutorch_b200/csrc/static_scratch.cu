@@ -18,7 +18,7 @@
 
 namespace {
 
-// Partial accumulators of split reductions ([output][split], 16 bytes each).  Device code may
+// Partial accumulators of split reductions ([output][split], kPartialSlotBytes each).  Device code may
 // name this array directly; host code may not use the name as an address (on the host it is
 // only a handle for cudaGetSymbolAddress), so the launches below receive g_scratch_dev[device].
 static __device__ __align__(256) unsigned char g_static_scratch[THCB200_STATIC_SCRATCH_BYTES];
@@ -109,7 +109,7 @@ extern "C" THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_s
   if (rc) return rc;
   if (pl.nsplit > 1) {
     const uint64_t noutputs = (pl.kind == kRedCol) ? pl.nslices * pl.I : pl.nslices;
-    const uint64_t need = noutputs * pl.nsplit * 16;
+    const uint64_t need = noutputs * pl.nsplit * kPartialSlotBytes;
     if (need > THCB200_STATIC_SCRATCH_BYTES) {
       set_error("reduce_dim_static: this reduction needs %llu bytes of partials, the static scratch holds %llu; "
                 "use thcb200_reduce_dim", (unsigned long long)need, (unsigned long long)THCB200_STATIC_SCRATCH_BYTES);

@@ -58,6 +58,7 @@ SIGNATURES.update({
     "sum": ("v", "TTli"), "prod": ("v", "TTli"), "mean": ("v", "TTli"), "norm": ("v", "TTrli"),
     "sumall": ("a", "T"), "prodall": ("a", "T"), "meanall": ("a", "T"),
     "min": ("v", "TLTli"), "max": ("v", "TLTli"), "minall": ("R", "T"), "maxall": ("R", "T"),
+    "var": ("v", "TTlii"), "std": ("v", "TTlii"), "dist": ("a", "TTr"),
     "normall": ("a", "Tr"), "varall": ("a", "Ti"), "stdall": ("a", "Ti"),
     "fill": ("v", "Tr"), "zero": ("v", "T"), "copy": ("v", "TT"), "copyIgnoringOverlaps": ("v", "TT"),
     "resizeAs": ("v", "TT"),

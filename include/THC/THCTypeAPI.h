@@ -192,6 +192,9 @@ THC_API int THCTensor_(equal)(THCState *state, THCTensor *self, THCTensor *src);
 /* ---- reductions (lib/THC/generic/THCTensorMathReduce.h) ---- */
 #if THC_T_FLOATING
 THC_API void THCTensor_(norm)(THCState *state, THCTensor *self, THCTensor *src, real value, long dimension, int keepdim);
+THC_API void THCTensor_(std)(THCState *state, THCTensor *self, THCTensor *src, long dim, int biased, int keepdim);
+THC_API void THCTensor_(var)(THCState *state, THCTensor *self, THCTensor *src, long dim, int biased, int keepdim);
+THC_API accreal THCTensor_(dist)(THCState *state, THCTensor *self, THCTensor *src, real value);
 THC_API accreal THCTensor_(normall)(THCState *state, THCTensor *self, real value);
 THC_API accreal THCTensor_(varall)(THCState *state, THCTensor *self, int biased);
 THC_API accreal THCTensor_(stdall)(THCState *state, THCTensor *self, int biased);

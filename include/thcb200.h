@@ -134,6 +134,7 @@ typedef enum thcb200_pre_op {
   THCB200_PRE_POWABS = 3,   /* |x| ** s   (norm p) */
   THCB200_PRE_NONZERO = 4,  /* x != 0 ? 1 : 0 (norm p = 0) */
   THCB200_PRE_SQDEV = 5,    /* (x - s) ** 2 (varall) */
+  THCB200_PRE_MOMENTS = 6,  /* running sums of x and x*x; only with a THCB200_POST_VAR_* / _STD_* step */
   THCB200_PRE_COUNT
 } thcb200_pre_op;
 
@@ -206,7 +207,12 @@ THCB200_API int thcb200_reduce_dim(thcb200_ctx *ctx, int rop, int pre, thcb200_s
 typedef enum thcb200_post_op {
   THCB200_POST_NONE = 0,
   THCB200_POST_DIV = 1,   /* out = fold / post_value */
-  THCB200_POST_POW = 2    /* out = fold ** post_value (floating types) */
+  THCB200_POST_POW = 2,   /* out = fold ** post_value (floating types) */
+  /* var / std along the dim from the sums of x and x*x (pre = THCB200_PRE_MOMENTS), in the
+   * accumulate type: E[x^2] - E[x]^2, with the n/(n-1) correction when unbiased, clamped at 0
+   * (lib/THC/THCTensorMathReduce.cuh:269-306, generic/THCTensorMathReduce.cu:76-126) */
+  THCB200_POST_VAR_BIASED = 3, THCB200_POST_VAR_UNBIASED = 4,
+  THCB200_POST_STD_BIASED = 5, THCB200_POST_STD_UNBIASED = 6
 } thcb200_post_op;
 THCB200_API int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
                             int post_kind, thcb200_scalar post_value, const thcb200_tensor *out,

@@ -59,6 +59,7 @@ class Oracle:
                                               C.c_double, C.c_int64, C.c_int64]
         self.lib.oracle_copy_convert.argtypes = [P(_Desc), P(_Desc)]
         self.lib.oracle_reduce_dim.argtypes = [C.c_int, C.c_int, C.c_double, P(_Desc), P(_Desc), P(_Desc), C.c_int]
+        self.lib.oracle_var_dim.argtypes = [P(_Desc), P(_Desc), C.c_int, C.c_int, C.c_int]
         self.lib.oracle_reduce_all.argtypes = [C.c_int, C.c_int, C.c_double, P(_Desc), P(C.c_double), P(C.c_int64)]
         self.set_threads(threads)
 
@@ -100,6 +101,14 @@ class Oracle:
                                         C.byref(sd), dim)
         assert rc == 0
         return (out, idx) if with_index else out
+
+    def var_dim(self, src: np.ndarray, dim: int, biased: bool, take_sqrt: bool) -> np.ndarray:
+        shape = list(src.shape)
+        shape[dim] = 1
+        out = np.zeros(shape, dtype=src.dtype)
+        od, sd = _desc(out), _desc(src)
+        assert self.lib.oracle_var_dim(C.byref(od), C.byref(sd), dim, int(biased), int(take_sqrt)) == 0
+        return out
 
     def reduce_all(self, rop: int, pre: int, s: float, src: np.ndarray):
         """Returns a float for floating element types (the double accumulator) and an int otherwise."""

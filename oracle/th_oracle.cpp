@@ -394,6 +394,38 @@ void reduce_dim_t(int rop, int pre, double s, const oracle_tensor &out, const or
   }
 }
 
+// var / std along a dim with TH's formula: running sum and sum of squares in the accumulate type,
+// E[x^2] - E[x]^2 (times n/(n-1) pieces when unbiased), clamped at zero
+// (composition of lib/THC/generic/THCTensorMathReduce.cu:76-126 with THCTensorMathReduce.cuh:269-306).
+template <typename T>
+void var_dim_t(const oracle_tensor &out, const oracle_tensor &in, int dim, int biased, int take_sqrt) {
+  oracle_tensor inb = in;
+  inb.sizes[dim] = 1;
+  const int64_t nout = numel(out);
+  const int64_t K = in.sizes[dim], sk = in.strides[dim];
+  Walker wi, wo;
+  wi.init(inb, 0);
+  wo.init(out, 0);
+  for (int64_t o = 0; o < nout; ++o) {
+    const T *p = (const T *)in.data + wi.off;
+    double s = 0, s2 = 0;
+    for (int64_t k = 0; k < K; ++k) {
+      const double z = (double)(typename Info<T>::M)p[k * sk];
+      s += z;
+      s2 += z * z;
+    }
+    const double n = (double)K;
+    double mean = s / n, v;
+    if (biased) v = s2 / n - mean * mean;
+    else v = s2 / (n - 1) - (n / (n - 1)) * mean * mean;
+    if (v < 0) v = 0;
+    if (take_sqrt) v = sqrt(v);
+    RunResult<T> r; r.f = v; r.i = 0; r.pos = 0;
+    ((T *)out.data)[wo.off] = from_result<T>(r);
+    wi.next(); wo.next();
+  }
+}
+
 template <typename T>
 void reduce_all_t(int rop, int pre, double s, const oracle_tensor &in, double *rf, int64_t *ri) {
   using A = typename AccOf<T>::type;
@@ -547,6 +579,15 @@ int oracle_reduce_dim(int rop, int pre, double s, const oracle_tensor *out, cons
     case 5: reduce_dim_t<f16>(rop, pre, s, *out, idx, *in, dim); return 0;
     case 6: reduce_dim_t<float>(rop, pre, s, *out, idx, *in, dim); return 0;
     case 7: reduce_dim_t<double>(rop, pre, s, *out, idx, *in, dim); return 0;
+  }
+  return -1;
+}
+
+int oracle_var_dim(const oracle_tensor *out, const oracle_tensor *in, int dim, int biased, int take_sqrt) {
+  switch (in->dtype) {
+    case 5: var_dim_t<f16>(*out, *in, dim, biased, take_sqrt); return 0;
+    case 6: var_dim_t<float>(*out, *in, dim, biased, take_sqrt); return 0;
+    case 7: var_dim_t<double>(*out, *in, dim, biased, take_sqrt); return 0;
   }
   return -1;
 }

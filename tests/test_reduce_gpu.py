@@ -223,3 +223,31 @@ def test_int_sum_is_exact_beyond_32_bits(state, oracle):
     out = thc.Tensor.new(state, "Int")
     out.call("sum", out, dx, 1, 1)
     assert_bit_equal(out.numpy(), x.astype(np.int64).sum(axis=1, keepdims=True).astype(np.int32), "Int.sum wraps on store only")
+
+
+@pytest.mark.parametrize("kind", FP_KINDS)
+@pytest.mark.parametrize("case", [0, 1, 2, 3, 4, 6, 7])
+def test_var_std_dim(state, oracle, kind, case):
+    """var / std along a dim (sum and sum of squares in the accumulate type, TH's formula)."""
+    shape, dim, layout = SHAPES[case]
+    r = rng("var_dim", kind, case)
+    x = make_view(r, kind, shape, layout)
+    dx = to_device(state, x)
+    for biased in (0, 1):
+        for name, take_sqrt in (("var", False), ("std", True)):
+            want = oracle.var_dim(x, dim, bool(biased), take_sqrt)
+            out = thc.Tensor.new(state, kind)
+            out.call(name, out, dx, dim, biased, 1)
+            scale = np.maximum(np.abs(want.astype(np.float64)), 1e-3)
+            assert_reduction_close(out.numpy(), want, REL[kind] * 8, scale, f"{kind}.{name} biased={biased} {shape} dim {dim} [{plan_name()}]")
+
+
+@pytest.mark.parametrize("kind", FP_KINDS)
+def test_dist(state, oracle, kind):
+    r = rng("dist", kind)
+    a = make_view(r, kind, (37, 129), "transposed")
+    b = make_view(r, kind, (37, 129), "contiguous")
+    da, db = to_device(state, a), to_device(state, b)
+    d = (np.ascontiguousarray(a) - np.ascontiguousarray(b)).astype(np.float64)   # difference rounded to the element type first
+    for p, want in ((0, float((d != 0).sum())), (1, np.abs(d).sum()), (2, np.sqrt((d * d).sum())), (3, (np.abs(d) ** 3).sum() ** (1 / 3))):
+        assert_reduction_close(da.call("dist", da, db, p), want, REL[kind] * 4, 1.0, f"{kind}.dist({p})")

@@ -1,0 +1,85 @@
+"""User-defined functors through the C++ template face (include/THC/THCApply.cuh), compiled into
+cutorch_b200/lib/libthcb200_usertest.so from tests/csrc/user_apply_test.cu the way a downstream CUDA
+library (cunn) would use cutorch's installed templates (lib/THC/THCApply.cuh:124-640)."""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from cutorch_b200 import _lib, thc
+from common import assert_bit_equal, make_view, rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def user():
+    _lib.load_library()
+    p = Path(_lib.library_path()).parent / "libthcb200_usertest.so"
+    if not p.exists():
+        pytest.fail(f"{p} is missing: run __graft_entry__.build()")
+    lib = C.CDLL(str(p))
+    lib.usertest_scale.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float]
+    lib.usertest_add_one.argtypes = [C.c_void_p, C.c_void_p]
+    lib.usertest_cross.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+    lib.usertest_less_than.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    return lib
+
+
+def test_apply2_user_functor_on_strided_views(state, user):
+    r = rng("user2")
+    for la, lb in (("contiguous", "contiguous"), ("transposed", "strided"), ("holes", "permuted")):
+        src = make_view(r, "Float", (6, 9, 11), la)
+        dst = make_view(r, "Float", (6, 9, 11), lb)
+        dsrc, ddst = to_device(state, src), to_device(state, dst)
+        assert user.usertest_scale(state.ptr, ddst.ptr, dsrc.ptr, 2.5) == 1
+        want = (np.ascontiguousarray(src) * np.float32(2.5)).astype(np.float32) + np.float32(1)
+        assert_bit_equal(ddst.numpy(), want, f"user functor {la}/{lb}")
+
+
+def test_apply2_different_shapes_same_count(state, user):
+    r = rng("user2b")
+    src = make_view(r, "Float", (4, 30), "transposed")
+    dst = thc.Tensor.new(state, "Float", 120)
+    assert user.usertest_scale(state.ptr, dst.ptr, to_device(state, src).ptr, 1.0) == 1
+    assert_bit_equal(dst.numpy(), np.ascontiguousarray(src).reshape(120) + np.float32(1), "1-D out, 2-D transposed in")
+    bad = thc.Tensor.new(state, "Float", 7)
+    assert user.usertest_scale(state.ptr, bad.ptr, dst.ptr, 1.0) == 0   # element counts differ -> false
+
+
+def test_apply1_in_place_and_overlapping_receiver(state, user):
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+    dx = to_device(state, x)
+    assert user.usertest_add_one(state.ptr, dx.ptr) == 1
+    assert_bit_equal(dx.numpy(), x + 1, "apply1 in place")
+    # an expanded (stride 0) receiver aliases: the op runs on a contiguous copy and is copied back
+    base = to_device(state, np.arange(4, dtype=np.float32).reshape(1, 4))
+    view = thc.Tensor.wrap(state, "Float", base.data_ptr, (3, 4), (0, 1), storage_elems=4)
+    assert user.usertest_add_one(state.ptr, view.ptr) == 1
+    assert_bit_equal(base.numpy(), np.arange(4, dtype=np.float32).reshape(1, 4) + 1, "apply1 on an expanded view")
+    empty = thc.Tensor.new(state, "Float")
+    assert user.usertest_add_one(state.ptr, empty.ptr) == 1   # no dimensions: no-op, true
+
+
+def test_apply3_functor_reaching_neighbours_through_pointers(state, user):
+    r = rng("user3")
+    x = make_view(r, "Float", (5, 3, 7), "contiguous")
+    y = make_view(r, "Float", (5, 3, 7), "permuted")
+    out = thc.Tensor.new(state, "Float", 5, 3, 7)
+    assert user.usertest_cross(state.ptr, out.ptr, to_device(state, x).ptr, to_device(state, y).ptr, 1) == 1
+    xs, ys = np.ascontiguousarray(x), np.ascontiguousarray(y)
+    want = np.zeros_like(xs)
+    for i in range(3):
+        j, k = (i + 1) % 3, (i + 2) % 3
+        want[:, i, :] = xs[:, j, :] * ys[:, k, :] - xs[:, k, :] * ys[:, j, :]
+    assert_bit_equal(out.numpy(), want, "cross through element pointers")
+
+
+def test_apply3_mixed_element_types(state, user):
+    r = rng("user3b")
+    a = make_view(r, "Double", (8, 13), "transposed")
+    b = make_view(r, "Double", (8, 13), "contiguous")
+    mask = thc.Tensor.new(state, "Byte", 8, 13)
+    assert user.usertest_less_than(state.ptr, mask.ptr, to_device(state, a).ptr, to_device(state, b).ptr) == 1
+    assert_bit_equal(mask.numpy(), (np.ascontiguousarray(a) < b).astype(np.uint8), "byte mask from double operands")
