@@ -1,8 +1,9 @@
 // Pointwise apply kernels for sm_100a and the per-call planner that picks one of them.
 //
 //   contig_vec : every operand collapses to one unit-stride run and is 16-byte aligned.
-//                Each thread owns kUnroll 16-byte vectors per operand, all loads issued
-//                before the first use; one tile per CTA, the tail handled by scalars.
+//                Each thread keeps 64 bytes per operand in flight as 32-byte (256-bit) or
+//                16-byte vectors, all loads issued before the first use; one tile per CTA,
+//                the tail handled by scalars.
 //   tiled      : some operands have their unit stride in a different dimension than the
 //                others (a transposed view).  A CTA stages a [TC x TJ] tile of those
 //                operands through shared memory so that both the global reads (along the
@@ -27,26 +28,33 @@ constexpr int kApplyUnroll = 4;
 // ----------------------------------------------------------------------------------
 // contig_vec
 // ----------------------------------------------------------------------------------
-template <int OP, typename T, int NIN>
+// VB = bytes per vector: 32 (256-bit ld/st.global of sm_100) when every operand is 32-byte aligned,
+// else 16.  Each thread keeps 64 bytes per operand in flight either way.
+template <int VB> constexpr int contig_unroll() { return 64 / VB; }
+template <typename T, int VB> constexpr uint64_t contig_tile() { return (uint64_t)kApplyThreads * contig_unroll<VB>() * (VB / sizeof(T)); }
+
+template <int OP, typename T, int NIN, int VB>
 __global__ void __launch_bounds__(kApplyThreads)
 apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
                         OpParams<T> p) {
-  constexpr int V = 16 / sizeof(T);                       // elements per 16-byte vector
-  constexpr uint64_t kTile = (uint64_t)kApplyThreads * kApplyUnroll * V;
+  constexpr int V = VB / sizeof(T);                       // elements per vector
+  constexpr int U = contig_unroll<VB>();
+  constexpr uint64_t kTile = contig_tile<T, VB>();
+  using Vec = typename VecBytes<VB>::type;
   const uint64_t base = (uint64_t)blockIdx.x * kTile;
   if (base + kTile <= n) {
-    Bytes16 va[kApplyUnroll], vb[kApplyUnroll], vc[kApplyUnroll];
+    Vec va[U], vb[U], vc[U];
 #pragma unroll
-    for (int u = 0; u < kApplyUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t i = base + ((uint64_t)u * kApplyThreads + threadIdx.x) * V;
-      if constexpr (NIN >= 1) va[u] = ld16_stream(a + i);
-      if constexpr (NIN >= 2) vb[u] = ld16_stream(b + i);
-      if constexpr (NIN >= 3) vc[u] = ld16_stream(c + i);
+      if constexpr (NIN >= 1) va[u] = ldv_stream<VB>(a + i);
+      if constexpr (NIN >= 2) vb[u] = ldv_stream<VB>(b + i);
+      if constexpr (NIN >= 3) vc[u] = ldv_stream<VB>(c + i);
     }
 #pragma unroll
-    for (int u = 0; u < kApplyUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t i = base + ((uint64_t)u * kApplyThreads + threadIdx.x) * V;
-      Bytes16 vo;
+      Vec vo;
       T *eo = reinterpret_cast<T *>(&vo);
       const T *ea = reinterpret_cast<const T *>(&va[u]);
       const T *eb = reinterpret_cast<const T *>(&vb[u]);
@@ -58,7 +66,7 @@ apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
         T z = NIN >= 3 ? ec[k] : T();
         eo[k] = pw_apply<OP, T>(p, x, y, z);
       }
-      st16(out + i, vo);
+      stv<VB>(out + i, vo);
     }
   } else {
     for (uint64_t i = base + threadIdx.x; i < n; i += kApplyThreads) {

@@ -35,11 +35,18 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
   const uint64_t n = plan.numel;
   switch (plan.kind) {
     case kApplyContigVec: {
-      constexpr uint64_t tile = (uint64_t)kApplyThreads * kApplyUnroll * (16 / sizeof(T));
+      bool wide = true;   // 256-bit accesses need 32-byte alignment of every operand
+      for (int o = 0; o <= NIN; ++o) if (((uintptr_t)data[o]) % 32 != 0) wide = false;
+      const uint64_t tile = wide ? contig_tile<T, 32>() : contig_tile<T, 16>();
       const uint64_t blocks = (n + tile - 1) / tile;
       if (blocks >= (1ULL << 31)) { set_error("pointwise: tensor too large"); return THCB200_ERR_DIMS; }
-      set_plan_name("contig_vec");
-      apply_contig_vec_kernel<OP, T, NIN><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, n, p);
+      if (wide) {
+        set_plan_name("contig_vec");
+        apply_contig_vec_kernel<OP, T, NIN, 32><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, n, p);
+      } else {
+        set_plan_name("contig_vec16");
+        apply_contig_vec_kernel<OP, T, NIN, 16><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, n, p);
+      }
       break;
     }
     case kApplyTiled: {

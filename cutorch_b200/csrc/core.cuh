@@ -171,4 +171,15 @@ __device__ __forceinline__ void st32(void *p, const Bytes32 &v) {
                   "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7]) : "memory");
 }
 
+// Width-generic forms: VecBytes<16> / VecBytes<32> and the matching streaming load / store.
+template <int VB> struct VecBytes;
+template <> struct VecBytes<16> { using type = Bytes16; };
+template <> struct VecBytes<32> { using type = Bytes32; };
+template <int VB> __device__ __forceinline__ typename VecBytes<VB>::type ldv_stream(const void *p) {
+  if constexpr (VB == 16) return ld16_stream(p); else return ld32_stream(p);
+}
+template <int VB> __device__ __forceinline__ void stv(void *p, const typename VecBytes<VB>::type &v) {
+  if constexpr (VB == 16) st16(p, v); else st32(p, v);
+}
+
 }  // namespace thcb

@@ -297,7 +297,7 @@ constexpr int kRedUnroll = 4;
 // reduce_all: persistent CTAs walk 16 KiB tiles block-cyclically; partial per CTA; the CTA
 // that draws the last ticket folds the partials in index order and writes the result.
 // ====================================================================================
-template <typename T, int MODE, bool VEC>
+template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided walk */>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
                   void *partials_raw, unsigned int *ticket, void *result) {
@@ -305,17 +305,18 @@ reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename 
   using Acc = typename F::Acc;
   struct Partial { Acc v; int has; };
   Partial *partials = reinterpret_cast<Partial *>(partials_raw);
-  constexpr int V = 16 / sizeof(T);
-  constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * (VEC ? V : 1);
+  constexpr bool VEC = VB != 0;
+  constexpr int V = VEC ? VB / (int)sizeof(T) : 1;
+  constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * V;
   Opt<F> acc = Opt<F>::start();
   const uint64_t ntiles = (n + kTile - 1) / kTile;
   for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t base = t * kTile;
     if constexpr (VEC) {
       if (base + kTile <= n) {
-        Bytes16 v[kRedUnroll];
+        typename VecBytes<VEC ? VB : 16>::type v[kRedUnroll];
 #pragma unroll
-        for (int u = 0; u < kRedUnroll; ++u) v[u] = ld16_stream(in + base + ((uint64_t)u * kRedThreads + threadIdx.x) * V);
+        for (int u = 0; u < kRedUnroll; ++u) v[u] = ldv_stream<VEC ? VB : 16>(in + base + ((uint64_t)u * kRedThreads + threadIdx.x) * V);
 #pragma unroll
         for (int u = 0; u < kRedUnroll; ++u) {
           const T *e = reinterpret_cast<const T *>(&v[u]);

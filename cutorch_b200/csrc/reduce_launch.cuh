@@ -23,13 +23,15 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   collapse_dims(sizes, strides, &nd, -1);
   if (nd > kGenericDims) { set_error("reduce_all: more than %d non-collapsible dimensions", kGenericDims); return THCB200_ERR_DIMS; }
   const uint64_t n = (uint64_t)in.numel;
-  const bool vec = nd == 1 && strides[0] == 1 && ((uintptr_t)in.data % 16) == 0;
-  constexpr int V = 16 / sizeof(T);
-  const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vec ? V : 1);
+  const bool unit = nd == 1 && strides[0] == 1;
+  // 256-bit loads when the base is 32-byte aligned, 128-bit when 16-byte aligned, else a strided walk
+  const int vb = !unit ? 0 : (((uintptr_t)in.data % 32) == 0 ? 32 : (((uintptr_t)in.data % 16) == 0 ? 16 : 0));
+  const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vb ? vb / sizeof(T) : 1);
   const uint64_t ntiles = (n + tile - 1) / tile;
-  // at most 8 CTAs per SM (all resident at once), sized so that every CTA gets the same
-  // number of tiles (to within one): a function of n and the SM count only
-  const uint64_t max_grid = (uint64_t)ctx->num_sms * 8;
+  // at most 4 CTAs per SM, all resident at once (measured on B200: more CTAs in flight lower the
+  // read bandwidth), sized so that every CTA gets the same number of tiles to within one: a
+  // function of n and the SM count only
+  const uint64_t max_grid = (uint64_t)ctx->num_sms * 4;
   const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;
   uint64_t grid = per_cta ? (ntiles + per_cta - 1) / per_cta : 1;
   if (grid < 1) grid = 1;
@@ -42,12 +44,15 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
     view.strides[i] = i < nd ? (uint64_t)strides[i] : 0;
   }
   const T *p = reinterpret_cast<const T *>(in.data);
-  if (vec) {
+  if (vb == 32) {
     set_plan_name("reduce_all_vec");
-    reduce_all_kernel<T, MODE, true><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
+    reduce_all_kernel<T, MODE, 32><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
+  } else if (vb == 16) {
+    set_plan_name("reduce_all_vec16");
+    reduce_all_kernel<T, MODE, 16><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
   } else {
     set_plan_name("reduce_all_strided");
-    reduce_all_kernel<T, MODE, false><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
+    reduce_all_kernel<T, MODE, 0><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
   }
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());
