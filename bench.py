@@ -31,7 +31,7 @@ COLS = 8192
 # cmul 3*4, add in place 2*4, max read 4, sumall read 4; plus 12 bytes per row of max outputs
 BYTES_PER_ELEM = 12 + 8 + 4 + 4
 BYTES_PER_ROW_EXTRA = 12
-CMUL_TRAFFIC_BYTES_PER_ELEM = (1073.752e6 + 485.120e6) / (16384 * 8192)
+CMUL_TRAFFIC_BYTES_PER_ELEM = (1073.752e6 + 497.472e6) / (16384 * 8192)
 METRIC = "thc_apply_reduce_algorithmic_hbm_throughput"
 UNIT = "GB/s"
 
@@ -284,7 +284,7 @@ def ours_main(args):
                 "achieved": dom["gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": dom["gbs"] / peak, "frac_of_nominal_8000": dom["gbs"] / 8000.0,
                 # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture summarised in
-                # profiles/c5_rows16384_contig_vec_row_argmax_reduce_all.md (11.615 B/element on a 16384-row slice;
+                # profiles/c5_rows16384_contig_vec_row_argmax_reduce_all.md (11.71 B/element on a 16384-row slice;
                 # traffic grows with the element count), scaled to the elements of one launch here
                 "traffic": int(CMUL_TRAFFIC_BYTES_PER_ELEM * n), "traffic_source": "ncu capture of a 16384-row slice, scaled by elements",
                 "per_kernel": {k: {"gbs": round(vv["gbs"], 1), "frac": round(vv["gbs"] / peak, 4), "avg_ms": round(vv["avg_ms"], 4)}
