@@ -192,6 +192,7 @@ void thcb200_ctx_destroy(thcb200_ctx *c) {
   if (c->dev_slot) cudaFree(c->dev_slot);
   if (c->host_slot) cudaFreeHost(c->host_slot);
   if (c->ws) cudaFree(c->ws);
+  if (c->mask_ws) cudaFree(c->mask_ws);
   cudaSetDevice(prev);
   delete c;
 }

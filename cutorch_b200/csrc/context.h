@@ -21,6 +21,15 @@ struct thcb200_ctx {
   int *status;            // device word: kernels record bounded-wait failures here
   void *host_slot;        // pinned, 64 bytes
   void *dev_slot;         // device, 64 bytes: result of reduce_all_host
+  // masked copy / select: tile counts and offsets of the mask counted last, and which mask
+  // view and stream they belong to (reused only when the caller says the mask is unchanged)
+  void *mask_ws;
+  size_t mask_ws_bytes;
+  const void *prep_mask;
+  uint64_t prep_layout;   // hash of the mask view's sizes and strides
+  int64_t prep_numel;
+  void *prep_stream;
+  int prep_valid;
 };
 
 namespace thcb {

@@ -1,0 +1,641 @@
+// Calls whose operands have two element types: comparisons that write a Byte tensor and the
+// Byte-masked fill / copy / select.  In cutorch these are THC_pointwiseApply2/3 instances with
+// mixed types (lib/THC/THCTensorMathCompare.cuh, THCTensorMathCompareT.cuh, THCTensorMasked.cuh)
+// plus a thrust prefix sum over a Long copy of the mask (lib/THC/generic/THCTensorMasked.cu:35-177).
+// Here: vector kernels when every operand is one unit-stride run, strided kernels otherwise, and
+// for copy / select a per-tile count + scan of tile counts + move, with the mask read as bytes.
+#include <string.h>
+
+#include "context.h"
+#include "core.cuh"
+#include "plan.h"
+
+namespace thcb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+enum Cmp { kLT = 0, kGT = 1, kLE = 2, kGE = 3, kEQ = 4, kNE = 5 };
+
+template <typename M>
+__device__ __forceinline__ uint32_t cmp_eval(int cmp, M a, M b) {
+  switch (cmp) {
+    case kLT: return a < b;
+    case kGT: return a > b;
+    case kLE: return a <= b;
+    case kGE: return a >= b;
+    case kEQ: return a == b;
+    default: return a != b;
+  }
+}
+
+template <int B> struct Word;
+template <> struct Word<1> { using type = uint8_t; };
+template <> struct Word<2> { using type = uint16_t; };
+template <> struct Word<4> { using type = uint32_t; };
+template <> struct Word<8> { using type = uint64_t; };
+template <> struct Word<16> { using type = Bytes16; };
+
+// ---------------------------------------------------------------------------------
+// compare, unit-stride operands: one 16-byte vector of `a` (and `b`) per step gives
+// EV = 16 / sizeof(T) results, stored as one EV-byte word.  Lanes take adjacent vectors.
+// ---------------------------------------------------------------------------------
+template <typename T, bool HAS_B>
+__global__ void __launch_bounds__(kThreads)
+compare_contig_kernel(uint8_t *out, const T *a, const T *b, uint64_t n, int cmp, typename TypeTraits<T>::Math s) {
+  using M = typename TypeTraits<T>::Math;
+  constexpr int EV = 16 / (int)sizeof(T);
+  using OutW = typename Word<EV>::type;
+  const uint64_t nvec = n / EV;
+  const uint64_t vbase = (uint64_t)blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
+  Bytes16 va[kUnroll], vb[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const uint64_t v = vbase + (uint64_t)u * kThreads;
+    if (v < nvec) {
+      va[u] = ld16_stream(reinterpret_cast<const Bytes16 *>(a) + v);
+      if constexpr (HAS_B) vb[u] = ld16_stream(reinterpret_cast<const Bytes16 *>(b) + v);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const uint64_t v = vbase + (uint64_t)u * kThreads;
+    if (v < nvec) {
+      const T *xa = reinterpret_cast<const T *>(&va[u]);
+      const T *xb = reinterpret_cast<const T *>(&vb[u]);
+      alignas(16) uint8_t r[EV];
+#pragma unroll
+      for (int e = 0; e < EV; ++e) {
+        const M y = HAS_B ? to_math<T>(xb[e]) : s;
+        r[e] = (uint8_t)cmp_eval<M>(cmp, to_math<T>(xa[e]), y);
+      }
+      reinterpret_cast<OutW *>(out)[v] = *reinterpret_cast<const OutW *>(r);
+    }
+  }
+  // elements past the last whole vector
+  if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - nvec * EV)) {
+    const uint64_t i = nvec * EV + threadIdx.x;
+    const M y = HAS_B ? to_math<T>(b[i]) : s;
+    out[i] = (uint8_t)cmp_eval<M>(cmp, to_math<T>(a[i]), y);
+  }
+}
+
+template <typename T, bool HAS_B, typename IndexT>
+__global__ void __launch_bounds__(kThreads)
+compare_strided_kernel(uint8_t *out, StridedView<IndexT> vo, const T *a, StridedView<IndexT> va, const T *b,
+                       StridedView<IndexT> vb, IndexT n, int cmp, typename TypeTraits<T>::Math s) {
+  using M = typename TypeTraits<T>::Math;
+  const IndexT base = (IndexT)blockIdx.x * (IndexT)(kThreads * kUnroll) + threadIdx.x;
+  T x[kUnroll], y[kUnroll];
+  IndexT oo[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const IndexT i = base + (IndexT)u * kThreads;
+    x[u] = T(); y[u] = T(); oo[u] = 0;
+    if (i < n) {
+      oo[u] = vo.offset(i);
+      x[u] = a[va.offset(i)];
+      if constexpr (HAS_B) y[u] = b[vb.offset(i)];
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const IndexT i = base + (IndexT)u * kThreads;
+    if (i < n) out[oo[u]] = (uint8_t)cmp_eval<M>(cmp, to_math<T>(x[u]), HAS_B ? to_math<T>(y[u]) : s);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// masked fill.  Elements are moved as raw words of their size (W = uintN_t).
+// Unit-stride: per 16-byte vector of t the EV mask bytes are one word; a vector whose mask
+// word is zero is neither read nor written, one whose mask bytes are all set is not read.
+// ---------------------------------------------------------------------------------
+template <typename W>
+__global__ void __launch_bounds__(kThreads)
+masked_fill_contig_kernel(W *t, const uint8_t *mask, uint64_t n, W value) {
+  constexpr int EV = 16 / (int)sizeof(W);
+  using MaskW = typename Word<EV>::type;
+  const uint64_t nvec = n / EV;
+  const uint64_t vbase = (uint64_t)blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
+  MaskW mw[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const uint64_t v = vbase + (uint64_t)u * kThreads;
+    mw[u] = MaskW();
+    if (v < nvec) mw[u] = reinterpret_cast<const MaskW *>(mask)[v];
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const uint64_t v = vbase + (uint64_t)u * kThreads;
+    if (v >= nvec) continue;
+    const uint8_t *mb = reinterpret_cast<const uint8_t *>(&mw[u]);
+    int nset = 0;
+#pragma unroll
+    for (int e = 0; e < EV; ++e) nset += mb[e] != 0;
+    if (nset == 0) continue;
+    Bytes16 x;
+    if (nset < EV) x = ld16(reinterpret_cast<const Bytes16 *>(t) + v);
+    W *xe = reinterpret_cast<W *>(&x);
+#pragma unroll
+    for (int e = 0; e < EV; ++e)
+      if (mb[e]) xe[e] = value;
+    st16(reinterpret_cast<Bytes16 *>(t) + v, x);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - nvec * EV)) {
+    const uint64_t i = nvec * EV + threadIdx.x;
+    if (mask[i]) t[i] = value;
+  }
+}
+
+template <typename W, typename IndexT>
+__global__ void __launch_bounds__(kThreads)
+masked_fill_strided_kernel(W *t, StridedView<IndexT> vt, const uint8_t *mask, StridedView<IndexT> vm, IndexT n, W value) {
+  const IndexT base = (IndexT)blockIdx.x * (IndexT)(kThreads * kUnroll) + threadIdx.x;
+  uint8_t m[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const IndexT i = base + (IndexT)u * kThreads;
+    m[u] = 0;
+    if (i < n) m[u] = mask[vm.offset(i)];
+  }
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) {
+    const IndexT i = base + (IndexT)u * kThreads;
+    if (i < n && m[u]) t[vt.offset(i)] = value;
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// masked copy / select.  The logical index space is cut into tiles of kTile elements; a CTA
+// of 8 warps owns one tile, warp w the 512 consecutive elements [w*512, w*512+512) of it, and
+// in step k lane l looks at element k*32 + l of those: a ballot per step is the mask of 32
+// consecutive elements, so positions inside a warp come from popcounts and need no scan.
+//   1. mask_tile_count_kernel: non-zero mask elements per tile.
+//   2. tile_scan_kernel (one CTA): exclusive prefix of the tile counts, and the total.
+//   3. masked_move_kernel: recomputes the ballots of its tile and moves the elements.
+// ---------------------------------------------------------------------------------
+constexpr int kSteps = 16;
+constexpr int kWarpSpan = 32 * kSteps;            // 512
+constexpr int kTile = (kThreads / 32) * kWarpSpan;  // 4096
+
+template <typename IndexT>
+__device__ __forceinline__ uint32_t warp_mask_ballots(const uint8_t *mask, const StridedView<IndexT> &vm, uint64_t wbase,
+                                                      uint64_t n, uint32_t (&ballots)[kSteps]) {
+  const unsigned lane = threadIdx.x & 31;
+  uint8_t m[kSteps];
+#pragma unroll
+  for (int k = 0; k < kSteps; ++k) {
+    const uint64_t i = wbase + (uint64_t)k * 32 + lane;
+    m[k] = 0;
+    if (i < n) m[k] = mask[vm.offset((IndexT)i)];
+  }
+  uint32_t total = 0;
+#pragma unroll
+  for (int k = 0; k < kSteps; ++k) {
+    ballots[k] = __ballot_sync(0xffffffffu, m[k] != 0);
+    total += __popc(ballots[k]);
+  }
+  return total;
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(kThreads)
+mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, uint32_t *counts) {
+  __shared__ uint32_t wsum[kThreads / 32];
+  const unsigned warp = threadIdx.x >> 5;
+  const uint64_t wbase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan;
+  uint32_t ballots[kSteps];
+  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, ballots);
+  if ((threadIdx.x & 31) == 0) wsum[warp] = total;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t s = 0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) s += wsum[w];
+    counts[blockIdx.x] = s;
+  }
+}
+
+// offsets[i] = counts[0] + ... + counts[i-1]; *total = sum of all.  One CTA of 1024 threads,
+// each owning a consecutive run of tiles.
+__global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts, uint64_t *offsets, uint64_t ntiles,
+                                                         int64_t *total) {
+  __shared__ uint64_t part[1024];
+  const uint64_t per = (ntiles + 1023) / 1024;
+  const uint64_t lo = (uint64_t)threadIdx.x * per;
+  const uint64_t hi = lo + per < ntiles ? lo + per : ntiles;
+  uint64_t s = 0;
+  for (uint64_t i = lo; i < hi; ++i) s += counts[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over the 1024 run sums
+  for (int d = 1; d < 1024; d <<= 1) {
+    uint64_t add = 0;
+    if ((int)threadIdx.x >= d) add = part[threadIdx.x - d];
+    __syncthreads();
+    part[threadIdx.x] += add;
+    __syncthreads();
+  }
+  uint64_t run = part[threadIdx.x] - s;  // exclusive prefix of this thread's run
+  for (uint64_t i = lo; i < hi; ++i) {
+    offsets[i] = run;
+    run += counts[i];
+  }
+  if (threadIdx.x == 1023) *total = (int64_t)part[1023];
+}
+
+// SELECT: packed[pos] = strided[i];  otherwise (copy): strided[i] = packed[pos]; for set mask
+// elements, pos = rank of i among them.  `packed` is walked through its own view too.
+template <typename W, typename IndexT, bool SELECT>
+__global__ void __launch_bounds__(kThreads)
+masked_move_kernel(W *strided, StridedView<IndexT> vs, W *packed, StridedView<IndexT> vp, const uint8_t *mask,
+                   StridedView<IndexT> vm, uint64_t n, const uint64_t *offsets) {
+  __shared__ uint32_t wsum[kThreads / 32];
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t wbase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan;
+  uint32_t ballots[kSteps];
+  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, ballots);
+  if (lane == 0) wsum[warp] = total;
+  __syncthreads();
+  uint64_t pos = offsets[blockIdx.x];
+  for (unsigned w = 0; w < warp; ++w) pos += wsum[w];
+  const uint32_t below = (1u << lane) - 1u;
+  if (SELECT) {
+    W x[kSteps];
+#pragma unroll
+    for (int k = 0; k < kSteps; ++k)
+      if ((ballots[k] >> lane) & 1u) x[k] = strided[vs.offset((IndexT)(wbase + (uint64_t)k * 32 + lane))];
+#pragma unroll
+    for (int k = 0; k < kSteps; ++k) {
+      if ((ballots[k] >> lane) & 1u) packed[vp.offset((IndexT)(pos + __popc(ballots[k] & below)))] = x[k];
+      pos += __popc(ballots[k]);
+    }
+  } else {
+    W x[kSteps];
+    uint64_t p = pos;
+#pragma unroll
+    for (int k = 0; k < kSteps; ++k) {
+      if ((ballots[k] >> lane) & 1u) x[k] = packed[vp.offset((IndexT)(p + __popc(ballots[k] & below)))];
+      p += __popc(ballots[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < kSteps; ++k)
+      if ((ballots[k] >> lane) & 1u) strided[vs.offset((IndexT)(wbase + (uint64_t)k * 32 + lane))] = x[k];
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+struct Collapsed {
+  int dims;
+  int64_t sizes[kMaxDims];
+  int64_t strides[kMaxDims];
+  bool unit;      // one run of stride 1
+  bool fits32;
+};
+
+// Collapses one operand on its own (TensorInfo::collapseDims).  False when more than
+// kGenericDims dims remain.
+bool collapse_view(const HostView &v, Collapsed *c) {
+  c->dims = v.ndim;
+  for (int i = 0; i < v.ndim; ++i) { c->sizes[i] = v.sizes[i]; c->strides[i] = v.strides[i]; }
+  if (c->dims == 0) { c->dims = 1; c->sizes[0] = 1; c->strides[0] = 1; }
+  collapse_dims(c->sizes, c->strides, &c->dims, -1);
+  c->unit = c->dims == 1 && c->strides[0] == 1;
+  c->fits32 = can_use_32bit(v);
+  return c->dims <= kGenericDims;
+}
+
+template <typename IndexT>
+StridedView<IndexT> make_view(const Collapsed &c) {
+  StridedView<IndexT> v;
+  v.dims = c.dims;
+  for (int i = 0; i < kGenericDims; ++i) {
+    if (i < c.dims) {
+      v.sizes[i] = DivHelper<IndexT>((uint64_t)c.sizes[i]);
+      v.strides[i] = (IndexT)c.strides[i];
+    } else {
+      v.sizes[i] = DivHelper<IndexT>(1);
+      v.strides[i] = 0;
+    }
+  }
+  return v;
+}
+
+inline bool aligned16(const void *p) { return ((uintptr_t)p) % 16 == 0; }
+
+int grid_for(uint64_t units, uint64_t per_cta, unsigned *grid, const char *what) {
+  const uint64_t blocks = (units + per_cta - 1) / per_cta;
+  if (blocks >= (1ULL << 31)) { set_error("%s: tensor too large", what); return THCB200_ERR_DIMS; }
+  *grid = (unsigned)(blocks ? blocks : 1);
+  return 0;
+}
+
+template <typename T>
+int compare_typed(int cmp, bool has_b, const HostView &vo, const HostView &va, const HostView &vb,
+                  thcb200_scalar s, cudaStream_t st) {
+  using M = typename TypeTraits<T>::Math;
+  M sv;
+  if constexpr (TypeTraits<T>::is_fp) sv = (M)s.f; else sv = (M)s.i;
+  Collapsed co, ca, cb;
+  bool ok = collapse_view(vo, &co) && collapse_view(va, &ca);
+  if (has_b) ok = ok && collapse_view(vb, &cb); else cb = ca;
+  if (!ok) { set_error("compare: a view keeps more than %d dims after collapsing", kGenericDims); return THCB200_ERR_DIMS; }
+  const uint64_t n = (uint64_t)vo.numel;
+  uint8_t *out = reinterpret_cast<uint8_t *>(vo.data);
+  const T *a = reinterpret_cast<const T *>(va.data);
+  const T *b = has_b ? reinterpret_cast<const T *>(vb.data) : nullptr;
+  unsigned grid;
+  if (co.unit && ca.unit && (!has_b || cb.unit) && aligned16(out) && aligned16(a) && aligned16(b)) {
+    constexpr int EV = 16 / (int)sizeof(T);
+    int rc = grid_for(n / EV, (uint64_t)kThreads * kUnroll, &grid, "compare");
+    if (rc) return rc;
+    set_plan_name("compare_contig_vec");
+    if (has_b) compare_contig_kernel<T, true><<<grid, kThreads, 0, st>>>(out, a, b, n, cmp, sv);
+    else compare_contig_kernel<T, false><<<grid, kThreads, 0, st>>>(out, a, b, n, cmp, sv);
+  } else {
+    int rc = grid_for(n, (uint64_t)kThreads * kUnroll, &grid, "compare");
+    if (rc) return rc;
+    const bool i32 = co.fits32 && ca.fits32 && (!has_b || cb.fits32);
+    set_plan_name(i32 ? "compare_strided32" : "compare_strided64");
+#define THCB_CMP_LAUNCH(HB, IDX)                                                                          \
+  compare_strided_kernel<T, HB, IDX><<<grid, kThreads, 0, st>>>(out, make_view<IDX>(co), a, make_view<IDX>(ca), b, \
+                                                                make_view<IDX>(cb), (IDX)n, cmp, sv)
+    if (i32) { if (has_b) THCB_CMP_LAUNCH(true, uint32_t); else THCB_CMP_LAUNCH(false, uint32_t); }
+    else { if (has_b) THCB_CMP_LAUNCH(true, uint64_t); else THCB_CMP_LAUNCH(false, uint64_t); }
+#undef THCB_CMP_LAUNCH
+  }
+  count_launch();
+  THCB_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// the scalar as the raw bits of an element of dtype `dt`
+uint64_t scalar_bits(int dt, thcb200_scalar s) {
+  uint64_t bits = 0;
+  switch (dt) {
+    case THCB200_U8: { uint8_t v = (uint8_t)s.i; memcpy(&bits, &v, 1); break; }
+    case THCB200_I8: { int8_t v = (int8_t)s.i; memcpy(&bits, &v, 1); break; }
+    case THCB200_I16: { int16_t v = (int16_t)s.i; memcpy(&bits, &v, 2); break; }
+    case THCB200_I32: { int32_t v = (int32_t)s.i; memcpy(&bits, &v, 4); break; }
+    case THCB200_I64: { int64_t v = s.i; memcpy(&bits, &v, 8); break; }
+    case THCB200_F16: { __half v = __float2half_rn((float)s.f); memcpy(&bits, &v, 2); break; }
+    case THCB200_F32: { float v = (float)s.f; memcpy(&bits, &v, 4); break; }
+    default: { double v = s.f; memcpy(&bits, &v, 8); break; }
+  }
+  return bits;
+}
+
+template <typename W>
+int masked_fill_sized(const HostView &vt, const HostView &vm, uint64_t bits, cudaStream_t st) {
+  Collapsed ct, cm;
+  if (!collapse_view(vt, &ct) || !collapse_view(vm, &cm)) {
+    set_error("masked_fill: a view keeps more than %d dims after collapsing", kGenericDims);
+    return THCB200_ERR_DIMS;
+  }
+  const uint64_t n = (uint64_t)vt.numel;
+  W *t = reinterpret_cast<W *>(vt.data);
+  const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
+  const W value = (W)bits;
+  unsigned grid;
+  if (ct.unit && cm.unit && aligned16(t) && aligned16(mask)) {
+    constexpr int EV = 16 / (int)sizeof(W);
+    int rc = grid_for(n / EV, (uint64_t)kThreads * kUnroll, &grid, "masked_fill");
+    if (rc) return rc;
+    set_plan_name("masked_fill_contig_vec");
+    masked_fill_contig_kernel<W><<<grid, kThreads, 0, st>>>(t, mask, n, value);
+  } else {
+    int rc = grid_for(n, (uint64_t)kThreads * kUnroll, &grid, "masked_fill");
+    if (rc) return rc;
+    if (ct.fits32 && cm.fits32) {
+      set_plan_name("masked_fill_strided32");
+      masked_fill_strided_kernel<W, uint32_t><<<grid, kThreads, 0, st>>>(t, make_view<uint32_t>(ct), mask,
+                                                                         make_view<uint32_t>(cm), (uint32_t)n, value);
+    } else {
+      set_plan_name("masked_fill_strided64");
+      masked_fill_strided_kernel<W, uint64_t><<<grid, kThreads, 0, st>>>(t, make_view<uint64_t>(ct), mask,
+                                                                         make_view<uint64_t>(cm), (uint64_t)n, value);
+    }
+  }
+  count_launch();
+  THCB_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// ---- mask counting shared by masked_count / masked_copy / masked_select ----
+uint64_t layout_hash(const HostView &v) {
+  uint64_t h = 1469598103934665603ULL;
+  auto mix = [&h](uint64_t x) { h = (h ^ x) * 1099511628211ULL; };
+  mix((uint64_t)v.ndim);
+  for (int i = 0; i < v.ndim; ++i) { mix((uint64_t)v.sizes[i]); mix((uint64_t)v.strides[i]); }
+  return h;
+}
+
+struct MaskPrep {
+  uint64_t ntiles;
+  uint64_t *offsets;   // device, ntiles entries
+  int64_t *total;      // device
+  Collapsed cm;
+};
+
+// Fills the context's tile offsets for this mask view (or finds them there when `reuse`).
+int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t st, MaskPrep *mp) {
+  if (!collapse_view(vm, &mp->cm)) {
+    set_error("masked: the mask keeps more than %d dims after collapsing", kGenericDims);
+    return THCB200_ERR_DIMS;
+  }
+  const uint64_t n = (uint64_t)vm.numel;
+  mp->ntiles = (n + kTile - 1) / kTile;
+  if (mp->ntiles >= (1ULL << 31)) { set_error("masked: tensor too large"); return THCB200_ERR_DIMS; }
+  // layout: [total: 8 B, padded to 256][offsets: 8 B x ntiles][counts: 4 B x ntiles]
+  const size_t need = 256 + mp->ntiles * 12;
+  const uint64_t lh = layout_hash(vm);
+  const bool hit = reuse && ctx->prep_valid && ctx->prep_mask == (const void *)vm.data && ctx->prep_numel == vm.numel &&
+                   ctx->prep_layout == lh && ctx->prep_stream == (void *)st && ctx->mask_ws_bytes >= need;
+  if (!hit && ctx->mask_ws_bytes < need) {
+    ctx->prep_valid = 0;
+    if (ctx->mask_ws) {
+      THCB_CUDA_TRY(cudaDeviceSynchronize());
+      cudaFree(ctx->mask_ws);
+      ctx->mask_ws = nullptr;
+      ctx->mask_ws_bytes = 0;
+    }
+    size_t want = 1 << 20;
+    while (want < need) want <<= 1;
+    if (cudaMalloc(&ctx->mask_ws, want) != cudaSuccess) {
+      cudaGetLastError();
+      ctx->mask_ws = nullptr;
+      set_error("masked: cannot allocate %zu bytes of tile offsets", want);
+      return THCB200_ERR_NOMEM;
+    }
+    ctx->mask_ws_bytes = want;
+  }
+  char *base = reinterpret_cast<char *>(ctx->mask_ws);
+  mp->total = reinterpret_cast<int64_t *>(base);
+  mp->offsets = reinterpret_cast<uint64_t *>(base + 256);
+  uint32_t *counts = reinterpret_cast<uint32_t *>(base + 256 + mp->ntiles * 8);
+  if (hit) return 0;
+  ctx->prep_valid = 0;
+  const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
+  if (mp->cm.fits32)
+    mask_tile_count_kernel<uint32_t><<<(unsigned)mp->ntiles, kThreads, 0, st>>>(mask, make_view<uint32_t>(mp->cm), n, counts);
+  else
+    mask_tile_count_kernel<uint64_t><<<(unsigned)mp->ntiles, kThreads, 0, st>>>(mask, make_view<uint64_t>(mp->cm), n, counts);
+  tile_scan_kernel<<<1, 1024, 0, st>>>(counts, mp->offsets, mp->ntiles, mp->total);
+  count_launch(2);
+  THCB_CUDA_TRY(cudaGetLastError());
+  ctx->prep_mask = vm.data;
+  ctx->prep_numel = vm.numel;
+  ctx->prep_layout = lh;
+  ctx->prep_stream = (void *)st;
+  ctx->prep_valid = 1;
+  return 0;
+}
+
+template <typename W, bool SELECT>
+int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView &vpacked, const HostView &vm,
+                      bool reuse, cudaStream_t st) {
+  MaskPrep mp;
+  int rc = prepare_mask(ctx, vm, reuse, st, &mp);
+  if (rc) return rc;
+  Collapsed cs, cp;
+  if (!collapse_view(vstrided, &cs) || !collapse_view(vpacked, &cp)) {
+    set_error("masked: a view keeps more than %d dims after collapsing", kGenericDims);
+    return THCB200_ERR_DIMS;
+  }
+  W *strided = reinterpret_cast<W *>(vstrided.data);
+  W *packed = reinterpret_cast<W *>(vpacked.data);
+  const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
+  const uint64_t n = (uint64_t)vm.numel;
+  if (cs.fits32 && cp.fits32 && mp.cm.fits32) {
+    set_plan_name(SELECT ? "masked_select32" : "masked_copy32");
+    masked_move_kernel<W, uint32_t, SELECT><<<(unsigned)mp.ntiles, kThreads, 0, st>>>(
+        strided, make_view<uint32_t>(cs), packed, make_view<uint32_t>(cp), mask, make_view<uint32_t>(mp.cm), n, mp.offsets);
+  } else {
+    set_plan_name(SELECT ? "masked_select64" : "masked_copy64");
+    masked_move_kernel<W, uint64_t, SELECT><<<(unsigned)mp.ntiles, kThreads, 0, st>>>(
+        strided, make_view<uint64_t>(cs), packed, make_view<uint64_t>(cp), mask, make_view<uint64_t>(mp.cm), n, mp.offsets);
+  }
+  count_launch();
+  THCB_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int check_mask(const thcb200_tensor *mask, HostView *vm, const char *what) {
+  int rc = to_host_view(mask, vm, what);
+  if (rc) return rc;
+  if (vm->dtype != THCB200_U8) { set_error("%s: the mask must be a U8 view", what); return THCB200_ERR_ARG; }
+  return 0;
+}
+
+}  // namespace
+}  // namespace thcb
+
+using namespace thcb;
+
+extern "C" {
+
+int thcb200_compare(thcb200_ctx *ctx, int cmp, const thcb200_tensor *out_u8, const thcb200_tensor *a,
+                    const thcb200_tensor *b, thcb200_scalar s, void *stream) {
+  if (!ctx) { set_error("compare: null context"); return THCB200_ERR_ARG; }
+  int code;
+  if (cmp >= THCB200_OP_LT && cmp <= THCB200_OP_NE) code = cmp - THCB200_OP_LT;
+  else if (cmp >= THCB200_OP_LT_S && cmp <= THCB200_OP_NE_S) code = cmp - THCB200_OP_LT_S;
+  else { set_error("compare: op %d is not a comparison", cmp); return THCB200_ERR_ARG; }
+  HostView vo, va, vb;
+  int rc = to_host_view(out_u8, &vo, "compare output");
+  if (!rc) rc = to_host_view(a, &va, "compare input 0");
+  if (!rc && b) rc = to_host_view(b, &vb, "compare input 1");
+  if (rc) return rc;
+  if (vo.dtype != THCB200_U8) { set_error("compare: the output must be a U8 view"); return THCB200_ERR_ARG; }
+  if (b && vb.dtype != va.dtype) { set_error("compare: inputs have different dtypes"); return THCB200_ERR_ARG; }
+  if (vo.numel != va.numel || (b && vb.numel != va.numel)) {
+    set_error("compare: operands have different element counts");
+    return THCB200_ERR_SIZE;
+  }
+  if (vo.numel == 0) return THCB200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool hb = b != nullptr;
+  switch (va.dtype) {
+    case THCB200_U8: return compare_typed<uint8_t>(code, hb, vo, va, vb, s, st);
+    case THCB200_I8: return compare_typed<int8_t>(code, hb, vo, va, vb, s, st);
+    case THCB200_I16: return compare_typed<int16_t>(code, hb, vo, va, vb, s, st);
+    case THCB200_I32: return compare_typed<int32_t>(code, hb, vo, va, vb, s, st);
+    case THCB200_I64: return compare_typed<int64_t>(code, hb, vo, va, vb, s, st);
+    case THCB200_F16: return compare_typed<__half>(code, hb, vo, va, vb, s, st);
+    case THCB200_F32: return compare_typed<float>(code, hb, vo, va, vb, s, st);
+    default: return compare_typed<double>(code, hb, vo, va, vb, s, st);
+  }
+}
+
+int thcb200_masked_fill(thcb200_ctx *ctx, const thcb200_tensor *t, const thcb200_tensor *mask_u8, thcb200_scalar value,
+                        void *stream) {
+  if (!ctx) { set_error("masked_fill: null context"); return THCB200_ERR_ARG; }
+  HostView vt, vm;
+  int rc = to_host_view(t, &vt, "masked_fill tensor");
+  if (!rc) rc = check_mask(mask_u8, &vm, "masked_fill");
+  if (rc) return rc;
+  if (vt.numel != vm.numel) { set_error("masked_fill: tensor and mask have different element counts"); return THCB200_ERR_SIZE; }
+  if (vt.numel == 0) return THCB200_OK;
+  const uint64_t bits = scalar_bits(vt.dtype, value);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dtype_size(vt.dtype)) {
+    case 1: return masked_fill_sized<uint8_t>(vt, vm, bits, st);
+    case 2: return masked_fill_sized<uint16_t>(vt, vm, bits, st);
+    case 4: return masked_fill_sized<uint32_t>(vt, vm, bits, st);
+    default: return masked_fill_sized<uint64_t>(vt, vm, bits, st);
+  }
+}
+
+int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8, int64_t *count_host, void *stream) {
+  if (!ctx || !count_host) { set_error("masked_count: null argument"); return THCB200_ERR_ARG; }
+  HostView vm;
+  int rc = check_mask(mask_u8, &vm, "masked_count");
+  if (rc) return rc;
+  if (vm.numel == 0) { *count_host = 0; return THCB200_OK; }
+  cudaStream_t st = (cudaStream_t)stream;
+  MaskPrep mp;
+  rc = prepare_mask(ctx, vm, false, st, &mp);
+  if (rc) return rc;
+  THCB_CUDA_TRY(cudaMemcpyAsync(ctx->host_slot, mp.total, 8, cudaMemcpyDeviceToHost, st));
+  THCB_CUDA_TRY(cudaStreamSynchronize(st));
+  memcpy(count_host, ctx->host_slot, 8);
+  return THCB200_OK;
+}
+
+static int masked_move(thcb200_ctx *ctx, bool select, const thcb200_tensor *strided, const thcb200_tensor *packed,
+                       const thcb200_tensor *mask_u8, void *stream, int flags, const char *what) {
+  if (!ctx) { set_error("%s: null context", what); return THCB200_ERR_ARG; }
+  HostView vs, vp, vm;
+  int rc = to_host_view(strided, &vs, what);
+  if (!rc) rc = to_host_view(packed, &vp, what);
+  if (!rc) rc = check_mask(mask_u8, &vm, what);
+  if (rc) return rc;
+  if (vs.dtype != vp.dtype) { set_error("%s: operands have different dtypes", what); return THCB200_ERR_ARG; }
+  if (vs.numel != vm.numel) { set_error("%s: tensor and mask have different element counts", what); return THCB200_ERR_SIZE; }
+  if (vm.numel == 0) return THCB200_OK;
+  const bool reuse = (flags & THCB200_FLAG_MASK_COUNTED) != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+#define THCB_MOVE(W) (select ? masked_move_sized<W, true>(ctx, vs, vp, vm, reuse, st) : masked_move_sized<W, false>(ctx, vs, vp, vm, reuse, st))
+  switch (dtype_size(vs.dtype)) {
+    case 1: return THCB_MOVE(uint8_t);
+    case 2: return THCB_MOVE(uint16_t);
+    case 4: return THCB_MOVE(uint32_t);
+    default: return THCB_MOVE(uint64_t);
+  }
+#undef THCB_MOVE
+}
+
+int thcb200_masked_copy(thcb200_ctx *ctx, const thcb200_tensor *t, const thcb200_tensor *mask_u8,
+                        const thcb200_tensor *src, void *stream, int flags) {
+  return masked_move(ctx, false, t, src, mask_u8, stream, flags, "masked_copy");
+}
+
+int thcb200_masked_select(thcb200_ctx *ctx, const thcb200_tensor *out, const thcb200_tensor *src,
+                          const thcb200_tensor *mask_u8, void *stream, int flags) {
+  return masked_move(ctx, true, src, out, mask_u8, stream, flags, "masked_select");
+}
+
+}  // extern "C"

@@ -755,6 +755,63 @@ template <typename R> typename RealTraits<R>::acc reduce_all_acc(THCState *state
   return (A)reduce_all_i<R>(state, rop, pre, s, self);
 }
 
+// ---- comparisons into a ByteTensor, Byte masks -----------------------------------------
+using ByteT = TensorT<unsigned char>;
+
+// self_ = (src1 CMP src2) or (src1 CMP value) as 0/1 bytes; self_ takes src1's size
+// (THC_logicalValue / THC_logicalTensor, lib/THC/THCTensorMathCompare.cuh:69-85,
+// THCTensorMathCompareT.cuh:52-72).
+template <typename R>
+void compare_to_byte(THCState *state, int op, ByteT *self_, TensorT<R> *src1, TensorT<R> *src2, thcb200_scalar s) {
+  check_gpu<unsigned char>(state, {self_});
+  check_gpu<R>(state, {src1, src2});
+  if ((void *)self_ != (void *)src1) tensor_raw_resize<unsigned char>(state, self_, src1->nDimension, src1->size, nullptr);
+  if (src2) THArgCheck(tensor_nelement<R>(src1) == tensor_nelement<R>(src2), 3, "sizes do not match");
+  thcb200_tensor dout = describe<unsigned char>(self_), da = describe<R>(src1), db;
+  if (src2) db = describe<R>(src2);
+  check_core(thcb200_compare(state_ctx(state), op, &dout, &da, src2 ? &db : nullptr, s, (void *)state_stream(state)));
+}
+
+template <typename R> void masked_fill(THCState *state, TensorT<R> *tensor, ByteT *mask, R value) {
+  check_gpu<R>(state, {tensor});
+  check_gpu<unsigned char>(state, {mask});
+  THArgCheck(tensor_nelement<R>(tensor) == tensor_nelement<unsigned char>(mask), 2, "sizes do not match");
+  thcb200_tensor dt = describe<R>(tensor), dm = describe<unsigned char>(mask);
+  check_core(thcb200_masked_fill(state_ctx(state), &dt, &dm, to_scalar<R>(value), (void *)state_stream(state)));
+}
+
+// lib/THC/generic/THCTensorMasked.cu:35-104.  `src` is read through its own strides, so no
+// contiguous copy of it is made.
+template <typename R> void masked_copy(THCState *state, TensorT<R> *tensor, ByteT *mask, TensorT<R> *src) {
+  check_gpu<R>(state, {tensor, src});
+  check_gpu<unsigned char>(state, {mask});
+  THArgCheck(tensor_nelement<unsigned char>(mask) == tensor_nelement<R>(tensor), 2,
+             "mask and tensor must have the same number of elements");
+  thcb200_tensor dt = describe<R>(tensor), dm = describe<unsigned char>(mask), ds = describe<R>(src);
+  int64_t total = 0;
+  check_core(thcb200_masked_count(state_ctx(state), &dm, &total, (void *)state_stream(state)));
+  THArgCheck(total <= (int64_t)tensor_nelement<R>(src), 2, "source nElements must be == mask `1` elements");
+  if (total == 0) return;
+  check_core(thcb200_masked_copy(state_ctx(state), &dt, &dm, &ds, (void *)state_stream(state), THCB200_FLAG_MASK_COUNTED));
+}
+
+// lib/THC/generic/THCTensorMasked.cu:119-177: `tensor` becomes 1-D with one element per set
+// mask element, in src's logical order.
+template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, TensorT<R> *src, ByteT *mask) {
+  check_gpu<R>(state, {tensor, src});
+  check_gpu<unsigned char>(state, {mask});
+  THArgCheck(tensor_nelement<unsigned char>(mask) == tensor_nelement<R>(src), 2, "sizes do not match");
+  THArgCheck(tensor != src, 1, "output must differ from the input");
+  thcb200_tensor dm = describe<unsigned char>(mask), ds = describe<R>(src);
+  int64_t total = 0;
+  check_core(thcb200_masked_count(state_ctx(state), &dm, &total, (void *)state_stream(state)));
+  long sz[1] = {(long)total};
+  tensor_raw_resize<R>(state, tensor, 1, sz, nullptr);
+  if (total == 0) return;
+  thcb200_tensor dt = describe<R>(tensor);
+  check_core(thcb200_masked_select(state_ctx(state), &dt, &ds, &dm, (void *)state_stream(state), THCB200_FLAG_MASK_COUNTED));
+}
+
 }  // namespace
 
 // ======================================================================================

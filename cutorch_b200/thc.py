@@ -62,7 +62,12 @@ SIGNATURES.update({
     "normall": ("a", "Tr"), "varall": ("a", "Ti"), "stdall": ("a", "Ti"),
     "fill": ("v", "Tr"), "zero": ("v", "T"), "copy": ("v", "TT"), "copyIgnoringOverlaps": ("v", "TT"),
     "resizeAs": ("v", "TT"),
+    "maskedFill": ("v", "TBr"), "maskedCopy": ("v", "TBT"), "maskedSelect": ("v", "TTB"),
 })
+# comparisons: <op>Value / <op>Tensor write a Byte tensor ("B"), the ...T forms the operands' type
+for _c in ("lt", "gt", "le", "ge", "eq", "ne"):
+    SIGNATURES.update({_c + "Value": ("v", "BTr"), _c + "ValueT": ("v", "TTr"),
+                       _c + "Tensor": ("v", "BTT"), _c + "TensorT": ("v", "TTT")})
 
 
 def _half_from_float(v: float) -> _Half:
@@ -366,10 +371,10 @@ class Tensor:
         creal, cacc = KINDS[self.kind][2], KINDS[self.kind][3]
         argtypes, cargs = [C.c_void_p], [self.state.ptr]
         for code, a in zip(spec, args):
-            if code in "TL":
+            if code in "TLB":
                 if not isinstance(a, Tensor):
                     raise TypeError(f"{name}: expected a tensor")
-                want = "Long" if code == "L" else self.kind
+                want = {"L": "Long", "B": "Byte"}.get(code, self.kind)
                 if a.kind != want:
                     raise TypeError(f"{name}: expected a {want} tensor, got {a.kind}")
                 argtypes.append(C.c_void_p)
@@ -395,7 +400,7 @@ class Tensor:
         """self:copy(src) with type conversion (THCTensor_(copyCuda<Type>))."""
         if src.kind == self.kind:
             return self.call("copy", self, src)
-        f = self.state.fn(self.kind, "copy" + KINDS[src.kind][0])
+        f = self.state.fn(self.kind, "copyCudaFloat" if src.kind == "Float" else "copy" + KINDS[src.kind][0])
         f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         f.restype = None
         f(self.state.ptr, self.ptr, src.ptr)

@@ -117,8 +117,9 @@ THC_API void THCTensor_(copyCudaShort)(THCState *state, THCTensor *dst, struct T
 THC_API void THCTensor_(copyCudaInt)(THCState *state, THCTensor *dst, struct THCudaIntTensor *src);
 THC_API void THCTensor_(copyCudaLong)(THCState *state, THCTensor *dst, struct THCudaLongTensor *src);
 THC_API void THCTensor_(copyCudaHalf)(THCState *state, THCTensor *dst, struct THCudaHalfTensor *src);
-THC_API void THCTensor_(copyCuda)(THCState *state, THCTensor *dst, struct THCudaTensor *src);
+THC_API void THCTensor_(copyCudaFloat)(THCState *state, THCTensor *dst, struct THCudaTensor *src);
 THC_API void THCTensor_(copyCudaDouble)(THCState *state, THCTensor *dst, struct THCudaDoubleTensor *src);
+THC_API void THCTensor_(copyCuda)(THCState *state, THCTensor *self, THCTensor *src);
 
 /* ---- pointwise math (lib/THC/generic/THCTensorMathPointwise.h) ---- */
 #if THC_T_FLOATING
@@ -188,6 +189,28 @@ THC_API void THCTensor_(bitand)(THCState *state, THCTensor *self, THCTensor *src
 THC_API void THCTensor_(bitor)(THCState *state, THCTensor *self, THCTensor *src, real value);
 THC_API void THCTensor_(bitxor)(THCState *state, THCTensor *self, THCTensor *src, real value);
 THC_API int THCTensor_(equal)(THCState *state, THCTensor *self, THCTensor *src);
+
+/* ---- comparisons (lib/THC/generic/THCTensorMathCompare.h:5-18, THCTensorMathCompareT.h:5-18):
+ * <op>Value / <op>Tensor write 0/1 into a ByteTensor resized to src's shape, the ...T forms
+ * into a tensor of the operands' own type ---- */
+#define THC_B200_DECLARE_COMPARE(NAME)                                                                                          \
+  THC_API void THCTensor_(TH_CONCAT_2(NAME, Value))(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value); \
+  THC_API void THCTensor_(TH_CONCAT_2(NAME, ValueT))(THCState *state, THCTensor *self_, THCTensor *src, real value);            \
+  THC_API void THCTensor_(TH_CONCAT_2(NAME, Tensor))(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2); \
+  THC_API void THCTensor_(TH_CONCAT_2(NAME, TensorT))(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_B200_DECLARE_COMPARE(lt)
+THC_B200_DECLARE_COMPARE(gt)
+THC_B200_DECLARE_COMPARE(le)
+THC_B200_DECLARE_COMPARE(ge)
+THC_B200_DECLARE_COMPARE(eq)
+THC_B200_DECLARE_COMPARE(ne)
+#undef THC_B200_DECLARE_COMPARE
+
+/* ---- Byte masks (lib/THC/generic/THCTensorMasked.h:5-36; the variants that take a host
+ * THByteTensor mask need torch7's TH and are not provided) ---- */
+THC_API void THCTensor_(maskedFill)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, real value);
+THC_API void THCTensor_(maskedCopy)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, THCTensor *src);
+THC_API void THCTensor_(maskedSelect)(THCState *state, THCTensor *tensor, THCTensor *src, struct THCudaByteTensor *mask);
 
 /* ---- reductions (lib/THC/generic/THCTensorMathReduce.h) ---- */
 #if THC_T_FLOATING

@@ -251,6 +251,48 @@ THCB200_API int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_s
 THCB200_API int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
                             const thcb200_tensor *in, void *result_host, void *stream);
 
+/* ---- operands of two element types: comparisons into Byte, Byte masks ------------------ */
+
+/* out[i] = (a[i] CMP b[i]) ? 1 : 0 with `out` a U8 view; `cmp` is one of THCB200_OP_LT..NE.
+ * With b == NULL the right-hand side is the scalar `s` (THCB200_OP_LT_S..NE_S are accepted
+ * too).  Equal element counts, each operand walked in its own row-major order.
+ * THC_logicalValue / THC_logicalTensor with a ByteTensor result:
+ * lib/THC/THCTensorMathCompare.cuh:5-85, THCTensorMathCompareT.cuh:5-72,
+ * generic/THCTensorMathCompare.cu:5-99 (ltValue ...), generic/THCTensorMathCompareT.cu:5-111. */
+THCB200_API int thcb200_compare(thcb200_ctx *ctx, int cmp, const thcb200_tensor *out_u8,
+                    const thcb200_tensor *a, const thcb200_tensor *b, thcb200_scalar s,
+                    void *stream);
+
+/* t[i] = value where mask[i] != 0 (mask: U8, same element count).
+ * lib/THC/generic/THCTensorMasked.cu:5-19, THCTensorMasked.cuh:16-26. */
+THCB200_API int thcb200_masked_fill(thcb200_ctx *ctx, const thcb200_tensor *t,
+                        const thcb200_tensor *mask_u8, thcb200_scalar value, void *stream);
+
+/* Number of non-zero mask elements, written as int64 to *count_host after a stream
+ * synchronize (the count the reference takes with sumall before maskedCopy / maskedSelect,
+ * lib/THC/generic/THCTensorMasked.cu:52,128).  The per-tile positions computed on the way stay
+ * in the context; a following masked_copy / masked_select on the same mask view and stream may
+ * reuse them by passing THCB200_FLAG_MASK_COUNTED, which asserts that the mask's contents have
+ * not changed in between. */
+#define THCB200_FLAG_MASK_COUNTED 2
+THCB200_API int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8,
+                         int64_t *count_host, void *stream);
+
+/* t[i] = src[k] where mask[i] != 0, k = number of non-zero mask elements before logical
+ * position i; src is walked in its own row-major order and must hold at least that many
+ * elements (checked by the caller through thcb200_masked_count).
+ * lib/THC/generic/THCTensorMasked.cu:35-104, THCTensorMasked.cuh:28-42. */
+THCB200_API int thcb200_masked_copy(thcb200_ctx *ctx, const thcb200_tensor *t,
+                        const thcb200_tensor *mask_u8, const thcb200_tensor *src, void *stream,
+                        int flags);
+
+/* out[k] = src[i] for every i with mask[i] != 0, in logical order; `out` is walked in its own
+ * row-major order and must hold at least thcb200_masked_count elements.
+ * lib/THC/generic/THCTensorMasked.cu:119-177, THCTensorMasked.cuh:44-56. */
+THCB200_API int thcb200_masked_select(thcb200_ctx *ctx, const thcb200_tensor *out,
+                          const thcb200_tensor *src, const thcb200_tensor *mask_u8, void *stream,
+                          int flags);
+
 #ifdef __cplusplus
 }
 #endif

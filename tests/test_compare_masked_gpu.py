@@ -1,0 +1,168 @@
+"""Comparisons into ByteTensors and Byte-masked fill / copy / select through the THC C API,
+against the numpy restatement in oracle/mixed_oracle.py.  Bit-exact: every result is a copy of
+an input element, a 0/1 byte, or the fill value.
+
+cutorch's own tests of these calls: test/test.lua:1768-1800 (logical ops on every layout),
+:2168-2330 (maskedSelect / maskedCopy / maskedFill, contiguous and transposed operands)."""
+import numpy as np
+import pytest
+
+from cutorch_b200 import thc
+from oracle import mixed_oracle as mo
+from common import ALL_KINDS, LAYOUTS, NP_OF_KIND, assert_bit_equal, make_view, rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+CMPS = ["lt", "gt", "le", "ge", "eq", "ne"]
+
+
+def small_ints(r, kind, shape, layout):
+    """Values from a small set so that equal elements are common."""
+    x = make_view(r, kind, shape, layout)
+    x[...] = r.integers(0, 5, size=shape).astype(x.dtype)
+    return x
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+@pytest.mark.parametrize("cmp", CMPS)
+def test_compare_value_to_byte(state, kind, cmp):
+    r = rng("cmpv", kind, cmp)
+    for shape, layout in [((10007,), "contiguous"), ((65, 33), "transposed"), ((7, 9, 10), "strided"), ((4099,), "offset")]:
+        x = small_ints(r, kind, shape, layout)
+        dx = to_device(state, x)
+        out = thc.Tensor.new(state, "Byte")
+        dx.call(cmp + "Value", out, dx, 2)
+        assert out.sizes == list(shape)
+        assert_bit_equal(out.numpy(), mo.compare(cmp, x, 2), f"{kind} {cmp}Value {layout}")
+        # same comparison into a tensor of the operand's type
+        outT = thc.Tensor.new(state, kind)
+        dx.call(cmp + "ValueT", outT, dx, 2)
+        assert_bit_equal(outT.numpy(), mo.compare(cmp, x, 2).astype(x.dtype), f"{kind} {cmp}ValueT {layout}")
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+@pytest.mark.parametrize("cmp", CMPS)
+def test_compare_tensor_to_byte(state, kind, cmp):
+    r = rng("cmpt", kind, cmp)
+    cases = [((20011,), "contiguous", "contiguous"), ((40, 50), "contiguous", "transposed"),
+             ((6, 5, 12), "permuted", "holes"), ((33, 17), "strided", "offset")]
+    for shape, la, lb in cases:
+        a, b = small_ints(r, kind, shape, la), small_ints(r, kind, shape, lb)
+        da, db = to_device(state, a), to_device(state, b)
+        out = thc.Tensor.new(state, "Byte")
+        da.call(cmp + "Tensor", out, da, db)
+        assert_bit_equal(out.numpy(), mo.compare(cmp, a, b), f"{kind} {cmp}Tensor {la}/{lb}")
+        outT = thc.Tensor.new(state, kind)
+        da.call(cmp + "TensorT", outT, da, db)
+        assert_bit_equal(outT.numpy(), mo.compare(cmp, a, b).astype(a.dtype), f"{kind} {cmp}TensorT {la}/{lb}")
+
+
+def test_compare_nan_and_half(state):
+    x = np.array([0.0, np.nan, 1.0, -np.inf, np.inf, 65504.0, -0.0], dtype=np.float16)
+    y = np.array([np.nan, np.nan, 1.0, -np.inf, 1.0, 65504.0, 0.0], dtype=np.float16)
+    for kind in ["Half", "Float", "Double"]:
+        a, b = x.astype(NP_OF_KIND[kind]), y.astype(NP_OF_KIND[kind])
+        da, db = to_device(state, a), to_device(state, b)
+        for cmp in CMPS:
+            out = thc.Tensor.new(state, "Byte")
+            da.call(cmp + "Tensor", out, da, db)
+            assert_bit_equal(out.numpy(), mo.compare(cmp, a, b), f"{kind} {cmp} NaN")
+
+
+def test_compare_into_strided_byte_output_and_different_shapes(state):
+    r = rng("cmp-shapes")
+    a = small_ints(r, "Float", (12, 10), "contiguous")
+    b = small_ints(r, "Float", (120,), "contiguous")   # same element count, other shape
+    da, db = to_device(state, a), to_device(state, b)
+    out = thc.Tensor.new(state, "Byte")
+    da.call("geTensor", out, da, db)
+    assert out.sizes == [12, 10]
+    assert_bit_equal(out.numpy(), mo.compare("ge", a, b), "different shapes")
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        da.call("geTensor", out, da, to_device(state, np.zeros(7, np.float32)))
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_masked_fill(state, kind):
+    r = rng("mfill", kind)
+    cases = [((10007,), "contiguous", "contiguous"), ((64, 48), "transposed", "contiguous"),
+             ((64, 48), "contiguous", "transposed"), ((5, 6, 7), "strided", "holes"), ((4100,), "offset", "offset")]
+    for shape, lt, lm in cases:
+        t = make_view(r, kind, shape, lt)
+        mask = make_view(r, "Byte", shape, lm)
+        mask[...] = r.integers(0, 2, size=shape).astype(np.uint8)
+        dt_, dm = to_device(state, t), to_device(state, mask)
+        dt_.maskedFill(dm, 3)
+        assert_bit_equal(dt_.numpy(), mo.masked_fill(t, mask, 3), f"{kind} maskedFill {lt}/{lm}")
+    # all set, none set, and mask bytes other than 1 count as set
+    for fill in (0, 1, 7):
+        t = make_view(r, kind, (3000,), "contiguous")
+        mask = np.full((3000,), fill, np.uint8)
+        dt_ = to_device(state, t)
+        dt_.maskedFill(to_device(state, mask), 1)
+        assert_bit_equal(dt_.numpy(), mo.masked_fill(t, mask, 1), f"{kind} maskedFill mask={fill}")
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_masked_select_and_copy(state, kind):
+    r = rng("msel", kind)
+    cases = [((10007,), "contiguous", "contiguous", 0.5), ((64, 130), "transposed", "contiguous", 0.1),
+             ((70, 66), "contiguous", "transposed", 0.9), ((5, 6, 7), "strided", "holes", 0.5),
+             ((9000,), "offset", "offset", 0.02), ((4096 * 3 + 5,), "contiguous", "contiguous", 1.0)]
+    for shape, ls, lm, density in cases:
+        src = make_view(r, kind, shape, ls)
+        mask = make_view(r, "Byte", shape, lm)
+        mask[...] = (r.uniform(size=shape) < density).astype(np.uint8)
+        dsrc, dm = to_device(state, src), to_device(state, mask)
+        out = thc.Tensor.new(state, kind)
+        out.maskedSelect(dsrc, dm)
+        want = mo.masked_select(src, mask)
+        assert out.sizes == [want.size]
+        assert_bit_equal(out.numpy(), want, f"{kind} maskedSelect {ls}/{lm}")
+        # maskedCopy: the selected positions of t receive consecutive elements of a (strided) source
+        t = make_view(r, kind, shape, ls)
+        packed = make_view(r, kind, (int(mask.sum()) + 3,), "strided")
+        dt_, dp = to_device(state, t), to_device(state, packed)
+        dt_.maskedCopy(dm, dp)
+        assert_bit_equal(dt_.numpy(), mo.masked_copy(t, mask, packed), f"{kind} maskedCopy {ls}/{lm}")
+
+
+def test_masked_edge_cases(state):
+    r = rng("medge")
+    src = make_view(r, "Float", (1000,), "contiguous")
+    dsrc = to_device(state, src)
+    zero = to_device(state, np.zeros(1000, np.uint8))
+    out = thc.Tensor.new(state, "Float")
+    out.maskedSelect(dsrc, zero)
+    assert out.nelement == 0
+    # maskedCopy with too few source elements is an argument error
+    ones = to_device(state, np.ones(1000, np.uint8))
+    with pytest.raises(thc.THCError, match="source nElements"):
+        dsrc.maskedCopy(ones, to_device(state, np.zeros(999, np.float32)))
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        out.maskedSelect(dsrc, to_device(state, np.ones(999, np.uint8)))
+    with pytest.raises(thc.THCError, match="same number of elements"):
+        dsrc.maskedCopy(to_device(state, np.ones(10, np.uint8)), dsrc)
+    # two selects in a row on different masks must not reuse each other's positions
+    m1 = (r.uniform(size=1000) < 0.3).astype(np.uint8)
+    m2 = (r.uniform(size=1000) < 0.7).astype(np.uint8)
+    for m in (m1, m2, m1):
+        out.maskedSelect(dsrc, to_device(state, m))
+        assert_bit_equal(out.numpy(), mo.masked_select(src, m), "alternating masks")
+
+
+def test_masked_select_large(state):
+    """2^26 elements: many tiles, the scan of tile counts runs over 16384 entries."""
+    r = rng("mlarge")
+    n = 1 << 26
+    src = r.standard_normal(n).astype(np.float32)
+    mask = (src > 0.25).astype(np.uint8)
+    dsrc, dm = to_device(state, src), to_device(state, mask)
+    out = thc.Tensor.new(state, "Float")
+    out.maskedSelect(dsrc, dm)
+    assert_bit_equal(out.numpy(), mo.masked_select(src, mask), "large maskedSelect")
+    bytes_out = thc.Tensor.new(state, "Byte")
+    dsrc.call("gtValue", bytes_out, dsrc, 0.25)
+    assert_bit_equal(bytes_out.numpy(), mask, "large gtValue")
+    dsrc.maskedFill(dm, 0.0)
+    assert_bit_equal(dsrc.numpy(), mo.masked_fill(src, mask, 0.0), "large maskedFill")
