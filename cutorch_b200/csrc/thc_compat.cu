@@ -755,6 +755,16 @@ template <typename R> typename RealTraits<R>::acc reduce_all_acc(THCState *state
   return (A)reduce_all_i<R>(state, rop, pre, s, self);
 }
 
+// self = inclusive scan of src along `dimension` (THCTensor_(scanDim),
+// lib/THC/generic/THCTensorMathScan.cu:76-104)
+template <typename R> void scan_dim(THCState *state, int rop, TensorT<R> *self, TensorT<R> *src, long dimension) {
+  check_gpu<R>(state, {self, src});
+  THArgCheck(dimension >= 0 && dimension < src->nDimension, 3, "dimension %d out of range", (int)dimension + TH_INDEX_BASE);
+  if (self != src) tensor_resize_as<R>(state, self, src);
+  thcb200_tensor dout = describe<R>(self), din = describe<R>(src);
+  check_core(thcb200_scan_dim(state_ctx(state), rop, &dout, &din, (int)dimension, (void *)state_stream(state)));
+}
+
 // ---- comparisons into a ByteTensor, Byte masks -----------------------------------------
 using ByteT = TensorT<unsigned char>;
 

@@ -206,6 +206,10 @@ THC_B200_DECLARE_COMPARE(eq)
 THC_B200_DECLARE_COMPARE(ne)
 #undef THC_B200_DECLARE_COMPARE
 
+/* ---- scans (lib/THC/generic/THCTensorMathScan.h:5-6) ---- */
+THC_API void THCTensor_(cumsum)(THCState *state, THCTensor *self, THCTensor *src, long dim);
+THC_API void THCTensor_(cumprod)(THCState *state, THCTensor *self, THCTensor *src, long dim);
+
 /* ---- Byte masks (lib/THC/generic/THCTensorMasked.h:5-36; the variants that take a host
  * THByteTensor mask need torch7's TH and are not provided) ---- */
 THC_API void THCTensor_(maskedFill)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, real value);

@@ -251,6 +251,15 @@ THCB200_API int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_s
 THCB200_API int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s,
                             const thcb200_tensor *in, void *result_host, void *stream);
 
+/* Inclusive scan along `dim`: out[.., k, ..] = in[.., 0, ..] (+|*) ... (+|*) in[.., k, ..]
+ * with rop = THCB200_RED_SUM (cumsum) or THCB200_RED_PROD (cumprod).  `out` has in's shape and
+ * dtype (any strides; out == in scans in place).  The running value is kept in the accumulate
+ * type of the reductions and rounded to the element type for every output.
+ * THCTensor_(scanDim): lib/THC/generic/THCTensorMathScan.cu:76-118, kernels
+ * lib/THC/THCTensorMathScan.cu:24-126. */
+THCB200_API int thcb200_scan_dim(thcb200_ctx *ctx, int rop, const thcb200_tensor *out,
+                     const thcb200_tensor *in, int dim, void *stream);
+
 /* ---- operands of two element types: comparisons into Byte, Byte masks ------------------ */
 
 /* out[i] = (a[i] CMP b[i]) ? 1 : 0 with `out` a U8 view; `cmp` is one of THCB200_OP_LT..NE.

@@ -110,6 +110,13 @@ class Oracle:
         assert self.lib.oracle_var_dim(C.byref(od), C.byref(sd), dim, int(biased), int(take_sqrt)) == 0
         return out
 
+    def scan_dim(self, prod: bool, src: np.ndarray, dim: int) -> np.ndarray:
+        """cumsum (prod=False) / cumprod (prod=True) of src along dim, as a dense array."""
+        out = np.zeros(src.shape, dtype=src.dtype)
+        od, sd = _desc(out), _desc(src)
+        assert self.lib.oracle_scan_dim(int(prod), C.byref(od), C.byref(sd), dim) == 0
+        return out
+
     def reduce_all(self, rop: int, pre: int, s: float, src: np.ndarray):
         """Returns a float for floating element types (the double accumulator) and an int otherwise."""
         f, i = C.c_double(0), C.c_int64(0)

@@ -426,6 +426,38 @@ void var_dim_t(const oracle_tensor &out, const oracle_tensor &in, int dim, int b
   }
 }
 
+// cumsum / cumprod along a dim: one running accumulator per slice, every output rounded from it
+// (the sequential form of THCTensor_kernel_scanOuterDim, lib/THC/THCTensorMathScan.cu:24-45, with
+// TH's accumulate type).  Integer accumulation wraps modulo 2^64.
+template <typename T>
+void scan_dim_t(int prod, const oracle_tensor &out, const oracle_tensor &in, int dim) {
+  using A = typename AccOf<T>::type;
+  oracle_tensor inb = in, outb = out;
+  inb.sizes[dim] = 1;
+  outb.sizes[dim] = 1;
+  const int64_t nslices = numel(inb);
+  const int64_t K = in.sizes[dim], ski = in.strides[dim], sko = out.strides[dim];
+  Walker wi, wo;
+  wi.init(inb, 0);
+  wo.init(outb, 0);
+  for (int64_t o = 0; o < nslices; ++o) {
+    const T *p = (const T *)in.data + wi.off;
+    T *q = (T *)out.data + wo.off;
+    RunResult<T> r; r.f = prod ? 1.0 : 0.0; r.i = prod ? 1 : 0; r.pos = 0;
+    for (int64_t k = 0; k < K; ++k) {
+      if constexpr (Info<T>::fp) {
+        const A z = (A)(typename Info<T>::M)p[k * ski];
+        r.f = prod ? r.f * z : r.f + z;
+      } else {
+        const uint64_t z = (uint64_t)(int64_t)p[k * ski];
+        r.i = (int64_t)(prod ? (uint64_t)r.i * z : (uint64_t)r.i + z);
+      }
+      q[k * sko] = from_result<T>(r);
+    }
+    wi.next(); wo.next();
+  }
+}
+
 template <typename T>
 void reduce_all_t(int rop, int pre, double s, const oracle_tensor &in, double *rf, int64_t *ri) {
   using A = typename AccOf<T>::type;
@@ -588,6 +620,20 @@ int oracle_var_dim(const oracle_tensor *out, const oracle_tensor *in, int dim, i
     case 5: var_dim_t<f16>(*out, *in, dim, biased, take_sqrt); return 0;
     case 6: var_dim_t<float>(*out, *in, dim, biased, take_sqrt); return 0;
     case 7: var_dim_t<double>(*out, *in, dim, biased, take_sqrt); return 0;
+  }
+  return -1;
+}
+
+int oracle_scan_dim(int prod, const oracle_tensor *out, const oracle_tensor *in, int dim) {
+  switch (in->dtype) {
+    case 0: scan_dim_t<uint8_t>(prod, *out, *in, dim); return 0;
+    case 1: scan_dim_t<int8_t>(prod, *out, *in, dim); return 0;
+    case 2: scan_dim_t<int16_t>(prod, *out, *in, dim); return 0;
+    case 3: scan_dim_t<int32_t>(prod, *out, *in, dim); return 0;
+    case 4: scan_dim_t<int64_t>(prod, *out, *in, dim); return 0;
+    case 5: scan_dim_t<f16>(prod, *out, *in, dim); return 0;
+    case 6: scan_dim_t<float>(prod, *out, *in, dim); return 0;
+    case 7: scan_dim_t<double>(prod, *out, *in, dim); return 0;
   }
   return -1;
 }
