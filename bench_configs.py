@@ -12,13 +12,15 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
 
     def W(t, kind):
-        return thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+        w = thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+        w._owner = t   # the wrapper holds a raw pointer: keep the torch tensor alive with it
+        return w
 
     clean = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     res_flush = torch.zeros(1, dtype=torch.int64, device=dev)
     tclean = W(clean, "Byte")
 
-    def timed(fn, nbytes, reps=10):
+    def timed(fn, nbytes, reps=10, rot=None):
         reps = reps_override or reps
         ts = []
         for _ in range(3):
@@ -37,9 +39,30 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         ts.sort()
         med = ts[len(ts) // 2]
         gbs = nbytes / (med * 1e-3) / 1e9
-        return {"gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "frac_of_nominal_8000": round(gbs / 8000.0, 4),
-                "median_us": round(med * 1e3, 2), "best_us": round(ts[0] * 1e3, 2), "bytes": nbytes}
+        r = {"gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "frac_of_nominal_8000": round(gbs / 8000.0, 4),
+             "median_us": round(med * 1e3, 2), "best_us": round(ts[0] * 1e3, 2), "bytes": nbytes}
+        if rot:
+            # The same call back to back over rotating buffer sets (together larger than 4x the L2, so
+            # every read comes from HBM), one event pair around the whole train: per-call time without
+            # the cost of an event pair and an idle GPU around each launch.
+            for f in rot:
+                f()
+            rounds = 6
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record(stream)
+            for _ in range(rounds):
+                for f in rot:
+                    f()
+            b.record(stream)
+            torch.cuda.synchronize()
+            per = a.elapsed_time(b) / (rounds * len(rot))
+            rg = nbytes / (per * 1e-3) / 1e9
+            r.update({"back_to_back_gbs": round(rg, 1), "back_to_back_frac": round(rg / peak, 4),
+                      "back_to_back_us": round(per * 1e3, 2), "buffer_sets": len(rot)})
+        return r
 
+    keep = []   # buffer sets of the back-to-back timings, dropped when their config is done
     g = torch.Generator(device=dev)
     g.manual_seed(7)
     res = torch.zeros(1, dtype=torch.float64, device=dev)
@@ -51,8 +74,12 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         y = torch.empty(n, device=dev).uniform_(-1, 1, generator=g)
         z = torch.empty(n, device=dev)
         tx, ty, tz = W(x, "Float"), W(y, "Float"), W(z, "Float")
-        out["c1_cadd_f32_16M"] = timed(lambda: tz.cadd(tx, 2.5, ty), 12 * n)
-        out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n)
+        sets = [(W(x.clone(), "Float"), W(y.clone(), "Float"), W(torch.empty_like(z), "Float")) for _ in range(8)]
+        keep.append(sets)
+        out["c1_cadd_f32_16M"] = timed(lambda: tz.cadd(tx, 2.5, ty), 12 * n,
+                                       rot=[(lambda s=s: s[2].cadd(s[0], 2.5, s[1])) for s in sets[:4]])
+        out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n,
+                                         rot=[(lambda s=s: s[0].sumall_to_device(res.data_ptr())) for s in sets])
 
     def c2():
         shape = (64, 256, 56, 56)
@@ -85,10 +112,15 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         rh = torch.empty(1, 8192, dtype=torch.float16, device=dev)
         th, th2, trh = W(h, "Half"), W(h2, "Half"), W(rh, "Half")
         n = h.numel()
-        out["c4_sigmoid_f16"] = timed(lambda: th2.sigmoid(th), 4 * n)
-        out["c4_mean_dim0_f16"] = timed(lambda: trh.mean(th2, 0, 1), 2 * n + 2 * 8192)
-        out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192)
-        del h, h2
+        hs = [(W(h.clone(), "Half"), W(torch.empty_like(h), "Half")) for _ in range(4)]
+        keep.append(hs)
+        out["c4_sigmoid_f16"] = timed(lambda: th2.sigmoid(th), 4 * n, rot=[(lambda s=s: s[1].sigmoid(s[0])) for s in hs])
+        out["c4_mean_dim0_f16"] = timed(lambda: trh.mean(th2, 0, 1), 2 * n + 2 * 8192,
+                                        rot=[(lambda s=s: trh.mean(s[0], 0, 1)) for s in hs])
+        out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192,
+                                         rot=[(lambda s=s: trh.norm(s[0], 2, 0, 1)) for s in hs])
+        keep.clear()
+        del h, h2, hs
         n = 134217728
         a = torch.randint(-2**20, 2**20 + 1, (n,), dtype=torch.int32, device=dev, generator=g)
         b = torch.randint(-7, 8, (n,), dtype=torch.int32, device=dev, generator=g)

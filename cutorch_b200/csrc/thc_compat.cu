@@ -765,6 +765,83 @@ template <typename R> void scan_dim(THCState *state, int rop, TensorT<R> *self, 
   check_core(thcb200_scan_dim(state_ctx(state), rop, &dout, &din, (int)dimension, (void *)state_stream(state)));
 }
 
+// self = lower / upper triangle of the matrix src (lib/THC/generic/THCTensorMathPairwise.cu:169-233)
+template <typename R> void tri(THCState *state, int upper, TensorT<R> *self, TensorT<R> *src, long k) {
+  check_gpu<R>(state, {self, src});
+  THArgCheck(src->nDimension == 2, 1, "expected a matrix");
+  if (self != src) tensor_resize_as<R>(state, self, src);
+  thcb200_tensor dout = describe<R>(self), din = describe<R>(src);
+  check_core(thcb200_tri(state_ctx(state), upper, (int64_t)k, &dout, &din, (void *)state_stream(state)));
+}
+
+// renorm: every slice src.select(dimension, j) whose p-norm exceeds maxnorm is scaled to norm
+// maxnorm (lib/THC/generic/THCTensorMathReduce.cu:47-74).  Composed from the dimension
+// reductions (sums of |x|^p over every other dim), the factor step and a broadcast multiply;
+// no transposed clone of the tensor is made.
+template <typename R>
+void renorm(THCState *state, TensorT<R> *self, TensorT<R> *src, R value, long dimension, R maxnorm) {
+  check_gpu<R>(state, {self, src});
+  THArgCheck(dimension >= 0 && dimension < src->nDimension, 3, "invalid dimension");
+  THArgCheck(real_to_double<R>(value) > 0, 2, "non-positive-norm not supported");
+  THArgCheck(src->nDimension > 1, 1, "need at least 2 dimensions");
+  const double p = real_to_double<R>(value);
+  thcb200_ctx *ctx = state_ctx(state);
+  void *st = (void *)state_stream(state);
+  // sums of |x|^p over every dim but `dimension`, one dim at a time from the innermost outward
+  TensorT<R> *cur = src;
+  bool first = true;
+  for (int d = src->nDimension - 1; d >= 0; --d) {
+    if (d == dimension) continue;
+    TensorT<R> *next = tensor_alloc<R>();
+    resize_reduced<R>(state, next, cur->size, cur->nDimension, d);
+    const int pre = !first ? THCB200_PRE_IDENTITY : (p == 1.0 ? THCB200_PRE_ABS : (p == 2.0 ? THCB200_PRE_SQUARE : THCB200_PRE_POWABS));
+    thcb200_tensor dout = describe<R>(next), din = describe<R>(cur);
+    thcb200_scalar s = {p, 0};
+    const int rc = thcb200_reduce_dim(ctx, THCB200_RED_SUM, pre, s, &dout, &din, d, st);
+    if (cur != src) tensor_free<R>(state, cur);
+    cur = next;
+    first = false;
+    if (rc) { tensor_free<R>(state, cur); check_core(rc); }
+  }
+  // cur: all sizes 1 except `dimension`
+  thcb200_tensor dsum = describe<R>(cur);
+  int rc = thcb200_renorm_factor(ctx, &dsum, &dsum, p, real_to_double<R>(maxnorm), st);
+  if (rc == 0) {
+    // the factors seen through src's shape: stride 0 along every other dim
+    long strides[THCB200_MAX_DIMS];
+    for (int d = 0; d < src->nDimension; ++d) strides[d] = d == dimension ? cur->stride[d] : 0;
+    TensorT<R> *wide = tensor_alloc<R>();
+    tensor_raw_set<R>(state, wide, cur->storage, cur->storageOffset, src->nDimension, src->size, strides);
+    if (self != src) tensor_resize_as<R>(state, self, src);
+    thcb200_tensor dout = describe<R>(self), din = describe<R>(src), dw = describe<R>(wide);
+    rc = thcb200_pointwise(ctx, THCB200_OP_MUL, &dout, &din, &dw, nullptr, 2, kZero, kZero, st);
+    tensor_free<R>(state, wide);
+  }
+  tensor_free<R>(state, cur);
+  check_core(rc);
+}
+
+// Half tensors renorm as float tensors and round once at the end (the half parity target is
+// FloatTensor math on the half values); sums of |x|^p would overflow half anyway.
+template <>
+void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half value, long dimension, half maxnorm) {
+  check_gpu<half>(state, {self, src});
+  THArgCheck(dimension >= 0 && dimension < src->nDimension, 3, "invalid dimension");
+  THArgCheck(src->nDimension > 1, 1, "need at least 2 dimensions");
+  TensorT<float> *wide = tensor_alloc<float>();
+  tensor_raw_resize<float>(state, wide, src->nDimension, src->size, nullptr);
+  try {
+    tensor_copy_convert<float, half>(state, wide, src);
+    renorm<float>(state, wide, wide, THC_half2float(value), dimension, THC_half2float(maxnorm));
+    if (self != src) tensor_resize_as<half>(state, self, src);
+    tensor_copy_convert<half, float>(state, self, wide);
+  } catch (...) {
+    tensor_free<float>(state, wide);
+    throw;
+  }
+  tensor_free<float>(state, wide);
+}
+
 // ---- comparisons into a ByteTensor, Byte masks -----------------------------------------
 using ByteT = TensorT<unsigned char>;
 

@@ -62,6 +62,7 @@ SIGNATURES.update({
     "normall": ("a", "Tr"), "varall": ("a", "Ti"), "stdall": ("a", "Ti"),
     "fill": ("v", "Tr"), "zero": ("v", "T"), "copy": ("v", "TT"), "copyIgnoringOverlaps": ("v", "TT"),
     "resizeAs": ("v", "TT"),
+    "tril": ("v", "TTl"), "triu": ("v", "TTl"), "renorm": ("v", "TTrlr"),
     "cumsum": ("v", "TTl"), "cumprod": ("v", "TTl"),
     "maskedFill": ("v", "TBr"), "maskedCopy": ("v", "TBT"), "maskedSelect": ("v", "TTB"),
 })

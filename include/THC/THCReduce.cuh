@@ -1,0 +1,230 @@
+/*
+ * THCReduce.cuh -- C++ template forms of the dimension reduction and the full reduction for
+ * user-defined functors, with the contracts of cutorch's installed templates:
+ *
+ *   template <typename TensorType, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+ *   bool THC_reduceDim(THCState*, TensorType* out, TensorType* in, const ModifyOp&, const ReduceOp&,
+ *                      const ReduceAccOp&, AccT init, int dim, int keepdim);        (lib/THC/THCReduce.cuh:258-271)
+ *   bool THC_reduceAll(THCState*, TensorType* in, const ModifyOp&, const ReduceOp&, const ReduceAccOp&,
+ *                      AccT init, AccT* out, int outOnDevice);                      (lib/THC/THCReduceAll.cuh:234-246)
+ *
+ * out[..., 0, ...] = (T) fold_i reduceOp(acc, modifyOp(in[..., i, ...])), acc starting at `init`;
+ * partial accumulators are merged with reduceAccOp.  `init` must be an identity of the fold: as in
+ * the reference every thread starts from it.  THC_reduceDim resizes `out` to in's sizes with
+ * size[dim] = 1 and squeezes that dim unless keepdim (lib/THC/THCReduce.cuh:328-332, 449-451).
+ * THC_reduceAll writes *out on the host after a synchronous copy, or on the device when
+ * outOnDevice (lib/THC/THCReduceAll.cuh:259-270, 333-335); a tensor without dimensions yields init.
+ * Both return false for more than 25 dims.
+ *
+ * The built-in reductions (sum, prod, min, max, norm ...) do not come through here: they use the
+ * vectorised kernels behind the C API.  These templates serve arbitrary functors and arbitrary
+ * trivially-copyable accumulator types, combining partials through shared memory in a fixed order.
+ *
+ * Include from a .cu file compiled for sm_100a and link libthcb200.
+ */
+#ifndef THCB200_THC_REDUCE_CUH
+#define THCB200_THC_REDUCE_CUH
+
+#include "THCApply.cuh"
+
+namespace thcb_user {
+
+constexpr int kReduceThreads = 256;
+
+// slice number -> element offsets of the input and the output (dims other than the reduced one)
+struct SliceView {
+  int n;
+  uint64_t size[THCB200_MAX_DIMS];
+  int64_t in_stride[THCB200_MAX_DIMS];
+  int64_t out_stride[THCB200_MAX_DIMS];
+  __device__ __forceinline__ void decode(uint64_t lin, int64_t &in_off, int64_t &out_off) const {
+    in_off = 0;
+    out_off = 0;
+    for (int d = n - 1; d >= 0; --d) {
+      const uint64_t q = lin / size[d], r = lin - q * size[d];
+      in_off += (int64_t)r * in_stride[d];
+      out_off += (int64_t)r * out_stride[d];
+      lin = q;
+    }
+  }
+};
+
+// Folds the accumulators of a CTA in thread order (0 with 1, then with 2 ... as a binary tree over
+// thread numbers), result in thread 0.  `buf` holds blockDim.x accumulators.
+template <typename AccT, typename ReduceAccOp>
+__device__ __forceinline__ AccT block_fold(AccT acc, AccT *buf, const ReduceAccOp &accOp) {
+  buf[threadIdx.x] = acc;
+  __syncthreads();
+  for (unsigned s = 1; s < blockDim.x; s <<= 1) {
+    const unsigned i = threadIdx.x * 2 * s;
+    if (i + s < blockDim.x) buf[i] = accOp(buf[i], buf[i + s]);
+    __syncthreads();
+  }
+  return buf[0];
+}
+
+// one CTA per slice; threads stride over the reduced dim
+template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_dim_cta_kernel(T *out, const T *in, SliceView sv, uint64_t K, int64_t strideK, AccT init, ModifyOp modifyOp,
+                      ReduceOp reduceOp, ReduceAccOp accOp) {
+  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
+  int64_t in_off, out_off;
+  sv.decode(blockIdx.x, in_off, out_off);
+  const T *p = in + in_off;
+  AccT acc = init;
+  for (uint64_t k = threadIdx.x; k < K; k += blockDim.x) acc = reduceOp(acc, modifyOp(p[(int64_t)k * strideK]));
+  acc = block_fold(acc, buf, accOp);
+  if (threadIdx.x == 0) out[out_off] = (T)acc;
+}
+
+// one thread per slice; neighbouring threads take neighbouring slices
+template <typename T, typename ModifyOp, typename ReduceOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_dim_thread_kernel(T *out, const T *in, SliceView sv, uint64_t nslices, uint64_t K, int64_t strideK, AccT init,
+                         ModifyOp modifyOp, ReduceOp reduceOp) {
+  const uint64_t s = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x;
+  if (s >= nslices) return;
+  int64_t in_off, out_off;
+  sv.decode(s, in_off, out_off);
+  const T *p = in + in_off;
+  AccT acc = init;
+  for (uint64_t k = 0; k < K; ++k) acc = reduceOp(acc, modifyOp(p[(int64_t)k * strideK]));
+  out[out_off] = (T)acc;
+}
+
+// full reduction, pass 1: every CTA strides over the logical index space and leaves one partial
+template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_all_partial_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp,
+                          ReduceAccOp accOp, AccT *partials) {
+  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
+  AccT acc = init;
+  for (uint64_t i = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kReduceThreads)
+    acc = reduceOp(acc, modifyOp(in[v.offset(i)]));
+  acc = block_fold(acc, buf, accOp);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
+// pass 2: one CTA folds the partials in index order
+template <typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_all_final_kernel(const AccT *partials, unsigned count, AccT init, ReduceAccOp accOp, AccT *result) {
+  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
+  AccT acc = init;
+  for (unsigned i = threadIdx.x; i < count; i += blockDim.x) acc = accOp(acc, partials[i]);
+  acc = block_fold(acc, buf, accOp);
+  if (threadIdx.x == 0) *result = acc;
+}
+
+template <typename TensorType> struct TensorShape;
+#define THCB_USER_SHAPE(TENSOR)                                                                       \
+  template <> struct TensorShape<TENSOR> {                                                            \
+    static void resize(THCState *s, TENSOR *t, THLongStorage *size) { TENSOR##_resize(s, t, size, 0); } \
+    static void squeeze1d(THCState *s, TENSOR *t, int dim) { TENSOR##_squeeze1d(s, t, t, dim); }      \
+  };
+THCB_USER_SHAPE(THCudaByteTensor)
+THCB_USER_SHAPE(THCudaCharTensor)
+THCB_USER_SHAPE(THCudaShortTensor)
+THCB_USER_SHAPE(THCudaIntTensor)
+THCB_USER_SHAPE(THCudaLongTensor)
+THCB_USER_SHAPE(THCudaHalfTensor)
+THCB_USER_SHAPE(THCudaTensor)
+THCB_USER_SHAPE(THCudaDoubleTensor)
+#undef THCB_USER_SHAPE
+
+}  // namespace thcb_user
+
+template <typename TensorType, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+bool THC_reduceDim(THCState *state, TensorType *out, TensorType *in, const ModifyOp &modifyOp, const ReduceOp &reduceOp,
+                   const ReduceAccOp &reduceAccOp, AccT init, int dim, int keepdim) {
+  using namespace thcb_user;
+  typedef typename TensorAccess<TensorType>::DataType T;
+  if (in->nDimension > THCB200_MAX_DIMS || out->nDimension > THCB200_MAX_DIMS) return false;
+  if (in->nDimension == 0) return true;
+  if (dim < 0 || dim >= in->nDimension) return false;
+  // out takes in's sizes with the reduced dim set to 1
+  THLongStorage *sizes = THLongStorage_newWithSize(in->nDimension);
+  for (int d = 0; d < in->nDimension; ++d) THLongStorage_set(sizes, d, d == dim ? 1 : in->size[d]);
+  TensorShape<TensorType>::resize(state, out, sizes);
+  THLongStorage_free(sizes);
+
+  SliceView sv;
+  sv.n = 0;
+  uint64_t nslices = 1;
+  for (int d = 0; d < in->nDimension; ++d) {
+    if (d == dim || in->size[d] == 1) continue;
+    sv.size[sv.n] = (uint64_t)in->size[d];
+    sv.in_stride[sv.n] = in->stride[d];
+    sv.out_stride[sv.n] = out->stride[d];
+    nslices *= (uint64_t)in->size[d];
+    ++sv.n;
+  }
+  const uint64_t K = (uint64_t)in->size[dim];
+  const int64_t strideK = in->stride[dim];
+  thcb200_tensor din = describe(in), dout = describe(out);
+  cudaStream_t st = THCState_getCurrentStream(state);
+  bool ok = true;
+  if (nslices > 0 && K > 0) {
+    // lanes along the reduced dim when it is the dense one or when there are too few slices to
+    // fill the GPU with a thread each; otherwise a thread per slice
+    const bool cta_per_slice = strideK == 1 || nslices < 148ull * 8 * kReduceThreads / 32;
+    if (cta_per_slice && nslices < (1ull << 31)) {
+      int threads = 32;
+      while (threads < kReduceThreads && (uint64_t)threads * 4 < K) threads <<= 1;
+      const size_t smem = (size_t)threads * sizeof(AccT);
+      if (smem > 48 * 1024) ok = false;
+      else
+        reduce_dim_cta_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)nslices, threads, smem, st>>>(
+            (T *)dout.data, (const T *)din.data, sv, K, strideK, init, modifyOp, reduceOp, reduceAccOp);
+    } else {
+      const uint64_t blocks = (nslices + kReduceThreads - 1) / kReduceThreads;
+      if (blocks >= (1ull << 31)) ok = false;
+      else
+        reduce_dim_thread_kernel<T, ModifyOp, ReduceOp, AccT><<<(unsigned)blocks, kReduceThreads, 0, st>>>(
+            (T *)dout.data, (const T *)din.data, sv, nslices, K, strideK, init, modifyOp, reduceOp);
+    }
+  }
+  if (ok && !keepdim) TensorShape<TensorType>::squeeze1d(state, out, dim);
+  return ok;
+}
+
+template <typename TensorType, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+bool THC_reduceAll(THCState *state, TensorType *in, const ModifyOp &modifyOp, const ReduceOp &reduceOp,
+                   const ReduceAccOp &reduceAccOp, AccT init, AccT *out, int outOnDevice) {
+  using namespace thcb_user;
+  typedef typename TensorAccess<TensorType>::DataType T;
+  if (in->nDimension > THCB200_MAX_DIMS) return false;
+  cudaStream_t st = THCState_getCurrentStream(state);
+  thcb200_tensor din = describe(in);
+  const int64_t n = numel(din);
+  if (in->nDimension == 0 || n == 0) {
+    if (!outOnDevice) { *out = init; return true; }
+    return cudaMemcpyAsync(out, &init, sizeof(AccT), cudaMemcpyHostToDevice, st) == cudaSuccess &&
+           cudaStreamSynchronize(st) == cudaSuccess;   // `init` lives on this frame: finish before returning
+  }
+  if (sizeof(AccT) * kReduceThreads > 48 * 1024) return false;
+  uint64_t blocks = ((uint64_t)n + (uint64_t)kReduceThreads * 8 - 1) / ((uint64_t)kReduceThreads * 8);
+  const uint64_t cap = 148 * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  // scratch: `blocks` partials and, for a host result, one slot for the total
+  AccT *scratch = 0;
+  if (cudaMallocAsync((void **)&scratch, sizeof(AccT) * (blocks + 1), st) != cudaSuccess) { cudaGetLastError(); return false; }
+  AccT *result = outOnDevice ? out : scratch + blocks;
+  const size_t smem = sizeof(AccT) * kReduceThreads;
+  reduce_all_partial_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
+      (const T *)din.data, collapse<uint64_t>(din), (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
+  reduce_all_final_kernel<ReduceAccOp, AccT><<<1, kReduceThreads, smem, st>>>(scratch, (unsigned)blocks, init, reduceAccOp, result);
+  bool ok = cudaGetLastError() == cudaSuccess;
+  if (ok && !outOnDevice) ok = cudaMemcpyAsync(out, result, sizeof(AccT), cudaMemcpyDeviceToHost, st) == cudaSuccess;
+  // the scratch is released in stream order; only a host result waits for the stream
+  cudaFreeAsync(scratch, st);
+  if (!outOnDevice) ok = (cudaStreamSynchronize(st) == cudaSuccess) && ok;
+  return ok;
+}
+
+#endif /* THCB200_THC_REDUCE_CUH */

@@ -210,6 +210,10 @@ THC_B200_DECLARE_COMPARE(ne)
 THC_API void THCTensor_(cumsum)(THCState *state, THCTensor *self, THCTensor *src, long dim);
 THC_API void THCTensor_(cumprod)(THCState *state, THCTensor *self, THCTensor *src, long dim);
 
+/* ---- triangles of a matrix (lib/THC/generic/THCTensorMath.h: tril, triu) ---- */
+THC_API void THCTensor_(tril)(THCState *state, THCTensor *self, THCTensor *src, long k);
+THC_API void THCTensor_(triu)(THCState *state, THCTensor *self, THCTensor *src, long k);
+
 /* ---- Byte masks (lib/THC/generic/THCTensorMasked.h:5-36; the variants that take a host
  * THByteTensor mask need torch7's TH and are not provided) ---- */
 THC_API void THCTensor_(maskedFill)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, real value);
@@ -222,6 +226,7 @@ THC_API void THCTensor_(norm)(THCState *state, THCTensor *self, THCTensor *src, 
 THC_API void THCTensor_(std)(THCState *state, THCTensor *self, THCTensor *src, long dim, int biased, int keepdim);
 THC_API void THCTensor_(var)(THCState *state, THCTensor *self, THCTensor *src, long dim, int biased, int keepdim);
 THC_API accreal THCTensor_(dist)(THCState *state, THCTensor *self, THCTensor *src, real value);
+THC_API void THCTensor_(renorm)(THCState *state, THCTensor *self, THCTensor *src, real value, long dimension, real max_norm);
 THC_API accreal THCTensor_(normall)(THCState *state, THCTensor *self, real value);
 THC_API accreal THCTensor_(varall)(THCState *state, THCTensor *self, int biased);
 THC_API accreal THCTensor_(stdall)(THCState *state, THCTensor *self, int biased);

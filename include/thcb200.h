@@ -260,6 +260,19 @@ THCB200_API int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb
 THCB200_API int thcb200_scan_dim(thcb200_ctx *ctx, int rop, const thcb200_tensor *out,
                      const thcb200_tensor *in, int dim, void *stream);
 
+/* Lower (upper = 0: keep c - r <= k) or upper (upper = 1: keep c - r >= k) triangle of a 2-D
+ * view; the other elements of `out` become 0.  out == in works in place.
+ * lib/THC/generic/THCTensorMathPairwise.cu:169-233, TensorTriOp lib/THC/THCTensorMathPairwise.cu:373-406. */
+THCB200_API int thcb200_tri(thcb200_ctx *ctx, int upper, int64_t k, const thcb200_tensor *out,
+                const thcb200_tensor *in, void *stream);
+
+/* factors[i] = n > maxnorm ? maxnorm / (n + 1e-7) : 1 with n = sums[i] ** (1/p): the scalar step
+ * of renorm between the per-slice sums of |x|^p (thcb200_reduce_dim with THCB200_PRE_POWABS ...)
+ * and the broadcast multiply.  Dense F32 or F64 operands.
+ * lib/THC/THCTensorMathReduce.cuh:160-183 (THCTensor_kernel_renorm, clip step). */
+THCB200_API int thcb200_renorm_factor(thcb200_ctx *ctx, const thcb200_tensor *factors,
+                          const thcb200_tensor *sums, double p, double maxnorm, void *stream);
+
 /* ---- operands of two element types: comparisons into Byte, Byte masks ------------------ */
 
 /* out[i] = (a[i] CMP b[i]) ? 1 : 0 with `out` a U8 view; `cmp` is one of THCB200_OP_LT..NE.

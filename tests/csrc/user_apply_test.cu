@@ -1,7 +1,8 @@
-// Test helper: user-defined functors run through the C++ template face of the apply
-// (include/THC/THCApply.cuh), the way a downstream CUDA library such as cunn uses cutorch.
+// Test helper: user-defined functors run through the C++ template faces of the apply and the
+// reductions (include/THC/THCApply.cuh, include/THC/THCReduce.cuh), the way a downstream CUDA library such as cunn uses cutorch.
 // Built into cutorch_b200/lib/libthcb200_usertest.so and driven from tests/test_template_api_gpu.py.
 #include "THC/THCApply.cuh"
+#include "THC/THCReduce.cuh"
 
 // out = in * k + 1
 struct ScaleAddOne {
@@ -28,6 +29,32 @@ struct Cross3 {
 // Mixed element types: byte mask = a < b
 struct LessThan {
   __device__ __forceinline__ void operator()(unsigned char *out, double *a, double *b) const { *out = *a < *b ? 1 : 0; }
+};
+
+// Reduction functors: modifyOp maps an element, reduceOp folds it into an accumulator, the third
+// functor merges two accumulators (the contract of THC_reduceDim / THC_reduceAll).
+struct Square { __device__ __forceinline__ float operator()(float x) const { return x * x; } };
+struct AbsF { __device__ __forceinline__ float operator()(float x) const { return x < 0 ? -x : x; } };
+struct AddF { __device__ __forceinline__ float operator()(float a, float b) const { return a + b; } };
+struct MaxF { __device__ __forceinline__ float operator()(float a, float b) const { return a > b ? a : b; } };
+struct IsPositive { __device__ __forceinline__ double operator()(double x) const { return x > 0 ? 1.0 : 0.0; } };
+struct CountL { __device__ __forceinline__ long operator()(long acc, double flag) const { return acc + (flag != 0.0 ? 1 : 0); } };
+struct AddL { __device__ __forceinline__ long operator()(long a, long b) const { return a + b; } };
+struct MinMax { int lo, hi; };
+struct IdentityI { __device__ __forceinline__ int operator()(int x) const { return x; } };
+struct MinMaxStep {
+  __device__ __forceinline__ MinMax operator()(MinMax a, int x) const {
+    if (x < a.lo) a.lo = x;
+    if (x > a.hi) a.hi = x;
+    return a;
+  }
+};
+struct MinMaxMerge {
+  __device__ __forceinline__ MinMax operator()(MinMax a, MinMax b) const {
+    if (b.lo < a.lo) a.lo = b.lo;
+    if (b.hi > a.hi) a.hi = b.hi;
+    return a;
+  }
 };
 
 extern "C" {
@@ -59,6 +86,35 @@ __attribute__((visibility("default"))) int usertest_cross(THCState *state, THCud
 
 __attribute__((visibility("default"))) int usertest_less_than(THCState *state, THCudaByteTensor *out, THCudaDoubleTensor *a, THCudaDoubleTensor *b) {
   return THC_pointwiseApply3(state, out, a, b, LessThan()) ? 1 : 0;
+}
+
+// ---- user functors through THC_reduceDim / THC_reduceAll (include/THC/THCReduce.cuh) ----
+
+// sum of squares along a dim, float accumulator
+__attribute__((visibility("default"))) int usertest_sumsq_dim(THCState *state, THCudaTensor *out, THCudaTensor *in, int dim, int keepdim) {
+  return THC_reduceDim(state, out, in, Square(), AddF(), AddF(), 0.0f, dim, keepdim) ? 1 : 0;
+}
+
+// largest |x| of a tensor, result on the host
+__attribute__((visibility("default"))) int usertest_absmax_all(THCState *state, THCudaTensor *in, float *out_host) {
+  return THC_reduceAll(state, in, AbsF(), MaxF(), MaxF(), 0.0f, out_host, 0) ? 1 : 0;
+}
+
+// number of positive elements of a double tensor as a long, result left on the device
+__attribute__((visibility("default"))) int usertest_count_positive_device(THCState *state, THCudaDoubleTensor *in, long *out_dev) {
+  return THC_reduceAll(state, in, IsPositive(), CountL(), AddL(), 0L, out_dev, 1) ? 1 : 0;
+}
+
+// smallest and largest element in one pass: a struct accumulator
+__attribute__((visibility("default"))) int usertest_minmax_all(THCState *state, THCudaIntTensor *in, int *lo, int *hi) {
+  MinMax init;
+  init.lo = 2147483647;
+  init.hi = -2147483647 - 1;
+  MinMax r = init;
+  const bool ok = THC_reduceAll(state, in, IdentityI(), MinMaxStep(), MinMaxMerge(), init, &r, 0);
+  *lo = r.lo;
+  *hi = r.hi;
+  return ok ? 1 : 0;
 }
 
 }  // extern "C"

@@ -83,3 +83,51 @@ def test_apply3_mixed_element_types(state, user):
     mask = thc.Tensor.new(state, "Byte", 8, 13)
     assert user.usertest_less_than(state.ptr, mask.ptr, to_device(state, a).ptr, to_device(state, b).ptr) == 1
     assert_bit_equal(mask.numpy(), (np.ascontiguousarray(a) < b).astype(np.uint8), "byte mask from double operands")
+
+
+# ---- THC_reduceDim / THC_reduceAll with user functors (include/THC/THCReduce.cuh) ----
+
+def test_reduce_dim_user_functors(state, user):
+    user.usertest_sumsq_dim.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+    r = rng("user-reduce-dim")
+    for shape, layout in [((40, 1000), "contiguous"), ((1000, 40), "transposed"), ((6, 7, 50), "permuted"),
+                          ((3000, 5), "contiguous"), ((9, 2000, 3), "holes")]:
+        # multiples of 1/4 so that float sums of squares are exact in any order
+        x = make_view(r, "Float", shape, layout)
+        x[...] = (r.integers(-8, 9, size=shape) / 4).astype(np.float32)
+        dx = to_device(state, x)
+        for dim in range(len(shape)):
+            for keepdim in (1, 0):
+                out = thc.Tensor.new(state, "Float")
+                assert user.usertest_sumsq_dim(state.ptr, out.ptr, dx.ptr, dim, keepdim) == 1
+                want = (np.asarray(x, dtype=np.float64) ** 2).sum(axis=dim, keepdims=bool(keepdim)).astype(np.float32)
+                assert out.sizes == list(want.shape), (shape, dim, keepdim)
+                assert_bit_equal(out.numpy(), want, f"user sum of squares {shape} {layout} dim {dim}")
+    out = thc.Tensor.new(state, "Float")
+    assert user.usertest_sumsq_dim(state.ptr, out.ptr, dx.ptr, 7, 1) == 0   # bad dim -> false
+
+
+def test_reduce_all_user_functors(state, user):
+    user.usertest_absmax_all.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
+    user.usertest_count_positive_device.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    user.usertest_minmax_all.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    r = rng("user-reduce-all")
+    for shape, layout in [((100003,), "contiguous"), ((300, 500), "transposed"), ((7, 9, 11), "strided"), ((5,), "contiguous"),
+                          ((3_000_000,), "contiguous")]:
+        x = make_view(r, "Float", shape, layout)
+        res = C.c_float(-1)
+        assert user.usertest_absmax_all(state.ptr, to_device(state, x).ptr, C.byref(res)) == 1
+        assert res.value == float(np.abs(x).max()), (shape, layout)
+        d = make_view(r, "Double", shape, layout)
+        slot = to_device(state, np.zeros(1, np.int64))
+        assert user.usertest_count_positive_device(state.ptr, to_device(state, d).ptr, C.c_void_p(slot.data_ptr)) == 1
+        assert int(slot.numpy()[0]) == int((d > 0).sum()), (shape, layout)
+        i = make_view(r, "Int", shape, layout)
+        i[...] = r.integers(-2**31, 2**31 - 1, size=shape).astype(np.int32)
+        lo, hi = C.c_int(0), C.c_int(0)
+        assert user.usertest_minmax_all(state.ptr, to_device(state, i).ptr, C.byref(lo), C.byref(hi)) == 1
+        assert (lo.value, hi.value) == (int(i.min()), int(i.max())), (shape, layout)
+    # a tensor without dimensions yields the initial value
+    res = C.c_float(-1)
+    assert user.usertest_absmax_all(state.ptr, thc.Tensor.new(state, "Float").ptr, C.byref(res)) == 1
+    assert res.value == 0.0

@@ -1,0 +1,79 @@
+"""tril / triu and renorm through the THC C API against oracle/matrix_oracle.py.
+
+cutorch's tests: test/test.lua:1411-1452 (tril, triu with random k on random matrices and their
+transposes), :1399-1409 (renorm over each dim of 2-D..4-D tensors).  tril / triu are bit-exact
+(every output is an input element or 0); renorm is held to the reduction tolerance."""
+import numpy as np
+import pytest
+
+from cutorch_b200 import thc
+from oracle import matrix_oracle as mx
+from common import ALL_KINDS, FP_KINDS, assert_bit_equal, make_view, rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_tril_triu(state, kind):
+    r = rng("tri", kind)
+    for shape, layout in [((37, 53), "contiguous"), ((53, 37), "transposed"), ((64, 1100), "holes"), ((1100, 9), "offset"),
+                          ((1, 1), "contiguous"), ((130, 130), "strided")]:
+        x = make_view(r, kind, shape, layout)
+        if x.dtype.kind != "f":
+            x[...] = r.integers(1, 9, size=shape).astype(x.dtype)
+        dx = to_device(state, x)
+        for k in (0, 1, -1, 5, -7, shape[1] + 3, -shape[0] - 3):
+            for name, upper in (("tril", False), ("triu", True)):
+                out = thc.Tensor.new(state, kind)
+                getattr(out, name)(dx, k)
+                assert out.sizes == list(shape)
+                assert_bit_equal(out.numpy(), mx.tri(x, k, upper), f"{kind} {name} k={k} {shape} {layout}")
+        # in place, and into a transposed output
+        y = to_device(state, x)
+        y.tril(y, 2)
+        assert_bit_equal(y.numpy(), mx.tri(x, 2, False), f"{kind} tril in place {layout}")
+        z = to_device(state, make_view(r, kind, shape, "transposed"))
+        z.triu(dx, -1)
+        assert_bit_equal(z.numpy(), mx.tri(x, -1, True), f"{kind} triu into transposed output {layout}")
+    with pytest.raises(thc.THCError, match="expected a matrix"):
+        thc.Tensor.new(state, kind).tril(to_device(state, make_view(r, kind, (3, 4, 5), "contiguous")), 0)
+
+
+REL = {"Half": 2e-3, "Float": 1e-5, "Double": 1e-12}
+
+
+@pytest.mark.parametrize("kind", FP_KINDS)
+def test_renorm(state, kind):
+    r = rng("renorm", kind)
+    cases = [((200, 64), "contiguous"), ((64, 200), "transposed"), ((7, 30, 11), "contiguous"), ((5, 6, 7, 8), "permuted"),
+             ((300, 33), "holes"), ((2, 5000), "contiguous")]
+    for shape, layout in cases:
+        x = make_view(r, kind, shape, layout)
+        x[...] = (r.standard_normal(shape) * r.uniform(0.2, 3.0, size=shape[:1] + (1,) * (len(shape) - 1))).astype(x.dtype)
+        dx = to_device(state, x)
+        for dim in range(len(shape)):
+            for p in (1, 2, 3, 2.5):
+                # a threshold that some slices exceed and some do not
+                moved = np.moveaxis(x.astype(np.float64), dim, 0).reshape(shape[dim], -1)
+                norms = (np.abs(moved) ** p).sum(axis=1) ** (1.0 / p)
+                maxnorm = float(x.dtype.type(float(np.median(norms)) * 1.003))   # as the `real` argument carries it
+                want = mx.renorm(x, p, dim, maxnorm)
+                out = thc.Tensor.new(state, kind)
+                out.renorm(dx, p, dim, maxnorm)
+                got = out.numpy()
+                assert out.sizes == list(shape)
+                tol = REL[kind] * np.maximum(np.abs(want.astype(np.float64)), 1e-30)
+                bad = np.abs(got.astype(np.float64) - want.astype(np.float64)) > tol
+                assert not bad.any(), f"{kind} renorm p={p} dim={dim} {shape} {layout}: {bad.sum()} off, first {np.argwhere(bad)[0]}"
+                # slices below the threshold are copied bit for bit
+                keep = np.moveaxis(np.broadcast_to(np.expand_dims(norms <= maxnorm * 0.999, tuple(range(1, len(shape)))),
+                                                   np.moveaxis(x, dim, 0).shape), 0, dim)
+                assert_bit_equal(got[keep], np.asarray(x)[keep], "slices under the threshold")
+        y = to_device(state, x)
+        y.renorm(y, 2, 0, 1.0)
+        want = mx.renorm(x, 2, 0, 1.0)
+        assert np.allclose(y.numpy().astype(np.float64), want.astype(np.float64), rtol=REL[kind], atol=0), "in place"
+    with pytest.raises(thc.THCError, match="at least 2 dimensions"):
+        thc.Tensor.new(state, kind).renorm(to_device(state, make_view(r, kind, (10,), "contiguous")), 2, 0, 1.0)
+    with pytest.raises(thc.THCError, match="non-positive-norm"):
+        thc.Tensor.new(state, kind).renorm(dx, -1, 0, 1.0)
