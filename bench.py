@@ -300,9 +300,9 @@ def ours_main(args):
         gbs, dt, nthreads = run_cpu(srows, 2, 1, None)
         cpu_baseline = {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port",
                         "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (2 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
-        if args.configs:
-            from bench_configs import run_small_configs
-            extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
+    if rank == 0 and world == 1 and args.configs:
+        from bench_configs import run_small_configs
+        extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
 
     if rank == 0:
         line = {
