@@ -842,6 +842,87 @@ void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half
   tensor_free<float>(state, wide);
 }
 
+// ---- indexed moves (lib/THC/generic/THCTensorIndex.cu, THCTensorScatterGather.cu) --------
+using LongT = TensorT<long>;
+template <typename R> R zero_real() { return R(); }
+
+template <typename R>
+void indexed(THCState *state, int mode, TensorT<R> *dst, TensorT<R> *src, LongT *index, int dim, bool vector, thcb200_scalar v) {
+  thcb200_tensor dd = describe<R>(dst), di = describe<long>(index), ds;
+  if (src) ds = describe<R>(src);
+  check_core(thcb200_indexed(state_ctx(state), mode, &dd, src ? &ds : nullptr, &di, dim, vector ? 1 : 0, v,
+                             (void *)state_stream(state)));
+}
+
+template <typename R> void index_vector_checks(THCState *state, TensorT<R> *a, TensorT<R> *b, LongT *indices, int dim, TensorT<R> *src) {
+  check_gpu<R>(state, {a, b});
+  check_gpu<long>(state, {indices});
+  THArgCheck(indices->nDimension == 1, 3, "expecting vector of indices");
+  THArgCheck(dim >= 0 && dim < src->nDimension, 4, "Indexing dim is out of bounds");
+  THArgCheck(src->nDimension > 0, 2, "Source tensor is empty");
+}
+
+template <typename R> void index_select(THCState *state, TensorT<R> *dst, TensorT<R> *src, int dim, LongT *indices) {
+  index_vector_checks<R>(state, dst, src, indices, dim, src);
+  THArgCheck(dst != src, 1, "output must differ from the input");
+  long sz[THCB200_MAX_DIMS];
+  THArgCheck(src->nDimension <= THCB200_MAX_DIMS, 3, CUTORCH_DIM_WARNING);
+  for (int d = 0; d < src->nDimension; ++d) sz[d] = src->size[d];
+  sz[dim] = indices->size[0];
+  tensor_raw_resize<R>(state, dst, src->nDimension, sz, nullptr);
+  indexed<R>(state, THCB200_INDEX_GATHER, dst, src, indices, dim, true, kZero);
+}
+
+template <typename R> void index_copy_or_add(THCState *state, int mode, TensorT<R> *dst, int dim, LongT *indices, TensorT<R> *src) {
+  index_vector_checks<R>(state, dst, src, indices, dim, src);
+  THArgCheck(indices->size[0] == src->size[dim], 4, "length of src.size[dim] is not equal to length of indices");
+  THArgCheck(dst->nDimension == src->nDimension, 2, "destination and source must have the same number of dimensions");
+  indexed<R>(state, mode, dst, src, indices, dim, true, kZero);
+}
+
+template <typename R> void index_fill(THCState *state, TensorT<R> *dst, int dim, LongT *indices, R value) {
+  index_vector_checks<R>(state, dst, nullptr, indices, dim, dst);
+  indexed<R>(state, THCB200_INDEX_SCATTER_FILL, dst, nullptr, indices, dim, true, to_scalar<R>(value));
+}
+
+template <typename R> void gather(THCState *state, TensorT<R> *tensor, TensorT<R> *src, int dim, LongT *index) {
+  check_gpu<R>(state, {tensor, src});
+  check_gpu<long>(state, {index});
+  THArgCheck(src->nDimension == tensor->nDimension, 2, "Input tensor must have same dimensions as output tensor");
+  THArgCheck(dim >= 0 && dim < tensor->nDimension, 3, "Index dimension is out of bounds");
+  THArgCheck(index->nDimension == src->nDimension, 4, "Index tensor must have same dimensions as input tensor");
+  for (int d = 0; d < tensor->nDimension; ++d) {
+    THArgCheck(index->size[d] == tensor->size[d], 4, "Index tensor must have the same size as output tensor.");
+    if (d != dim)
+      THArgCheck(tensor->size[d] == src->size[d], 2,
+                 "Input tensor must have same size as output tensor apart from the specified dimension");
+  }
+  indexed<R>(state, THCB200_INDEX_GATHER, tensor, src, index, dim, false, kZero);
+}
+
+template <typename R> void scatter(THCState *state, int mode, TensorT<R> *tensor, int dim, LongT *index, TensorT<R> *src, R value) {
+  check_gpu<R>(state, {tensor, src});
+  check_gpu<long>(state, {index});
+  THArgCheck(dim >= 0 && dim < tensor->nDimension, 2, "Index dimension is out of bounds");
+  if (src) {
+    THArgCheck(index->nDimension == src->nDimension, 3, "Index tensor must have same dimensions as input tensor");
+    THArgCheck(src->nDimension == tensor->nDimension, 4, "Input tensor must have same dimensions as output tensor");
+    for (int d = 0; d < tensor->nDimension; ++d) {
+      THArgCheck(index->size[d] == src->size[d], 3, "Index tensor must have the same size as input tensor.");
+      if (d != dim)
+        THArgCheck(tensor->size[d] == src->size[d], 4,
+                   "Input tensor must have same size as output tensor apart from the specified dimension");
+    }
+  } else {
+    THArgCheck(index->nDimension == tensor->nDimension, 3, "Index tensor must have same dimensions as output tensor");
+    for (int d = 0; d < tensor->nDimension; ++d)
+      if (d != dim)
+        THArgCheck(tensor->size[d] == index->size[d], 4,
+                   "Index tensor must have same size as output tensor apart from the specified dimension");
+  }
+  indexed<R>(state, mode, tensor, src, index, dim, false, to_scalar<R>(value));
+}
+
 // ---- comparisons into a ByteTensor, Byte masks -----------------------------------------
 using ByteT = TensorT<unsigned char>;
 

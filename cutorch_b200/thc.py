@@ -63,6 +63,8 @@ SIGNATURES.update({
     "fill": ("v", "Tr"), "zero": ("v", "T"), "copy": ("v", "TT"), "copyIgnoringOverlaps": ("v", "TT"),
     "resizeAs": ("v", "TT"),
     "tril": ("v", "TTl"), "triu": ("v", "TTl"), "renorm": ("v", "TTrlr"),
+    "indexSelect": ("v", "TTiL"), "indexCopy": ("v", "TiLT"), "indexAdd": ("v", "TiLT"), "indexFill": ("v", "TiLr"),
+    "gather": ("v", "TTiL"), "scatter": ("v", "TiLT"), "scatterAdd": ("v", "TiLT"), "scatterFill": ("v", "TiLr"),
     "cumsum": ("v", "TTl"), "cumprod": ("v", "TTl"),
     "maskedFill": ("v", "TBr"), "maskedCopy": ("v", "TBT"), "maskedSelect": ("v", "TTB"),
 })

@@ -210,6 +210,18 @@ THC_B200_DECLARE_COMPARE(ne)
 THC_API void THCTensor_(cumsum)(THCState *state, THCTensor *self, THCTensor *src, long dim);
 THC_API void THCTensor_(cumprod)(THCState *state, THCTensor *self, THCTensor *src, long dim);
 
+/* ---- indexed moves; positions are 1-based (lib/THC/generic/THCTensorIndex.h:5-8,
+ * THCTensorScatterGather.h:5-8).  The ..._long variants, which take a torch7 CPU index tensor,
+ * need TH and are not provided ---- */
+THC_API void THCTensor_(indexSelect)(THCState *state, THCTensor *tensor, THCTensor *src, int dim, struct THCudaLongTensor *index);
+THC_API void THCTensor_(indexCopy)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
+THC_API void THCTensor_(indexAdd)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
+THC_API void THCTensor_(indexFill)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, real val);
+THC_API void THCTensor_(gather)(THCState *state, THCTensor *tensor, THCTensor *src, int dim, struct THCudaLongTensor *index);
+THC_API void THCTensor_(scatter)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, THCTensor *src);
+THC_API void THCTensor_(scatterAdd)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, THCTensor *src);
+THC_API void THCTensor_(scatterFill)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, real value);
+
 /* ---- triangles of a matrix (lib/THC/generic/THCTensorMath.h: tril, triu) ---- */
 THC_API void THCTensor_(tril)(THCState *state, THCTensor *self, THCTensor *src, long k);
 THC_API void THCTensor_(triu)(THCState *state, THCTensor *self, THCTensor *src, long k);

@@ -273,6 +273,34 @@ THCB200_API int thcb200_tri(thcb200_ctx *ctx, int upper, int64_t k, const thcb20
 THCB200_API int thcb200_renorm_factor(thcb200_ctx *ctx, const thcb200_tensor *factors,
                           const thcb200_tensor *sums, double p, double maxnorm, void *stream);
 
+/* ---- indexed moves along one dim ------------------------------------------------------- */
+
+/* For every coordinate tuple c of the iteration space, p = index value (1-based), and c' = c with
+ * c'[dim] = p - 1:
+ *   GATHER        dst[c]  = src[c']      iteration space: dst's shape
+ *   SCATTER       dst[c'] = src[c]       iteration space: src's shape
+ *   SCATTER_ADD   dst[c'] += src[c]      (atomic; duplicates accumulate in no fixed order)
+ *   SCATTER_FILL  dst[c'] = value        iteration space: the index's shape (index_is_vector: dst's
+ *                                        shape with the indexed dim as long as the vector)
+ * `index` is an I64 view of the iteration space's shape, read at c; with index_is_vector it is a
+ * 1-D view read at c[dim].  That covers gather / scatter / scatterAdd / scatterFill
+ * (lib/THC/generic/THCTensorScatterGather.cu:8-351) and, with a vector, indexSelect (GATHER),
+ * indexCopy (SCATTER), indexAdd (SCATTER_ADD) and indexFill (SCATTER_FILL)
+ * (lib/THC/generic/THCTensorIndex.cu:14-589).  Positions outside 1..size[dim] are skipped and
+ * counted (see thcb200_take_index_errors) instead of asserting on the device. */
+typedef enum thcb200_index_mode {
+  THCB200_INDEX_GATHER = 0,
+  THCB200_INDEX_SCATTER = 1,
+  THCB200_INDEX_SCATTER_ADD = 2,
+  THCB200_INDEX_SCATTER_FILL = 3
+} thcb200_index_mode;
+THCB200_API int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst,
+                    const thcb200_tensor *src, const thcb200_tensor *index, int dim,
+                    int index_is_vector, thcb200_scalar value, void *stream);
+/* Number of out-of-range positions skipped by thcb200_indexed on this context since the last
+ * call of this function; waits for the stream. */
+THCB200_API int thcb200_take_index_errors(thcb200_ctx *ctx, int64_t *count_host, void *stream);
+
 /* ---- operands of two element types: comparisons into Byte, Byte masks ------------------ */
 
 /* out[i] = (a[i] CMP b[i]) ? 1 : 0 with `out` a U8 view; `cmp` is one of THCB200_OP_LT..NE.
