@@ -133,7 +133,46 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         td = W(d, "Double")
         out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5)
 
-    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4)):
+    def nxt():
+        """The callers either side of the path (comparisons into bytes, masks, scans, indexed moves,
+        triangles, renorm), each on a tensor far larger than the L2.  Bytes are the compulsory
+        reads and writes of the call; extra passes an implementation makes do not count."""
+        n = 134217728
+        x = torch.empty(n, device=dev).normal_(generator=g)
+        tx = W(x, "Float")
+        m = torch.empty(n, dtype=torch.uint8, device=dev)
+        tm = W(m, "Byte")
+        out["f1_gtValue_f32_to_byte_128M"] = timed(lambda: tx.call("gtValue", tm, tx, 0.0), 5 * n, reps=5)
+        cnt = int(m.sum().item())
+        y = x.clone()
+        ty = W(y, "Float")
+        out["f1_maskedFill_f32_128M_half_set"] = timed(lambda: ty.maskedFill(tm, 0.0), 9 * n, reps=5)
+        sel = thc.Tensor.new(state, "Float")
+        out["f1_maskedSelect_f32_128M_half_set"] = timed(lambda: sel.maskedSelect(tx, tm), 5 * n + 4 * cnt, reps=5)
+        out["f2_cumsum_f32_1d_128M"] = timed(lambda: ty.cumsum(tx, 0), 8 * n, reps=5)
+        del y, m
+        mat = x.view(16384, 8192)
+        mo = torch.empty_like(mat)
+        tmat, tmo = W(mat, "Float"), W(mo, "Float")
+        out["f2_cumsum_f32_16384x8192_dim1"] = timed(lambda: tmo.cumsum(tmat, 1), 8 * n, reps=5)
+        out["f2_cumsum_f32_16384x8192_dim0"] = timed(lambda: tmo.cumsum(tmat, 0), 8 * n, reps=5)
+        sq = x.view(-1)[: 11584 * 11584].view(11584, 11584)
+        so = torch.empty_like(sq)
+        tsq, tso = W(sq, "Float"), W(so, "Float")
+        nsq = 11584 * 11584
+        out["a5_tril_f32_11584x11584"] = timed(lambda: tso.tril(tsq, 0), 6 * nsq, reps=5)
+        emb = x.view(524288, 256)
+        eo = torch.empty_like(emb)
+        temb, teo = W(emb, "Float"), W(eo, "Float")
+        out["f2_renorm_f32_524288x256_dim0"] = timed(lambda: teo.renorm(temb, 2, 0, 15.0), 12 * n, reps=5)
+        idx = torch.randint(1, 524288 + 1, (524288,), dtype=torch.int64, device=dev, generator=g)
+        tidx = W(idx, "Long")
+        out["f4_indexSelect_f32_524288_rows_of_256"] = timed(lambda: teo.indexSelect(temb, 0, tidx), 8 * n + 8 * 524288, reps=5)
+        gi = torch.randint(1, 256 + 1, (524288, 256), dtype=torch.int64, device=dev, generator=g)
+        tgi = W(gi, "Long")
+        out["f4_gather_f32_524288x256_dim1"] = timed(lambda: teo.gather(temb, 1, tgi), (8 + 8) * n, reps=5)
+
+    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt)):
         if only is None or name in only:
             fn()
             torch.cuda.synchronize()

@@ -30,6 +30,8 @@ constexpr int kIdxUnroll = 4;
 
 enum IdxMode { kIdxCopy = 0, kIdxAdd = 1, kIdxFill = 2 };
 
+struct alignas(16) Word16 { uint32_t w[4]; };
+
 template <typename IndexT>
 struct IdxPlan {
   int nd;
@@ -42,6 +44,7 @@ struct IdxPlan {
 };
 
 template <typename T> __device__ __forceinline__ void atomic_add_elem(T *p, T v) { atomicAdd(p, v); }
+template <> __device__ __forceinline__ void atomic_add_elem<Word16>(Word16 *, Word16) {}   // never used: adds are per element
 template <> __device__ __forceinline__ void atomic_add_elem<int64_t>(int64_t *p, int64_t v) {
   atomicAdd(reinterpret_cast<unsigned long long *>(p), (unsigned long long)v);
 }
@@ -237,6 +240,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
   h.redirect_stride = redir.strides[dim];
   h.limit = redir.sizes[dim];
   bool prev_mergeable = false;
+  int h_dim = -1;   // entry of the indexed dim among the collapsed ones
   for (int d = 0; d < nd; ++d) {
     if (it[d] == 1) continue;
     const int64_t sp = plain ? plain->strides[d] : 0;
@@ -250,6 +254,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
       h.redir[h.nd - 1] = sr;
       h.index[h.nd - 1] = sx;
     } else {
+      if (d == dim) h_dim = h.nd;
       h.size[h.nd] = it[d];
       h.plain[h.nd] = sp;
       h.redir[h.nd] = sr;
@@ -276,6 +281,29 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
     }
   }
   const uint64_t bits = fill ? value_bits(vd.dtype, value) : 0;
+  // Whole 16-byte words move when the innermost run is dense on both sides, every position of it
+  // shares one index entry, and all other strides keep 16-byte alignment (the index* calls on
+  // rows of a matrix): same kernel, element = 16 bytes.
+  {
+    const int esz = (int)dtype_size(vd.dtype);
+    const int V = 16 / esz;
+    const int L = h.nd - 1;
+    bool vec = V > 1 && L >= 0 && L != h_dim && h.redir[L] == 1 && (fill || h.plain[L] == 1) && h.index[L] == 0 &&
+               h.size[L] % V == 0 && h.redirect_stride % V == 0 && (uintptr_t)dp % 16 == 0 && (fill || (uintptr_t)sp % 16 == 0);
+    for (int d = 0; vec && d < L; ++d)
+      if (h.plain[d] % V != 0 || h.redir[d] % V != 0) vec = false;
+    if (vec) {
+      h.size[L] /= V;
+      for (int d = 0; d < L; ++d) { h.plain[d] /= V; h.redir[d] /= V; }
+      h.redirect_stride /= V;
+      h.n /= (uint64_t)V;
+      Word16 w;
+      for (int b = 0; b < 16; b += esz) memcpy(reinterpret_cast<char *>(&w) + b, &bits, (size_t)esz);
+      if (fill) return launch_indexed<Word16, kIdxFill, true>(ctx, h, dp, sp, xp, w, st);
+      return redirect_dst ? launch_indexed<Word16, kIdxCopy, true>(ctx, h, dp, sp, xp, w, st)
+                          : launch_indexed<Word16, kIdxCopy, false>(ctx, h, dp, sp, xp, w, st);
+    }
+  }
 #define THCB_IDX_SIZED(W) (fill ? launch_move_sized<W, kIdxFill>(ctx, true, h, dp, sp, xp, bits, st) \
                                 : launch_move_sized<W, kIdxCopy>(ctx, redirect_dst, h, dp, sp, xp, bits, st))
   switch (dtype_size(vd.dtype)) {

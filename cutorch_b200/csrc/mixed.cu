@@ -179,10 +179,31 @@ constexpr int kSteps = 16;
 constexpr int kWarpSpan = 32 * kSteps;            // 512
 constexpr int kTile = (kThreads / 32) * kWarpSpan;  // 4096
 
+// ballots[k] = mask bits of elements wbase + k*32 .. + 31.  With `vec` (unit-stride, 16-byte
+// aligned mask) a lane reads its 16 consecutive mask bytes in one load and the per-step words
+// are put together from two lanes' 16-bit masks.
 template <typename IndexT>
 __device__ __forceinline__ uint32_t warp_mask_ballots(const uint8_t *mask, const StridedView<IndexT> &vm, uint64_t wbase,
-                                                      uint64_t n, uint32_t (&ballots)[kSteps]) {
+                                                      uint64_t n, bool vec, uint32_t (&ballots)[kSteps]) {
   const unsigned lane = threadIdx.x & 31;
+  uint32_t total = 0;
+  if (vec && wbase + kWarpSpan <= n) {
+    const Bytes16 v = ld16_stream(mask + wbase + (uint64_t)lane * 16);
+    uint32_t bits = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) bits |= (((v.w[w] >> (8 * b)) & 0xFFu) != 0 ? 1u : 0u) << (4 * w + b);
+    }
+#pragma unroll
+    for (int k = 0; k < kSteps; ++k) {
+      const uint32_t lo = __shfl_sync(0xffffffffu, bits, 2 * k);
+      const uint32_t hi = __shfl_sync(0xffffffffu, bits, 2 * k + 1);
+      ballots[k] = lo | (hi << 16);
+      total += __popc(ballots[k]);
+    }
+    return total;
+  }
   uint8_t m[kSteps];
 #pragma unroll
   for (int k = 0; k < kSteps; ++k) {
@@ -190,7 +211,6 @@ __device__ __forceinline__ uint32_t warp_mask_ballots(const uint8_t *mask, const
     m[k] = 0;
     if (i < n) m[k] = mask[vm.offset((IndexT)i)];
   }
-  uint32_t total = 0;
 #pragma unroll
   for (int k = 0; k < kSteps; ++k) {
     ballots[k] = __ballot_sync(0xffffffffu, m[k] != 0);
@@ -199,21 +219,95 @@ __device__ __forceinline__ uint32_t warp_mask_ballots(const uint8_t *mask, const
   return total;
 }
 
-template <typename IndexT>
-__global__ void __launch_bounds__(kThreads)
-mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, uint32_t *counts) {
+// 0x80 in every byte of w that is not zero
+__device__ __forceinline__ uint32_t nonzero_bytes(uint32_t w) {
+  return (((w & 0x7F7F7F7Fu) + 0x7F7F7F7Fu) | w) & 0x80808080u;
+}
+// one bit per byte of a 16-byte mask vector: bit j set when byte j is not zero
+__device__ __forceinline__ uint32_t nonzero_bits16(const Bytes16 &v) {
+  uint32_t bits = 0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    // the four flags sit at bits 7, 15, 23, 31; the multiply lines them up at bits 21..24
+    const uint32_t nib = (((nonzero_bytes(v.w[w]) >> 7) * 0x00204081u) >> 21) & 0xFu;
+    bits |= nib << (4 * w);
+  }
+  return bits;
+}
+
+// Unit-stride, 16-byte aligned mask, whole tiles only: a thread counts its 16 bytes with bit
+// arithmetic, a CTA the 4096 of its tile.
+__global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint32_t *counts) {
   __shared__ uint32_t wsum[kThreads / 32];
-  const unsigned warp = threadIdx.x >> 5;
-  const uint64_t wbase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan;
-  uint32_t ballots[kSteps];
-  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, ballots);
-  if ((threadIdx.x & 31) == 0) wsum[warp] = total;
+  const Bytes16 v = ld16_stream(mask + (uint64_t)blockIdx.x * kTile + (uint64_t)threadIdx.x * 16);
+  uint32_t c = 0;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) c += __popc(nonzero_bytes(v.w[w]));
+  c = __reduce_add_sync(0xffffffffu, c);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
   __syncthreads();
   if (threadIdx.x == 0) {
     uint32_t s = 0;
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) s += wsum[w];
     counts[blockIdx.x] = s;
+  }
+}
+
+// maskedSelect with a unit-stride aligned mask and a unit-stride aligned source, whole tiles only.
+// A lane owns 16 consecutive elements: one 16-byte mask load, sizeof(W) 16-byte data loads.  The
+// selected elements of a warp are packed into its slice of shared memory and leave as coalesced
+// stores (the packed side keeps its own strides).
+template <typename W, typename IndexT>
+__global__ void __launch_bounds__(kThreads)
+masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const uint8_t *mask, const uint64_t *offsets) {
+  __shared__ uint32_t wsum[kThreads / 32];
+  __shared__ W stage[kThreads / 32][kWarpSpan];
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
+  const Bytes16 mv = ld16_stream(mask + ebase);
+  alignas(16) W e[16];
+  constexpr int NV = (int)sizeof(W);   // 16-byte vectors holding 16 elements
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+    *reinterpret_cast<Bytes16 *>(reinterpret_cast<char *>(e) + 16 * v) =
+        ld16_stream(reinterpret_cast<const char *>(src + ebase) + 16 * v);
+  const uint32_t bits = nonzero_bits16(mv);
+  const uint32_t cnt = __popc(bits);
+  uint32_t incl = cnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= (unsigned)d) incl += y;
+  }
+  const uint32_t wtotal = __shfl_sync(0xffffffffu, incl, 31);
+  if (lane == 0) wsum[warp] = wtotal;
+  uint32_t r = incl - cnt;
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    if ((bits >> j) & 1u) stage[warp][r++] = e[j];
+  __syncthreads();
+  uint64_t pos = offsets[blockIdx.x];
+  for (unsigned w = 0; w < warp; ++w) pos += wsum[w];
+  for (uint32_t i = lane; i < wtotal; i += 32) packed[vp.offset((IndexT)(pos + i))] = stage[warp][i];
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(kThreads)
+mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, bool vec, uint32_t *counts, uint32_t tile0) {
+  __shared__ uint32_t wsum[kThreads / 32];
+  const unsigned warp = threadIdx.x >> 5;
+  const uint64_t tile = (uint64_t)blockIdx.x + tile0;
+  const uint64_t wbase = tile * kTile + (uint64_t)warp * kWarpSpan;
+  uint32_t ballots[kSteps];
+  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, vec, ballots);
+  if ((threadIdx.x & 31) == 0) wsum[warp] = total;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t s = 0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) s += wsum[w];
+    counts[tile] = s;
   }
 }
 
@@ -250,15 +344,16 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts,
 template <typename W, typename IndexT, bool SELECT>
 __global__ void __launch_bounds__(kThreads)
 masked_move_kernel(W *strided, StridedView<IndexT> vs, W *packed, StridedView<IndexT> vp, const uint8_t *mask,
-                   StridedView<IndexT> vm, uint64_t n, const uint64_t *offsets) {
+                   StridedView<IndexT> vm, uint64_t n, bool vec, const uint64_t *offsets, uint32_t tile0) {
   __shared__ uint32_t wsum[kThreads / 32];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint64_t wbase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan;
+  const uint64_t tile = (uint64_t)blockIdx.x + tile0;
+  const uint64_t wbase = tile * kTile + (uint64_t)warp * kWarpSpan;
   uint32_t ballots[kSteps];
-  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, ballots);
+  const uint32_t total = warp_mask_ballots<IndexT>(mask, vm, wbase, n, vec, ballots);
   if (lane == 0) wsum[warp] = total;
   __syncthreads();
-  uint64_t pos = offsets[blockIdx.x];
+  uint64_t pos = offsets[tile];
   for (unsigned w = 0; w < warp; ++w) pos += wsum[w];
   const uint32_t below = (1u << lane) - 1u;
   if (SELECT) {
@@ -479,12 +574,25 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   if (hit) return 0;
   ctx->prep_valid = 0;
   const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
-  if (mp->cm.fits32)
-    mask_tile_count_kernel<uint32_t><<<(unsigned)mp->ntiles, kThreads, 0, st>>>(mask, make_view<uint32_t>(mp->cm), n, counts);
-  else
-    mask_tile_count_kernel<uint64_t><<<(unsigned)mp->ntiles, kThreads, 0, st>>>(mask, make_view<uint64_t>(mp->cm), n, counts);
+  const bool mask_vec = mp->cm.unit && aligned16(mask);
+  // whole tiles of a unit-stride aligned mask go through the vector count; the rest (a ragged last
+  // tile, or any other layout) through the strided one
+  const uint64_t full = mask_vec ? n / kTile : 0;
+  int launches = 1;
+  if (full > 0) {
+    mask_tile_count_vec_kernel<<<(unsigned)full, kThreads, 0, st>>>(mask, counts);
+    ++launches;
+  }
+  if (full < mp->ntiles) {
+    const unsigned rest = (unsigned)(mp->ntiles - full);
+    if (mp->cm.fits32)
+      mask_tile_count_kernel<uint32_t><<<rest, kThreads, 0, st>>>(mask, make_view<uint32_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
+    else
+      mask_tile_count_kernel<uint64_t><<<rest, kThreads, 0, st>>>(mask, make_view<uint64_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
+    ++launches;
+  }
   tile_scan_kernel<<<1, 1024, 0, st>>>(counts, mp->offsets, mp->ntiles, mp->total);
-  count_launch(2);
+  count_launch(launches);
   THCB_CUDA_TRY(cudaGetLastError());
   ctx->prep_mask = vm.data;
   ctx->prep_numel = vm.numel;
@@ -509,16 +617,32 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
   W *packed = reinterpret_cast<W *>(vpacked.data);
   const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
   const uint64_t n = (uint64_t)vm.numel;
-  if (cs.fits32 && cp.fits32 && mp.cm.fits32) {
-    set_plan_name(SELECT ? "masked_select32" : "masked_copy32");
-    masked_move_kernel<W, uint32_t, SELECT><<<(unsigned)mp.ntiles, kThreads, 0, st>>>(
-        strided, make_view<uint32_t>(cs), packed, make_view<uint32_t>(cp), mask, make_view<uint32_t>(mp.cm), n, mp.offsets);
-  } else {
-    set_plan_name(SELECT ? "masked_select64" : "masked_copy64");
-    masked_move_kernel<W, uint64_t, SELECT><<<(unsigned)mp.ntiles, kThreads, 0, st>>>(
-        strided, make_view<uint64_t>(cs), packed, make_view<uint64_t>(cp), mask, make_view<uint64_t>(mp.cm), n, mp.offsets);
+  const bool mask_vec = mp.cm.unit && aligned16(mask);
+  const bool i32 = cs.fits32 && cp.fits32 && mp.cm.fits32;
+  // select from a dense aligned source under a dense aligned mask: whole tiles take the vector kernel
+  uint64_t full = 0;
+  int launches = 0;
+  if (SELECT && mask_vec && cs.unit && aligned16(strided)) {
+    full = n / kTile;
+    if (full > 0) {
+      set_plan_name(i32 ? "masked_select_vec32" : "masked_select_vec64");
+      if (i32) masked_select_vec_kernel<W, uint32_t><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
+      else masked_select_vec_kernel<W, uint64_t><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      ++launches;
+    }
   }
-  count_launch();
+  if (full < mp.ntiles) {
+    const unsigned rest = (unsigned)(mp.ntiles - full);
+    if (full == 0) set_plan_name(SELECT ? (i32 ? "masked_select32" : "masked_select64") : (i32 ? "masked_copy32" : "masked_copy64"));
+    if (i32)
+      masked_move_kernel<W, uint32_t, SELECT><<<rest, kThreads, 0, st>>>(strided, make_view<uint32_t>(cs), packed, make_view<uint32_t>(cp), mask,
+                                                                       make_view<uint32_t>(mp.cm), n, mask_vec, mp.offsets, (uint32_t)full);
+    else
+      masked_move_kernel<W, uint64_t, SELECT><<<rest, kThreads, 0, st>>>(strided, make_view<uint64_t>(cs), packed, make_view<uint64_t>(cp), mask,
+                                                                       make_view<uint64_t>(mp.cm), n, mask_vec, mp.offsets, (uint32_t)full);
+    ++launches;
+  }
+  count_launch(launches);
   THCB_CUDA_TRY(cudaGetLastError());
   return 0;
 }

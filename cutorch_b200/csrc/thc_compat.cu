@@ -90,8 +90,16 @@ struct THCState {
 
 namespace {
 
-cudaError_t default_malloc(void *, void **p, size_t n, cudaStream_t) { return cudaMalloc(p, n); }
-cudaError_t default_free(void *, void *p) { return cudaFree(p); }
+cudaStream_t state_stream(THCState *state);
+
+// Default device allocator: stream-ordered (cudaMallocAsync / cudaFreeAsync from the device's
+// default memory pool, which keeps freed blocks for reuse).  It plays the part of cutorch's
+// caching allocator (lib/THC/THCCachingAllocator.cpp): temporaries and resized outputs on the hot
+// path cost no device synchronisation.  A block is returned in the order of the stream that is
+// current when it is freed, so a storage has to be freed while the stream that last used it is
+// current (or after that stream was synchronised).
+cudaError_t default_malloc(void *, void **p, size_t n, cudaStream_t st) { return cudaMallocAsync(p, n, st); }
+cudaError_t default_free(void *ctx, void *p) { return cudaFreeAsync(p, state_stream((THCState *)ctx)); }
 
 int current_device() {
   int d = 0;
@@ -173,9 +181,19 @@ void THCudaInit(THCState *state) {
   state->defaultAllocator.free = default_free;
   state->defaultAllocator.emptyCache = nullptr;
   state->defaultAllocator.cacheInfo = nullptr;
-  state->defaultAllocator.state = nullptr;
+  state->defaultAllocator.state = state;
   state->allocator = &state->defaultAllocator;
   state->initialised = 1;
+  // keep freed blocks in the pools instead of returning them to the driver at every synchronise
+  for (int d = 0; d < n; ++d) {
+    cudaMemPool_t pool;
+    if (cudaDeviceGetDefaultMemPool(&pool, d) == cudaSuccess) {
+      unsigned long long keep = ~0ull;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    } else {
+      cudaGetLastError();
+    }
+  }
   API_END
 }
 
@@ -375,8 +393,9 @@ template <typename R> void storage_resize(THCState *state, StorageT<R> *s, ptrdi
     }
   }
   if (s->data && (s->flag & TH_STORAGE_FREEMEM)) {
-    // the old block may still be read by work queued on the stream
-    THCudaCheck(cudaStreamSynchronize(state_stream(state)));
+    // the old block may still be read by work queued on the stream: the default allocator frees in
+    // stream order; any other allocator gets a quiet stream first
+    if (s->allocator->free != default_free) THCudaCheck(cudaStreamSynchronize(state_stream(state)));
     s->allocator->free(s->allocatorContext, s->data);
   }
   s->data = nd;

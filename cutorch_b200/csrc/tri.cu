@@ -15,47 +15,120 @@ namespace thcb {
 namespace {
 
 constexpr int kTriThreads = 256;
-constexpr int kTriUnroll = 4;
+constexpr int kTriUnroll = 4;   // fast-dim elements per thread
+constexpr int kTriRows = 8;     // slow-dim lines per CTA
 
 // fast dim f (lanes), slow dim s.  row_is_fast tells which of them is the matrix row.
+// A CTA covers kTriThreads * kTriUnroll positions of the fast dim on kTriRows lines of the slow one.
 template <typename W>
 __global__ void __launch_bounds__(kTriThreads)
 tri_kernel(W *out, const W *in, uint64_t nfast, uint64_t nslow, int64_t of, int64_t os, int64_t inf, int64_t ins,
            int64_t k, int upper, int row_is_fast, uint32_t tiles_f) {
-  const uint64_t slow = blockIdx.x / tiles_f;
-  const uint64_t f0 = (uint64_t)(blockIdx.x - slow * tiles_f) * (kTriThreads * kTriUnroll) + threadIdx.x;
-  W x[kTriUnroll];
-  bool keep[kTriUnroll];
+  const uint64_t stile = blockIdx.x / tiles_f;
+  const uint64_t f0 = (uint64_t)(blockIdx.x - stile * tiles_f) * (kTriThreads * kTriUnroll) + threadIdx.x;
+  // two lines at a time: all of their loads are issued before the first store (out may be in)
+  for (int line = 0; line < kTriRows; line += 2) {
+    W x[2][kTriUnroll];
 #pragma unroll
-  for (int u = 0; u < kTriUnroll; ++u) {
-    const uint64_t f = f0 + (uint64_t)u * kTriThreads;
-    const int64_t r = row_is_fast ? (int64_t)f : (int64_t)slow;
-    const int64_t c = row_is_fast ? (int64_t)slow : (int64_t)f;
-    keep[u] = f < nfast && (upper ? (c - r >= k) : (c - r <= k));
-    x[u] = W(0);
-    if (keep[u]) x[u] = in[(int64_t)f * inf + (int64_t)slow * ins];
+    for (int l = 0; l < 2; ++l) {
+      const uint64_t slow = stile * kTriRows + line + l;
+#pragma unroll
+      for (int u = 0; u < kTriUnroll; ++u) {
+        const uint64_t f = f0 + (uint64_t)u * kTriThreads;
+        const int64_t r = row_is_fast ? (int64_t)f : (int64_t)slow;
+        const int64_t c = row_is_fast ? (int64_t)slow : (int64_t)f;
+        const bool keep = slow < nslow && f < nfast && (upper ? (c - r >= k) : (c - r <= k));
+        x[l][u] = W(0);
+        if (keep) x[l][u] = in[(int64_t)f * inf + (int64_t)slow * ins];
+      }
+    }
+#pragma unroll
+    for (int l = 0; l < 2; ++l) {
+      const uint64_t slow = stile * kTriRows + line + l;
+#pragma unroll
+      for (int u = 0; u < kTriUnroll; ++u) {
+        const uint64_t f = f0 + (uint64_t)u * kTriThreads;
+        if (slow < nslow && f < nfast) out[(int64_t)f * of + (int64_t)slow * os] = x[l][u];
+      }
+    }
   }
+}
+
+// Rows with unit stride in both tensors, 16-byte aligned: a thread moves whole 16-byte vectors
+// (V elements); a vector entirely outside the triangle is stored as zeros without being read.
+template <typename W>
+__global__ void __launch_bounds__(kTriThreads)
+tri_vec_kernel(W *out, const W *in, uint64_t ncols, uint64_t nrows, int64_t orow, int64_t irow, int64_t k, int upper,
+               uint32_t tiles_f) {
+  constexpr int V = 16 / (int)sizeof(W);
+  const uint64_t nvec = ncols / V;   // ncols is a multiple of V
+  const uint64_t stile = blockIdx.x / tiles_f;
+  const uint64_t v0 = (uint64_t)(blockIdx.x - stile * tiles_f) * (kTriThreads * kTriUnroll) + threadIdx.x;
+  for (int line = 0; line < kTriRows; line += 2) {
+    Bytes16 x[2][kTriUnroll];
 #pragma unroll
-  for (int u = 0; u < kTriUnroll; ++u) {
-    const uint64_t f = f0 + (uint64_t)u * kTriThreads;
-    if (f < nfast) out[(int64_t)f * of + (int64_t)slow * os] = x[u];
+    for (int l = 0; l < 2; ++l) {
+      const uint64_t r = stile * kTriRows + line + l;
+#pragma unroll
+      for (int u = 0; u < kTriUnroll; ++u) {
+        const uint64_t v = v0 + (uint64_t)u * kTriThreads;
+        const int64_t c0 = (int64_t)(v * V);
+        // does any element of the vector lie inside the triangle?
+        const bool any = r < nrows && v < nvec && (upper ? (c0 + V - 1 - (int64_t)r >= k) : (c0 - (int64_t)r <= k));
+        x[l][u] = Bytes16();
+        if (any) {
+          x[l][u] = ld16_stream(in + (int64_t)r * irow + c0);
+          W *e = reinterpret_cast<W *>(&x[l][u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const int64_t d = c0 + j - (int64_t)r;
+            if (!(upper ? d >= k : d <= k)) e[j] = W(0);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int l = 0; l < 2; ++l) {
+      const uint64_t r = stile * kTriRows + line + l;
+#pragma unroll
+      for (int u = 0; u < kTriUnroll; ++u) {
+        const uint64_t v = v0 + (uint64_t)u * kTriThreads;
+        if (r < nrows && v < nvec) st16(out + (int64_t)r * orow + (int64_t)(v * V), x[l][u]);
+      }
+    }
   }
 }
 
 template <typename W>
 int launch_tri(const HostView &vo, const HostView &vi, int64_t k, int upper, cudaStream_t st) {
+  constexpr int V = 16 / (int)sizeof(W);
+  W *op = reinterpret_cast<W *>(vo.data);
+  const W *ip = reinterpret_cast<const W *>(vi.data);
+  if (V > 1 && vo.strides[1] == 1 && vi.strides[1] == 1 && vo.sizes[1] % V == 0 && vo.strides[0] % V == 0 &&
+      vi.strides[0] % V == 0 && (uintptr_t)op % 16 == 0 && (uintptr_t)ip % 16 == 0) {
+    const uint64_t nvec = (uint64_t)vo.sizes[1] / V;
+    const uint64_t tiles_f = (nvec + kTriThreads * kTriUnroll - 1) / (kTriThreads * kTriUnroll);
+    const uint64_t blocks = tiles_f * (((uint64_t)vo.sizes[0] + kTriRows - 1) / kTriRows);
+    if (blocks >= (1ull << 31)) { set_error("tri: matrix too large"); return THCB200_ERR_DIMS; }
+    set_plan_name("tri_rows_vec");
+    tri_vec_kernel<W><<<(unsigned)blocks, kTriThreads, 0, st>>>(op, ip, (uint64_t)vo.sizes[1], (uint64_t)vo.sizes[0],
+                                                                vo.strides[0], vi.strides[0], k, upper, (uint32_t)tiles_f);
+    count_launch();
+    THCB_CUDA_TRY(cudaGetLastError());
+    return 0;
+  }
   // lanes along the dim where the output's stride is smaller in magnitude
   auto mag = [](int64_t s) { return s < 0 ? -s : s; };
   const int fast = mag(vo.strides[1]) <= mag(vo.strides[0]) ? 1 : 0;
   const int slow = 1 - fast;
   const uint64_t nfast = (uint64_t)vo.sizes[fast], nslow = (uint64_t)vo.sizes[slow];
   const uint64_t tiles_f = (nfast + kTriThreads * kTriUnroll - 1) / (kTriThreads * kTriUnroll);
-  const uint64_t blocks = tiles_f * nslow;
+  const uint64_t blocks = tiles_f * ((nslow + kTriRows - 1) / kTriRows);
   if (blocks >= (1ull << 31) || tiles_f >= (1ull << 31)) { set_error("tri: matrix too large"); return THCB200_ERR_DIMS; }
   set_plan_name(fast == 1 ? "tri_rows" : "tri_cols");
-  tri_kernel<W><<<(unsigned)blocks, kTriThreads, 0, st>>>(reinterpret_cast<W *>(vo.data), reinterpret_cast<const W *>(vi.data),
-                                                          nfast, nslow, vo.strides[fast], vo.strides[slow], vi.strides[fast],
-                                                          vi.strides[slow], k, upper, fast == 0 ? 1 : 0, (uint32_t)tiles_f);
+  tri_kernel<W><<<(unsigned)blocks, kTriThreads, 0, st>>>(op, ip, nfast, nslow, vo.strides[fast], vo.strides[slow],
+                                                          vi.strides[fast], vi.strides[slow], k, upper, fast == 0 ? 1 : 0,
+                                                          (uint32_t)tiles_f);
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());
   return 0;
