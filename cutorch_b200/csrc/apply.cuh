@@ -80,6 +80,73 @@ apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
 }
 
 // ----------------------------------------------------------------------------------
+// rows: the operands collapse to two dims [R, C]; along C every operand is either dense
+// (stride 1) or constant (stride 0: one value per row, e.g. an expanded per-row factor); along
+// R any stride, 0 included (an expanded bias vector).  Rows with padding between them land here
+// too.  A thread moves 16-byte vectors of the dense operands and reads the constant ones as
+// scalars; the CTA is shaped [ty rows x tx vectors] with tx = the power of two covering C.
+// ----------------------------------------------------------------------------------
+constexpr int kRowsUnroll = 4;
+struct RowsPlan {
+  uint32_t R, Cvec;        // rows; 16-byte vectors per row
+  uint32_t tiles_c;        // CTAs along C
+  int log2_tx;             // threads along C = 1 << log2_tx (<= 256)
+  int64_t row_stride[4];   // elements
+  int constant[4];         // 1: stride 0 along C
+};
+
+template <int OP, typename T, int NIN>
+__global__ void __launch_bounds__(kApplyThreads)
+apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpParams<T> p) {
+  constexpr int V = 16 / (int)sizeof(T);
+  constexpr int U = kRowsUnroll;
+  const unsigned tx = 1u << pl.log2_tx, ty = kApplyThreads >> pl.log2_tx;
+  const unsigned x = threadIdx.x & (tx - 1), y = threadIdx.x >> pl.log2_tx;
+  const uint32_t ctile = blockIdx.x % pl.tiles_c, rtile = blockIdx.x / pl.tiles_c;
+  const uint32_t cv = ctile * tx + x;
+  if (cv >= pl.Cvec) return;
+  const T *in[3] = {a, b, c};
+  Bytes16 v[3][U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint32_t r = (rtile * U + u) * ty + y;
+    if (r < pl.R) {
+#pragma unroll
+      for (int o = 0; o < NIN; ++o) {
+        const T *row = in[o] + (int64_t)r * pl.row_stride[o + 1];
+        if (pl.constant[o + 1]) {
+          const T s = *row;
+          T *e = reinterpret_cast<T *>(&v[o][u]);
+#pragma unroll
+          for (int k = 0; k < V; ++k) e[k] = s;
+        } else {
+          v[o][u] = ld16_stream(row + (uint64_t)cv * V);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint32_t r = (rtile * U + u) * ty + y;
+    if (r < pl.R) {
+      Bytes16 vo;
+      T *eo = reinterpret_cast<T *>(&vo);
+      const T *ea = reinterpret_cast<const T *>(&v[0][u]);
+      const T *eb = reinterpret_cast<const T *>(&v[1][u]);
+      const T *ec = reinterpret_cast<const T *>(&v[2][u]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        T xx = NIN >= 1 ? ea[k] : T();
+        T yy = NIN >= 2 ? eb[k] : T();
+        T zz = NIN >= 3 ? ec[k] : T();
+        eo[k] = pw_apply<OP, T>(p, xx, yy, zz);
+      }
+      st16(out + (int64_t)r * pl.row_stride[0] + (uint64_t)cv * V, vo);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------
 // generic
 // ----------------------------------------------------------------------------------
 template <int OP, typename T, int NIN, typename IndexT>

@@ -65,6 +65,14 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       apply_tiled_kernel<OP, T, NIN><<<(unsigned)blocks, kTiledThreads, smem, st>>>(out, a, b, c, t, p, plan.tiled_slots);
       break;
     }
+    case kApplyRows: {
+      const RowsPlan &r = plan.rows;
+      const uint64_t rows_per_cta = (uint64_t)(kApplyThreads >> r.log2_tx) * kRowsUnroll;
+      const uint64_t blocks = (uint64_t)r.tiles_c * (((uint64_t)r.R + rows_per_cta - 1) / rows_per_cta);
+      set_plan_name("rows");
+      apply_rows_kernel<OP, T, NIN><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+      break;
+    }
     case kApplyGeneric: {
       const uint64_t tile = (uint64_t)kApplyThreads * kApplyUnroll;
       const uint64_t blocks = (n + tile - 1) / tile;

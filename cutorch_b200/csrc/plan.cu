@@ -232,6 +232,36 @@ bool try_tiled(const Dims &d, int nops, size_t elem_size, ApplyPlan *plan) {
   return true;
 }
 
+// Two collapsed dims, every operand dense or constant along the inner one (see apply_rows_kernel).
+bool try_rows(const Dims &d, int nops, const HostView *ops, size_t elem_size, ApplyPlan *plan) {
+  if (d.n != 2 || elem_size == 0) return false;
+  const int64_t V = (int64_t)(16 / elem_size);
+  const int64_t R = d.size[0], C = d.size[1];
+  if (C % V != 0 || R >= (1LL << 31) || C / V >= (1LL << 31)) return false;
+  if (d.stride[0][1] != 1) return false;   // the output has to be dense along C
+  RowsPlan &rp = plan->rows;
+  for (int o = 0; o < 4; ++o) { rp.row_stride[o] = 0; rp.constant[o] = 0; }
+  for (int o = 0; o < nops; ++o) {
+    const int64_t sc = d.stride[o][1], sr = d.stride[o][0];
+    if (sc == 1) {
+      if (sr % V != 0 || ((uintptr_t)ops[o].data) % 16 != 0) return false;
+    } else if (sc != 0) {
+      return false;
+    }
+    rp.row_stride[o] = sr;
+    rp.constant[o] = sc == 0 ? 1 : 0;
+  }
+  rp.R = (uint32_t)R;
+  rp.Cvec = (uint32_t)(C / V);
+  int lg = 0;
+  while ((1u << lg) < rp.Cvec && lg < 8) ++lg;
+  rp.log2_tx = lg;
+  rp.tiles_c = (rp.Cvec + (1u << lg) - 1) >> lg;
+  const uint64_t rows_per_cta = (uint64_t)(256 >> lg) * kRowsUnroll;
+  const uint64_t blocks = (uint64_t)rp.tiles_c * (((uint64_t)R + rows_per_cta - 1) / rows_per_cta);
+  return blocks < (1ULL << 31);
+}
+
 }  // namespace
 
 void make_apply_plan(const HostView *ops, int nops, size_t elem_size, ApplyPlan *plan) {
@@ -296,6 +326,7 @@ void make_apply_plan(const HostView *ops, int nops, size_t elem_size, ApplyPlan 
     }
     if (all_unit && elem_size) { plan->kind = kApplyContigVec; plan->index64 = true; return; }
     if (elem_size && try_tiled(f, nops, elem_size, plan)) { plan->kind = kApplyTiled; plan->index64 = false; return; }
+    if (elem_size && try_rows(f, nops, ops, elem_size, plan)) { plan->kind = kApplyRows; plan->index64 = false; return; }
   } else {
     // Shapes differ (only the element counts agree): every operand is walked in its own
     // row-major order, as THC_pointwiseApply does.

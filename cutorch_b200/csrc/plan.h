@@ -29,7 +29,7 @@ void offset_range(const HostView &v, int64_t *lo, int64_t *hi);
 // TensorUtils::canUse32BitIndexMath (lib/THC/THCTensorTypeUtils.cu:220-245).
 bool can_use_32bit(const HostView &v);
 
-enum ApplyKind { kApplyContigVec = 0, kApplyTiled = 1, kApplyGeneric = 2, kApplyDeep = 3 };
+enum ApplyKind { kApplyContigVec = 0, kApplyTiled = 1, kApplyGeneric = 2, kApplyDeep = 3, kApplyRows = 4 };
 
 struct ApplyPlan {
   ApplyKind kind;
@@ -44,6 +44,8 @@ struct ApplyPlan {
   // tiled
   TiledPlan tiled;
   int tiled_slots;                 // number of operands staged through shared memory
+  // rows
+  RowsPlan rows;
 };
 
 // ops[0] is the output.  All views hold the same number of elements.

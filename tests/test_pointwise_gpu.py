@@ -354,3 +354,45 @@ def test_large_contiguous_matches_numpy(state):
         else:
             want = (a.astype(np.int64) * b.astype(np.int64)).astype(a.dtype)
         assert_bit_equal(out.numpy(), want, f"{kind} cmul 1e6")
+
+
+@pytest.mark.parametrize("kind", ["Byte", "Int", "Half", "Float", "Double"])
+def test_rows_plan_expanded_and_padded_operands(state, oracle, kind):
+    """Two collapsed dims with operands that are dense or constant along the inner one: per-row
+    factors and bias rows seen through stride-0 (expanded) views, and rows with padding.  These
+    take the `rows` kernel; results must equal the oracle's walk of the same strided views."""
+    import ctypes as C
+    lib = state.lib
+    lib.thcb200_last_plan.restype = C.c_char_p
+    r = rng("rows", kind)
+    R, Cc = 301, 256
+    x = make_view(r, kind, (R, Cc), "contiguous")
+    per_row = np.broadcast_to(make_view(r, kind, (R, 1), "contiguous"), (R, Cc))     # strides (1, 0)
+    per_col = np.broadcast_to(make_view(r, kind, (1, Cc), "contiguous"), (R, Cc))    # strides (0, 1)
+    padded = random_array(r, kind, (R, Cc + 32))[:, :Cc]                             # row stride C + 32
+    v = as_real(kind, 2)
+    cases = [("cmul", "MUL", [x, per_row], ()), ("cadd", "CADD", [x, per_col], (v,)),
+             ("addcmul", "ADDCMUL", [x, per_row, per_col], (v,)), ("cmul", "MUL", [padded, x], ()),
+             ("cmax", "CMAX", [per_col, padded], ())]
+    for name, op, ins, scal in cases:
+        want = oracle.pointwise(OP[op], np.zeros((R, Cc), x.dtype), ins, *scal)
+        dins = [to_device(state, a) for a in ins]
+        out = thc.Tensor.new(state, kind)
+        if name == "cadd":
+            out.cadd(dins[0], v, dins[1])
+        elif name == "addcmul":
+            out.addcmul(dins[0], v, dins[1], dins[2])
+        else:
+            getattr(out, name)(dins[0], dins[1])
+        assert lib.thcb200_last_plan().decode() == "rows", (name, lib.thcb200_last_plan().decode())
+        check(kind, out.numpy(), want, True, f"{kind}.{name} rows plan")
+        # into a padded output
+        dout = to_device(state, random_array(r, kind, (R, Cc + 32))[:, :Cc])
+        if name == "cadd":
+            dout.cadd(dins[0], v, dins[1])
+        elif name == "addcmul":
+            dout.addcmul(dins[0], v, dins[1], dins[2])
+        else:
+            getattr(dout, name)(dins[0], dins[1])
+        assert lib.thcb200_last_plan().decode() == "rows"
+        check(kind, dout.numpy(), want, True, f"{kind}.{name} rows plan, padded output")
