@@ -75,7 +75,31 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
   const T *ip = in + ioff;
   T *op = out + ooff;
   A carry = scan_identity<A, PROD>();
-  if (!TOTAL_ONLY && carries) carry = carries[unit];
+  if constexpr (TOTAL_ONLY) {
+    // only the fold of the chunk is wanted: every lane folds what it loads, one butterfly at the end
+    A acc = scan_identity<A, PROD>();
+    for (uint64_t base = k0; base < k1; base += (uint64_t)32 * V * U) {
+      Pack<T, V> x[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
+        if (pos < k1) x[u] = *reinterpret_cast<const Pack<T, V> *>(ip + pos);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
+        if (pos < k1) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc = scan_op<A, PROD>(acc, to_acc<T, A>(x[u].v[j]));
+        }
+      }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) acc = scan_op<A, PROD>(acc, __shfl_xor_sync(0xffffffffu, acc, d));
+    if (lane == 0) carries[unit] = acc;
+    return;
+  }
+  if (carries) carry = carries[unit];
   for (uint64_t base = k0; base < k1; base += (uint64_t)32 * V * U) {
     Pack<T, V> x[U];
 #pragma unroll
@@ -116,15 +140,14 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
   if (TOTAL_ONLY && lane == 0) carries[unit] = carry;
 }
 
-// chunk totals -> exclusive carries, in place; a warp per row, lanes own consecutive segments
+// chunk totals -> exclusive carries, in place; a CTA per row, threads own consecutive segments
 template <typename A, bool PROD>
 __global__ void __launch_bounds__(kScanThreads) scan_row_carry_kernel(A *carries, uint64_t nrows, uint32_t S) {
-  const unsigned lane = threadIdx.x & 31;
-  const uint64_t row = (uint64_t)blockIdx.x * kScanWarps + (threadIdx.x >> 5);
-  if (row >= nrows) return;
-  A *c = carries + row * S;
-  const uint32_t per = (S + 31) / 32;
-  const uint32_t lo = lane * per < S ? lane * per : S;
+  __shared__ A wtot[kScanWarps];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  A *c = carries + (uint64_t)blockIdx.x * S;
+  const uint32_t per = (S + kScanThreads - 1) / kScanThreads;
+  const uint32_t lo = threadIdx.x * per < S ? threadIdx.x * per : S;
   const uint32_t hi = lo + per < S ? lo + per : S;
   A tot = scan_identity<A, PROD>();
   for (uint32_t i = lo; i < hi; ++i) tot = scan_op<A, PROD>(tot, c[i]);
@@ -134,8 +157,12 @@ __global__ void __launch_bounds__(kScanThreads) scan_row_carry_kernel(A *carries
     const A y = __shfl_up_sync(0xffffffffu, incl, d);
     if (lane >= (unsigned)d) incl = scan_op<A, PROD>(y, incl);
   }
-  A run = __shfl_up_sync(0xffffffffu, incl, 1);
-  if (lane == 0) run = scan_identity<A, PROD>();
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  A run = scan_identity<A, PROD>();
+  for (unsigned w = 0; w < warp; ++w) run = scan_op<A, PROD>(run, wtot[w]);
+  A excl = __shfl_up_sync(0xffffffffu, incl, 1);
+  if (lane != 0) run = scan_op<A, PROD>(run, excl);
   for (uint32_t i = lo; i < hi; ++i) {
     const A v = c[i];
     c[i] = run;
@@ -397,7 +424,7 @@ int launch_scan(thcb200_ctx *ctx, const HostView &in, const HostView &out, int d
         if (pl.vec) scan_row_kernel<T, PROD, true, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
         else scan_row_kernel<T, PROD, false, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
         unsigned g2;
-        if ((rc = blocks_for(pl.nslices, kScanWarps, &g2))) return rc;
+        if ((rc = blocks_for(pl.nslices, 1, &g2))) return rc;
         scan_row_carry_kernel<A, PROD><<<g2, kScanThreads, 0, st>>>(carries, pl.nslices, pl.S);
         launches += 2;
       }
