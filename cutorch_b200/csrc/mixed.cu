@@ -235,22 +235,32 @@ __device__ __forceinline__ uint32_t nonzero_bits16(const Bytes16 &v) {
   return bits;
 }
 
-// Unit-stride, 16-byte aligned mask, whole tiles only: a thread counts its 16 bytes with bit
-// arithmetic, a CTA the 4096 of its tile.
-__global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint32_t *counts) {
-  __shared__ uint32_t wsum[kThreads / 32];
-  const Bytes16 v = ld16_stream(mask + (uint64_t)blockIdx.x * kTile + (uint64_t)threadIdx.x * 16);
-  uint32_t c = 0;
+// Unit-stride, 16-byte aligned mask, whole tiles only: a thread counts its 16 bytes of a tile with
+// bit arithmetic; a CTA takes kCountTiles consecutive tiles, all loads first.
+constexpr int kCountTiles = 4;
+__global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint64_t full_tiles, uint32_t *counts) {
+  __shared__ uint32_t wsum[kCountTiles][kThreads / 32];
+  const uint64_t tile0 = (uint64_t)blockIdx.x * kCountTiles;
+  Bytes16 v[kCountTiles];
 #pragma unroll
-  for (int w = 0; w < 4; ++w) c += __popc(nonzero_bytes(v.w[w]));
-  c = __reduce_add_sync(0xffffffffu, c);
-  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
+  for (int t = 0; t < kCountTiles; ++t) {
+    v[t] = Bytes16();
+    if (tile0 + t < full_tiles) v[t] = ld16_stream(mask + (tile0 + t) * kTile + (uint64_t)threadIdx.x * 16);
+  }
+#pragma unroll
+  for (int t = 0; t < kCountTiles; ++t) {
+    uint32_t c = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) c += __popc(nonzero_bytes(v[t].w[w]));
+    c = __reduce_add_sync(0xffffffffu, c);
+    if ((threadIdx.x & 31) == 0) wsum[t][threadIdx.x >> 5] = c;
+  }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < kCountTiles && tile0 + threadIdx.x < full_tiles) {
     uint32_t s = 0;
 #pragma unroll
-    for (int w = 0; w < kThreads / 32; ++w) s += wsum[w];
-    counts[blockIdx.x] = s;
+    for (int w = 0; w < kThreads / 32; ++w) s += wsum[threadIdx.x][w];
+    counts[tile0 + threadIdx.x] = s;
   }
 }
 
@@ -311,32 +321,45 @@ mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, 
   }
 }
 
-// offsets[i] = counts[0] + ... + counts[i-1]; *total = sum of all.  One CTA of 1024 threads,
-// each owning a consecutive run of tiles.
+// offsets[i] = counts[0] + ... + counts[i-1]; *total = sum of all.  One CTA of 1024 threads: warp w
+// owns a consecutive span of tiles and walks it 32 tiles at a time with coalesced loads (first to
+// add its span up, then, once the 32 span totals are scanned, to write the offsets).
 __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts, uint64_t *offsets, uint64_t ntiles,
                                                          int64_t *total) {
-  __shared__ uint64_t part[1024];
-  const uint64_t per = (ntiles + 1023) / 1024;
-  const uint64_t lo = (uint64_t)threadIdx.x * per;
-  const uint64_t hi = lo + per < ntiles ? lo + per : ntiles;
+  __shared__ uint64_t span_total[32];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint64_t steps = (ntiles + 1023) / 1024;          // 32-tile steps per warp
+  const uint64_t lo = (uint64_t)warp * steps * 32;
   uint64_t s = 0;
-  for (uint64_t i = lo; i < hi; ++i) s += counts[i];
-  part[threadIdx.x] = s;
+  for (uint64_t j = 0; j < steps; j += 4) {
+    uint32_t v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint64_t i = lo + (j + u) * 32 + lane;
+      v[u] = (j + u < steps && i < ntiles) ? counts[i] : 0u;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s += v[u];
+  }
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+  if (lane == 0) span_total[warp] = s;
   __syncthreads();
-  // Hillis-Steele inclusive scan over the 1024 run sums
-  for (int d = 1; d < 1024; d <<= 1) {
-    uint64_t add = 0;
-    if ((int)threadIdx.x >= d) add = part[threadIdx.x - d];
-    __syncthreads();
-    part[threadIdx.x] += add;
-    __syncthreads();
+  uint64_t run = 0;
+  for (unsigned w = 0; w < warp; ++w) run += span_total[w];
+  if (threadIdx.x == 1023) *total = (int64_t)(run + s);
+  for (uint64_t j = 0; j < steps; ++j) {
+    const uint64_t i = lo + j * 32 + lane;
+    const uint32_t v = i < ntiles ? counts[i] : 0u;
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= (unsigned)d) incl += y;
+    }
+    if (i < ntiles) offsets[i] = run + (incl - v);
+    run += __shfl_sync(0xffffffffu, incl, 31);
   }
-  uint64_t run = part[threadIdx.x] - s;  // exclusive prefix of this thread's run
-  for (uint64_t i = lo; i < hi; ++i) {
-    offsets[i] = run;
-    run += counts[i];
-  }
-  if (threadIdx.x == 1023) *total = (int64_t)part[1023];
 }
 
 // SELECT: packed[pos] = strided[i];  otherwise (copy): strided[i] = packed[pos]; for set mask
@@ -580,7 +603,7 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   const uint64_t full = mask_vec ? n / kTile : 0;
   int launches = 1;
   if (full > 0) {
-    mask_tile_count_vec_kernel<<<(unsigned)full, kThreads, 0, st>>>(mask, counts);
+    mask_tile_count_vec_kernel<<<(unsigned)((full + kCountTiles - 1) / kCountTiles), kThreads, 0, st>>>(mask, full, counts);
     ++launches;
   }
   if (full < mp->ntiles) {

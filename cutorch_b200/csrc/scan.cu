@@ -236,10 +236,19 @@ __global__ void __launch_bounds__(kScanThreads) scan_col_carry_kernel(A *carries
   const uint64_t o = t / I, col = t - o * I;
   A *c = carries + o * S * I + col;
   A run = scan_identity<A, PROD>();
-  for (uint32_t i = 0; i < S; ++i) {
-    const A v = c[(uint64_t)i * I];
-    c[(uint64_t)i * I] = run;
-    run = scan_op<A, PROD>(run, v);
+  // eight totals are loaded before the first carry is stored (loads and stores alias otherwise)
+  for (uint32_t i0 = 0; i0 < S; i0 += 8) {
+    A v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i0 + u < S) v[u] = c[(uint64_t)(i0 + u) * I];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (i0 + u < S) {
+        c[(uint64_t)(i0 + u) * I] = run;
+        run = scan_op<A, PROD>(run, v[u]);
+      }
+    }
   }
 }
 

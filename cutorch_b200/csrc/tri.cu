@@ -73,16 +73,21 @@ tri_vec_kernel(W *out, const W *in, uint64_t ncols, uint64_t nrows, int64_t orow
       for (int u = 0; u < kTriUnroll; ++u) {
         const uint64_t v = v0 + (uint64_t)u * kTriThreads;
         const int64_t c0 = (int64_t)(v * V);
-        // does any element of the vector lie inside the triangle?
-        const bool any = r < nrows && v < nvec && (upper ? (c0 + V - 1 - (int64_t)r >= k) : (c0 - (int64_t)r <= k));
+        // d = column - row - k of the vector's first element; element j is kept when d + j >= 0
+        // (upper) or d + j <= 0 (lower)
+        const int64_t d = c0 - (int64_t)r - k;
+        const bool inside = r < nrows && v < nvec;
+        const bool any = inside && (upper ? d + (V - 1) >= 0 : d <= 0);
+        const bool all = upper ? d >= 0 : d + (V - 1) <= 0;
         x[l][u] = Bytes16();
         if (any) {
           x[l][u] = ld16_stream(in + (int64_t)r * irow + c0);
-          W *e = reinterpret_cast<W *>(&x[l][u]);
+          if (!all) {
+            W *e = reinterpret_cast<W *>(&x[l][u]);
+            const int dd = (int)d;   // |d| < V here
 #pragma unroll
-          for (int j = 0; j < V; ++j) {
-            const int64_t d = c0 + j - (int64_t)r;
-            if (!(upper ? d >= k : d <= k)) e[j] = W(0);
+            for (int j = 0; j < V; ++j)
+              if (!(upper ? dd + j >= 0 : dd + j <= 0)) e[j] = W(0);
           }
         }
       }
