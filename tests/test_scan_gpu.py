@@ -96,6 +96,32 @@ def test_scan_exact_values_and_plans(state, oracle):
         assert_bit_equal(out.numpy(), oracle.scan_dim(False, x, dim), f"exact cumsum {shape} dim {dim}")
 
 
+@pytest.mark.parametrize("kind", ["Float", "Int", "Half", "Double", "Byte"])
+def test_scan_long_rows_one_pass(state, oracle, kind):
+    """Rows of millions of elements (thousands of chunks per row), ragged ends, more than one row."""
+    r = rng("scan-long", kind)
+    per_tile = 256 * 4 * (16 // NP_OF_KIND[kind].itemsize)
+    for rows, tiles, extra in [(1, 1030, 8 * 3), (3, 2100, 16 * 5), (2, 33, 0)]:
+        K = tiles * per_tile + extra
+        x = make_view(r, kind, (rows, K), "contiguous")
+        if kind in INT_KINDS:
+            x[...] = r.integers(0, 3, size=x.shape).astype(x.dtype)
+        elif kind == "Half":
+            x[...] = (r.integers(-2, 3, size=x.shape) / 4).astype(x.dtype)   # running sums stay exact in float
+        else:
+            x[...] = (r.integers(-1000, 1001, size=x.shape) / 8).astype(x.dtype)
+        dx = to_device(state, x)
+        out = thc.Tensor.new(state, kind)
+        out.cumsum(dx, 1)
+        want = oracle.scan_dim(False, x, 1)
+        if kind == "Half":
+            check_scan(kind, out.numpy(), want, x, 1, False, f"{kind} long rows {rows}x{K}")
+        else:
+            assert_bit_equal(out.numpy(), want, f"{kind} long rows {rows}x{K}")
+        dx.cumsum(dx, 1)
+        assert_bit_equal(dx.numpy(), out.numpy(), f"{kind} long rows in place")
+
+
 def test_scan_repeatable_and_errors(state):
     r = rng("scan-rep")
     x = r.standard_normal((8, 1 << 18)).astype(np.float32)
