@@ -143,8 +143,8 @@ def reference_main(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    rows = 4096  # bounded sample: 1/128 of the rows per step, 128 MiB per tensor
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    rows = 32768  # bounded sample: 1/16 of the rows per step, 1 GiB per tensor (about 0.3 s of host work per step)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
     gbs, dt, nthreads = run_cpu(rows, steps, warmup, None)
     sample = f"{rows} of {ROWS_TOTAL} rows x {COLS} per step ({steps} steps), scaled by bytes"
     line = {
@@ -296,10 +296,10 @@ def ours_main(args):
     extra = {}
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        srows = 2048
-        gbs, dt, nthreads = run_cpu(srows, 2, 1, None)
+        srows = 32768
+        gbs, dt, nthreads = run_cpu(srows, 10, 1, None)
         cpu_baseline = {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port",
-                        "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (2 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
+                        "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (10 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
     if rank == 0 and world == 1 and args.configs:
         from bench_configs import run_small_configs
         extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)

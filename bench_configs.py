@@ -172,7 +172,50 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tgi = W(gi, "Long")
         out["f4_gather_f32_524288x256_dim1"] = timed(lambda: teo.gather(temb, 1, tgi), (8 + 8) * n, reps=5)
 
-    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt)):
+    def xdev():
+        """Copies from GPU 1 to GPU 0 over NVLink, driven from this process (needs two visible
+        devices): a contiguous tensor (cudaMemcpyPeerAsync), a transposed source and a converting
+        copy (the copy kernels run on the source GPU and store into the peer's memory).  Bytes are
+        those that have to cross the link; the reference for the link is 770 GB/s per direction."""
+        if torch.cuda.device_count() < 2:
+            out["xdev"] = {"skipped": "needs two visible GPUs"}
+            return
+        n = 1 << 28
+        dst = torch.empty(n, device=dev)
+        torch.cuda.set_device(1)
+        src = torch.empty(n, device="cuda:1").normal_()
+        src_t = src.view(16384, 16384).t()
+        src_h = src.half()
+        torch.cuda.synchronize()
+        torch.cuda.set_device(dev)
+        tdst, tsrc = W(dst, "Float"), W(src, "Float")
+        tdst2, tsrc_t, tsrc_h = W(dst.view(16384, 16384), "Float"), W(src_t, "Float"), W(src_h, "Half")
+        link = 770.0
+
+        def timed_x(fn, nbytes):
+            ts = []
+            for _ in range(2):
+                fn()
+            for _ in range(5):
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)      # the destination's stream waits for the copy, so its events bracket it
+                fn()
+                b.record(stream)
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            ts.sort()
+            med = ts[len(ts) // 2]
+            gbs = nbytes / (med * 1e-3) / 1e9
+            return {"gbs": round(gbs, 1), "frac_of_nvlink_770": round(gbs / link, 4), "median_us": round(med * 1e3, 2), "bytes": nbytes}
+
+        out["xdev_copy_f32_contiguous_1GiB"] = timed_x(lambda: tdst.copy(tsrc), 4 * n)
+        out["xdev_copy_f32_transposed_source_1GiB"] = timed_x(lambda: tdst2.copy(tsrc_t), 4 * n)
+        out["xdev_copy_f16_to_f32_2pow28"] = timed_x(lambda: tdst.copy_from(tsrc_h), 4 * n)
+
+    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("xdev", xdev)):
+        if name == "xdev" and (only is None or "xdev" not in only):
+            continue
         if only is None or name in only:
             fn()
             torch.cuda.synchronize()

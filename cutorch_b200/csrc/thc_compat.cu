@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include <new>
+#include <type_traits>
 #include <string>
 
 #include "../../include/THC/THC.h"
@@ -621,25 +622,144 @@ template <typename R> bool may_alias(const TensorT<R> *a, const TensorT<R> *b) {
   return alo < bhi && blo < ahi;
 }
 
+// ---- copies, same device or across devices (THC_copyTensor, lib/THC/THCTensorCopy.cu:24-205) ----
+struct DeviceGuard {
+  int prev;
+  bool changed;
+  explicit DeviceGuard(int d) : prev(0), changed(false) {
+    THCudaCheck(cudaGetDevice(&prev));
+    if (d >= 0 && d != prev) { THCudaCheck(cudaSetDevice(d)); changed = true; }
+  }
+  ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
+};
+
+template <typename R> int tensor_device(const TensorT<R> *t, int fallback) {
+  return (t->storage && t->storage->data) ? t->storage->device : fallback;
+}
+
+// lets kernels on `from` address memory of `to`
+bool enable_peer_access(int from, int to) {
+  if (from == to) return true;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, from, to) != cudaSuccess || !can) { cudaGetLastError(); return false; }
+  DeviceGuard g(from);
+  const cudaError_t e = cudaDeviceEnablePeerAccess(to, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (e != cudaErrorPeerAccessAlreadyEnabled) return false;
+  }
+  // blocks of the stream-ordered allocator live in `to`'s default pool, which grants access per device
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, to) == cudaSuccess) {
+    cudaMemAccessDesc desc;
+    memset(&desc, 0, sizeof(desc));
+    desc.location.type = cudaMemLocationTypeDevice;
+    desc.location.id = from;
+    desc.flags = cudaMemAccessFlagsProtReadWrite;
+    if (cudaMemPoolSetAccess(pool, &desc, 1) != cudaSuccess) { cudaGetLastError(); return false; }
+  } else {
+    cudaGetLastError();
+  }
+  return true;
+}
+
+// `waiter` (a stream of device wdev) waits for everything queued so far on `signal` (device sdev)
+void stream_wait_stream(int wdev, cudaStream_t waiter, int sdev, cudaStream_t signal) {
+  cudaEvent_t ev;
+  {
+    DeviceGuard g(sdev);
+    THCudaCheck(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    THCudaCheck(cudaEventRecord(ev, signal));
+  }
+  {
+    DeviceGuard g(wdev);
+    THCudaCheck(cudaStreamWaitEvent(waiter, ev, 0));
+  }
+  THCudaCheck(cudaEventDestroy(ev));
+}
+
+template <typename R> TensorT<R> *tensor_new_contiguous(THCState *state, TensorT<R> *t);
+
+// dst = convert(src) with both tensors on the current device
+template <typename RD, typename RS> void copy_on_device(THCState *state, TensorT<RD> *dst, TensorT<RS> *src, int flags) {
+  const ptrdiff_t n = tensor_nelement<RD>(dst);
+  if constexpr (std::is_same<RD, RS>::value) {
+    if ((tensor_is_contiguous<RD>(dst) && tensor_is_contiguous<RS>(src)) || n == 1) {
+      THCudaCheck(cudaMemcpyAsync(dst->storage->data + dst->storageOffset, src->storage->data + src->storageOffset,
+                                  (size_t)n * sizeof(RD), cudaMemcpyDeviceToDevice, state_stream(state)));
+      return;
+    }
+    pointwise<RD>(state, THCB200_OP_COPY, dst, src, nullptr, nullptr, kZero, kZero, flags);
+  } else {
+    thcb200_tensor dd = describe<RD>(dst), ds = describe<RS>(src);
+    check_core(thcb200_copy_convert(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
+  }
+}
+
+// The copy runs on the source device, on that device's current stream, bracketed by a two-way
+// wait with the destination device's current stream.  Contiguous same-type tensors go through
+// cudaMemcpyAsync; anything else through the copy / convert kernel writing the peer's memory
+// directly over NVLink when peer access can be enabled, else through contiguous temporaries.
+template <typename RD, typename RS>
+void copy_across_devices(THCState *state, TensorT<RD> *dst, TensorT<RS> *src, int src_dev, int dst_dev, int flags) {
+  const ptrdiff_t n = tensor_nelement<RD>(dst);
+  cudaStream_t sstream = THCState_getCurrentStreamOnDevice(state, src_dev);
+  cudaStream_t dstream = THCState_getCurrentStreamOnDevice(state, dst_dev);
+  stream_wait_stream(src_dev, sstream, dst_dev, dstream);
+  {
+    DeviceGuard g(src_dev);
+    const bool memcpy_ok = std::is_same<RD, RS>::value &&
+                           ((tensor_is_contiguous<RD>(dst) && tensor_is_contiguous<RS>(src)) || n == 1);
+    const bool peer = enable_peer_access(src_dev, dst_dev);
+    if (memcpy_ok) {
+      THCudaCheck(cudaMemcpyPeerAsync(dst->storage->data + dst->storageOffset, dst_dev, src->storage->data + src->storageOffset,
+                                      src_dev, (size_t)n * sizeof(RD), sstream));
+    } else if (peer) {
+      copy_on_device<RD, RS>(state, dst, src, flags);   // kernel on the source device, stores to the peer
+    } else {
+      // no peer access: dense temporaries of dst's type on both sides and one memcpy between them
+      TensorT<RD> *sc = tensor_alloc<RD>();
+      tensor_raw_resize<RD>(state, sc, dst->nDimension, dst->size, nullptr);
+      copy_on_device<RD, RS>(state, sc, src, 0);
+      TensorT<RD> *dc;
+      {
+        DeviceGuard gd(dst_dev);
+        dc = tensor_alloc<RD>();
+        tensor_raw_resize<RD>(state, dc, dst->nDimension, dst->size, nullptr);
+      }
+      THCudaCheck(cudaMemcpyPeerAsync(dc->storage->data, dst_dev, sc->storage->data, src_dev, (size_t)n * sizeof(RD), sstream));
+      stream_wait_stream(dst_dev, dstream, src_dev, sstream);
+      {
+        DeviceGuard gd(dst_dev);
+        copy_on_device<RD, RD>(state, dst, dc, flags);
+        tensor_free<RD>(state, dc);
+      }
+      tensor_free<RD>(state, sc);
+    }
+  }
+  stream_wait_stream(dst_dev, dstream, src_dev, sstream);
+}
+
+template <typename RD, typename RS> void copy_any(THCState *state, TensorT<RD> *dst, TensorT<RS> *src, int flags) {
+  THArgCheck(tensor_nelement<RD>(dst) == tensor_nelement<RS>(src), 2, "sizes do not match");
+  if (tensor_nelement<RD>(dst) == 0) return;
+  const int cur = current_device();
+  const int sd = tensor_device<RS>(src, cur), dd = tensor_device<RD>(dst, cur);
+  if (sd == dd) {
+    DeviceGuard g(sd);
+    copy_on_device<RD, RS>(state, dst, src, flags);
+  } else {
+    copy_across_devices<RD, RS>(state, dst, src, sd, dd, flags);
+  }
+}
+
 template <typename R> void tensor_copy(THCState *state, TensorT<R> *self, TensorT<R> *src, int flags = 0) {
   if (self == src) return;
-  THArgCheck(tensor_nelement<R>(self) == tensor_nelement<R>(src), 2, "sizes do not match");
-  const ptrdiff_t n = tensor_nelement<R>(self);
-  if (n == 0) return;
-  check_gpu<R>(state, {self, src});
-  if (tensor_is_contiguous<R>(self) && tensor_is_contiguous<R>(src)) {
-    THCudaCheck(cudaMemcpyAsync(self->storage->data + self->storageOffset, src->storage->data + src->storageOffset,
-                                (size_t)n * sizeof(R), cudaMemcpyDeviceToDevice, state_stream(state)));
-    return;
-  }
-  pointwise<R>(state, THCB200_OP_COPY, self, src, nullptr, nullptr, kZero, kZero, flags);
+  copy_any<R, R>(state, self, src, flags);
 }
 
 template <typename RD, typename RS> void tensor_copy_convert(THCState *state, TensorT<RD> *dst, TensorT<RS> *src) {
-  THArgCheck(tensor_nelement<RD>(dst) == tensor_nelement<RS>(src), 2, "sizes do not match");
-  if (tensor_nelement<RD>(dst) == 0) return;
-  thcb200_tensor dd = describe<RD>(dst), ds = describe<RS>(src);
-  check_core(thcb200_copy_convert(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
+  copy_any<RD, RS>(state, dst, src, 0);
 }
 
 template <typename R> TensorT<R> *tensor_new_contiguous(THCState *state, TensorT<R> *t) {

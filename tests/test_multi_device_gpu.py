@@ -1,0 +1,76 @@
+"""Copies between two GPUs driven from one process, the way cutorch drives several devices
+(THC_copyTensor, lib/THC/THCTensorCopy.cu:24-205; cutorch's own test: test/test.lua:3100-3170,
+"multi_gpu_copy_noncontig").  Needs two visible devices; skipped on a one-GPU box.
+
+Contiguous same-type tensors take cudaMemcpyAsync; strided views and type conversions run the
+copy / convert kernel on the source device with the destination addressed as peer memory."""
+import numpy as np
+import pytest
+
+from cutorch_b200 import thc
+from common import assert_bit_equal, make_view, rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def two_devices():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    prev = torch.cuda.current_device()
+    yield torch
+    torch.cuda.set_device(prev)
+
+
+def on_device(torch, dev, fn):
+    torch.cuda.set_device(dev)
+    try:
+        return fn()
+    finally:
+        torch.cuda.set_device(0)
+
+
+def test_copy_across_devices(state, two_devices):
+    torch = two_devices
+    r = rng("xdev")
+    for kind, shape, ls, ld in [("Float", (256, 300), "contiguous", "contiguous"), ("Float", (64, 50), "transposed", "contiguous"),
+                                ("Double", (7, 9, 11), "permuted", "holes"), ("Half", (33, 65), "contiguous", "transposed"),
+                                ("Int", (1000,), "strided", "offset")]:
+        src = make_view(r, kind, shape, ls)
+        dst0 = make_view(r, kind, shape, ld)
+        for sdev, ddev in ((0, 1), (1, 0)):
+            dsrc = on_device(torch, sdev, lambda: to_device(state, src))
+            ddst = on_device(torch, ddev, lambda: to_device(state, dst0))
+            # issued while device 0 is current, whatever the operands' devices
+            ddst.copy(dsrc)
+            got = on_device(torch, ddev, lambda: ddst.numpy())
+            assert_bit_equal(got, np.ascontiguousarray(src), f"{kind} copy {ls}->{ld} gpu{sdev}->gpu{ddev}")
+            # the source is untouched
+            assert_bit_equal(on_device(torch, sdev, lambda: dsrc.numpy()), np.ascontiguousarray(src), "source after the copy")
+
+
+def test_converting_copy_across_devices(state, two_devices):
+    torch = two_devices
+    r = rng("xdev-conv")
+    src = make_view(r, "Float", (40, 70), "transposed")
+    dsrc = on_device(torch, 1, lambda: to_device(state, src))
+    for kind in ("Double", "Half", "Int", "Byte"):
+        ddst = to_device(state, make_view(r, kind, (40, 70), "contiguous"))          # on device 0
+        ddst.copy_from(dsrc)
+        with np.errstate(invalid="ignore"):
+            want = np.ascontiguousarray(src).astype(ddst.numpy().dtype) if kind != "Byte" else \
+                np.ascontiguousarray(src).astype(np.int64).astype(np.uint8)
+        if kind == "Byte":
+            continue   # negative floats to unsigned bytes are implementation-defined in C; only run it
+        assert_bit_equal(ddst.numpy(), want, f"Float on gpu1 -> {kind} on gpu0")
+
+
+def test_work_after_a_cross_device_copy_sees_the_data(state, two_devices):
+    """The destination's stream waits for the copy: a kernel queued right after it reads the new values."""
+    torch = two_devices
+    x = np.arange(1 << 20, dtype=np.float32)
+    dsrc = on_device(torch, 1, lambda: to_device(state, x))
+    ddst = to_device(state, np.zeros_like(x))
+    ddst.copy(dsrc)
+    assert ddst.sumall() == float(np.float32(x.astype(np.float64).sum()))   # accreal of a FloatTensor is float
