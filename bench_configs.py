@@ -60,6 +60,33 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
             rg = nbytes / (per * 1e-3) / 1e9
             r.update({"back_to_back_gbs": round(rg, 1), "back_to_back_frac": round(rg / peak, 4),
                       "back_to_back_us": round(per * 1e3, 2), "buffer_sets": len(rot)})
+            # the same train recorded once into a CUDA graph and replayed: no per-call host work
+            side = torch.cuda.Stream(device=dev)
+            didx = dev.index if dev.index is not None else 0
+            state.set_stream(side.cuda_stream, didx)
+            try:
+                with torch.cuda.stream(side):
+                    for f in rot:
+                        f()
+                    side.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        for f in rot:
+                            f()
+                    graph.replay()
+                    side.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(side)
+                    for _ in range(rounds):
+                        graph.replay()
+                    b.record(side)
+                    side.synchronize()
+                per = a.elapsed_time(b) / (rounds * len(rot))
+                rg = nbytes / (per * 1e-3) / 1e9
+                r.update({"graph_replay_gbs": round(rg, 1), "graph_replay_frac": round(rg / peak, 4),
+                          "graph_replay_us": round(per * 1e3, 2)})
+            finally:
+                state.set_stream(stream.cuda_stream, didx)
         return r
 
     keep = []   # buffer sets of the back-to-back timings, dropped when their config is done

@@ -137,3 +137,46 @@ def test_int64_indexing_path(state):
     assert int(buf[stride + 7]) == 7 and int(buf[8]) == 0
     del buf
     torch.cuda.empty_cache()
+
+
+def test_int64_offsets_in_the_mixed_type_scan_and_index_kernels(state):
+    """The same huge-stride view through the calls that have their own kernels: comparison into
+    bytes, masked fill / select, scans and indexed moves all have to carry 64-bit offsets."""
+    torch = pytest.importorskip("torch")
+    lib = _lib.load_library()
+    dev = torch.device("cuda", 0)
+    buf = torch.zeros(5 * 2**30, dtype=torch.uint8, device=dev)
+    stride = 2**32 + 16
+    host = np.arange(16, dtype=np.uint8).reshape(2, 8) + 1
+    buf[0:8] = torch.from_numpy(host[0]).to(dev)
+    buf[stride:stride + 8] = torch.from_numpy(host[1]).to(dev)
+    t = thc.Tensor.wrap(state, "Byte", buf.data_ptr(), (2, 8), (stride, 1), storage_elems=5 * 2**30)
+    # comparison into a dense byte tensor
+    out = thc.Tensor.new(state, "Byte")
+    t.call("gtValue", out, t, 8)
+    assert lib.thcb200_last_plan() == b"compare_strided64"
+    assert out.numpy().tolist() == (host > 8).astype(np.uint8).tolist()
+    # masked select / fill with the huge view as source / target
+    mask = thc.Tensor.from_numpy(state, (host % 2 == 0).astype(np.uint8))
+    sel = thc.Tensor.new(state, "Byte")
+    sel.maskedSelect(t, mask)
+    assert lib.thcb200_last_plan() == b"masked_select64"
+    assert sel.numpy().tolist() == host[host % 2 == 0].tolist()
+    # scans along both dims (rows are 8 long: the per-slice walk; columns: strided)
+    for dim in (0, 1):
+        c = thc.Tensor.new(state, "Byte")
+        c.cumsum(t, dim)
+        assert c.numpy().tolist() == np.cumsum(host, axis=dim, dtype=np.uint64).astype(np.uint8).tolist()
+    # indexed moves: pick rows, then write one back through the huge stride
+    idx = thc.Tensor.from_numpy(state, np.array([2, 1, 2], np.int64))
+    picked = thc.Tensor.new(state, "Byte")
+    picked.indexSelect(t, 0, idx)
+    assert picked.numpy().tolist() == host[[1, 0, 1]].tolist()
+    t.indexFill(0, thc.Tensor.from_numpy(state, np.array([2], np.int64)), 9)
+    t.maskedFill(mask, 0)
+    torch.cuda.synchronize()
+    want_row1 = np.where(host[1] % 2 == 0, 0, 9).astype(np.uint8)
+    assert buf[stride:stride + 8].cpu().numpy().tolist() == want_row1.tolist()
+    assert buf[0:8].cpu().numpy().tolist() == np.where(host[0] % 2 == 0, 0, host[0]).tolist()
+    del buf
+    torch.cuda.empty_cache()
