@@ -10,7 +10,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
 #include <new>
+#include <set>
 #include <type_traits>
 #include <string>
 
@@ -100,7 +102,23 @@ cudaStream_t state_stream(THCState *state);
 // current when it is freed, so a storage has to be freed while the stream that last used it is
 // current (or after that stream was synchronised).
 cudaError_t default_malloc(void *, void **p, size_t n, cudaStream_t st) { return cudaMallocAsync(p, n, st); }
-cudaError_t default_free(void *ctx, void *p) { return cudaFreeAsync(p, state_stream((THCState *)ctx)); }
+
+// States that are initialised right now: a storage may outlive its THCState, and must not follow a
+// dangling pointer when it is finally freed (it is then released in the order of the null stream).
+std::mutex g_live_states_mutex;
+std::set<const void *> g_live_states;
+void mark_state(const void *state, bool live) {
+  std::lock_guard<std::mutex> lock(g_live_states_mutex);
+  if (live) g_live_states.insert(state); else g_live_states.erase(state);
+}
+cudaError_t default_free(void *ctx, void *p) {
+  bool live;
+  {
+    std::lock_guard<std::mutex> lock(g_live_states_mutex);
+    live = g_live_states.count(ctx) != 0;
+  }
+  return cudaFreeAsync(p, live ? state_stream((THCState *)ctx) : (cudaStream_t)0);
+}
 
 int current_device() {
   int d = 0;
@@ -185,6 +203,7 @@ void THCudaInit(THCState *state) {
   state->defaultAllocator.state = state;
   state->allocator = &state->defaultAllocator;
   state->initialised = 1;
+  mark_state(state, true);
   // keep freed blocks in the pools instead of returning them to the driver at every synchronise
   for (int d = 0; d < n; ++d) {
     cudaMemPool_t pool;
@@ -200,6 +219,7 @@ void THCudaInit(THCState *state) {
 
 void THCudaShutdown(THCState *state) {
   if (!state || !state->initialised) return;
+  mark_state(state, false);
   for (int d = 0; d < state->numDevices; ++d) {
     if (state->ctx[d]) thcb200_ctx_destroy(state->ctx[d]);
     if (state->current[d]) THCStream_free(state->current[d]);

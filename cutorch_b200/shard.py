@@ -41,7 +41,7 @@ def combine_partials(partial: torch.Tensor, op: str = "sum", group=None) -> torc
 
 
 def combine_index_partials(values: torch.Tensor, positions: torch.Tensor, shard_start: int, is_max: bool = True,
-                           group=None) -> tuple[torch.Tensor, torch.Tensor]:
+                           group=None, state=None) -> tuple[torch.Tensor, torch.Tensor]:
     """max / min with 1-based positions along the sharded dim.
 
     `values` / `positions` are this rank's results over its own block (positions 1-based inside
@@ -56,9 +56,40 @@ def combine_index_partials(values: torch.Tensor, positions: torch.Tensor, shard_
     ps = [torch.empty_like(gpos) for _ in range(world)]
     dist.all_gather(vs, values.contiguous(), group=group)
     dist.all_gather(ps, gpos.contiguous(), group=group)
-    best_v, best_p = vs[0].clone(), ps[0].clone()
-    for v, p in zip(vs[1:], ps[1:]):
-        if values.is_floating_point():
+    return combine_gathered(torch.stack(vs), torch.stack(ps), is_max, state)
+
+
+_KIND_OF_TORCH = {torch.uint8: "Byte", torch.int8: "Char", torch.int16: "Short", torch.int32: "Int", torch.int64: "Long",
+                  torch.float16: "Half", torch.float32: "Float", torch.float64: "Double"}
+
+
+def combine_gathered(vals: torch.Tensor, poss: torch.Tensor, is_max: bool = True, state=None):
+    """Combines per-rank (value, global position) pairs stacked along dim 0 (rank order = block
+    order) into the values and positions one scan over the unsharded dim would give.
+
+    With a THC `state` and CUDA tensors the combine runs on this library's kernels: a max / min
+    with positions along dim 0 (first occurrence, a NaN wins: the rule of the unsharded call, and
+    the lowest rank among equals is the lowest global position) followed by a gather of the
+    positions.  Without one (the CPU tests) the same rule is applied with torch operations."""
+    if state is not None and vals.is_cuda:
+        from . import thc
+
+        def wrap(t, kind):
+            w = thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+            w._owner = t
+            return w
+        vals, poss = vals.contiguous(), poss.contiguous()
+        kind = _KIND_OF_TORCH[vals.dtype]
+        best_v = torch.empty((1,) + tuple(vals.shape[1:]), dtype=vals.dtype, device=vals.device)
+        which = torch.empty((1,) + tuple(vals.shape[1:]), dtype=torch.int64, device=vals.device)
+        best_p = torch.empty_like(which)
+        tv, tw = wrap(best_v, kind), wrap(which, "Long")
+        (tv.max if is_max else tv.min)(tw, wrap(vals, kind), 0, 1)
+        wrap(best_p, "Long").gather(wrap(poss, "Long"), 0, tw)
+        return best_v[0], best_p[0]
+    best_v, best_p = vals[0].clone(), poss[0].clone()
+    for v, p in zip(vals[1:], poss[1:]):
+        if vals.is_floating_point():
             bn, vn = torch.isnan(best_v), torch.isnan(v)
         else:
             bn = vn = torch.zeros_like(v, dtype=torch.bool)

@@ -251,3 +251,28 @@ def test_dist(state, oracle, kind):
     d = (np.ascontiguousarray(a) - np.ascontiguousarray(b)).astype(np.float64)   # difference rounded to the element type first
     for p, want in ((0, float((d != 0).sum())), (1, np.abs(d).sum()), (2, np.sqrt((d * d).sum())), (3, (np.abs(d) ** 3).sum() ** (1 / 3))):
         assert_reduction_close(da.call("dist", da, db, p), want, REL[kind] * 4, 1.0, f"{kind}.dist({p})")
+
+
+def test_combine_of_gathered_value_position_pairs_on_the_gpu(state):
+    """The combine step of a max / min with positions along a sharded dim (cutorch_b200.shard):
+    on the GPU it is this library's max-with-positions over the rank dim plus a gather of the
+    positions, and has to agree with the rule applied by plain torch operations on the host."""
+    import torch
+    from cutorch_b200.shard import combine_gathered
+    r = rng("combine-gathered")
+    world, n = 8, 5000
+    vals = r.integers(-3, 4, size=(world, n)).astype(np.float32)      # many ties across ranks
+    vals[r.uniform(size=vals.shape) < 0.01] = np.nan                  # a NaN wins, the first one
+    rows_per_rank = 100
+    poss = (r.integers(1, rows_per_rank + 1, size=(world, n)) + np.arange(world)[:, None] * rows_per_rank).astype(np.int64)
+    stream = torch.cuda.current_stream()
+    state.set_stream(stream.cuda_stream, 0)
+    try:
+        for is_max in (True, False):
+            want_v, want_p = combine_gathered(torch.from_numpy(vals), torch.from_numpy(poss), is_max, None)
+            got_v, got_p = combine_gathered(torch.from_numpy(vals).cuda(), torch.from_numpy(poss).cuda(), is_max, state)
+            torch.cuda.synchronize()
+            assert_bit_equal(got_v.cpu().numpy(), want_v.numpy(), f"combined values, max={is_max}")
+            assert_bit_equal(got_p.cpu().numpy(), want_p.numpy(), f"combined positions, max={is_max}")
+    finally:
+        state.set_stream(0, 0)
