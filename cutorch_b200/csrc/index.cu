@@ -70,26 +70,27 @@ template <> __device__ __forceinline__ void atomic_add_elem<int16_t>(int16_t *p,
 template <typename T, int MODE, bool REDIRECT_DST, typename IndexT>
 __global__ void __launch_bounds__(kIdxThreads)
 indexed_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, IndexT n, T value, unsigned int *errors) {
+  // Offsets are kept in IndexT: with 32-bit indices every tensor's largest offset fits 32 bits, so
+  // sums taken modulo 2^32 are exact.
   const IndexT base = (IndexT)blockIdx.x * (IndexT)(kIdxThreads * kIdxUnroll) + threadIdx.x;
-  int64_t off_plain[kIdxUnroll], off_redir[kIdxUnroll];
+  IndexT off_plain[kIdxUnroll], off_redir[kIdxUnroll];
   int64_t pos[kIdxUnroll];
   bool live[kIdxUnroll];
 #pragma unroll
   for (int u = 0; u < kIdxUnroll; ++u) {
     IndexT lin = base + (IndexT)u * kIdxThreads;
     live[u] = lin < n;
-    int64_t op = 0, orr = 0, oi = 0;
+    IndexT op = 0, orr = 0, oi = 0;
     if (live[u]) {
-#pragma unroll
-      for (int d = kGenericDims - 1; d >= 0; --d) {
-        if (d < p.nd) {
-          IndexT q, r;
-          p.size[d].divmod(lin, q, r);
-          op += (int64_t)r * p.plain[d];
-          orr += (int64_t)r * p.redir[d];
-          oi += (int64_t)r * p.index[d];
-          lin = q;
-        }
+      // only the dims in use are walked (the plan sits in constant memory, indexed at run time)
+#pragma unroll 1
+      for (int d = p.nd - 1; d >= 0; --d) {
+        IndexT q, r;
+        p.size[d].divmod(lin, q, r);
+        op += r * (IndexT)p.plain[d];
+        orr += r * (IndexT)p.redir[d];
+        oi += r * (IndexT)p.index[d];
+        lin = q;
       }
       pos[u] = index[oi] - 1;   // positions are 1-based (TH_INDEX_BASE)
     }
@@ -101,7 +102,7 @@ indexed_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, In
   for (int u = 0; u < kIdxUnroll; ++u) {
     if (!live[u]) continue;
     if ((uint64_t)pos[u] >= (uint64_t)p.limit) { live[u] = false; ++bad; continue; }
-    off_redir[u] += pos[u] * p.redirect_stride;
+    off_redir[u] += (IndexT)pos[u] * (IndexT)p.redirect_stride;
   }
   if (bad) atomicAdd(errors, bad);
   T x[kIdxUnroll];
@@ -127,6 +128,7 @@ struct HostIdxPlan {
   int64_t size[kMaxDims], plain[kMaxDims], redir[kMaxDims], index[kMaxDims];
   int64_t redirect_stride, limit;
   uint64_t n;
+  bool fits32;   // element counts and largest offsets of all three tensors fit 32 bits
 };
 
 template <typename IndexT>
@@ -152,7 +154,7 @@ int launch_indexed(thcb200_ctx *ctx, const HostIdxPlan &h, void *dst, const void
   const uint64_t blocks = (h.n + per_cta - 1) / per_cta;
   if (blocks >= (1ull << 31)) { set_error("indexed: tensor too large"); return THCB200_ERR_DIMS; }
   unsigned int *errors = reinterpret_cast<unsigned int *>(ctx->status) + 1;
-  if (h.n < (1ull << 32) - per_cta) {
+  if (h.fits32 && h.n < (1ull << 32) - per_cta) {
     set_plan_name("indexed32");
     indexed_kernel<T, MODE, REDIRECT_DST, uint32_t><<<(unsigned)blocks, kIdxThreads, 0, st>>>(
         (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint32_t>(h), (uint32_t)h.n, value, errors);
@@ -237,6 +239,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
   HostIdxPlan h;
   h.nd = 0;
   h.n = n;
+  h.fits32 = can_use_32bit(vd) && can_use_32bit(vi) && (fill || can_use_32bit(vs));
   h.redirect_stride = redir.strides[dim];
   h.limit = redir.sizes[dim];
   bool prev_mergeable = false;
