@@ -1,6 +1,7 @@
 """Generates the golden fixtures of tests/golden/ from cutorch's own code.
 
-Needs oracle/_ref/libref_check.so, i.e. a checkout of cutorch at /root/reference (make -C oracle).
+Needs oracle/_ref/libref_check.so, i.e. a checkout of cutorch where oracle/Makefile's REF points
+(make -C oracle REF=<cutorch tree>).
 The fixtures travel with the repository so that the checks also run where the reference tree is
 absent:
   collapse_dims.json  TensorInfo::collapseDims outputs (lib/THC/THCTensorInfo.cuh:74-224) and
