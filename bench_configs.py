@@ -199,6 +199,23 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tgi = W(gi, "Long")
         out["f4_gather_f32_524288x256_dim1"] = timed(lambda: teo.gather(temb, 1, tgi), (8 + 8) * n, reps=5)
 
+    def generic():
+        """Layouts that only the generic strided walk can take: rows of an odd length with an odd
+        pitch (no 16-byte alignment from row to row), and three operands permuted three different ways."""
+        R, Cc, pitch = 16384, 8191, 8195
+        bufs = [torch.empty(R, pitch, device=dev).normal_(generator=g) for _ in range(3)]
+        a, b, o = (t[:, :Cc] for t in bufs)
+        ta, tb, to_ = W(a, "Float"), W(b, "Float"), W(o, "Float")
+        n = R * Cc
+        out["a4_cadd_f32_odd_rows_16384x8191_pitch_8195"] = timed(lambda: to_.cadd(ta, 2.5, tb), 12 * n, reps=5)
+        base = [torch.empty(256, 512, 1024, device=dev).normal_(generator=g) for _ in range(3)]
+        p0 = base[0]                                  # (256, 512, 1024) contiguous
+        p1 = base[1].view(512, 256, 1024).transpose(0, 1)   # dims 0 and 1 swapped in memory
+        p2 = base[2].view(256, 1024, 512).transpose(1, 2)   # dims 1 and 2 swapped in memory
+        t0, t1, t2 = W(p0, "Float"), W(p1, "Float"), W(p2, "Float")
+        n = p0.numel()
+        out["a4_cmul_f32_three_permutations_256x512x1024"] = timed(lambda: t0.cmul(t1, t2), 12 * n, reps=5)
+
     def xdev():
         """Copies from GPU 1 to GPU 0 over NVLink, driven from this process (needs two visible
         devices): a contiguous tensor (cudaMemcpyPeerAsync), a transposed source and a converting
@@ -240,7 +257,7 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         out["xdev_copy_f32_transposed_source_1GiB"] = timed_x(lambda: tdst2.copy(tsrc_t), 4 * n)
         out["xdev_copy_f16_to_f32_2pow28"] = timed_x(lambda: tdst.copy_from(tsrc_h), 4 * n)
 
-    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("xdev", xdev)):
+    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("generic", generic), ("xdev", xdev)):
         if name == "xdev" and (only is None or "xdev" not in only):
             continue
         if only is None or name in only:

@@ -86,41 +86,46 @@ apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
 // too.  A thread moves 16-byte vectors of the dense operands and reads the constant ones as
 // scalars; the CTA is shaped [ty rows x tx vectors] with tx = the power of two covering C.
 // ----------------------------------------------------------------------------------
-constexpr int kRowsUnroll = 4;
+constexpr int kRowsUnroll = 4;      // rows per thread
+constexpr int kRowsScalarCols = 4;  // column slots per thread when elements move one by one
 struct RowsPlan {
-  uint32_t R, Cvec;        // rows; 16-byte vectors per row
+  uint32_t R, Cvec;        // rows; units per row (16-byte vectors, or single elements when !vec)
   uint32_t tiles_c;        // CTAs along C
   int log2_tx;             // threads along C = 1 << log2_tx (<= 256)
+  int vec;                 // 1: 16-byte vectors (rows aligned), 0: single elements (any pitch)
   int64_t row_stride[4];   // elements
   int constant[4];         // 1: stride 0 along C
 };
 
-template <int OP, typename T, int NIN>
+// V = elements per unit: 16 / sizeof(T), or 1 for rows whose pitch or base breaks the alignment.
+template <int OP, typename T, int NIN, int V>
 __global__ void __launch_bounds__(kApplyThreads)
 apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpParams<T> p) {
-  constexpr int V = 16 / (int)sizeof(T);
   constexpr int U = kRowsUnroll;
+  constexpr int UC = V == 1 ? kRowsScalarCols : 1;
+  struct alignas(V * sizeof(T)) Unit { T v[V]; };
   const unsigned tx = 1u << pl.log2_tx, ty = kApplyThreads >> pl.log2_tx;
   const unsigned x = threadIdx.x & (tx - 1), y = threadIdx.x >> pl.log2_tx;
   const uint32_t ctile = blockIdx.x % pl.tiles_c, rtile = blockIdx.x / pl.tiles_c;
-  const uint32_t cv = ctile * tx + x;
-  if (cv >= pl.Cvec) return;
   const T *in[3] = {a, b, c};
-  Bytes16 v[3][U];
+  Unit v[3][U][UC];
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const uint32_t r = (rtile * U + u) * ty + y;
-    if (r < pl.R) {
 #pragma unroll
-      for (int o = 0; o < NIN; ++o) {
-        const T *row = in[o] + (int64_t)r * pl.row_stride[o + 1];
-        if (pl.constant[o + 1]) {
-          const T s = *row;
-          T *e = reinterpret_cast<T *>(&v[o][u]);
+    for (int k = 0; k < UC; ++k) {
+      const uint32_t cv = (ctile * UC + k) * tx + x;
+      if (r < pl.R && cv < pl.Cvec) {
 #pragma unroll
-          for (int k = 0; k < V; ++k) e[k] = s;
-        } else {
-          v[o][u] = ld16_stream(row + (uint64_t)cv * V);
+        for (int o = 0; o < NIN; ++o) {
+          const T *row = in[o] + (int64_t)r * pl.row_stride[o + 1];
+          if (pl.constant[o + 1]) {
+            const T s = *row;
+#pragma unroll
+            for (int j = 0; j < V; ++j) v[o][u][k].v[j] = s;
+          } else {
+            v[o][u][k] = *reinterpret_cast<const Unit *>(row + (uint64_t)cv * V);
+          }
         }
       }
     }
@@ -128,20 +133,20 @@ apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpPar
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const uint32_t r = (rtile * U + u) * ty + y;
-    if (r < pl.R) {
-      Bytes16 vo;
-      T *eo = reinterpret_cast<T *>(&vo);
-      const T *ea = reinterpret_cast<const T *>(&v[0][u]);
-      const T *eb = reinterpret_cast<const T *>(&v[1][u]);
-      const T *ec = reinterpret_cast<const T *>(&v[2][u]);
 #pragma unroll
-      for (int k = 0; k < V; ++k) {
-        T xx = NIN >= 1 ? ea[k] : T();
-        T yy = NIN >= 2 ? eb[k] : T();
-        T zz = NIN >= 3 ? ec[k] : T();
-        eo[k] = pw_apply<OP, T>(p, xx, yy, zz);
+    for (int k = 0; k < UC; ++k) {
+      const uint32_t cv = (ctile * UC + k) * tx + x;
+      if (r < pl.R && cv < pl.Cvec) {
+        Unit vo;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          T xx = NIN >= 1 ? v[0][u][k].v[j] : T();
+          T yy = NIN >= 2 ? v[1][u][k].v[j] : T();
+          T zz = NIN >= 3 ? v[2][u][k].v[j] : T();
+          vo.v[j] = pw_apply<OP, T>(p, xx, yy, zz);
+        }
+        *reinterpret_cast<Unit *>(out + (int64_t)r * pl.row_stride[0] + (uint64_t)cv * V) = vo;
       }
-      st16(out + (int64_t)r * pl.row_stride[0] + (uint64_t)cv * V, vo);
     }
   }
 }

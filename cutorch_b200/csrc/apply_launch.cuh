@@ -69,8 +69,13 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       const RowsPlan &r = plan.rows;
       const uint64_t rows_per_cta = (uint64_t)(kApplyThreads >> r.log2_tx) * kRowsUnroll;
       const uint64_t blocks = (uint64_t)r.tiles_c * (((uint64_t)r.R + rows_per_cta - 1) / rows_per_cta);
-      set_plan_name("rows");
-      apply_rows_kernel<OP, T, NIN><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+      if (r.vec) {
+        set_plan_name("rows");
+        apply_rows_kernel<OP, T, NIN, 16 / (int)sizeof(T)><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+      } else {
+        set_plan_name("rows_scalar");
+        apply_rows_kernel<OP, T, NIN, 1><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+      }
       break;
     }
     case kApplyGeneric: {

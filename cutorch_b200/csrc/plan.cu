@@ -233,30 +233,37 @@ bool try_tiled(const Dims &d, int nops, size_t elem_size, ApplyPlan *plan) {
 }
 
 // Two collapsed dims, every operand dense or constant along the inner one (see apply_rows_kernel).
+// Rows move as 16-byte vectors when every dense operand keeps that alignment from row to row,
+// else element by element.
 bool try_rows(const Dims &d, int nops, const HostView *ops, size_t elem_size, ApplyPlan *plan) {
   if (d.n != 2 || elem_size == 0) return false;
   const int64_t V = (int64_t)(16 / elem_size);
   const int64_t R = d.size[0], C = d.size[1];
-  if (C % V != 0 || R >= (1LL << 31) || C / V >= (1LL << 31)) return false;
+  if (R >= (1LL << 31) || C >= (1LL << 31)) return false;
   if (d.stride[0][1] != 1) return false;   // the output has to be dense along C
   RowsPlan &rp = plan->rows;
+  bool vec = C % V == 0;
   for (int o = 0; o < 4; ++o) { rp.row_stride[o] = 0; rp.constant[o] = 0; }
   for (int o = 0; o < nops; ++o) {
     const int64_t sc = d.stride[o][1], sr = d.stride[o][0];
     if (sc == 1) {
-      if (sr % V != 0 || ((uintptr_t)ops[o].data) % 16 != 0) return false;
+      if (sr % V != 0 || ((uintptr_t)ops[o].data) % 16 != 0) vec = false;
     } else if (sc != 0) {
       return false;
     }
     rp.row_stride[o] = sr;
     rp.constant[o] = sc == 0 ? 1 : 0;
   }
+  rp.vec = vec ? 1 : 0;
   rp.R = (uint32_t)R;
-  rp.Cvec = (uint32_t)(C / V);
+  rp.Cvec = (uint32_t)(vec ? C / V : C);
+  const uint32_t per_thread = vec ? 1 : kRowsScalarCols;
+  const uint32_t slots = (rp.Cvec + per_thread - 1) / per_thread;   // threads wanted along C
   int lg = 0;
-  while ((1u << lg) < rp.Cvec && lg < 8) ++lg;
+  while ((1u << lg) < slots && lg < 8) ++lg;
   rp.log2_tx = lg;
-  rp.tiles_c = (rp.Cvec + (1u << lg) - 1) >> lg;
+  const uint32_t per_cta = (1u << lg) * per_thread;
+  rp.tiles_c = (rp.Cvec + per_cta - 1) / per_cta;
   const uint64_t rows_per_cta = (uint64_t)(256 >> lg) * kRowsUnroll;
   const uint64_t blocks = (uint64_t)rp.tiles_c * (((uint64_t)R + rows_per_cta - 1) / rows_per_cta);
   return blocks < (1ULL << 31);
