@@ -215,6 +215,13 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         t0, t1, t2 = W(p0, "Float"), W(p1, "Float"), W(p2, "Float")
         n = p0.numel()
         out["a4_cmul_f32_three_permutations_256x512x1024"] = timed(lambda: t0.cmul(t1, t2), 12 * n, reps=5)
+        del base, p0, p1, p2, t0, t1, t2
+        # a window cut out of three larger 3-D tensors: three dims, none of them collapsible
+        big = [torch.empty(258, 514, 1004, device=dev).normal_(generator=g) for _ in range(3)]
+        w0, w1, w2 = (t[1:257, 1:513, 2:1002] for t in big)
+        tw0, tw1, tw2 = W(w0, "Float"), W(w1, "Float"), W(w2, "Float")
+        n = 256 * 512 * 1000
+        out["a4_cmul_f32_window_256x512x1000_of_258x514x1004"] = timed(lambda: tw0.cmul(tw1, tw2), 12 * n, reps=5)
 
     def xdev():
         """Copies from GPU 1 to GPU 0 over NVLink, driven from this process (needs two visible

@@ -80,21 +80,41 @@ apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
 }
 
 // ----------------------------------------------------------------------------------
-// rows: the operands collapse to two dims [R, C]; along C every operand is either dense
-// (stride 1) or constant (stride 0: one value per row, e.g. an expanded per-row factor); along
-// R any stride, 0 included (an expanded bias vector).  Rows with padding between them land here
-// too.  A thread moves 16-byte vectors of the dense operands and reads the constant ones as
-// scalars; the CTA is shaped [ty rows x tx vectors] with tx = the power of two covering C.
+// rows: along the innermost collapsed dim C every operand is either dense (stride 1) or constant
+// (stride 0: one value per row, e.g. an expanded per-row factor); the outer dims (up to
+// kRowsOuterDims of them, R rows in all) may have any strides, 0 included (an expanded bias
+// vector), and need not collapse (a window cut out of a larger tensor).  Rows with padding
+// between them land here too.  A row's offsets are decoded once per thread and row; a thread
+// moves 16-byte vectors of the dense operands and reads the constant ones as scalars; the CTA
+// is shaped [ty rows x tx vectors] with tx = the power of two covering C.
 // ----------------------------------------------------------------------------------
 constexpr int kRowsUnroll = 4;      // rows per thread
 constexpr int kRowsScalarCols = 4;  // column slots per thread when elements move one by one
+constexpr int kRowsOuterDims = 7;
 struct RowsPlan {
   uint32_t R, Cvec;        // rows; units per row (16-byte vectors, or single elements when !vec)
   uint32_t tiles_c;        // CTAs along C
   int log2_tx;             // threads along C = 1 << log2_tx (<= 256)
   int vec;                 // 1: 16-byte vectors (rows aligned), 0: single elements (any pitch)
-  int64_t row_stride[4];   // elements
+  int nouter;              // outer dims (>= 1); row number = row-major index over them
+  FastDiv32 outer_size[kRowsOuterDims];
+  int64_t outer_stride[4][kRowsOuterDims];   // elements, per operand
   int constant[4];         // 1: stride 0 along C
+  // element offsets of row r in the four operands
+  __device__ __forceinline__ void row_offsets(uint32_t r, int64_t (&off)[4]) const {
+    off[0] = off[1] = off[2] = off[3] = 0;
+    uint32_t rem = r;
+#pragma unroll 1
+    for (int i = nouter - 1; i >= 1; --i) {
+      uint32_t q, m;
+      outer_size[i].divmod(rem, q, m);
+#pragma unroll
+      for (int o = 0; o < 4; ++o) off[o] += (int64_t)m * outer_stride[o][i];
+      rem = q;
+    }
+#pragma unroll
+    for (int o = 0; o < 4; ++o) off[o] += (int64_t)rem * outer_stride[o][0];
+  }
 };
 
 // V = elements per unit: 16 / sizeof(T), or 1 for rows whose pitch or base breaks the alignment.
@@ -109,16 +129,20 @@ apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpPar
   const uint32_t ctile = blockIdx.x % pl.tiles_c, rtile = blockIdx.x / pl.tiles_c;
   const T *in[3] = {a, b, c};
   Unit v[3][U][UC];
+  int64_t out_off[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const uint32_t r = (rtile * U + u) * ty + y;
+    int64_t off[4] = {0, 0, 0, 0};
+    if (r < pl.R) pl.row_offsets(r, off);
+    out_off[u] = off[0];
 #pragma unroll
     for (int k = 0; k < UC; ++k) {
       const uint32_t cv = (ctile * UC + k) * tx + x;
       if (r < pl.R && cv < pl.Cvec) {
 #pragma unroll
         for (int o = 0; o < NIN; ++o) {
-          const T *row = in[o] + (int64_t)r * pl.row_stride[o + 1];
+          const T *row = in[o] + off[o + 1];
           if (pl.constant[o + 1]) {
             const T s = *row;
 #pragma unroll
@@ -145,7 +169,7 @@ apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpPar
           T zz = NIN >= 3 ? v[2][u][k].v[j] : T();
           vo.v[j] = pw_apply<OP, T>(p, xx, yy, zz);
         }
-        *reinterpret_cast<Unit *>(out + (int64_t)r * pl.row_stride[0] + (uint64_t)cv * V) = vo;
+        *reinterpret_cast<Unit *>(out + out_off[u] + (uint64_t)cv * V) = vo;
       }
     }
   }

@@ -236,22 +236,34 @@ bool try_tiled(const Dims &d, int nops, size_t elem_size, ApplyPlan *plan) {
 // Rows move as 16-byte vectors when every dense operand keeps that alignment from row to row,
 // else element by element.
 bool try_rows(const Dims &d, int nops, const HostView *ops, size_t elem_size, ApplyPlan *plan) {
-  if (d.n != 2 || elem_size == 0) return false;
+  if (d.n < 2 || d.n - 1 > kRowsOuterDims || elem_size == 0) return false;
+  const int nouter = d.n - 1;
   const int64_t V = (int64_t)(16 / elem_size);
-  const int64_t R = d.size[0], C = d.size[1];
-  if (R >= (1LL << 31) || C >= (1LL << 31)) return false;
-  if (d.stride[0][1] != 1) return false;   // the output has to be dense along C
+  const int64_t C = d.size[nouter];
+  int64_t R = 1;
+  for (int i = 0; i < nouter; ++i) {
+    if (d.size[i] >= (1LL << 31)) return false;
+    R *= d.size[i];
+    if (R >= (1LL << 31)) return false;
+  }
+  if (C >= (1LL << 31)) return false;
+  if (d.stride[0][nouter] != 1) return false;   // the output has to be dense along C
   RowsPlan &rp = plan->rows;
   bool vec = C % V == 0;
-  for (int o = 0; o < 4; ++o) { rp.row_stride[o] = 0; rp.constant[o] = 0; }
+  rp.nouter = nouter;
+  for (int i = 0; i < kRowsOuterDims; ++i) {
+    rp.outer_size[i] = FastDiv32(i < nouter ? (uint32_t)d.size[i] : 1u);
+    for (int o = 0; o < 4; ++o) rp.outer_stride[o][i] = 0;
+  }
+  for (int o = 0; o < 4; ++o) rp.constant[o] = 0;
   for (int o = 0; o < nops; ++o) {
-    const int64_t sc = d.stride[o][1], sr = d.stride[o][0];
-    if (sc == 1) {
-      if (sr % V != 0 || ((uintptr_t)ops[o].data) % 16 != 0) vec = false;
-    } else if (sc != 0) {
-      return false;
+    const int64_t sc = d.stride[o][nouter];
+    if (sc != 0 && sc != 1) return false;
+    if (sc == 1 && ((uintptr_t)ops[o].data) % 16 != 0) vec = false;
+    for (int i = 0; i < nouter; ++i) {
+      rp.outer_stride[o][i] = d.stride[o][i];
+      if (sc == 1 && d.stride[o][i] % V != 0) vec = false;
     }
-    rp.row_stride[o] = sr;
     rp.constant[o] = sc == 0 ? 1 : 0;
   }
   rp.vec = vec ? 1 : 0;

@@ -126,8 +126,8 @@ def test_int64_indexing_path(state):
     stride = 2**32 + 16
     buf[0] = 3
     buf[stride] = 4
-    # three dims that do not collapse (the middle stride is 3, not 2): the generic walk
-    t = thc.Tensor.wrap(state, "Byte", buf.data_ptr(), (2, 3, 2), (stride, 3, 1), storage_elems=5 * 2**30)
+    # three dims that do not collapse and an inner stride of 2: only the generic walk takes this
+    t = thc.Tensor.wrap(state, "Byte", buf.data_ptr(), (2, 3, 2), (stride, 5, 2), storage_elems=5 * 2**30)
     assert _lib.load_library().thcb200_can_use_32bit(C.byref(t.descriptor())) == 0
     out = thc.Tensor.new(state, "Byte")
     out.add(t, 1)
@@ -135,12 +135,15 @@ def test_int64_indexing_path(state):
     assert out.numpy().reshape(2, 6).tolist() == [[4, 1, 1, 1, 1, 1], [5, 1, 1, 1, 1, 1]]
     t.fill(7)
     torch.cuda.synchronize()
-    assert int(buf[stride + 7]) == 7 and int(buf[8]) == 0 and int(buf[2]) == 0
+    assert int(buf[stride + 12]) == 7 and int(buf[7]) == 7 and int(buf[8]) == 0 and int(buf[1]) == 0
+    buf.zero_()
+    buf[0] = 3
+    buf[stride] = 4
     # two dims with a dense inner one: the row walk, whose row offsets are 64-bit as well
     t2 = thc.Tensor.wrap(state, "Byte", buf.data_ptr(), (2, 8), (stride, 1), storage_elems=5 * 2**30)
     out.add(t2, 1)
     assert _lib.load_library().thcb200_last_plan() == b"rows_scalar"
-    assert out.numpy().tolist() == [[8, 8, 1, 8, 8, 1, 8, 8], [8, 8, 1, 8, 8, 1, 8, 8]]
+    assert out.numpy().tolist() == [[4, 1, 1, 1, 1, 1, 1, 1], [5, 1, 1, 1, 1, 1, 1, 1]]
     del buf
     torch.cuda.empty_cache()
 
