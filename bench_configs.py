@@ -222,6 +222,17 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tw0, tw1, tw2 = W(w0, "Float"), W(w1, "Float"), W(w2, "Float")
         n = 256 * 512 * 1000
         out["a4_cmul_f32_window_256x512x1000_of_258x514x1004"] = timed(lambda: tw0.cmul(tw1, tw2), 12 * n, reps=5)
+        # full reductions of views that are not one dense run
+        out["a9_sumall_f32_window_256x512x1000"] = timed(lambda: tw0.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
+        tr = big[1].view(258 * 514, 1004).t()
+        ttr = W(tr, "Float")
+        out["a9_sumall_f32_transposed_1004x132612"] = timed(lambda: ttr.sumall_to_device(res.data_ptr()), 4 * tr.numel(), reps=5)
+        rowsum = torch.empty(256, 512, 1, device=dev)
+        trs = W(rowsum, "Float")
+        out["a7_sum_dim2_f32_window_256x512x1000"] = timed(lambda: trs.sum(tw0, 2, 1), 4 * n, reps=5)
+        colsum = torch.empty(1, 512, 1000, device=dev)
+        tcs = W(colsum, "Float")
+        out["a7_sum_dim0_f32_window_256x512x1000"] = timed(lambda: tcs.sum(tw0, 0, 1), 4 * n, reps=5)
 
     def xdev():
         """Copies from GPU 1 to GPU 0 over NVLink, driven from this process (needs two visible

@@ -294,51 +294,15 @@ constexpr int kRedWarps = kRedThreads / 32;
 constexpr int kRedUnroll = 4;
 
 // ====================================================================================
-// reduce_all: persistent CTAs walk 16 KiB tiles block-cyclically; partial per CTA; the CTA
-// that draws the last ticket folds the partials in index order and writes the result.
+// Tail shared by the full-reduction kernels: fold the CTA's accumulators, store the CTA's
+// partial, and let the CTA that draws the last ticket fold all partials in index order.
 // ====================================================================================
-template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided walk */>
-__global__ void __launch_bounds__(kRedThreads)
-reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
-                  void *partials_raw, unsigned int *ticket, void *result) {
+template <typename T, int MODE>
+__device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void *partials_raw, unsigned int *ticket, void *result) {
   using F = Folder<T, MODE>;
   using Acc = typename F::Acc;
   struct Partial { Acc v; int has; };
   Partial *partials = reinterpret_cast<Partial *>(partials_raw);
-  constexpr bool VEC = VB != 0;
-  constexpr int V = VEC ? VB / (int)sizeof(T) : 1;
-  constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * V;
-  Opt<F> acc = Opt<F>::start();
-  const uint64_t ntiles = (n + kTile - 1) / kTile;
-  for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
-    const uint64_t base = t * kTile;
-    if constexpr (VEC) {
-      if (base + kTile <= n) {
-        typename VecBytes<VEC ? VB : 16>::type v[kRedUnroll];
-#pragma unroll
-        for (int u = 0; u < kRedUnroll; ++u) v[u] = ldv_stream<VEC ? VB : 16>(in + base + ((uint64_t)u * kRedThreads + threadIdx.x) * V);
-#pragma unroll
-        for (int u = 0; u < kRedUnroll; ++u) {
-          const T *e = reinterpret_cast<const T *>(&v[u]);
-#pragma unroll
-          for (int k = 0; k < V; ++k) acc.feed(F::pre(e[k], prm));
-        }
-      } else {
-        for (uint64_t i = base + threadIdx.x; i < n; i += kRedThreads) acc.feed(F::pre(in[i], prm));
-      }
-    } else {
-      T x[kRedUnroll];
-      bool ok[kRedUnroll];
-#pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
-        const uint64_t i = base + (uint64_t)u * kRedThreads + threadIdx.x;
-        ok[u] = i < n;
-        if (ok[u]) x[u] = in[view.offset(i)];
-      }
-#pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) if (ok[u]) acc.feed(F::pre(x[u], prm));
-    }
-  }
   __shared__ Partial sm[kRedWarps];
   __shared__ bool is_last;
   acc = warp_fold_opt<F>(acc);
@@ -375,6 +339,124 @@ reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename 
     else *reinterpret_cast<int64_t *>(result) = (int64_t)b.v;
     *ticket = 0;  // ready for the next launch on this stream
   }
+}
+
+// ====================================================================================
+// reduce_all over a view that is not one dense run but whose innermost dim (after sorting the
+// dims by stride: a full reduction is order-free) has stride 1: padded rows, windows of larger
+// tensors.  Tiles are [ty rows x tx units] like the rows apply; a row's offset is decoded from
+// its number once per thread and row; units are 16-byte vectors when every row start keeps that
+// alignment, else single elements.
+// ====================================================================================
+constexpr int kRedRowsOuterDims = 7;
+constexpr int kRedRowsScalarCols = 4;
+struct RedRowsView {
+  int nouter;
+  FastDiv32 outer_size[kRedRowsOuterDims];
+  int64_t outer_stride[kRedRowsOuterDims];
+  uint32_t R, Cunits;       // rows; units per row
+  uint32_t tiles_c;
+  FastDiv32 tiles_c_div;
+  int log2_tx;
+  __device__ __forceinline__ int64_t row_offset(uint32_t r) const {
+    int64_t off = 0;
+    uint32_t rem = r;
+#pragma unroll 1
+    for (int i = nouter - 1; i >= 1; --i) {
+      uint32_t q, m;
+      outer_size[i].divmod(rem, q, m);
+      off += (int64_t)m * outer_stride[i];
+      rem = q;
+    }
+    return off + (int64_t)rem * outer_stride[0];
+  }
+};
+
+template <typename T, int MODE, int V>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Folder<T, MODE>::Params prm,
+                       void *partials_raw, unsigned int *ticket, void *result) {
+  using F = Folder<T, MODE>;
+  struct alignas(V * sizeof(T)) Unit { T v[V]; };
+  constexpr int U = kRedUnroll;
+  constexpr int UC = V == 1 ? kRedRowsScalarCols : 1;   // column slots per thread
+  const unsigned tx = 1u << rv.log2_tx, ty = kRedThreads >> rv.log2_tx;
+  const unsigned x = threadIdx.x & (tx - 1), y = threadIdx.x >> rv.log2_tx;
+  Opt<F> acc = Opt<F>::start();
+  for (uint32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    uint32_t rtile, ctile;
+    rv.tiles_c_div.divmod(t, rtile, ctile);
+    Unit v[U][UC];
+    bool ok[U][UC];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t r = (rtile * U + u) * ty + y;
+      const T *row = in + (r < rv.R ? rv.row_offset(r) : 0);
+#pragma unroll
+      for (int k = 0; k < UC; ++k) {
+        const uint32_t cu = (ctile * UC + k) * tx + x;
+        ok[u][k] = r < rv.R && cu < rv.Cunits;
+        if (ok[u][k]) v[u][k] = *reinterpret_cast<const Unit *>(row + (uint64_t)cu * V);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int k = 0; k < UC; ++k) {
+        if (ok[u][k]) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc.feed(F::pre(v[u][k].v[j], prm));
+        }
+      }
+    }
+  }
+  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
+}
+
+// ====================================================================================
+// reduce_all: persistent CTAs walk 16 KiB tiles block-cyclically; partial per CTA; the CTA
+// that draws the last ticket folds the partials in index order and writes the result.
+// ====================================================================================
+template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided walk */>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
+                  void *partials_raw, unsigned int *ticket, void *result) {
+  using F = Folder<T, MODE>;
+  constexpr bool VEC = VB != 0;
+  constexpr int V = VEC ? VB / (int)sizeof(T) : 1;
+  constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * V;
+  Opt<F> acc = Opt<F>::start();
+  const uint64_t ntiles = (n + kTile - 1) / kTile;
+  for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const uint64_t base = t * kTile;
+    if constexpr (VEC) {
+      if (base + kTile <= n) {
+        typename VecBytes<VEC ? VB : 16>::type v[kRedUnroll];
+#pragma unroll
+        for (int u = 0; u < kRedUnroll; ++u) v[u] = ldv_stream<VEC ? VB : 16>(in + base + ((uint64_t)u * kRedThreads + threadIdx.x) * V);
+#pragma unroll
+        for (int u = 0; u < kRedUnroll; ++u) {
+          const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+          for (int k = 0; k < V; ++k) acc.feed(F::pre(e[k], prm));
+        }
+      } else {
+        for (uint64_t i = base + threadIdx.x; i < n; i += kRedThreads) acc.feed(F::pre(in[i], prm));
+      }
+    } else {
+      T x[kRedUnroll];
+      bool ok[kRedUnroll];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const uint64_t i = base + (uint64_t)u * kRedThreads + threadIdx.x;
+        ok[u] = i < n;
+        if (ok[u]) x[u] = in[view.offset(i)];
+      }
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) if (ok[u]) acc.feed(F::pre(x[u], prm));
+    }
+  }
+  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
 }
 
 // ====================================================================================

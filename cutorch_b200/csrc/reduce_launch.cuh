@@ -2,6 +2,8 @@
 // type instantiates reduce_all_typed<T>, reduce_dim_typed<T> and reduce_dim_index_typed<T>.
 #pragma once
 
+#include <algorithm>
+
 #include "context.h"
 #include "plan.h"
 #include "reduce.cuh"
@@ -16,14 +18,79 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   using F = Folder<T, MODE>;
   typename F::Params prm;
   if constexpr (TypeTraits<T>::is_fp) prm.s = (typename F::Scalar)s.f; else prm.s = (typename F::Scalar)s.i;
-  // collapsed view of the input
+  // A full reduction does not depend on the order of the elements: the dims are walked from the
+  // largest stride to the smallest, so a permuted (transposed) tensor collapses like its base.
   int64_t sizes[kMaxDims], strides[kMaxDims];
-  int nd = in.ndim;
-  for (int i = 0; i < nd; ++i) { sizes[i] = in.sizes[i]; strides[i] = in.strides[i]; }
+  int nd = 0;
+  {
+    int order[kMaxDims], m = 0;
+    for (int i = 0; i < in.ndim; ++i) if (in.sizes[i] != 1) order[m++] = i;
+    std::stable_sort(order, order + m, [&](int a, int b) {
+      const int64_t sa = in.strides[a] < 0 ? -in.strides[a] : in.strides[a];
+      const int64_t sb = in.strides[b] < 0 ? -in.strides[b] : in.strides[b];
+      return sa > sb;
+    });
+    for (int i = 0; i < m; ++i) { sizes[i] = in.sizes[order[i]]; strides[i] = in.strides[order[i]]; }
+    nd = m;
+    if (nd == 0) { nd = 1; sizes[0] = 1; strides[0] = 1; }
+  }
   collapse_dims(sizes, strides, &nd, -1);
   if (nd > kGenericDims) { set_error("reduce_all: more than %d non-collapsible dimensions", kGenericDims); return THCB200_ERR_DIMS; }
   const uint64_t n = (uint64_t)in.numel;
   const bool unit = nd == 1 && strides[0] == 1;
+  const T *p = reinterpret_cast<const T *>(in.data);
+  const uint64_t max_grid = (uint64_t)ctx->num_sms * 4;
+
+  // dense rows under strided outer dims (padded rows, windows): the row walk
+  if (!unit && nd >= 2 && nd - 1 <= kRedRowsOuterDims && strides[nd - 1] == 1) {
+    constexpr int VF = 16 / (int)sizeof(T);
+    const int nouter = nd - 1;
+    uint64_t R = 1;
+    bool fits = sizes[nouter] < (1LL << 31);
+    bool vec = sizes[nouter] % VF == 0 && ((uintptr_t)in.data % 16) == 0;
+    for (int i = 0; i < nouter; ++i) {
+      R *= (uint64_t)sizes[i];
+      if (sizes[i] >= (1LL << 31) || R >= (1ull << 31)) fits = false;
+      if (strides[i] % VF != 0) vec = false;
+    }
+    if (fits) {
+      RedRowsView rv;
+      rv.nouter = nouter;
+      for (int i = 0; i < kRedRowsOuterDims; ++i) {
+        rv.outer_size[i] = FastDiv32(i < nouter ? (uint32_t)sizes[i] : 1u);
+        rv.outer_stride[i] = i < nouter ? strides[i] : 0;
+      }
+      rv.R = (uint32_t)R;
+      rv.Cunits = (uint32_t)(vec ? sizes[nouter] / VF : sizes[nouter]);
+      const uint32_t per_thread = vec ? 1 : kRedRowsScalarCols;
+      const uint32_t slots = (rv.Cunits + per_thread - 1) / per_thread;
+      int lg = 0;
+      while ((1u << lg) < slots && lg < 8) ++lg;
+      rv.log2_tx = lg;
+      const uint32_t per_tile = (1u << lg) * per_thread;
+      rv.tiles_c = (rv.Cunits + per_tile - 1) / per_tile;
+      rv.tiles_c_div = FastDiv32(rv.tiles_c);
+      const uint64_t rows_per_tile = (uint64_t)(kRedThreads >> lg) * kRedUnroll;
+      const uint64_t ntiles = (uint64_t)rv.tiles_c * ((R + rows_per_tile - 1) / rows_per_tile);
+      if (ntiles < (1ull << 31)) {
+        const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;
+        const uint64_t grid = (ntiles + per_cta - 1) / per_cta;
+        void *partials = ctx_workspace(ctx, grid * 16);
+        if (!partials) return THCB200_ERR_NOMEM;
+        if (vec) {
+          set_plan_name("reduce_all_rows_vec");
+          reduce_all_rows_kernel<T, MODE, VF><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
+        } else {
+          set_plan_name("reduce_all_rows");
+          reduce_all_rows_kernel<T, MODE, 1><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
+        }
+        count_launch();
+        THCB_CUDA_TRY(cudaGetLastError());
+        return 0;
+      }
+    }
+  }
+
   // 256-bit loads when the base is 32-byte aligned, 128-bit when 16-byte aligned, else a strided walk
   const int vb = !unit ? 0 : (((uintptr_t)in.data % 32) == 0 ? 32 : (((uintptr_t)in.data % 16) == 0 ? 16 : 0));
   const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vb ? vb / sizeof(T) : 1);
@@ -31,7 +98,6 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   // at most 4 CTAs per SM, all resident at once (measured on B200: more CTAs in flight lower the
   // read bandwidth), sized so that every CTA gets the same number of tiles to within one: a
   // function of n and the SM count only
-  const uint64_t max_grid = (uint64_t)ctx->num_sms * 4;
   const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;
   uint64_t grid = per_cta ? (ntiles + per_cta - 1) / per_cta : 1;
   if (grid < 1) grid = 1;
@@ -43,7 +109,6 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
     view.sizes[i] = DivHelper<uint64_t>(i < nd ? (uint64_t)sizes[i] : 1);
     view.strides[i] = i < nd ? (uint64_t)strides[i] : 0;
   }
-  const T *p = reinterpret_cast<const T *>(in.data);
   if (vb == 32) {
     set_plan_name("reduce_all_vec");
     reduce_all_kernel<T, MODE, 32><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
