@@ -344,17 +344,15 @@ __device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void
 // ====================================================================================
 // reduce_all over a view that is not one dense run but whose innermost dim (after sorting the
 // dims by stride: a full reduction is order-free) has stride 1: padded rows, windows of larger
-// tensors.  Tiles are [ty rows x tx units] like the rows apply; a row's offset is decoded from
-// its number once per thread and row; units are 16-byte vectors when every row start keeps that
-// alignment, else single elements.
+// tensors.  Tiles are [ty rows x tx vectors] like the rows apply; a row's offset is decoded from
+// its number once per thread and row.
 // ====================================================================================
 constexpr int kRedRowsOuterDims = 7;
-constexpr int kRedRowsScalarCols = 4;
 struct RedRowsView {
   int nouter;
   FastDiv32 outer_size[kRedRowsOuterDims];
   int64_t outer_stride[kRedRowsOuterDims];
-  uint32_t R, Cunits;       // rows; units per row
+  uint32_t R, Cunits;       // rows; elements per row
   uint32_t tiles_c;
   FastDiv32 tiles_c_div;
   int log2_tx;
@@ -372,42 +370,56 @@ struct RedRowsView {
   }
 };
 
-template <typename T, int MODE, int V>
+// Rows need not start on a 16-byte boundary: per row the elements before the first boundary and
+// after the last whole vector (at most 2 * (V - 1) of them) are read one by one by the first
+// threads of the row's first column tile; everything between moves as 16-byte vectors.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Folder<T, MODE>::Params prm,
                        void *partials_raw, unsigned int *ticket, void *result) {
   using F = Folder<T, MODE>;
-  struct alignas(V * sizeof(T)) Unit { T v[V]; };
+  constexpr int V = 16 / (int)sizeof(T);
   constexpr int U = kRedUnroll;
-  constexpr int UC = V == 1 ? kRedRowsScalarCols : 1;   // column slots per thread
   const unsigned tx = 1u << rv.log2_tx, ty = kRedThreads >> rv.log2_tx;
   const unsigned x = threadIdx.x & (tx - 1), y = threadIdx.x >> rv.log2_tx;
+  const uint32_t C = rv.Cunits;   // elements per row
   Opt<F> acc = Opt<F>::start();
   for (uint32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     uint32_t rtile, ctile;
     rv.tiles_c_div.divmod(t, rtile, ctile);
-    Unit v[U][UC];
-    bool ok[U][UC];
+    const uint32_t cu = ctile * tx + x;       // vector number inside the row's aligned part
+    Bytes16 v[U];
+    T edge[U];
+    bool ok[U], eok[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t r = (rtile * U + u) * ty + y;
-      const T *row = in + (r < rv.R ? rv.row_offset(r) : 0);
-#pragma unroll
-      for (int k = 0; k < UC; ++k) {
-        const uint32_t cu = (ctile * UC + k) * tx + x;
-        ok[u][k] = r < rv.R && cu < rv.Cunits;
-        if (ok[u][k]) v[u][k] = *reinterpret_cast<const Unit *>(row + (uint64_t)cu * V);
+      ok[u] = false;
+      eok[u] = false;
+      if (r < rv.R) {
+        const T *row = in + rv.row_offset(r);
+        const uint32_t mis = (uint32_t)((reinterpret_cast<uintptr_t>(row) / sizeof(T)) % V);
+        uint32_t head = mis ? V - mis : 0;
+        if (head > C) head = C;
+        const uint32_t nvec = (C - head) / V;
+        const uint32_t tail0 = head + nvec * V;          // first element after the vectors
+        ok[u] = cu < nvec;
+        if (ok[u]) v[u] = ld16_stream(row + head + (uint64_t)cu * V);
+        // edge elements: x < head takes row[x], head <= x < head + (C - tail0) takes the tail
+        if (ctile == 0 && x < head + (C - tail0)) {
+          eok[u] = true;
+          edge[u] = row[x < head ? x : tail0 + (x - head)];
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
+      if (ok[u]) {
+        const T *e = reinterpret_cast<const T *>(&v[u]);
 #pragma unroll
-      for (int k = 0; k < UC; ++k) {
-        if (ok[u][k]) {
-#pragma unroll
-          for (int j = 0; j < V; ++j) acc.feed(F::pre(v[u][k].v[j], prm));
-        }
+        for (int j = 0; j < V; ++j) acc.feed(F::pre(e[j], prm));
       }
+      if (eok[u]) acc.feed(F::pre(edge[u], prm));
     }
   }
   reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
@@ -581,7 +593,19 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
   fast.reset();
   uint64_t k = k0;
   if constexpr (VEC) {
-    // whole 16-byte vectors, kRedUnroll of them in flight per thread (split_len is a multiple of V)
+    // A unit need not start on a 16-byte boundary (odd row lengths, windows): the elements up to
+    // the boundary are taken one by one, in position order before everything else.
+    {
+      const uint64_t mis = (reinterpret_cast<uintptr_t>(row + k0) / sizeof(T)) % V;
+      uint64_t head = mis ? V - mis : 0;
+      if (head > k1 - k0) head = k1 - k0;
+      for (uint64_t i = k0 + gt; i < k0 + head; i += GROUP) {
+        if constexpr (INDEX) fast.feed(row[i], (uint32_t)(i - k0));
+        else acc.feed(F::pre(row[i], prm));
+      }
+      k = k0 + head;
+    }
+    // whole 16-byte vectors, kRedUnroll of them in flight per thread
     constexpr uint64_t kStep = (uint64_t)GROUP * V * kRedUnroll;
     for (; k + kStep <= k1; k += kStep) {
       Bytes16 v[kRedUnroll];
@@ -597,14 +621,25 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
         }
       }
     }
-    for (; k + (uint64_t)GROUP * V <= k1; k += (uint64_t)GROUP * V) {
-      Bytes16 v = ld16_stream(row + k + (uint64_t)gt * V);
-      const T *e = reinterpret_cast<const T *>(&v);
+    // the whole vectors that are left (fewer than one full step), again all in flight together
+    {
+      const uint64_t nrem = (k1 - k) / V;
+      Bytes16 v[kRedUnroll];
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        if constexpr (INDEX) fast.feed(e[j], (uint32_t)(k - k0) + (uint32_t)(gt * V + j));
-        else acc.feed(F::pre(e[j], prm));
+      for (int u = 0; u < kRedUnroll; ++u)
+        if ((uint64_t)u * GROUP + gt < nrem) v[u] = ld16_stream(row + k + ((uint64_t)u * GROUP + gt) * V);
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        if ((uint64_t)u * GROUP + gt < nrem) {
+          const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            if constexpr (INDEX) fast.feed(e[j], (uint32_t)(k - k0) + (uint32_t)((u * GROUP + gt) * V + j));
+            else acc.feed(F::pre(e[j], prm));
+          }
+        }
       }
+      k += nrem * V;
     }
   }
   for (uint64_t i = k + gt; i < k1; i += GROUP) {

@@ -47,11 +47,9 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
     const int nouter = nd - 1;
     uint64_t R = 1;
     bool fits = sizes[nouter] < (1LL << 31);
-    bool vec = sizes[nouter] % VF == 0 && ((uintptr_t)in.data % 16) == 0;
     for (int i = 0; i < nouter; ++i) {
       R *= (uint64_t)sizes[i];
       if (sizes[i] >= (1LL << 31) || R >= (1ull << 31)) fits = false;
-      if (strides[i] % VF != 0) vec = false;
     }
     if (fits) {
       RedRowsView rv;
@@ -61,14 +59,16 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
         rv.outer_stride[i] = i < nouter ? strides[i] : 0;
       }
       rv.R = (uint32_t)R;
-      rv.Cunits = (uint32_t)(vec ? sizes[nouter] / VF : sizes[nouter]);
-      const uint32_t per_thread = vec ? 1 : kRedRowsScalarCols;
-      const uint32_t slots = (rv.Cunits + per_thread - 1) / per_thread;
+      rv.Cunits = (uint32_t)sizes[nouter];
+      // threads along the row: enough for its whole vectors, and for the up to 2 (V - 1) edge elements
+      uint32_t slots = (uint32_t)(sizes[nouter] / VF);
+      if (slots < 2u * (VF - 1)) slots = 2u * (VF - 1);
+      if (slots < 1) slots = 1;
       int lg = 0;
       while ((1u << lg) < slots && lg < 8) ++lg;
       rv.log2_tx = lg;
-      const uint32_t per_tile = (1u << lg) * per_thread;
-      rv.tiles_c = (rv.Cunits + per_tile - 1) / per_tile;
+      rv.tiles_c = (uint32_t)((sizes[nouter] / VF + (1u << lg) - 1) >> lg);
+      if (rv.tiles_c < 1) rv.tiles_c = 1;
       rv.tiles_c_div = FastDiv32(rv.tiles_c);
       const uint64_t rows_per_tile = (uint64_t)(kRedThreads >> lg) * kRedUnroll;
       const uint64_t ntiles = (uint64_t)rv.tiles_c * ((R + rows_per_tile - 1) / rows_per_tile);
@@ -77,13 +77,8 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
         const uint64_t grid = (ntiles + per_cta - 1) / per_cta;
         void *partials = ctx_workspace(ctx, grid * 16);
         if (!partials) return THCB200_ERR_NOMEM;
-        if (vec) {
-          set_plan_name("reduce_all_rows_vec");
-          reduce_all_rows_kernel<T, MODE, VF><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
-        } else {
-          set_plan_name("reduce_all_rows");
-          reduce_all_rows_kernel<T, MODE, 1><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
-        }
+        set_plan_name("reduce_all_rows");
+        reduce_all_rows_kernel<T, MODE><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
         count_launch();
         THCB_CUDA_TRY(cudaGetLastError());
         return 0;
@@ -233,8 +228,8 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
   if (row) {
     pl->nslices = nout;
     if (pl->K < 64) { pl->kind = kRedStrided; return 0; }
-    bool vec = ptr_aligned;
-    for (int i = 0; i < m.n; ++i) if (m.in_stride[i] % vec_elems != 0) vec = false;
+    // the row kernel peels each unit up to a 16-byte boundary itself: no alignment needed
+    const bool vec = true;
     pl->vec = vec;
     const uint64_t warp_step = 32ull * vec_elems * kRedUnroll;       // elements per warp iteration
     const uint64_t block_step = (uint64_t)kRedThreads * vec_elems * kRedUnroll;
