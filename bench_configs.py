@@ -222,6 +222,11 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tw0, tw1, tw2 = W(w0, "Float"), W(w1, "Float"), W(w2, "Float")
         n = 256 * 512 * 1000
         out["a4_cmul_f32_window_256x512x1000_of_258x514x1004"] = timed(lambda: tw0.cmul(tw1, tw2), 12 * n, reps=5)
+        # dense 1-D runs that start one element past a 16-byte boundary
+        flat = [t.view(-1)[1:1 + (1 << 27)] for t in big]
+        tf0, tf1, tf2 = (W(t, "Float") for t in flat)
+        out["a4_cadd_f32_1d_2p27_misaligned_by_one"] = timed(lambda: tf0.cadd(tf1, 2.5, tf2), 12 * (1 << 27), reps=5)
+        out["a9_sumall_f32_1d_2p27_misaligned_by_one"] = timed(lambda: tf1.sumall_to_device(res.data_ptr()), 4 * (1 << 27), reps=5)
         # full reductions of views that are not one dense run
         out["a9_sumall_f32_window_256x512x1000"] = timed(lambda: tw0.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
         tr = big[1].view(258 * 514, 1004).t()

@@ -432,12 +432,14 @@ reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Fo
 template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided walk */>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
-                  void *partials_raw, unsigned int *ticket, void *result) {
+                  void *partials_raw, unsigned int *ticket, void *result, const T *edge, uint32_t nedge) {
   using F = Folder<T, MODE>;
   constexpr bool VEC = VB != 0;
   constexpr int V = VEC ? VB / (int)sizeof(T) : 1;
   constexpr uint64_t kTile = (uint64_t)kRedThreads * kRedUnroll * V;
   Opt<F> acc = Opt<F>::start();
+  // elements in front of the first vector boundary of a dense run (fewer than one vector)
+  if (blockIdx.x == 0 && threadIdx.x < nedge) acc.feed(F::pre(edge[threadIdx.x], prm));
   const uint64_t ntiles = (n + kTile - 1) / kTile;
   for (uint64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const uint64_t base = t * kTile;

@@ -86,10 +86,25 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
     }
   }
 
-  // 256-bit loads when the base is 32-byte aligned, 128-bit when 16-byte aligned, else a strided walk
-  const int vb = !unit ? 0 : (((uintptr_t)in.data % 32) == 0 ? 32 : (((uintptr_t)in.data % 16) == 0 ? 16 : 0));
+  // A dense run is read as 256-bit vectors from its first 32-byte boundary on; the few elements in
+  // front of it go to the first threads of CTA 0.  Anything else takes the per-element walk.
+  const T *body = p;
+  uint64_t nbody = n;
+  uint32_t nedge = 0;
+  int vb = 0;
+  if (unit) {
+    constexpr uint64_t V32 = 32 / sizeof(T);
+    const uint64_t mis = ((uintptr_t)in.data / sizeof(T)) % V32;
+    uint64_t head = mis ? V32 - mis : 0;
+    if (head > n) head = n;
+    nedge = (uint32_t)head;
+    body = p + head;
+    nbody = n - head;
+    vb = 32;
+  }
   const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vb ? vb / sizeof(T) : 1);
-  const uint64_t ntiles = (n + tile - 1) / tile;
+  uint64_t ntiles = (nbody + tile - 1) / tile;
+  if (ntiles < 1) ntiles = 1;
   // at most 4 CTAs per SM, all resident at once (measured on B200: more CTAs in flight lower the
   // read bandwidth), sized so that every CTA gets the same number of tiles to within one: a
   // function of n and the SM count only
@@ -105,14 +120,11 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
     view.strides[i] = i < nd ? (uint64_t)strides[i] : 0;
   }
   if (vb == 32) {
-    set_plan_name("reduce_all_vec");
-    reduce_all_kernel<T, MODE, 32><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
-  } else if (vb == 16) {
-    set_plan_name("reduce_all_vec16");
-    reduce_all_kernel<T, MODE, 16><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
+    set_plan_name(nedge ? "reduce_all_vec_peeled" : "reduce_all_vec");
+    reduce_all_kernel<T, MODE, 32><<<(unsigned)grid, kRedThreads, 0, st>>>(body, view, nbody, prm, partials, ctx->tickets, result, p, nedge);
   } else {
     set_plan_name("reduce_all_strided");
-    reduce_all_kernel<T, MODE, 0><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result);
+    reduce_all_kernel<T, MODE, 0><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result, p, 0u);
   }
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());
