@@ -183,6 +183,9 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tmat, tmo = W(mat, "Float"), W(mo, "Float")
         out["f2_cumsum_f32_16384x8192_dim1"] = timed(lambda: tmo.cumsum(tmat, 1), 8 * n, reps=5)
         out["f2_cumsum_f32_16384x8192_dim0"] = timed(lambda: tmo.cumsum(tmat, 0), 8 * n, reps=5)
+        odd, oddo = x[: 16384 * 8191].view(16384, 8191), mo.view(-1)[: 16384 * 8191].view(16384, 8191)
+        todd, toddo = W(odd, "Float"), W(oddo, "Float")
+        out["f2_cumsum_f32_16384x8191_dim1_odd_rows"] = timed(lambda: toddo.cumsum(todd, 1), 8 * 16384 * 8191, reps=5)
         sq = x.view(-1)[: 11584 * 11584].view(11584, 11584)
         so = torch.empty_like(sq)
         tsq, tso = W(sq, "Float"), W(so, "Float")

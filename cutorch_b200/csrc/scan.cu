@@ -75,20 +75,35 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
   const T *ip = in + ioff;
   T *op = out + ooff;
   A carry = scan_identity<A, PROD>();
+  // Vector layout: a unit need not start on a 16-byte boundary (input and output rows share their
+  // misalignment); [k0, kb) before the first boundary and [ke, k1) after the last whole vector
+  // (fewer than V elements each) are taken one element per lane.
+  uint64_t kb = k0, ke = k1;
+  if constexpr (VEC) {
+    const uint64_t mis = (reinterpret_cast<uintptr_t>(ip + k0) / sizeof(T)) % V;
+    uint64_t head = mis ? V - mis : 0;
+    if (head > k1 - k0) head = k1 - k0;
+    kb = k0 + head;
+    ke = kb + (k1 - kb) / V * V;
+  }
   if constexpr (TOTAL_ONLY) {
     // only the fold of the chunk is wanted: every lane folds what it loads, one butterfly at the end
     A acc = scan_identity<A, PROD>();
-    for (uint64_t base = k0; base < k1; base += (uint64_t)32 * V * U) {
+    if constexpr (VEC) {
+      if (lane < kb - k0) acc = to_acc<T, A>(ip[k0 + lane]);
+      if (lane < k1 - ke) acc = scan_op<A, PROD>(acc, to_acc<T, A>(ip[ke + lane]));
+    }
+    for (uint64_t base = kb; base < ke; base += (uint64_t)32 * V * U) {
       Pack<T, V> x[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
-        if (pos < k1) x[u] = *reinterpret_cast<const Pack<T, V> *>(ip + pos);
+        if (pos < ke) x[u] = *reinterpret_cast<const Pack<T, V> *>(ip + pos);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
-        if (pos < k1) {
+        if (pos < ke) {
 #pragma unroll
           for (int j = 0; j < V; ++j) acc = scan_op<A, PROD>(acc, to_acc<T, A>(x[u].v[j]));
         }
@@ -100,17 +115,37 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
     return;
   }
   if (carries) carry = carries[unit];
-  for (uint64_t base = k0; base < k1; base += (uint64_t)32 * V * U) {
+  // one element per lane: the pieces in front of and behind the whole vectors
+  auto lane_step = [&](uint64_t start, uint64_t count) {
+    if (count == 0) return;   // uniform over the warp
+    const bool live = lane < count;
+    const A e = live ? to_acc<T, A>(ip[start + lane]) : scan_identity<A, PROD>();
+    const A incl = [&] {
+      A v = e;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const A y = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= (unsigned)d) v = scan_op<A, PROD>(y, v);
+      }
+      return v;
+    }();
+    A excl = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (lane == 0) excl = scan_identity<A, PROD>();
+    if (live) op[start + lane] = from_acc<T, A>(scan_op<A, PROD>(scan_op<A, PROD>(carry, excl), e));
+    carry = scan_op<A, PROD>(carry, __shfl_sync(0xffffffffu, incl, 31));
+  };
+  if constexpr (VEC) lane_step(k0, kb - k0);
+  for (uint64_t base = kb; base < ke; base += (uint64_t)32 * V * U) {
     Pack<T, V> x[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;   // VEC: K and chunk_len are multiples of V
-      if (pos < k1) x[u] = *reinterpret_cast<const Pack<T, V> *>(ip + pos);
+      const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
+      if (pos < ke) x[u] = *reinterpret_cast<const Pack<T, V> *>(ip + pos);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint64_t pos = base + ((uint64_t)u * 32 + lane) * V;
-      const bool live = pos < k1;
+      const bool live = pos < ke;
       A a[V];
 #pragma unroll
       for (int j = 0; j < V; ++j) {
@@ -123,21 +158,19 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
         const A y = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= (unsigned)d) incl = scan_op<A, PROD>(y, incl);
       }
-      if (!TOTAL_ONLY) {
-        A excl = __shfl_up_sync(0xffffffffu, incl, 1);
-        if (lane == 0) excl = scan_identity<A, PROD>();
-        const A pre = scan_op<A, PROD>(carry, excl);
-        if (live) {
-          Pack<T, V> y;
+      A excl = __shfl_up_sync(0xffffffffu, incl, 1);
+      if (lane == 0) excl = scan_identity<A, PROD>();
+      const A pre = scan_op<A, PROD>(carry, excl);
+      if (live) {
+        Pack<T, V> y;
 #pragma unroll
-          for (int j = 0; j < V; ++j) y.v[j] = from_acc<T, A>(scan_op<A, PROD>(pre, a[j]));
-          *reinterpret_cast<Pack<T, V> *>(op + pos) = y;
-        }
+        for (int j = 0; j < V; ++j) y.v[j] = from_acc<T, A>(scan_op<A, PROD>(pre, a[j]));
+        *reinterpret_cast<Pack<T, V> *>(op + pos) = y;
       }
       carry = scan_op<A, PROD>(carry, __shfl_sync(0xffffffffu, incl, 31));
     }
   }
-  if (TOTAL_ONLY && lane == 0) carries[unit] = carry;
+  if constexpr (VEC) lane_step(ke, k1 - ke);
 }
 
 // chunk totals -> exclusive carries, in place; a CTA per row, threads own consecutive segments
@@ -328,9 +361,11 @@ void plan_scan(const thcb200_ctx *ctx, const HostView &in, const HostView &out, 
       prev = i;
     }
     pl->nslices = nother;
-    bool vec = aligned && pl->K % vfull == 0;
+    // vectors from each unit's first 16-byte boundary: input and output rows only have to share
+    // their misalignment
+    bool vec = ((uintptr_t)in.data % 16) == ((uintptr_t)out.data % 16);
     for (int i = 0; i < pl->map.n; ++i)
-      if (pl->map.in_stride[i] % vfull != 0 || pl->map.out_stride[i] % vfull != 0) vec = false;
+      if ((pl->map.in_stride[i] - pl->map.out_stride[i]) % vfull != 0) vec = false;
     pl->vec = vec;
     const uint64_t step = 32ull * (vec ? vfull : 1) * kScanUnroll;
     if (nother < target_warps / 2 && pl->K >= 4 * step) {
