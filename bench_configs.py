@@ -225,6 +225,16 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         tw0, tw1, tw2 = W(w0, "Float"), W(w1, "Float"), W(w2, "Float")
         n = 256 * 512 * 1000
         out["a4_cmul_f32_window_256x512x1000_of_258x514x1004"] = timed(lambda: tw0.cmul(tw1, tw2), 12 * n, reps=5)
+        # dimension reductions of a matrix with an odd number of columns (rows start at every alignment)
+        om = bufs[0].view(-1)[: 16384 * 8191].view(16384, 8191)
+        tom = W(om, "Float")
+        oc, orow = torch.empty(1, 8191, device=dev), torch.empty(16384, 1, device=dev)
+        oci = torch.empty(1, 8191, dtype=torch.int64, device=dev)
+        toc, torow, toci = W(oc, "Float"), W(orow, "Float"), W(oci, "Long")
+        no = 16384 * 8191
+        out["a7_sum_dim0_f32_16384x8191_odd_columns"] = timed(lambda: toc.sum(tom, 0, 1), 4 * no, reps=5)
+        out["a8_max_dim0_f32_16384x8191_odd_columns"] = timed(lambda: toc.max(toci, tom, 0, 1), 4 * no, reps=5)
+        out["a7_sum_dim1_f32_16384x8191_odd_columns"] = timed(lambda: torow.sum(tom, 1, 1), 4 * no, reps=5)
         # dense 1-D runs that start one element past a 16-byte boundary
         flat = [t.view(-1)[1:1 + (1 << 27)] for t in big]
         tf0, tf1, tf2 = (W(t, "Float") for t in flat)
