@@ -197,6 +197,17 @@ void thcb200_ctx_destroy(thcb200_ctx *c) {
   delete c;
 }
 
+void *thcb200_ctx_workspace(thcb200_ctx *ctx, size_t min_bytes, size_t *bytes) {
+  if (!ctx) { set_error("ctx_workspace: null context"); return nullptr; }
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (prev != ctx->device) cudaSetDevice(ctx->device);
+  void *p = ctx_workspace(ctx, min_bytes);
+  if (prev != ctx->device) cudaSetDevice(prev);
+  if (bytes) *bytes = p ? ctx->ws_bytes : 0;
+  return p;
+}
+
 const char *thcb200_last_error(void) { return get_error(); }
 int64_t thcb200_launch_count(void) { return launch_count(); }
 const char *thcb200_last_plan(void) { return get_plan_name(); }

@@ -89,6 +89,9 @@ struct THCState {
   THCDeviceAllocator *allocator;
   THCDeviceAllocator defaultAllocator;
   int initialised;
+  unsigned char *p2pOff;      // numDevices x numDevices: 1 = direct access switched off by the caller
+  cudaDeviceProp *props;      // per device, filled on first request
+  unsigned char *propsValid;
 };
 
 namespace {
@@ -195,6 +198,9 @@ void THCudaInit(THCState *state) {
   state->numDevices = n;
   state->ctx = (thcb200_ctx **)calloc((size_t)(n > 0 ? n : 1), sizeof(thcb200_ctx *));
   state->current = (THCStream **)calloc((size_t)(n > 0 ? n : 1), sizeof(THCStream *));
+  state->p2pOff = (unsigned char *)calloc((size_t)(n > 0 ? n * n : 1), 1);
+  state->props = (cudaDeviceProp *)calloc((size_t)(n > 0 ? n : 1), sizeof(cudaDeviceProp));
+  state->propsValid = (unsigned char *)calloc((size_t)(n > 0 ? n : 1), 1);
   state->defaultAllocator.malloc = default_malloc;
   state->defaultAllocator.realloc = nullptr;
   state->defaultAllocator.free = default_free;
@@ -226,8 +232,14 @@ void THCudaShutdown(THCState *state) {
   }
   free(state->ctx);
   free(state->current);
+  free(state->p2pOff);
+  free(state->props);
+  free(state->propsValid);
   state->ctx = nullptr;
   state->current = nullptr;
+  state->p2pOff = nullptr;
+  state->props = nullptr;
+  state->propsValid = nullptr;
   state->initialised = 0;
 }
 
@@ -261,6 +273,60 @@ void THCState_setStream(THCState *state, THCStream *stream) {
 }
 THCDeviceAllocator *THCState_getDeviceAllocator(THCState *state) { return state->allocator; }
 void THCState_setDeviceAllocator(THCState *state, THCDeviceAllocator *allocator) { state->allocator = allocator; }
+int THCState_getPeerToPeerAccess(THCState *state, int dev, int devToAccess) {
+  API_BEGIN
+  THArgCheck(dev >= 0 && dev < state->numDevices, 2, "%d is not a device", dev);
+  THArgCheck(devToAccess >= 0 && devToAccess < state->numDevices, 3, "%d is not a device", devToAccess);
+  if (dev == devToAccess) return 1;
+  if (state->p2pOff[dev * state->numDevices + devToAccess]) return 0;
+  int can = 0;
+  THCudaCheck(cudaDeviceCanAccessPeer(&can, dev, devToAccess));
+  return can;
+  API_END_RET(0)
+}
+void THCState_setPeerToPeerAccess(THCState *state, int dev, int devToAccess, int enable) {
+  API_BEGIN
+  THArgCheck(dev >= 0 && dev < state->numDevices, 2, "%d is not a device", dev);
+  THArgCheck(devToAccess >= 0 && devToAccess < state->numDevices, 3, "%d is not a device", devToAccess);
+  if (enable && dev != devToAccess) {
+    int can = 0;
+    THCudaCheck(cudaDeviceCanAccessPeer(&can, dev, devToAccess));
+    if (!can) th_error("p2p access from device %d to device %d is not possible", dev, devToAccess);
+  }
+  state->p2pOff[dev * state->numDevices + devToAccess] = enable ? 0 : 1;
+  API_END
+}
+struct cudaDeviceProp *THCState_getCurrentDeviceProperties(THCState *state) {
+  API_BEGIN
+  const int d = current_device();
+  if (!state->propsValid[d]) {
+    THCudaCheck(cudaGetDeviceProperties(&state->props[d], d));
+    state->propsValid[d] = 1;
+  }
+  return &state->props[d];
+  API_END_RET(nullptr)
+}
+void *THCState_getCurrentDeviceScratchSpace(THCState *state) {
+  API_BEGIN
+  size_t bytes = 0;
+  return thcb200_ctx_workspace(state_ctx(state), 128 * 1024, &bytes);
+  API_END_RET(nullptr)
+}
+size_t THCState_getCurrentDeviceScratchSpaceSize(THCState *state) {
+  API_BEGIN
+  size_t bytes = 0;
+  thcb200_ctx_workspace(state_ctx(state), 128 * 1024, &bytes);
+  return bytes;
+  API_END_RET(0)
+}
+void __THCudaCheck(cudaError_t err, const char *file, const int line) {
+  API_BEGIN
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    th_error("cuda runtime error (%d) : %s at %s:%d", (int)err, cudaGetErrorString(err), file, line);
+  }
+  API_END
+}
 cudaError_t THCudaMalloc(THCState *state, void **ptr, size_t size) {
   return state->allocator->malloc(state->allocator->state, ptr, size, state_stream(state));
 }
@@ -730,7 +796,7 @@ void copy_across_devices(THCState *state, TensorT<RD> *dst, TensorT<RS> *src, in
     DeviceGuard g(src_dev);
     const bool memcpy_ok = std::is_same<RD, RS>::value &&
                            ((tensor_is_contiguous<RD>(dst) && tensor_is_contiguous<RS>(src)) || n == 1);
-    const bool peer = enable_peer_access(src_dev, dst_dev);
+    const bool peer = !state->p2pOff[src_dev * state->numDevices + dst_dev] && enable_peer_access(src_dev, dst_dev);
     if (memcpy_ok) {
       THCudaCheck(cudaMemcpyPeerAsync(dst->storage->data + dst->storageOffset, dst_dev, src->storage->data + src->storageOffset,
                                       src_dev, (size_t)n * sizeof(RD), sstream));

@@ -103,6 +103,15 @@ THC_API THCStream *THCState_getStream(THCState *state);
 THC_API void THCState_setStream(THCState *state, THCStream *stream);
 THC_API THCDeviceAllocator *THCState_getDeviceAllocator(THCState *state);
 THC_API void THCState_setDeviceAllocator(THCState *state, THCDeviceAllocator *allocator);
+/* 1 if copies may let device `dev` address memory of `devToAccess` directly (the hardware allows
+ * it and it has not been switched off with ..._setPeerToPeerAccess); lib/THC/THCGeneral.h.in:131-138 */
+THC_API int THCState_getPeerToPeerAccess(THCState *state, int dev, int devToAccess);
+THC_API void THCState_setPeerToPeerAccess(THCState *state, int dev, int devToAccess, int enable);
+THC_API struct cudaDeviceProp *THCState_getCurrentDeviceProperties(THCState *state);
+/* scratch space of the current device (lib/THC/THCGeneral.h.in:188-192): at least 128 KiB */
+THC_API void *THCState_getCurrentDeviceScratchSpace(THCState *state);
+THC_API size_t THCState_getCurrentDeviceScratchSpaceSize(THCState *state);
+THC_API void __THCudaCheck(cudaError_t err, const char *file, const int line);
 THC_API cudaError_t THCudaMalloc(THCState *state, void **ptr, size_t size);
 THC_API cudaError_t THCudaFree(THCState *state, void *ptr);
 THC_API THCStream *THCStream_new(int flags);

@@ -146,6 +146,11 @@ typedef struct thcb200_ctx thcb200_ctx;
 
 THCB200_API int thcb200_ctx_create(thcb200_ctx **out, int device);
 THCB200_API void thcb200_ctx_destroy(thcb200_ctx *ctx);
+/* The context's scratch buffer on its device, grown to at least `min_bytes` (256-byte aligned;
+ * *bytes receives its size).  The reductions use it for their partials, so its contents are
+ * only stable between calls on the context; NULL when it cannot be allocated.  It stands for
+ * THCState_getCurrentDeviceScratchSpace (lib/THC/THCGeneral.c:677-712). */
+THCB200_API void *thcb200_ctx_workspace(thcb200_ctx *ctx, size_t min_bytes, size_t *bytes);
 THCB200_API const char *thcb200_last_error(void);
 /* Number of kernels this library has launched in this process (all contexts). */
 THCB200_API int64_t thcb200_launch_count(void);

@@ -189,3 +189,27 @@ def test_int64_offsets_in_the_mixed_type_scan_and_index_kernels(state):
     assert buf[0:8].cpu().numpy().tolist() == np.where(host[0] % 2 == 0, 0, host[0]).tolist()
     del buf
     torch.cuda.empty_cache()
+
+
+def test_state_services(state):
+    """The THCState services the path's callers consult: scratch space of the current device and
+    the cached device properties (lib/THC/THCGeneral.h.in:146,188-192)."""
+    lib = state.lib
+    lib.THCState_getCurrentDeviceScratchSpace.restype = C.c_void_p
+    lib.THCState_getCurrentDeviceScratchSpace.argtypes = [C.c_void_p]
+    lib.THCState_getCurrentDeviceScratchSpaceSize.restype = C.c_size_t
+    lib.THCState_getCurrentDeviceScratchSpaceSize.argtypes = [C.c_void_p]
+    lib.THCState_getCurrentDeviceProperties.restype = C.c_void_p
+    lib.THCState_getCurrentDeviceProperties.argtypes = [C.c_void_p]
+    lib.THCState_getPeerToPeerAccess.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    p = lib.THCState_getCurrentDeviceScratchSpace(state.ptr)
+    n = lib.THCState_getCurrentDeviceScratchSpaceSize(state.ptr)
+    assert p and p % 256 == 0 and n >= 128 * 1024
+    props = lib.THCState_getCurrentDeviceProperties(state.ptr)
+    assert props
+    name = C.string_at(props, 256).split(b"\0")[0].decode()     # cudaDeviceProp starts with char name[256]
+    assert "NVIDIA" in name or len(name) > 0
+    assert lib.THCState_getPeerToPeerAccess(state.ptr, 0, 0) == 1
+    assert lib.THCState_getPeerToPeerAccess(state.ptr, 0, 99) == 0
+    with pytest.raises(thc.THCError, match="is not a device"):
+        state.check()

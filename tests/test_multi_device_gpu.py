@@ -74,3 +74,31 @@ def test_work_after_a_cross_device_copy_sees_the_data(state, two_devices):
     ddst = to_device(state, np.zeros_like(x))
     ddst.copy(dsrc)
     assert ddst.sumall() == float(np.float32(x.astype(np.float64).sum()))   # accreal of a FloatTensor is float
+
+
+def test_copy_without_peer_access_goes_through_dense_temporaries(state, two_devices):
+    """With direct access switched off (THCState_setPeerToPeerAccess) a strided or converting copy
+    is staged through contiguous temporaries on both devices, as in the reference; the values are
+    the same."""
+    import ctypes as C
+    torch = two_devices
+    lib = state.lib
+    lib.THCState_getPeerToPeerAccess.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    lib.THCState_setPeerToPeerAccess.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+    r = rng("xdev-nop2p")
+    src = make_view(r, "Float", (50, 64), "transposed")
+    dst0 = make_view(r, "Float", (50, 64), "holes")
+    assert lib.THCState_getPeerToPeerAccess(state.ptr, 1, 0) == 1
+    lib.THCState_setPeerToPeerAccess(state.ptr, 1, 0, 0)
+    try:
+        assert lib.THCState_getPeerToPeerAccess(state.ptr, 1, 0) == 0
+        dsrc = on_device(torch, 1, lambda: to_device(state, src))
+        ddst = to_device(state, dst0)
+        ddst.copy(dsrc)
+        assert_bit_equal(ddst.numpy(), np.ascontiguousarray(src), "staged strided copy gpu1 -> gpu0")
+        dd = to_device(state, np.zeros((50, 64), np.float64))
+        dd.copy_from(dsrc)
+        assert_bit_equal(dd.numpy(), np.ascontiguousarray(src).astype(np.float64), "staged converting copy gpu1 -> gpu0")
+    finally:
+        lib.THCState_setPeerToPeerAccess(state.ptr, 1, 0, 1)
+    assert lib.THCState_getPeerToPeerAccess(state.ptr, 1, 0) == 1
