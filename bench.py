@@ -124,7 +124,13 @@ def run_cpu(rows: int, steps: int, warmup: int, threads: int | None):
     from oracle import Oracle
     from cutorch_b200._lib import OP, RED
     o = Oracle()
-    nthreads = threads or o.max_threads()
+    # all the host threads this process may run on (torchrun sets OMP_NUM_THREADS=1 for its
+    # children, which would otherwise leave the CPU arm with one thread)
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    nthreads = threads or max(avail, o.max_threads())
     o.set_threads(nthreads)
     rng = np.random.default_rng(1234)
     x = rng.standard_normal((rows, COLS), dtype=np.float32)
