@@ -396,3 +396,43 @@ def test_rows_plan_expanded_and_padded_operands(state, oracle, kind):
             getattr(dout, name)(dins[0], dins[1])
         assert lib.thcb200_last_plan().decode() == "rows"
         check(kind, dout.numpy(), want, True, f"{kind}.{name} rows plan, padded output")
+
+
+SPECIALS = [0.0, -0.0, 1.0, -1.0, 0.5, -0.5, 2.0, 1e-3, -1e-3, 10.0, -10.0, 88.0, -88.0, 710.0, -710.0,
+            float("inf"), float("-inf"), float("nan")]
+
+
+@pytest.mark.parametrize("kind", FP_KINDS)
+def test_unary_math_on_special_values(state, oracle, kind):
+    """Zeros of both signs, infinities, NaN, the largest and smallest magnitudes of the type and
+    its subnormals through every unary function: the results have to be the oracle's (NaN where
+    it gives NaN, the same infinities and signed zeros), within the usual ulp bars elsewhere."""
+    dt = NP_OF_KIND[kind]
+    fi = np.finfo(dt)
+    vals = SPECIALS + [float(fi.max), float(-fi.max), float(fi.tiny), float(-fi.tiny),
+                       float(fi.smallest_subnormal), float(-fi.smallest_subnormal), float(fi.tiny) / 4]
+    with np.errstate(over="ignore"):
+        x = np.array(vals, dtype=np.float64).astype(dt)
+    dx = to_device(state, x)
+    for name, (op, _lo, _hi, exact) in sorted(UNARY_FP.items()):
+        with np.errstate(all="ignore"):
+            want = oracle.pointwise(OP[op], np.zeros(x.shape, dt), [x])
+        out = thc.Tensor.new(state, kind)
+        getattr(out, name)(dx)
+        got = out.numpy()
+        # same NaNs, same infinities, same zeros (with sign)
+        assert np.array_equal(np.isnan(got), np.isnan(want)), f"{kind}.{name}: NaN pattern {got} vs {want}"
+        fin = np.isfinite(want) & (want != 0)
+        assert np.array_equal(got[~fin & ~np.isnan(want)].view(np.uint8), want[~fin & ~np.isnan(want)].view(np.uint8)), \
+            f"{kind}.{name}: infinities / zeros differ: {got} vs {want}"
+        ulp = ULP_EXCEPTIONS.get((kind, name), 2)
+        if exact:
+            assert_bit_equal(got[fin], want[fin], f"{kind}.{name} on special values")
+        else:
+            assert_ulp(got[fin], want[fin], 1 if kind == "Half" else ulp, f"{kind}.{name} on special values")
+    for name in ("abs", "neg", "sign"):
+        with np.errstate(all="ignore"):
+            want = oracle.pointwise(OP[name.upper()], np.zeros(x.shape, dt), [x])
+        out = thc.Tensor.new(state, kind)
+        getattr(out, name)(dx)
+        assert_bit_equal(out.numpy(), want, f"{kind}.{name} on special values")
