@@ -253,6 +253,31 @@ int64_t thcb200_index_to_offset(const thcb200_tensor *t, int64_t linear) {
   return off;
 }
 
+const char *thcb200_pointwise_plan(const thcb200_tensor *out, const thcb200_tensor *in0, const thcb200_tensor *in1,
+                                   const thcb200_tensor *in2, int nin) {
+  if (nin < 0 || nin > 3) { set_error("pointwise_plan: nin out of range"); return nullptr; }
+  const thcb200_tensor *t[4] = {out, in0, in1, in2};
+  HostView v[4];
+  for (int o = 0; o <= nin; ++o) {
+    if (to_host_view(t[o], &v[o], "pointwise_plan operand")) return nullptr;
+    if (v[o].dtype != v[0].dtype) { set_error("pointwise_plan: operands have different dtypes"); return nullptr; }
+    if (v[o].numel != v[0].numel) { set_error("pointwise_plan: operands have different element counts"); return nullptr; }
+  }
+  ApplyPlan plan;
+  make_apply_plan(v, nin + 1, dtype_size(v[0].dtype), &plan);
+  switch (plan.kind) {
+    case kApplyContigVec: {
+      bool wide = true;
+      for (int o = 0; o <= nin; ++o) if (((uintptr_t)v[o].data) % 32 != 0) wide = false;
+      return wide ? "contig_vec" : "contig_vec16";
+    }
+    case kApplyTiled: return "tiled";
+    case kApplyRows: return plan.rows.vec ? "rows" : "rows_scalar";
+    case kApplyGeneric: return plan.index64 ? "generic64" : "generic32";
+    default: return "deep";
+  }
+}
+
 int thcb200_pointwise(thcb200_ctx *ctx, int op, const thcb200_tensor *out, const thcb200_tensor *in0,
                       const thcb200_tensor *in1, const thcb200_tensor *in2, int nin, thcb200_scalar s0,
                       thcb200_scalar s1, void *stream) {

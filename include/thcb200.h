@@ -175,6 +175,12 @@ THCB200_API int thcb200_can_use_32bit(const thcb200_tensor *t);
 /* Element offset of logical (row-major) index `linear` in the view. */
 THCB200_API int64_t thcb200_index_to_offset(const thcb200_tensor *t, int64_t linear);
 
+/* Name of the kernel family thcb200_pointwise would pick for these views ("contig_vec",
+ * "contig_vec16", "tiled", "rows", "rows_scalar", "generic32", "generic64", "deep"), without
+ * launching anything: the planner is host code.  NULL (and thcb200_last_error) on bad views. */
+THCB200_API const char *thcb200_pointwise_plan(const thcb200_tensor *out, const thcb200_tensor *in0,
+                                   const thcb200_tensor *in1, const thcb200_tensor *in2, int nin);
+
 /* ---- device work ----------------------------------------------------------------- */
 
 /* out = op(in...).  Operands need equal element counts, not equal shapes; each is
