@@ -145,6 +145,30 @@ def run_cpu(rows: int, steps: int, warmup: int, threads: int | None):
     return step_bytes(rows) / dt / 1e9, dt, nthreads
 
 
+def host_description():
+    """CPU model name and the number of hardware threads this process may use."""
+    model = "unknown"
+    try:
+        with open("/proc/cpuinfo") as f:
+            for ln in f:
+                if ln.lower().startswith("model name"):
+                    model = ln.split(":", 1)[1].strip()
+                    break
+    except OSError:
+        pass
+    try:
+        avail = len(os.sched_getaffinity(0))
+    except AttributeError:
+        avail = os.cpu_count() or 1
+    return {"cpu_model": model, "nproc": os.cpu_count(), "usable_threads": avail}
+
+
+def one_thread_baseline():
+    """TH's own strided apply and reduce loops are serial: the same step on one host thread (2048 rows, 3 steps)."""
+    gbs, _, _ = run_cpu(2048, 3, 1, 1)
+    return {"value": gbs, "unit": UNIT, "cores": 1, "sample": f"2048 of {ROWS_TOTAL} rows x {COLS} (3 steps after 1 warm-up)"}
+
+
 def reference_main(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -159,7 +183,8 @@ def reference_main(args):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "c5: cmul, add 1, row max+argmax, sum-all on fp32 524288x8192 (row sample on the host)",
                    "impl_note": "TH CPU semantics restated in oracle/th_oracle.cpp (torch7's TH is not in the cutorch tree)"},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port", "sample": sample,
+                         "one_thread": one_thread_baseline(), "host": host_description()},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -305,7 +330,8 @@ def ours_main(args):
         srows = 32768
         gbs, dt, nthreads = run_cpu(srows, 10, 1, None)
         cpu_baseline = {"value": gbs, "unit": UNIT, "cores": nthreads, "kind": "port",
-                        "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (10 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads"}
+                        "sample": f"{srows} of {ROWS_TOTAL} rows x {COLS} (10 steps after 1 warm-up), oracle/th_oracle.cpp with {nthreads} threads",
+                        "one_thread": one_thread_baseline(), "host": host_description()}
     if rank == 0 and world == 1 and args.configs:
         from bench_configs import run_small_configs
         extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
