@@ -279,9 +279,24 @@ __device__ __forceinline__ I int_apply(I s0, I s1, I a, I b, I c) {
   else return a;
 }
 
+// Half sigmoid.  The stored result keeps 11 significand bits, so the float evaluation can use the
+// special-function unit's ex2 and rcp directly (each within 2 float ulp, i.e. 2^-22 relative): the
+// rounded half equals the one obtained from expf and an IEEE division except where the float value
+// lies within 2^-21 of a half rounding boundary, and differs by one half ulp there.  The exact
+// forms cost about 20 issue slots per element, which holds a 2-byte stream below the HBM rate.
+// Limits: ex2(+inf) = inf -> rcp = 0; ex2(-inf) = 0 -> 1; NaN stays NaN.
+__device__ __forceinline__ float sigmoid_for_half(float a) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+
 template <int OP, typename T>
 __device__ __forceinline__ T pw_apply(const OpParams<T> &p, T a, T b, T c) {
-  if constexpr (TypeTraits<T>::is_fp) {
+  if constexpr (OP == THCB200_OP_SIGMOID && sizeof(T) == 2 && TypeTraits<T>::is_fp) {
+    return from_math<T>(sigmoid_for_half(to_math<T>(a)));
+  } else if constexpr (TypeTraits<T>::is_fp) {
     using M = typename TypeTraits<T>::Math;
     return from_math<T>(fp_apply<OP, M>(p.s0, p.s1, to_math<T>(a), to_math<T>(b), to_math<T>(c)));
   } else {

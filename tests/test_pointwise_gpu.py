@@ -436,3 +436,29 @@ def test_unary_math_on_special_values(state, oracle, kind):
         out = thc.Tensor.new(state, kind)
         getattr(out, name)(dx)
         assert_bit_equal(out.numpy(), want, f"{kind}.{name} on special values")
+
+
+def test_half_unary_math_over_every_bit_pattern(state, oracle):
+    """A Half tensor has 65536 possible elements: every one of them through every unary function.
+    Same NaNs, same infinities and zeros; finite results within one half ulp of the oracle's (which
+    evaluates in double and rounds once); and, since the half evaluation runs in float, all but a
+    sliver of them bit-equal."""
+    x = np.arange(65536, dtype=np.uint16).view(np.float16)
+    dx = to_device(state, x)
+    for name, (op, _lo, _hi, exact) in sorted(UNARY_FP.items()):
+        with np.errstate(all="ignore"):
+            want = oracle.pointwise(OP[op], np.zeros(x.shape, np.float16), [x])
+        out = thc.Tensor.new(state, "Half")
+        getattr(out, name)(dx)
+        got = out.numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want)), f"Half.{name}: NaN pattern"
+        rest = ~np.isnan(want)
+        fin = np.isfinite(want) & (want != 0)
+        edge = rest & ~fin
+        assert np.array_equal(got[edge].view(np.uint16), want[edge].view(np.uint16)), f"Half.{name}: infinities / zeros"
+        if exact:
+            assert_bit_equal(got[fin], want[fin], f"Half.{name} over all inputs")
+        else:
+            assert_ulp(got[fin], want[fin], 1, f"Half.{name} over all inputs")
+            differing = int((got[fin].view(np.uint16) != want[fin].view(np.uint16)).sum())
+            assert differing <= 0.02 * fin.sum(), f"Half.{name}: {differing} of {int(fin.sum())} results off by one ulp"
