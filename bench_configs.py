@@ -194,7 +194,7 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         emb = x.view(524288, 256)
         eo = torch.empty_like(emb)
         temb, teo = W(emb, "Float"), W(eo, "Float")
-        out["f2_renorm_f32_524288x256_dim0"] = timed(lambda: teo.renorm(temb, 2, 0, 15.0), 12 * n, reps=5)
+        out["f2_renorm_f32_524288x256_dim0"] = timed(lambda: teo.renorm(temb, 2, 0, 15.0), 8 * n, reps=5)
         idx = torch.randint(1, 524288 + 1, (524288,), dtype=torch.int64, device=dev, generator=g)
         tidx = W(idx, "Long")
         out["f4_indexSelect_f32_524288_rows_of_256"] = timed(lambda: teo.indexSelect(temb, 0, tidx), 8 * n + 8 * 524288, reps=5)

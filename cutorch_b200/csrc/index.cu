@@ -18,6 +18,8 @@
 #include <cuda_fp16.h>
 #include <string.h>
 
+#include <type_traits>
+
 #include "context.h"
 #include "core.cuh"
 #include "plan.h"
@@ -120,6 +122,73 @@ indexed_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, In
     else atomic_add_elem<T>(q, x[u]);
   }
 }
+
+// Four neighbours of the innermost dim per thread, for the layouts where that dim has unit stride
+// on the plain side and in the index tensor (gather / scatter on contiguous tensors): one decode of
+// the linear position, one 32-byte load of four index entries and one vector access on the plain
+// side per four elements; only the redirected side is touched element by element.  p.size[nd-1]
+// counts groups of four.
+template <typename T> struct alignas(4 * sizeof(T)) Quad { T e[4]; };
+
+template <typename T, int MODE, bool REDIRECT_DST, typename IndexT>
+__global__ void __launch_bounds__(kIdxThreads)
+indexed_quad_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, IndexT nquads, T value, unsigned int *errors) {
+  const IndexT quad = (IndexT)blockIdx.x * (IndexT)kIdxThreads + threadIdx.x;
+  if (quad >= nquads) return;
+  const int L = p.nd - 1;
+  IndexT lin, r, op, orr, oi;
+  p.size[L].divmod(quad, lin, r);
+  r *= 4;
+  op = r;
+  oi = r;
+  orr = r * (IndexT)p.redir[L];
+#pragma unroll 1
+  for (int d = L - 1; d >= 0; --d) {
+    IndexT q;
+    p.size[d].divmod(lin, q, r);
+    op += r * (IndexT)p.plain[d];
+    orr += r * (IndexT)p.redir[d];
+    oi += r * (IndexT)p.index[d];
+    lin = q;
+  }
+  union { Bytes32 b; int64_t e[4]; } ix;
+  ix.b = ld32_stream(index + oi);
+  IndexT off[4];
+  bool ok[4];
+  unsigned int bad = 0;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t pos = ix.e[u] - 1;   // positions are 1-based (TH_INDEX_BASE)
+    ok[u] = (uint64_t)pos < (uint64_t)p.limit;
+    bad += ok[u] ? 0u : 1u;
+    off[u] = orr + (IndexT)u * (IndexT)p.redir[L] + (IndexT)pos * (IndexT)p.redirect_stride;
+  }
+  if (bad) atomicAdd(errors, bad);
+  if constexpr (REDIRECT_DST) {
+    Quad<T> x;
+    if constexpr (MODE != kIdxFill) x = *reinterpret_cast<const Quad<T> *>(src + op);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (!ok[u]) continue;
+      if constexpr (MODE == kIdxCopy) dst[off[u]] = x.e[u];
+      else if constexpr (MODE == kIdxFill) dst[off[u]] = value;
+      else atomic_add_elem<T>(dst + off[u], x.e[u]);
+    }
+  } else {
+    Quad<T> x;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (ok[u]) x.e[u] = src[off[u]];
+    if (bad == 0) {
+      *reinterpret_cast<Quad<T> *>(dst + op) = x;
+    } else {   // elements with a position out of range stay as they are
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (ok[u]) dst[op + u] = x.e[u];
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
@@ -129,6 +198,7 @@ struct HostIdxPlan {
   int64_t redirect_stride, limit;
   uint64_t n;
   bool fits32;   // element counts and largest offsets of all three tensors fit 32 bits
+  bool quads;    // size[nd-1] and n count groups of four neighbours (indexed_quad_kernel)
 };
 
 template <typename IndexT>
@@ -154,6 +224,23 @@ int launch_indexed(thcb200_ctx *ctx, const HostIdxPlan &h, void *dst, const void
   const uint64_t blocks = (h.n + per_cta - 1) / per_cta;
   if (blocks >= (1ull << 31)) { set_error("indexed: tensor too large"); return THCB200_ERR_DIMS; }
   unsigned int *errors = reinterpret_cast<unsigned int *>(ctx->status) + 1;
+  if constexpr (!std::is_same<T, Word16>::value) {
+    if (h.quads) {
+      const uint64_t qblocks = (h.n + kIdxThreads - 1) / kIdxThreads;
+      if (h.fits32) {
+        set_plan_name("indexed_quad32");
+        indexed_quad_kernel<T, MODE, REDIRECT_DST, uint32_t><<<(unsigned)qblocks, kIdxThreads, 0, st>>>(
+            (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint32_t>(h), (uint32_t)h.n, value, errors);
+      } else {
+        set_plan_name("indexed_quad64");
+        indexed_quad_kernel<T, MODE, REDIRECT_DST, uint64_t><<<(unsigned)qblocks, kIdxThreads, 0, st>>>(
+            (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint64_t>(h), (uint64_t)h.n, value, errors);
+      }
+      count_launch();
+      THCB_CUDA_TRY(cudaGetLastError());
+      return 0;
+    }
+  }
   if (h.fits32 && h.n < (1ull << 32) - per_cta) {
     set_plan_name("indexed32");
     indexed_kernel<T, MODE, REDIRECT_DST, uint32_t><<<(unsigned)blocks, kIdxThreads, 0, st>>>(
@@ -239,6 +326,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
   HostIdxPlan h;
   h.nd = 0;
   h.n = n;
+  h.quads = false;
   h.fits32 = can_use_32bit(vd) && can_use_32bit(vi) && (fill || can_use_32bit(vs));
   h.redirect_stride = redir.strides[dim];
   h.limit = redir.sizes[dim];
@@ -271,6 +359,20 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
   void *dp = vd.data;
   const void *sp = fill ? nullptr : vs.data;
   const void *xp = vi.data;
+  // Groups of four neighbours: the innermost dim has unit stride on the plain side and in the
+  // index tensor, and every other stride of those two keeps the vectors aligned.
+  auto try_quads = [&]() {
+    const int esz = (int)dtype_size(vd.dtype);
+    const int L = h.nd - 1;
+    if (L < 0 || h.index[L] != 1 || (plain && h.plain[L] != 1) || h.size[L] % 4 != 0) return;
+    if ((uintptr_t)xp % 32 != 0 || (plain && (uintptr_t)plain->data % (uintptr_t)(4 * esz) != 0)) return;
+    for (int d = 0; d < L; ++d)
+      if (h.index[d] % 4 != 0 || h.plain[d] % 4 != 0) return;
+    h.size[L] /= 4;
+    h.n /= 4;
+    h.quads = true;
+  };
+  if (mode == THCB200_INDEX_SCATTER_ADD) try_quads();
   if (mode == THCB200_INDEX_SCATTER_ADD) {
     switch (vd.dtype) {
       case THCB200_U8: return launch_indexed<uint8_t, kIdxAdd, true>(ctx, h, dp, sp, xp, 0, st);
@@ -307,6 +409,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
                           : launch_indexed<Word16, kIdxCopy, false>(ctx, h, dp, sp, xp, w, st);
     }
   }
+  try_quads();
 #define THCB_IDX_SIZED(W) (fill ? launch_move_sized<W, kIdxFill>(ctx, true, h, dp, sp, xp, bits, st) \
                                 : launch_move_sized<W, kIdxCopy>(ctx, redirect_dst, h, dp, sp, xp, bits, st))
   switch (dtype_size(vd.dtype)) {

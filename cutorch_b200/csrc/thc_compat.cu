@@ -1012,6 +1012,13 @@ void renorm(THCState *state, TensorT<R> *self, TensorT<R> *src, R value, long di
   const double p = real_to_double<R>(value);
   thcb200_ctx *ctx = state_ctx(state);
   void *st = (void *)state_stream(state);
+  if (self != src) tensor_resize_as<R>(state, self, src);
+  {  // slices that are short dense runs: one pass
+    thcb200_tensor dout = describe<R>(self), din = describe<R>(src);
+    const int rc = thcb200_renorm_rows(ctx, &dout, &din, (int)dimension, p, real_to_double<R>(maxnorm), st);
+    if (rc == THCB200_OK) return;
+    if (rc != THCB200_ERR_UNSUPPORTED) check_core(rc);
+  }
   // sums of |x|^p over every dim but `dimension`, one dim at a time from the innermost outward
   TensorT<R> *cur = src;
   bool first = true;
@@ -1037,7 +1044,6 @@ void renorm(THCState *state, TensorT<R> *self, TensorT<R> *src, R value, long di
     for (int d = 0; d < src->nDimension; ++d) strides[d] = d == dimension ? cur->stride[d] : 0;
     TensorT<R> *wide = tensor_alloc<R>();
     tensor_raw_set<R>(state, wide, cur->storage, cur->storageOffset, src->nDimension, src->size, strides);
-    if (self != src) tensor_resize_as<R>(state, self, src);
     thcb200_tensor dout = describe<R>(self), din = describe<R>(src), dw = describe<R>(wide);
     rc = thcb200_pointwise(ctx, THCB200_OP_MUL, &dout, &din, &dw, nullptr, 2, kZero, kZero, st);
     tensor_free<R>(state, wide);
@@ -1053,12 +1059,20 @@ void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half
   check_gpu<half>(state, {self, src});
   THArgCheck(dimension >= 0 && dimension < src->nDimension, 3, "invalid dimension");
   THArgCheck(src->nDimension > 1, 1, "need at least 2 dimensions");
+  THArgCheck(THC_half2float(value) > 0, 2, "non-positive-norm not supported");
+  if (self != src) tensor_resize_as<half>(state, self, src);
+  {
+    thcb200_tensor dout = describe<half>(self), din = describe<half>(src);
+    const int rc = thcb200_renorm_rows(state_ctx(state), &dout, &din, (int)dimension, (double)THC_half2float(value),
+                                       (double)THC_half2float(maxnorm), (void *)state_stream(state));
+    if (rc == THCB200_OK) return;
+    if (rc != THCB200_ERR_UNSUPPORTED) check_core(rc);
+  }
   TensorT<float> *wide = tensor_alloc<float>();
   tensor_raw_resize<float>(state, wide, src->nDimension, src->size, nullptr);
   try {
     tensor_copy_convert<float, half>(state, wide, src);
     renorm<float>(state, wide, wide, THC_half2float(value), dimension, THC_half2float(maxnorm));
-    if (self != src) tensor_resize_as<half>(state, self, src);
     tensor_copy_convert<half, float>(state, self, wide);
   } catch (...) {
     tensor_free<float>(state, wide);

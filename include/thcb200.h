@@ -284,6 +284,17 @@ THCB200_API int thcb200_tri(thcb200_ctx *ctx, int upper, int64_t k, const thcb20
 THCB200_API int thcb200_renorm_factor(thcb200_ctx *ctx, const thcb200_tensor *factors,
                           const thcb200_tensor *sums, double p, double maxnorm, void *stream);
 
+/* renorm in one pass: every slice in.select(dim, j) whose p-norm exceeds maxnorm is written to
+ * out scaled by maxnorm / (norm + 1e-7), every other slice is copied.  Taken only when each slice
+ * of both views is one dense, 16-byte aligned run of at most 2048 16-byte vectors (a warp or a
+ * CTA holds it in registers between the fold and the scaling); any other layout returns
+ * THCB200_ERR_UNSUPPORTED before anything is launched, and the caller composes renorm from
+ * thcb200_reduce_dim, thcb200_renorm_factor and a broadcast multiply.  F16 (computed as float,
+ * rounded once), F32, F64; out == in works in place.
+ * lib/THC/generic/THCTensorMathReduce.cu:47-74, lib/THC/THCTensorMathReduce.cuh:132-183. */
+THCB200_API int thcb200_renorm_rows(thcb200_ctx *ctx, const thcb200_tensor *out, const thcb200_tensor *in,
+                        int dim, double p, double maxnorm, void *stream);
+
 /* ---- indexed moves along one dim ------------------------------------------------------- */
 
 /* For every coordinate tuple c of the iteration space, p = index value (1-based), and c' = c with

@@ -139,3 +139,58 @@ def test_index_select_large_rows(state):
     out = thc.Tensor.new(state, "Float")
     out.indexSelect(to_device(state, table), 0, to_device(state, idx))
     assert_bit_equal(out.numpy(), table[idx - 1], "large indexSelect")
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_gather_scatter_four_neighbours_per_thread(state, kind):
+    """Contiguous tensors whose innermost size is a multiple of four take the kernel that handles
+    four neighbours per thread (one 32-byte index load, one vector access on the plain side); same
+    results bit for bit, out-of-range positions skipped and counted there too."""
+    from cutorch_b200 import _lib
+    lib = _lib.load_library()
+    lib.thcb200_take_index_errors.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.c_void_p]
+    r = rng("gather quads", kind)
+    count = C.c_int64(-1)
+    for shape in ((64, 256), (3, 20, 36)):
+        src = exact_values(r, kind, shape, "contiguous")
+        dsrc = to_device(state, src)
+        for dim in range(len(shape)):
+            n = shape[dim]
+            oshape = list(shape)
+            if dim != len(shape) - 1:
+                oshape[dim] = n + 3
+            index = r.integers(1, n + 1, size=oshape).astype(np.int64)
+            out = thc.Tensor.new(state, kind, *oshape)
+            out.gather(dsrc, dim, to_device(state, index))
+            assert lib.thcb200_last_plan() == b"indexed_quad32"
+            assert_bit_equal(out.numpy(), io.gather(src, dim, index), f"{kind} gather {shape} dim {dim}")
+            dst = exact_values(r, kind, shape, "contiguous")
+            perm = (np.argsort(r.uniform(size=shape), axis=dim).astype(np.int64) + 1)
+            ddst = to_device(state, dst)
+            ddst.scatter(dim, to_device(state, perm), dsrc)
+            assert lib.thcb200_last_plan() == b"indexed_quad32"
+            assert_bit_equal(ddst.numpy(), io.scatter(dst, dim, perm, src), f"{kind} scatter {shape} dim {dim}")
+            hits = r.integers(1, n + 1, size=shape).astype(np.int64)
+            ddst = to_device(state, dst)
+            ddst.scatterAdd(dim, to_device(state, hits), dsrc)
+            assert lib.thcb200_last_plan() == b"indexed_quad32"
+            assert_bit_equal(ddst.numpy(), io.scatter_add(dst, dim, hits, src), f"{kind} scatterAdd {shape} dim {dim}")
+            ddst = to_device(state, dst)
+            ddst.scatterFill(dim, to_device(state, hits), 2)
+            assert lib.thcb200_last_plan() == b"indexed_quad32"
+            assert_bit_equal(ddst.numpy(), io.scatter_fill(dst, dim, hits, 2), f"{kind} scatterFill {shape} dim {dim}")
+            # positions out of range: those elements keep what the output held
+            lib.thcb200_take_index_errors(C.c_void_p(state.context), C.byref(count), C.c_void_p(state.stream))
+            broken = index.copy()
+            flat = broken.reshape(-1)
+            where = r.choice(flat.size, size=37, replace=False)
+            flat[where] = r.choice([0, -5, n + 1, n + 1000], size=37)
+            before = exact_values(r, kind, tuple(oshape), "contiguous")
+            dout = to_device(state, before)
+            dout.gather(dsrc, dim, to_device(state, broken))
+            want = io.gather(src, dim, np.where((broken >= 1) & (broken <= n), broken, 1))
+            mask = ((broken < 1) | (broken > n))
+            want[mask] = before[mask]
+            assert_bit_equal(dout.numpy(), want, f"{kind} gather with positions out of range {shape} dim {dim}")
+            lib.thcb200_take_index_errors(C.c_void_p(state.context), C.byref(count), C.c_void_p(state.stream))
+            assert count.value == 37

@@ -8,7 +8,7 @@ import pytest
 
 from cutorch_b200 import thc
 from oracle import matrix_oracle as mx
-from common import ALL_KINDS, FP_KINDS, assert_bit_equal, make_view, rng, to_device
+from common import ALL_KINDS, FP_KINDS, NP_OF_KIND, assert_bit_equal, make_view, rng, to_device
 
 pytestmark = pytest.mark.gpu
 
@@ -77,3 +77,47 @@ def test_renorm(state, kind):
         thc.Tensor.new(state, kind).renorm(to_device(state, make_view(r, kind, (10,), "contiguous")), 2, 0, 1.0)
     with pytest.raises(thc.THCError, match="non-positive-norm"):
         thc.Tensor.new(state, kind).renorm(dx, -1, 0, 1.0)
+
+
+@pytest.mark.parametrize("kind", FP_KINDS)
+def test_renorm_one_pass_and_composed_forms_agree(state, kind):
+    """Slices that are short dense runs take the one-pass kernel (a warp or a CTA keeps the slice in
+    registers), every other layout the composed form; both against the oracle over the slice
+    lengths where the kernel changes shape (vectors per thread, warp or CTA per slice)."""
+    from cutorch_b200 import _lib
+    lib = _lib.load_library()
+    r = rng("renorm forms", kind)
+    elems = {"Half": 8, "Float": 4, "Double": 2}[kind]   # elements per 16-byte vector
+    for nvec in (1, 3, 32, 33, 64, 100, 128, 129, 256, 257, 512, 700, 1024, 1025, 2048, 2049):
+        rows, length = 37, nvec * elems
+        x = (r.standard_normal((rows, length)) * r.uniform(0.2, 3.0, size=(rows, 1))).astype(NP_OF_KIND[kind])
+        dx = to_device(state, x)
+        for p in (1, 2, 3):
+            norms = (np.abs(x.astype(np.float64)) ** p).sum(axis=1) ** (1.0 / p)
+            maxnorm = float(x.dtype.type(float(np.median(norms)) * 1.003))
+            out = thc.Tensor.new(state, kind)
+            out.renorm(dx, p, 0, maxnorm)
+            assert (lib.thcb200_last_plan() == b"renorm_rows") == (nvec <= 2048), (nvec, lib.thcb200_last_plan())
+            want = mx.renorm(x, p, 0, maxnorm)
+            got = out.numpy()
+            tol = REL[kind] * np.maximum(np.abs(want.astype(np.float64)), 1e-30)
+            assert (np.abs(got.astype(np.float64) - want.astype(np.float64)) <= tol).all(), f"{kind} renorm rows of {length}, p={p}"
+            keep = norms <= maxnorm * 0.999
+            assert_bit_equal(got[keep], x[keep], "slices under the threshold")
+    # an odd slice length, and slices along the inner dim of a contiguous matrix: composed form
+    x = r.standard_normal((64, 255)).astype(NP_OF_KIND[kind])
+    dx = to_device(state, x)
+    for dim in (0, 1):
+        out = thc.Tensor.new(state, kind)
+        out.renorm(dx, 2, dim, 1.0)
+        assert lib.thcb200_last_plan() != b"renorm_rows"
+        want = mx.renorm(x, 2, dim, 1.0)
+        assert np.allclose(out.numpy().astype(np.float64), want.astype(np.float64), rtol=REL[kind], atol=0)
+    # the columns of a transposed matrix are dense runs: one pass again, in place
+    base = r.standard_normal((48, 512)).astype(NP_OF_KIND[kind])
+    dt = to_device(state, base)
+    view = dt.transpose(0, 1)
+    view.renorm(view, 2, 1, 1.0)
+    assert lib.thcb200_last_plan() == b"renorm_rows"
+    want = mx.renorm(base.T, 2, 1, 1.0)
+    assert np.allclose(view.numpy().astype(np.float64), want.astype(np.float64), rtol=REL[kind], atol=0)
