@@ -265,10 +265,12 @@ __global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uin
 }
 
 // maskedSelect with a unit-stride aligned mask and a unit-stride aligned source, whole tiles only.
-// A lane owns 16 consecutive elements: one 16-byte mask load, sizeof(W) 16-byte data loads.  The
-// selected elements of a warp are packed into its slice of shared memory and leave as coalesced
-// stores (the packed side keeps its own strides).
-template <typename W, typename IndexT>
+// A lane owns 16 consecutive elements: one 16-byte mask load and the 16 * sizeof(W) bytes of data
+// in 32-byte loads when the source allows (WIDE), so that every sector is fetched by exactly one
+// instruction: with 16-byte loads and no L1 allocation two instructions fetch each sector from the
+// L2.  The selected elements of a warp are packed into its slice of shared memory and leave as
+// coalesced stores (the packed side keeps its own strides).
+template <typename W, typename IndexT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const uint8_t *mask, const uint64_t *offsets) {
   __shared__ uint32_t wsum[kThreads / 32];
@@ -276,12 +278,19 @@ masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const 
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
   const Bytes16 mv = ld16_stream(mask + ebase);
-  alignas(16) W e[16];
+  alignas(32) W e[16];
   constexpr int NV = (int)sizeof(W);   // 16-byte vectors holding 16 elements
+  if constexpr (WIDE && NV >= 2) {
 #pragma unroll
-  for (int v = 0; v < NV; ++v)
-    *reinterpret_cast<Bytes16 *>(reinterpret_cast<char *>(e) + 16 * v) =
-        ld16_stream(reinterpret_cast<const char *>(src + ebase) + 16 * v);
+    for (int v = 0; v < NV / 2; ++v)
+      *reinterpret_cast<Bytes32 *>(reinterpret_cast<char *>(e) + 32 * v) =
+          ld32_stream(reinterpret_cast<const char *>(src + ebase) + 32 * v);
+  } else {
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+      *reinterpret_cast<Bytes16 *>(reinterpret_cast<char *>(e) + 16 * v) =
+          ld16_stream(reinterpret_cast<const char *>(src + ebase) + 16 * v);
+  }
   const uint32_t bits = nonzero_bits16(mv);
   const uint32_t cnt = __popc(bits);
   uint32_t incl = cnt;
@@ -649,8 +658,11 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
     full = n / kTile;
     if (full > 0) {
       set_plan_name(i32 ? "masked_select_vec32" : "masked_select_vec64");
-      if (i32) masked_select_vec_kernel<W, uint32_t><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
-      else masked_select_vec_kernel<W, uint64_t><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      const bool wide = ((uintptr_t)strided) % 32 == 0;
+      if (i32 && wide) masked_select_vec_kernel<W, uint32_t, true><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
+      else if (i32) masked_select_vec_kernel<W, uint32_t, false><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
+      else if (wide) masked_select_vec_kernel<W, uint64_t, true><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      else masked_select_vec_kernel<W, uint64_t, false><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
       ++launches;
     }
   }
