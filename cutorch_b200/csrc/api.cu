@@ -169,7 +169,8 @@ int thcb200_ctx_create(thcb200_ctx **out, int device) {
   if (e == cudaSuccess) e = cudaMalloc((void **)&c->status, 64);
   if (e == cudaSuccess) e = cudaMemset(c->status, 0, 64);
   if (e == cudaSuccess) e = cudaMalloc(&c->dev_slot, 64);
-  if (e == cudaSuccess) e = cudaHostAlloc(&c->host_slot, 64, cudaHostAllocDefault);
+  if (e == cudaSuccess) e = cudaHostAlloc(&c->host_slot, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e == cudaSuccess) e = cudaHostGetDevicePointer(&c->host_slot_dev, c->host_slot, 0);
   if (e == cudaSuccess) e = cudaMalloc(&c->ws, 1 << 20);
   if (e == cudaSuccess) c->ws_bytes = 1 << 20;
   cudaSetDevice(prev);
@@ -337,6 +338,10 @@ static int check_reduce_common(thcb200_ctx *ctx, const thcb200_tensor *in, HostV
   return to_host_view(in, vin, what);
 }
 
+// bytes [16, 24) of the pinned slot receive the result of thcb200_reduce_all_host; the first bytes
+// stay the staging area of the small host <-> device copies
+static constexpr size_t kHostResultOffset = 16;
+
 int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, const thcb200_tensor *in,
                        void *result_dev, void *stream) {
   HostView vin;
@@ -353,6 +358,11 @@ int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, con
     const bool one = (mode == kProd || mode == kAll);
     union { double d; int64_t i; } u;
     if (fp) u.d = one ? 1.0 : 0.0; else u.i = one ? 1 : 0;
+    if (result_dev == (char *)ctx->host_slot_dev + kHostResultOffset) {   // thcb200_reduce_all_host
+      THCB_CUDA_TRY(cudaStreamSynchronize(st));
+      memcpy((char *)ctx->host_slot + kHostResultOffset, &u, 8);
+      return THCB200_OK;
+    }
     memcpy(ctx->host_slot, &u, 8);
     THCB_CUDA_TRY(cudaMemcpyAsync(result_dev, ctx->host_slot, 8, cudaMemcpyHostToDevice, st));
     return THCB200_OK;
@@ -364,12 +374,12 @@ int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s
                             void *result_host, void *stream) {
   if (!result_host) { set_error("reduce_all_host: null result pointer"); return THCB200_ERR_ARG; }
   if (!ctx) { set_error("reduce_all_host: null context"); return THCB200_ERR_ARG; }
-  int rc = thcb200_reduce_all(ctx, rop, pre, s, in, ctx->dev_slot, stream);
+  // The kernel that finishes the fold stores the result straight into the pinned, mapped host
+  // slot: no device-to-host copy is enqueued behind it, the stream synchronisation is all.
+  int rc = thcb200_reduce_all(ctx, rop, pre, s, in, (char *)ctx->host_slot_dev + kHostResultOffset, stream);
   if (rc) return rc;
-  cudaStream_t st = (cudaStream_t)stream;
-  THCB_CUDA_TRY(cudaMemcpyAsync(ctx->host_slot, ctx->dev_slot, 8, cudaMemcpyDeviceToHost, st));
-  THCB_CUDA_TRY(cudaStreamSynchronize(st));
-  memcpy(result_host, ctx->host_slot, 8);
+  THCB_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  memcpy(result_host, (char *)ctx->host_slot + kHostResultOffset, 8);
   return THCB200_OK;
 }
 

@@ -19,7 +19,8 @@ struct thcb200_ctx {
   size_t ws_bytes;
   unsigned int *tickets;  // kNumTickets counters, zero between launches (kernels reset them)
   int *status;            // device word: kernels record bounded-wait failures here
-  void *host_slot;        // pinned, 64 bytes
+  void *host_slot;        // pinned, mapped, 64 bytes
+  void *host_slot_dev;    // the device-side address of host_slot: kernels store results straight to the host
   void *dev_slot;         // device, 64 bytes: result of reduce_all_host
   // masked copy / select: tile counts and offsets of the mask counted last, and which mask
   // view and stream they belong to (reused only when the caller says the mask is unchanged)

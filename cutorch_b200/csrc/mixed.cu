@@ -334,7 +334,7 @@ mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, 
 // owns a consecutive span of tiles and walks it 32 tiles at a time with coalesced loads (first to
 // add its span up, then, once the 32 span totals are scanned, to write the offsets).
 __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts, uint64_t *offsets, uint64_t ntiles,
-                                                         int64_t *total) {
+                                                         int64_t *total, int64_t *total_host) {
   __shared__ uint64_t span_total[32];
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint64_t steps = (ntiles + 1023) / 1024;          // 32-tile steps per warp
@@ -356,7 +356,10 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts,
   __syncthreads();
   uint64_t run = 0;
   for (unsigned w = 0; w < warp; ++w) run += span_total[w];
-  if (threadIdx.x == 1023) *total = (int64_t)(run + s);
+  if (threadIdx.x == 1023) {
+    *total = (int64_t)(run + s);
+    *total_host = (int64_t)(run + s);   // mapped pinned memory: the caller reads it after a stream synchronisation
+  }
   for (uint64_t j = 0; j < steps; ++j) {
     const uint64_t i = lo + j * 32 + lane;
     const uint32_t v = i < ntiles ? counts[i] : 0u;
@@ -560,6 +563,9 @@ uint64_t layout_hash(const HostView &v) {
   return h;
 }
 
+// bytes [24, 32) of the context's pinned, mapped slot receive the number of set mask elements
+constexpr size_t kHostCountOffset = 24;
+
 struct MaskPrep {
   uint64_t ntiles;
   uint64_t *offsets;   // device, ntiles entries
@@ -623,7 +629,8 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
       mask_tile_count_kernel<uint64_t><<<rest, kThreads, 0, st>>>(mask, make_view<uint64_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
     ++launches;
   }
-  tile_scan_kernel<<<1, 1024, 0, st>>>(counts, mp->offsets, mp->ntiles, mp->total);
+  tile_scan_kernel<<<1, 1024, 0, st>>>(counts, mp->offsets, mp->ntiles, mp->total,
+                                       reinterpret_cast<int64_t *>((char *)ctx->host_slot_dev + kHostCountOffset));
   count_launch(launches);
   THCB_CUDA_TRY(cudaGetLastError());
   ctx->prep_mask = vm.data;
@@ -758,9 +765,8 @@ int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8, int64_
   MaskPrep mp;
   rc = prepare_mask(ctx, vm, false, st, &mp);
   if (rc) return rc;
-  THCB_CUDA_TRY(cudaMemcpyAsync(ctx->host_slot, mp.total, 8, cudaMemcpyDeviceToHost, st));
   THCB_CUDA_TRY(cudaStreamSynchronize(st));
-  memcpy(count_host, ctx->host_slot, 8);
+  memcpy(count_host, (char *)ctx->host_slot + kHostCountOffset, 8);
   return THCB200_OK;
 }
 
