@@ -160,7 +160,6 @@ int thcb200_ctx_create(thcb200_ctx **out, int device) {
   THCB_CUDA_TRY(cudaGetDevice(&prev));
   THCB_CUDA_TRY(cudaSetDevice(device));
   thcb200_ctx *c = new thcb200_ctx();
-  memset(c, 0, sizeof(*c));
   c->device = device;
   cudaError_t e = cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, device);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
@@ -200,6 +199,7 @@ void thcb200_ctx_destroy(thcb200_ctx *c) {
 
 void *thcb200_ctx_workspace(thcb200_ctx *ctx, size_t min_bytes, size_t *bytes) {
   if (!ctx) { set_error("ctx_workspace: null context"); return nullptr; }
+  THCB_CTX_LOCK(ctx);
   int prev = 0;
   cudaGetDevice(&prev);
   if (prev != ctx->device) cudaSetDevice(ctx->device);
@@ -351,6 +351,7 @@ int thcb200_reduce_all(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s, con
   if (mode < 0) { set_error("reduce_all: unknown reduce op %d / pre op %d", rop, pre); return THCB200_ERR_ARG; }
   if (!result_dev) { set_error("reduce_all: null result pointer"); return THCB200_ERR_ARG; }
   cudaStream_t st = (cudaStream_t)stream;
+  THCB_CTX_LOCK(ctx);
   if (vin.numel == 0) {
     // THC_reduceAll on an empty tensor yields the initial value (lib/THC/THCReduceAll.cuh:253-257)
     if (mode == kMin || mode == kMax) { set_error("reduce_all: min/max of an empty tensor"); return THCB200_ERR_ARG; }
@@ -376,6 +377,7 @@ int thcb200_reduce_all_host(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s
   if (!ctx) { set_error("reduce_all_host: null context"); return THCB200_ERR_ARG; }
   // The kernel that finishes the fold stores the result straight into the pinned, mapped host
   // slot: no device-to-host copy is enqueued behind it, the stream synchronisation is all.
+  THCB_CTX_LOCK(ctx);
   int rc = thcb200_reduce_all(ctx, rop, pre, s, in, (char *)ctx->host_slot_dev + kHostResultOffset, stream);
   if (rc) return rc;
   THCB_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
@@ -421,6 +423,7 @@ int thcb200_reduce_dim_post(thcb200_ctx *ctx, int rop, int pre, thcb200_scalar s
   if (rc) return rc;
   if (vout.numel == 0) return THCB200_OK;
   if (post_kind >= THCB200_POST_VAR_BIASED) post.f = (double)vin.sizes[dim];  // n of the var/std formulas
+  THCB_CTX_LOCK(ctx);
   return kReduceDim[vin.dtype](ctx, mode, vin, vout, dim, s, post, (cudaStream_t)stream);
 }
 
@@ -441,6 +444,7 @@ int thcb200_reduce_dim_index(thcb200_ctx *ctx, int rop, const thcb200_tensor *va
   rc = check_reduce_dim(vin, vidx, dim, "reduce_dim_index (indices)");
   if (rc) return rc;
   if (vval.numel == 0) return THCB200_OK;
+  THCB_CTX_LOCK(ctx);
   return kReduceDimIndex[vin.dtype](ctx, rop == THCB200_RED_MAX, vin, vval, vidx, dim, (cudaStream_t)stream);
 }
 

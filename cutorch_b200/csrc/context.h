@@ -5,13 +5,20 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/thcb200.h"
 
 namespace thcb {
 constexpr int kNumTickets = 4096;
 }
 
+// The scratch of a context (workspace, ticket counters, result slots, mask offsets) is reused
+// from call to call, which is safe in the order of ONE stream: calls on streams that may run
+// concurrently need a context each.  Several host threads may share a context; `lock` serialises
+// their calls (including the wait for a result that comes back through the pinned slot).
 struct thcb200_ctx {
+  std::recursive_mutex lock;
   int device;
   int num_sms;
   int max_smem_optin;
@@ -32,6 +39,8 @@ struct thcb200_ctx {
   void *prep_stream;
   int prep_valid;
 };
+
+#define THCB_CTX_LOCK(ctx) std::lock_guard<std::recursive_mutex> thcb_ctx_guard((ctx)->lock)
 
 namespace thcb {
 

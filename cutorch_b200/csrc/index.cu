@@ -423,6 +423,7 @@ int thcb200_indexed(thcb200_ctx *ctx, int mode, const thcb200_tensor *dst, const
 
 int thcb200_take_index_errors(thcb200_ctx *ctx, int64_t *count_host, void *stream) {
   if (!ctx || !count_host) { set_error("take_index_errors: null argument"); return THCB200_ERR_ARG; }
+  THCB_CTX_LOCK(ctx);
   cudaStream_t st = (cudaStream_t)stream;
   unsigned int *errors = reinterpret_cast<unsigned int *>(ctx->status) + 1;
   THCB_CUDA_TRY(cudaMemcpyAsync(ctx->host_slot, errors, sizeof(unsigned int), cudaMemcpyDeviceToHost, st));

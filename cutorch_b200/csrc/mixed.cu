@@ -761,6 +761,7 @@ int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8, int64_
   int rc = check_mask(mask_u8, &vm, "masked_count");
   if (rc) return rc;
   if (vm.numel == 0) { *count_host = 0; return THCB200_OK; }
+  THCB_CTX_LOCK(ctx);
   cudaStream_t st = (cudaStream_t)stream;
   MaskPrep mp;
   rc = prepare_mask(ctx, vm, false, st, &mp);
@@ -781,6 +782,7 @@ static int masked_move(thcb200_ctx *ctx, bool select, const thcb200_tensor *stri
   if (vs.dtype != vp.dtype) { set_error("%s: operands have different dtypes", what); return THCB200_ERR_ARG; }
   if (vs.numel != vm.numel) { set_error("%s: tensor and mask have different element counts", what); return THCB200_ERR_SIZE; }
   if (vm.numel == 0) return THCB200_OK;
+  THCB_CTX_LOCK(ctx);
   const bool reuse = (flags & THCB200_FLAG_MASK_COUNTED) != 0;
   cudaStream_t st = (cudaStream_t)stream;
 #define THCB_MOVE(W) (select ? masked_move_sized<W, true>(ctx, vs, vp, vm, reuse, st) : masked_move_sized<W, false>(ctx, vs, vp, vm, reuse, st))

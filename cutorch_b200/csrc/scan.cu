@@ -527,6 +527,7 @@ extern "C" int thcb200_scan_dim(thcb200_ctx *ctx, int rop, const thcb200_tensor 
   for (int i = 0; i < vin.ndim; ++i)
     if (vin.sizes[i] != vout.sizes[i]) { set_error("scan_dim: output and input have different shapes"); return THCB200_ERR_SIZE; }
   if (vin.numel == 0) return THCB200_OK;
+  THCB_CTX_LOCK(ctx);
   cudaStream_t st = (cudaStream_t)stream;
   const bool prod = rop == THCB200_RED_PROD;
   switch (vin.dtype) {

@@ -93,8 +93,7 @@ extern "C" THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_s
 
   // A stand-in context whose workspace is the static array: the shared launch code then finds
   // its partials buffer large enough and never grows it.
-  thcb200_ctx view_ctx;
-  memset(&view_ctx, 0, sizeof(view_ctx));
+  thcb200_ctx view_ctx{};
   view_ctx.device = device;
   view_ctx.num_sms = g_num_sms[device];
   view_ctx.ws = g_scratch_dev[device];

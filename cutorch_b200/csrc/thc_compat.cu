@@ -10,10 +10,13 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <new>
 #include <set>
 #include <type_traits>
+#include <utility>
+#include <vector>
 #include <string>
 
 #include "../../include/THC/THC.h"
@@ -82,10 +85,18 @@ void record_failure(const THFailure &f) {
 // ======================================================================================
 // State
 // ======================================================================================
+// Contexts of one device, one per stream that has been current on it: the scratch of a context
+// is only safe in the order of a single stream (cutorch keeps its scratch space per stream for the
+// same reason, lib/THC/THCGeneral.c:563-590).
+struct CtxTable {
+  std::mutex m;
+  std::vector<std::pair<cudaStream_t, thcb200_ctx *>> v;
+};
+
 struct THCState {
   int numDevices;
-  thcb200_ctx **ctx;          // one per device, created on first use
-  THCStream **current;        // current stream per device (null = default stream)
+  CtxTable *tables;           // per device; contexts are created on first use
+  unsigned long long epoch;   // distinguishes this initialisation from earlier ones at the same address
   THCDeviceAllocator *allocator;
   THCDeviceAllocator defaultAllocator;
   int initialised;
@@ -129,20 +140,75 @@ int current_device() {
   return d;
 }
 
+// The current stream of each device is a property of the calling thread, as in cutorch
+// (THCThreadLocal in lib/THC/THCGeneral.c:516-561): a thread that never called
+// THCState_setStream works on the default stream whatever other threads have set.
+std::atomic<unsigned long long> g_state_epoch{0};
+
+struct ThreadStreams {
+  struct Entry {
+    const THCState *state;
+    unsigned long long epoch;
+    std::vector<THCStream *> current;   // per device; null = default stream
+  };
+  std::vector<Entry> entries;
+  static void release(Entry &e) {
+    for (THCStream *s : e.current) if (s) THCStream_free(s);
+    e.current.clear();
+  }
+  // the calling thread's streams for this initialisation of `state` (created empty on demand)
+  Entry *find(const THCState *state, bool create) {
+    for (size_t i = 0; i < entries.size(); ++i) {
+      if (entries[i].state != state) continue;
+      if (entries[i].epoch == state->epoch) return &entries[i];
+      release(entries[i]);               // left over from a state that was shut down
+      entries.erase(entries.begin() + (long)i);
+      break;
+    }
+    if (!create) return nullptr;
+    entries.push_back(Entry{state, state->epoch, std::vector<THCStream *>((size_t)(state->numDevices > 0 ? state->numDevices : 1), nullptr)});
+    return &entries.back();
+  }
+  void drop(const THCState *state) {
+    for (size_t i = 0; i < entries.size(); ++i)
+      if (entries[i].state == state) { release(entries[i]); entries.erase(entries.begin() + (long)i); return; }
+  }
+  ~ThreadStreams() { for (Entry &e : entries) release(e); }
+};
+thread_local ThreadStreams t_streams;
+
+THCStream *thread_stream(THCState *state, int device) {
+  if (!state || !state->initialised || device < 0 || device >= state->numDevices) return nullptr;
+  ThreadStreams::Entry *e = t_streams.find(state, false);
+  return e ? e->current[(size_t)device] : nullptr;
+}
+
+cudaStream_t state_stream(THCState *state) {
+  THCStream *s = thread_stream(state, current_device());
+  return s ? s->stream : (cudaStream_t)0;
+}
+
+// The context of the current device and the calling thread's current stream on it.
 thcb200_ctx *state_ctx(THCState *state) {
   if (!state || !state->initialised) th_error("THCState is not initialised (call THCudaInit)");
   const int d = current_device();
   if (d >= state->numDevices) th_error("current device %d out of range", d);
-  if (!state->ctx[d]) {
-    if (thcb200_ctx_create(&state->ctx[d], d) != 0) th_error("%s", thcb200_last_error());
+  const cudaStream_t st = state_stream(state);
+  struct Last { const THCState *state; unsigned long long epoch; int device; cudaStream_t stream; thcb200_ctx *ctx; };
+  thread_local Last last = {nullptr, 0, -1, nullptr, nullptr};
+  if (last.ctx && last.state == state && last.epoch == state->epoch && last.device == d && last.stream == st) return last.ctx;
+  CtxTable &t = state->tables[d];
+  thcb200_ctx *ctx = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(t.m);
+    for (auto &e : t.v) if (e.first == st) { ctx = e.second; break; }
+    if (!ctx) {
+      if (thcb200_ctx_create(&ctx, d) != 0) th_error("%s", thcb200_last_error());
+      t.v.emplace_back(st, ctx);
+    }
   }
-  return state->ctx[d];
-}
-
-cudaStream_t state_stream(THCState *state) {
-  const int d = current_device();
-  if (state && state->initialised && d < state->numDevices && state->current[d]) return state->current[d]->stream;
-  return 0;
+  last = Last{state, state->epoch, d, st, ctx};
+  return ctx;
 }
 
 }  // namespace
@@ -196,8 +262,8 @@ void THCudaInit(THCState *state) {
   int n = 0;
   THCudaCheck(cudaGetDeviceCount(&n));
   state->numDevices = n;
-  state->ctx = (thcb200_ctx **)calloc((size_t)(n > 0 ? n : 1), sizeof(thcb200_ctx *));
-  state->current = (THCStream **)calloc((size_t)(n > 0 ? n : 1), sizeof(THCStream *));
+  state->tables = new CtxTable[(size_t)(n > 0 ? n : 1)];
+  state->epoch = ++g_state_epoch;
   state->p2pOff = (unsigned char *)calloc((size_t)(n > 0 ? n * n : 1), 1);
   state->props = (cudaDeviceProp *)calloc((size_t)(n > 0 ? n : 1), sizeof(cudaDeviceProp));
   state->propsValid = (unsigned char *)calloc((size_t)(n > 0 ? n : 1), 1);
@@ -226,17 +292,14 @@ void THCudaInit(THCState *state) {
 void THCudaShutdown(THCState *state) {
   if (!state || !state->initialised) return;
   mark_state(state, false);
-  for (int d = 0; d < state->numDevices; ++d) {
-    if (state->ctx[d]) thcb200_ctx_destroy(state->ctx[d]);
-    if (state->current[d]) THCStream_free(state->current[d]);
-  }
-  free(state->ctx);
-  free(state->current);
+  for (int d = 0; d < state->numDevices; ++d)
+    for (auto &e : state->tables[d].v) thcb200_ctx_destroy(e.second);
+  delete[] state->tables;
+  t_streams.drop(state);   // other threads' entries are recognised as stale by the epoch
   free(state->p2pOff);
   free(state->props);
   free(state->propsValid);
-  state->ctx = nullptr;
-  state->current = nullptr;
+  state->tables = nullptr;
   state->p2pOff = nullptr;
   state->props = nullptr;
   state->propsValid = nullptr;
@@ -250,14 +313,12 @@ cudaStream_t THCState_getCurrentStream(THCState *state) {
   API_END_RET(0)
 }
 cudaStream_t THCState_getCurrentStreamOnDevice(THCState *state, int device) {
-  if (state && state->initialised && device >= 0 && device < state->numDevices && state->current[device])
-    return state->current[device]->stream;
-  return 0;
+  THCStream *s = thread_stream(state, device);
+  return s ? s->stream : (cudaStream_t)0;
 }
 THCStream *THCState_getStream(THCState *state) {
   API_BEGIN
-  const int d = current_device();
-  return state->current[d];
+  return thread_stream(state, current_device());
   API_END_RET(nullptr)
 }
 void THCState_setStream(THCState *state, THCStream *stream) {
@@ -267,8 +328,10 @@ void THCState_setStream(THCState *state, THCStream *stream) {
     THArgCheck(stream->device == d, 2, "stream belongs to another device");
     THCStream_retain(stream);
   }
-  if (state->current[d]) THCStream_free(state->current[d]);
-  state->current[d] = stream;
+  if (!state->initialised || d >= state->numDevices) th_error("THCState_setStream: state not initialised for device %d", d);
+  ThreadStreams::Entry *e = t_streams.find(state, true);
+  if (e->current[(size_t)d]) THCStream_free(e->current[(size_t)d]);
+  e->current[(size_t)d] = stream;
   API_END
 }
 THCDeviceAllocator *THCState_getDeviceAllocator(THCState *state) { return state->allocator; }

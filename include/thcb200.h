@@ -138,10 +138,15 @@ typedef enum thcb200_pre_op {
   THCB200_PRE_COUNT
 } thcb200_pre_op;
 
-/* Opaque per-device context: the reduction workspace (per-block partials, tickets),
- * a pinned host slot for results and cached device properties.  It replaces the
- * scratch-space services of THCState (lib/THC/THCGeneral.c:677-712).  A context may be
- * used from one stream at a time. */
+/* Opaque context of one device: the reduction workspace (per-block partials, tickets),
+ * a pinned, mapped host slot that kernels store host-bound results into, and cached device
+ * properties.  It replaces the scratch-space services of THCState, which are kept per device and
+ * per stream there (lib/THC/THCGeneral.c:563-590, 677-712).
+ *   Streams: the scratch is reused from call to call, which is safe in the order of one stream;
+ *   give every stream whose work may overlap another's a context of its own (the THC layer keeps
+ *   one per device and stream that has been current).
+ *   Threads: several host threads may call into one context; the calls that use its scratch are
+ *   serialised by a lock inside it, including the wait for a result returned to the host. */
 typedef struct thcb200_ctx thcb200_ctx;
 
 THCB200_API int thcb200_ctx_create(thcb200_ctx **out, int device);

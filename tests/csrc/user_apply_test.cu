@@ -1,6 +1,9 @@
 // Test helper: user-defined functors run through the C++ template faces of the apply and the
 // reductions (include/THC/THCApply.cuh, include/THC/THCReduce.cuh), the way a downstream CUDA library such as cunn uses cutorch.
 // Built into cutorch_b200/lib/libthcb200_usertest.so and driven from tests/test_template_api_gpu.py.
+#include <thread>
+#include <vector>
+
 #include "THC/THCApply.cuh"
 #include "THC/THCReduce.cuh"
 
@@ -115,6 +118,66 @@ __attribute__((visibility("default"))) int usertest_minmax_all(THCState *state, 
   *lo = r.lo;
   *hi = r.hi;
   return ok ? 1 : 0;
+}
+
+// Several host threads share one THCState (cutorch: test/test_shutdown.lua:55, one state for all
+// Lua threads).  Thread 0 stays on the default stream; every other thread makes a stream of its own
+// current (thread-local, lib/THC/THCGeneral.c:516-561) and checks that it alone sees it.  Each then
+// runs, `iters` times on its own tensors, the calls that keep partial results in per-stream scratch:
+// a full sum, a sum over the outer dim split over many CTAs, a chunked cumulative sum.  All values are
+// small integers, so every expected result is exact.  Returns the number of wrong results.
+__attribute__((visibility("default"))) int usertest_threads(THCState *state, int nthreads, int iters) {
+  std::vector<int> bad((size_t)nthreads, 0);
+  std::vector<std::thread> pool;
+  const cudaStream_t mine_before = THCState_getCurrentStream(state);
+  int device = 0;
+  cudaGetDevice(&device);
+  for (int t = 0; t < nthreads; ++t) {
+    pool.emplace_back([state, t, iters, device, &bad]() {
+      int wrong = 0;
+      cudaSetDevice(device);
+      THCStream *stream = nullptr;
+      if (THCState_getCurrentStream(state) != 0) ++wrong;          // a new thread starts on the default stream
+      if (t > 0) {
+        stream = THCStream_new(cudaStreamNonBlocking);
+        THCState_setStream(state, stream);
+        if (THCState_getCurrentStream(state) != stream->stream) ++wrong;
+      }
+      const long rows = 4096, cols = 256, n1 = 1 << 22;
+      const float v = (float)(t + 1);
+      THCudaTensor *m = THCudaTensor_newWithSize2d(state, rows, cols);
+      THCudaTensor *colsum = THCudaTensor_newWithSize2d(state, 1, cols);
+      THCudaTensor *line = THCudaTensor_newWithSize1d(state, n1);
+      THCudaTensor *scan = THCudaTensor_newWithSize1d(state, n1);
+      THCudaTensor_fill(state, m, v);
+      THCudaTensor_fill(state, line, 1.0f);
+      for (int i = 0; i < iters; ++i) {
+        if (THCudaTensor_sumall(state, m) != v * (float)(rows * cols)) ++wrong;
+        THCudaTensor_sum(state, colsum, m, 0, 1);
+        if (THCudaTensor_sumall(state, colsum) != v * (float)(rows * cols)) ++wrong;
+        if (THCudaTensor_maxall(state, colsum) != v * (float)rows) ++wrong;
+        THCudaTensor_cumsum(state, scan, line, 0);
+        if (THCudaTensor_maxall(state, scan) != (float)n1) ++wrong;
+        if (THCudaTensor_sumall(state, scan) != (float)((double)n1 * (double)(n1 + 1) / 2.0)) ++wrong;
+      }
+      if (THCB200_errorOccurred()) ++wrong;
+      THCudaTensor_free(state, m);
+      THCudaTensor_free(state, colsum);
+      THCudaTensor_free(state, line);
+      THCudaTensor_free(state, scan);
+      cudaStreamSynchronize(THCState_getCurrentStream(state));
+      if (stream) {
+        THCState_setStream(state, nullptr);
+        THCStream_free(stream);
+      }
+      bad[(size_t)t] = wrong;
+    });
+  }
+  for (auto &th : pool) th.join();
+  int total = 0;
+  for (int b : bad) total += b;
+  if (THCState_getCurrentStream(state) != mine_before) ++total;   // the caller's own current stream is untouched
+  return total;
 }
 
 }  // extern "C"

@@ -131,3 +131,11 @@ def test_reduce_all_user_functors(state, user):
     res = C.c_float(-1)
     assert user.usertest_absmax_all(state.ptr, thc.Tensor.new(state, "Float").ptr, C.byref(res)) == 1
     assert res.value == 0.0
+
+
+def test_host_threads_share_a_state_with_a_stream_each(state, user):
+    """Four host threads on one THCState: the current stream is per thread, and the split
+    reductions and chunked scans of concurrent streams keep their partials apart."""
+    user.usertest_threads.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    assert user.usertest_threads(state.ptr, 4, 25) == 0
+    state.check()
