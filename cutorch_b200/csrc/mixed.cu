@@ -277,6 +277,7 @@ masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const 
   __shared__ W stage[kThreads / 32][kWarpSpan];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
+  uint64_t pos = offsets[blockIdx.x];   // needed last: in flight together with the mask and the data
   const Bytes16 mv = ld16_stream(mask + ebase);
   alignas(32) W e[16];
   constexpr int NV = (int)sizeof(W);   // 16-byte vectors holding 16 elements
@@ -306,7 +307,6 @@ masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const 
   for (int j = 0; j < 16; ++j)
     if ((bits >> j) & 1u) stage[warp][r++] = e[j];
   __syncthreads();
-  uint64_t pos = offsets[blockIdx.x];
   for (unsigned w = 0; w < warp; ++w) pos += wsum[w];
   for (uint32_t i = lane; i < wtotal; i += 32) packed[vp.offset((IndexT)(pos + i))] = stage[warp][i];
 }
@@ -339,16 +339,17 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts,
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint64_t steps = (ntiles + 1023) / 1024;          // 32-tile steps per warp
   const uint64_t lo = (uint64_t)warp * steps * 32;
+  constexpr int B = 8;   // loads in flight per lane: a step is one dependent round trip to the L2
   uint64_t s = 0;
-  for (uint64_t j = 0; j < steps; j += 4) {
-    uint32_t v[4];
+  for (uint64_t j = 0; j < steps; j += B) {
+    uint32_t v[B];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < B; ++u) {
       const uint64_t i = lo + (j + u) * 32 + lane;
       v[u] = (j + u < steps && i < ntiles) ? counts[i] : 0u;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) s += v[u];
+    for (int u = 0; u < B; ++u) s += v[u];
   }
 #pragma unroll
   for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
@@ -360,17 +361,28 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts,
     *total = (int64_t)(run + s);
     *total_host = (int64_t)(run + s);   // mapped pinned memory: the caller reads it after a stream synchronisation
   }
-  for (uint64_t j = 0; j < steps; ++j) {
-    const uint64_t i = lo + j * 32 + lane;
-    const uint32_t v = i < ntiles ? counts[i] : 0u;
-    uint32_t incl = v;
+  for (uint64_t j = 0; j < steps; j += B) {
+    uint32_t v[B], incl[B];
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= (unsigned)d) incl += y;
+    for (int u = 0; u < B; ++u) {
+      const uint64_t i = lo + (j + u) * 32 + lane;
+      v[u] = (j + u < steps && i < ntiles) ? counts[i] : 0u;
     }
-    if (i < ntiles) offsets[i] = run + (incl - v);
-    run += __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+    for (int u = 0; u < B; ++u) {
+      incl[u] = v[u];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t y = __shfl_up_sync(0xffffffffu, incl[u], d);
+        if (lane >= (unsigned)d) incl[u] += y;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < B; ++u) {
+      const uint64_t i = lo + (j + u) * 32 + lane;
+      if (j + u < steps && i < ntiles) offsets[i] = run + (incl[u] - v[u]);
+      run += __shfl_sync(0xffffffffu, incl[u], 31);
+    }
   }
 }
 
