@@ -166,3 +166,26 @@ def test_masked_select_large(state):
     assert_bit_equal(bytes_out.numpy(), mask, "large gtValue")
     dsrc.maskedFill(dm, 0.0)
     assert_bit_equal(dsrc.numpy(), mo.masked_fill(src, mask, 0.0), "large maskedFill")
+
+
+@pytest.mark.parametrize("n", [4096 * 1024, 4096 * 1024 + 1, 4096 * 2500 + 77])
+def test_masked_select_many_tiles(state, n):
+    """More than 1024 tiles of 4096 elements: the tile offsets are scanned by several CTAs, each
+    adding up the counts before its span.  Densities differ from region to region so that a wrong
+    carry shows."""
+    r = rng("msel tiles", str(n))
+    src = r.integers(-2**31, 2**31 - 1, size=n, dtype=np.int64).astype(np.int32)
+    density = np.repeat(r.uniform(0, 1, size=n // 65536 + 1), 65536)[:n]
+    mask = (r.uniform(size=n) < density).astype(np.uint8)
+    dsrc, dm = to_device(state, src), to_device(state, mask)
+    out = thc.Tensor.new(state, "Int")
+    out.maskedSelect(dsrc, dm)
+    want = src[mask != 0]
+    assert out.sizes == [want.size]
+    assert_bit_equal(out.numpy(), want, f"maskedSelect over {n} elements")
+    t = np.zeros(n, np.int32)
+    dt_ = to_device(state, t)
+    dt_.maskedCopy(dm, to_device(state, want))
+    back = dt_.numpy()
+    assert_bit_equal(back[mask != 0], want, "maskedCopy puts the selected elements back")
+    assert not back[mask == 0].any()
