@@ -124,6 +124,14 @@ struct StridedView {
   }
 };
 
+// a / b for a 32-bit divisor: nothing for b == 1, the 32-bit divide when a fits (a 64-bit
+// division is over a hundred instructions on the GPU).
+__device__ __forceinline__ uint64_t div_by_u32(uint64_t a, uint32_t b) {
+  if (b == 1) return a;
+  if ((a >> 32) == 0) return (uint32_t)a / b;
+  return a / b;
+}
+
 // Host-side plain description of one operand after validation.
 struct HostView {
   char *data;

@@ -269,8 +269,24 @@ template <typename F> __device__ __forceinline__ Opt<F> warp_fold_opt(Opt<F> a) 
   return a;
 }
 
+// One step of a mixed-radix decode: lin = q * size + r.  The outermost dim needs no division, and
+// operands below 2^32 take the 32-bit divide: a 64-bit division is over a hundred instructions,
+// which a warp reducing a row of a thousand elements notices (two of them per row were 40 % of
+// the instructions of `sum` over the last dim of a 3-D window).
+__device__ __forceinline__ void radix_step(uint64_t lin, uint64_t size, bool outermost, uint64_t &q, uint64_t &r) {
+  if (outermost) { q = 0; r = lin; }
+  else if (((lin | size) >> 32) == 0) {
+    const uint32_t l = (uint32_t)lin, s = (uint32_t)size, qq = l / s;
+    q = qq;
+    r = l - qq * s;
+  } else {
+    q = lin / size;
+    r = lin - q * size;
+  }
+}
+
 // Decodes a slice number into element offsets of the input and output(s); the dims are the
-// non-reduced ones.  Evaluated once per slice, so plain 64-bit division is acceptable.
+// non-reduced ones.  Evaluated once per slice.
 struct SliceMap {
   int n;
   uint64_t size[kMaxDims];
@@ -280,7 +296,8 @@ struct SliceMap {
   __device__ __forceinline__ void decode(uint64_t lin, int64_t &in_off, int64_t &out_off, int64_t &idx_off) const {
     in_off = 0; out_off = 0; idx_off = 0;
     for (int d = n - 1; d >= 0; --d) {
-      uint64_t q = lin / size[d], r = lin - q * size[d];
+      uint64_t q, r;
+      radix_step(lin, size[d], d == 0, q, r);
       in_off += (int64_t)r * in_stride[d];
       out_off += (int64_t)r * out_stride[d];
       idx_off += (int64_t)r * idx_stride[d];
@@ -344,8 +361,8 @@ __device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void
 // ====================================================================================
 // reduce_all over a view that is not one dense run but whose innermost dim (after sorting the
 // dims by stride: a full reduction is order-free) has stride 1: padded rows, windows of larger
-// tensors.  Tiles are [ty rows x tx vectors] like the rows apply; a row's offset is decoded from
-// its number once per thread and row.
+// tensors.  Tiles are [ty rows x (tx * kRedRowsSlots) vectors]; a row's offset is decoded from its
+// number once per thread and tile.
 // ====================================================================================
 constexpr int kRedRowsOuterDims = 7;
 struct RedRowsView {
@@ -372,14 +389,18 @@ struct RedRowsView {
 
 // Rows need not start on a 16-byte boundary: per row the elements before the first boundary and
 // after the last whole vector (at most 2 * (V - 1) of them) are read one by one by the first
-// threads of the row's first column tile; everything between moves as 16-byte vectors.
+// threads of the row's first column tile; everything between moves as 16-byte vectors.  A thread
+// takes kRedRowsSlots vectors of one row per tile, tx apart, so the row's offset and alignment are
+// worked out once per kRedRowsSlots loads (with one vector per decode the kernel was bound by
+// instruction issue: 104 M warp instructions for 134 M floats).
+constexpr int kRedRowsSlots = 8;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Folder<T, MODE>::Params prm,
                        void *partials_raw, unsigned int *ticket, void *result) {
   using F = Folder<T, MODE>;
   constexpr int V = 16 / (int)sizeof(T);
-  constexpr int U = kRedUnroll;
+  constexpr int W = kRedRowsSlots;
   const unsigned tx = 1u << rv.log2_tx, ty = kRedThreads >> rv.log2_tx;
   const unsigned x = threadIdx.x & (tx - 1), y = threadIdx.x >> rv.log2_tx;
   const uint32_t C = rv.Cunits;   // elements per row
@@ -387,40 +408,33 @@ reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Fo
   for (uint32_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
     uint32_t rtile, ctile;
     rv.tiles_c_div.divmod(t, rtile, ctile);
-    const uint32_t cu = ctile * tx + x;       // vector number inside the row's aligned part
-    Bytes16 v[U];
-    T edge[U];
-    bool ok[U], eok[U];
+    const uint32_t r = rtile * ty + y;
+    if (r >= rv.R) continue;
+    const T *row = in + rv.row_offset(r);
+    const uint32_t mis = (uint32_t)((reinterpret_cast<uintptr_t>(row) / sizeof(T)) % V);
+    uint32_t head = mis ? V - mis : 0;
+    if (head > C) head = C;
+    const uint32_t nvec = (C - head) / V;
+    const uint32_t tail0 = head + nvec * V;          // first element after the vectors
+    const T *vrow = row + head;
+    const uint32_t cu0 = ctile * (tx * W) + x;        // this thread's first vector of the row's aligned part
+    Bytes16 v[W];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t r = (rtile * U + u) * ty + y;
-      ok[u] = false;
-      eok[u] = false;
-      if (r < rv.R) {
-        const T *row = in + rv.row_offset(r);
-        const uint32_t mis = (uint32_t)((reinterpret_cast<uintptr_t>(row) / sizeof(T)) % V);
-        uint32_t head = mis ? V - mis : 0;
-        if (head > C) head = C;
-        const uint32_t nvec = (C - head) / V;
-        const uint32_t tail0 = head + nvec * V;          // first element after the vectors
-        ok[u] = cu < nvec;
-        if (ok[u]) v[u] = ld16_stream(row + head + (uint64_t)cu * V);
-        // edge elements: x < head takes row[x], head <= x < head + (C - tail0) takes the tail
-        if (ctile == 0 && x < head + (C - tail0)) {
-          eok[u] = true;
-          edge[u] = row[x < head ? x : tail0 + (x - head)];
-        }
-      }
-    }
+    for (int w = 0; w < W; ++w)
+      if (cu0 + (uint32_t)w * tx < nvec) v[w] = ld16_stream(vrow + (uint64_t)(cu0 + (uint32_t)w * tx) * V);
+    // edge elements: x < head takes row[x], head <= x < head + (C - tail0) takes the tail
+    T edge = T();
+    const bool eok = ctile == 0 && x < head + (C - tail0);
+    if (eok) edge = row[x < head ? x : tail0 + (x - head)];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (ok[u]) {
-        const T *e = reinterpret_cast<const T *>(&v[u]);
+    for (int w = 0; w < W; ++w) {
+      if (cu0 + (uint32_t)w * tx < nvec) {
+        const T *e = reinterpret_cast<const T *>(&v[w]);
 #pragma unroll
         for (int j = 0; j < V; ++j) acc.feed(F::pre(e[j], prm));
       }
-      if (eok[u]) acc.feed(F::pre(edge[u], prm));
     }
+    if (eok) acc.feed(F::pre(edge, prm));
   }
   reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
 }
@@ -582,7 +596,7 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
   const uint64_t unit = WARP_PER_UNIT ? (uint64_t)blockIdx.x * kRedWarps + warp : blockIdx.x;
   const uint64_t nunits = nslices * nsplit;
   const bool active = unit < nunits;
-  const uint64_t slice = active ? unit / nsplit : 0;
+  const uint64_t slice = active ? div_by_u32(unit, nsplit) : 0;
   const uint32_t split = active ? (uint32_t)(unit - slice * nsplit) : 0;
   int64_t in_off = 0, out_off = 0, idx_off = 0;
   if (active) map.decode(slice, in_off, out_off, idx_off);
@@ -595,41 +609,35 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
   fast.reset();
   uint64_t k = k0;
   if constexpr (VEC) {
-    // A unit need not start on a 16-byte boundary (odd row lengths, windows): the elements up to
-    // the boundary are taken one by one, in position order before everything else.
-    {
-      const uint64_t mis = (reinterpret_cast<uintptr_t>(row + k0) / sizeof(T)) % V;
-      uint64_t head = mis ? V - mis : 0;
-      if (head > k1 - k0) head = k1 - k0;
-      for (uint64_t i = k0 + gt; i < k0 + head; i += GROUP) {
-        if constexpr (INDEX) fast.feed(row[i], (uint32_t)(i - k0));
-        else acc.feed(F::pre(row[i], prm));
-      }
-      k = k0 + head;
-    }
+    // A unit need not start on a 16-byte boundary (odd row lengths, windows): the up to V - 1
+    // elements before the first boundary and after the last whole vector go one to a lane.  They
+    // are loaded first and fed in position order (head, vectors, tail: the position scans keep the
+    // first occurrence by replacing on strictly better values only), the head after the first
+    // batch of vector loads is under way, so a short row costs one memory latency, not three.
+    const uint64_t mis = (reinterpret_cast<uintptr_t>(row + k0) / sizeof(T)) % V;
+    uint64_t head = mis ? V - mis : 0;
+    if (head > k1 - k0) head = k1 - k0;
+    const uint64_t tail0 = k0 + head + (k1 - k0 - head) / V * V;   // first element after the whole vectors
+    const bool has_head = (uint64_t)gt < head, has_tail = (uint64_t)gt < k1 - tail0;
+    T eh = T(), et = T();
+    if (has_head) eh = row[k0 + gt];
+    if (has_tail) et = row[tail0 + gt];
+    bool head_fed = false;
     // whole 16-byte vectors, kRedUnroll of them in flight per thread
     constexpr uint64_t kStep = (uint64_t)GROUP * V * kRedUnroll;
-    for (; k + kStep <= k1; k += kStep) {
-      Bytes16 v[kRedUnroll];
-#pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) v[u] = ld16_stream(row + k + ((uint64_t)u * GROUP + gt) * V);
-#pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
-        const T *e = reinterpret_cast<const T *>(&v[u]);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          if constexpr (INDEX) fast.feed(e[j], (uint32_t)(k - k0) + (uint32_t)((u * GROUP + gt) * V + j));
-          else acc.feed(F::pre(e[j], prm));
-        }
-      }
-    }
-    // the whole vectors that are left (fewer than one full step), again all in flight together
-    {
-      const uint64_t nrem = (k1 - k) / V;
+    for (k = k0 + head; k < tail0; k += kStep) {
+      const uint64_t nrem = (tail0 - k) / V;
       Bytes16 v[kRedUnroll];
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u)
         if ((uint64_t)u * GROUP + gt < nrem) v[u] = ld16_stream(row + k + ((uint64_t)u * GROUP + gt) * V);
+      if (!head_fed) {
+        head_fed = true;
+        if (has_head) {
+          if constexpr (INDEX) fast.feed(eh, (uint32_t)gt);
+          else acc.feed(F::pre(eh, prm));
+        }
+      }
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u) {
         if ((uint64_t)u * GROUP + gt < nrem) {
@@ -641,8 +649,16 @@ reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t 
           }
         }
       }
-      k += nrem * V;
     }
+    if (!head_fed && has_head) {
+      if constexpr (INDEX) fast.feed(eh, (uint32_t)gt);
+      else acc.feed(F::pre(eh, prm));
+    }
+    if (has_tail) {
+      if constexpr (INDEX) fast.feed(et, (uint32_t)(tail0 - k0) + (uint32_t)gt);
+      else acc.feed(F::pre(et, prm));
+    }
+    k = k1;
   }
   for (uint64_t i = k + gt; i < k1; i += GROUP) {
     if constexpr (INDEX) fast.feed(row[i], (uint32_t)(i - k0));
@@ -738,9 +754,9 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
   using VecT = typename ColVec<V * sizeof(T), T>::type;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // blockIdx.x -> (outer, split, inner tile)
-  uint64_t b = blockIdx.x;
-  const uint32_t ti = (uint32_t)(b % tiles_i); b /= tiles_i;
-  const uint32_t split = (uint32_t)(b % nsplit); b /= nsplit;
+  uint32_t b = blockIdx.x;
+  const uint32_t ti = b % tiles_i; b /= tiles_i;
+  const uint32_t split = b % nsplit; b /= nsplit;
   const uint64_t outer = b;
   int64_t in_off, out_off, idx_off;
   map.decode(outer, in_off, out_off, idx_off);

@@ -60,17 +60,18 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
       }
       rv.R = (uint32_t)R;
       rv.Cunits = (uint32_t)sizes[nouter];
-      // threads along the row: enough for its whole vectors, and for the up to 2 (V - 1) edge elements
-      uint32_t slots = (uint32_t)(sizes[nouter] / VF);
+      // threads along the row: each takes kRedRowsSlots vectors; at least the up to 2 (V - 1) edge elements
+      uint32_t slots = (uint32_t)((sizes[nouter] / VF + kRedRowsSlots - 1) / kRedRowsSlots);
       if (slots < 2u * (VF - 1)) slots = 2u * (VF - 1);
       if (slots < 1) slots = 1;
       int lg = 0;
       while ((1u << lg) < slots && lg < 8) ++lg;
       rv.log2_tx = lg;
-      rv.tiles_c = (uint32_t)((sizes[nouter] / VF + (1u << lg) - 1) >> lg);
+      const uint64_t vec_per_tile = (uint64_t)kRedRowsSlots << lg;
+      rv.tiles_c = (uint32_t)((sizes[nouter] / VF + vec_per_tile - 1) / vec_per_tile);
       if (rv.tiles_c < 1) rv.tiles_c = 1;
       rv.tiles_c_div = FastDiv32(rv.tiles_c);
-      const uint64_t rows_per_tile = (uint64_t)(kRedThreads >> lg) * kRedUnroll;
+      const uint64_t rows_per_tile = (uint64_t)(kRedThreads >> lg);
       const uint64_t ntiles = (uint64_t)rv.tiles_c * ((R + rows_per_tile - 1) / rows_per_tile);
       if (ntiles < (1ull << 31)) {
         const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;

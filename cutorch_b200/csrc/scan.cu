@@ -35,7 +35,16 @@ struct ScanMap {
   __device__ __forceinline__ void decode(uint64_t lin, int64_t &in_off, int64_t &out_off) const {
     in_off = 0; out_off = 0;
     for (int d = n - 1; d >= 0; --d) {
-      const uint64_t q = lin / size[d], r = lin - q * size[d];
+      uint64_t q, r;
+      if (d == 0) { q = 0; r = lin; }                    // the outermost dim needs no division
+      else if (((lin | size[d]) >> 32) == 0) {           // 32-bit operands: the short divide
+        const uint32_t l = (uint32_t)lin, s = (uint32_t)size[d], qq = l / s;
+        q = qq;
+        r = l - qq * s;
+      } else {
+        q = lin / size[d];
+        r = lin - q * size[d];
+      }
       in_off += (int64_t)r * in_stride[d];
       out_off += (int64_t)r * out_stride[d];
       lin = q;
@@ -67,7 +76,7 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
   const unsigned lane = threadIdx.x & 31;
   const uint64_t unit = (uint64_t)blockIdx.x * kScanWarps + (threadIdx.x >> 5);
   if (unit >= nrows * S) return;
-  const uint64_t row = unit / S;
+  const uint64_t row = div_by_u32(unit, S);
   const uint64_t k0 = (unit - row * S) * chunk_len;
   const uint64_t k1 = k0 + chunk_len < K ? k0 + chunk_len : K;
   int64_t ioff, ooff;
@@ -216,9 +225,9 @@ scan_col_kernel(const T *in, T *out, ScanMap map, uint64_t nouter, uint64_t K, i
   const unsigned lane = threadIdx.x & 31;
   const uint64_t unit = (uint64_t)blockIdx.x * kScanWarps + (threadIdx.x >> 5);
   if (unit >= nouter * S * tiles_i) return;
-  const uint64_t oc = unit / tiles_i;
+  const uint64_t oc = div_by_u32(unit, tiles_i);
   const uint32_t ti = (uint32_t)(unit - oc * tiles_i);
-  const uint64_t o = oc / S;
+  const uint64_t o = div_by_u32(oc, S);
   const uint64_t col = ((uint64_t)ti * 32 + lane) * V;
   if (col >= I) return;
   const uint64_t k0 = (oc - o * S) * chunk_len;
