@@ -1144,6 +1144,74 @@ void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half
   tensor_free<float>(state, wide);
 }
 
+// ---- CPU <-> GPU tensors (lib/THC/generic/THCTensorCopy.c:7-164) --------------------------
+// Every TH CPU tensor has the same layout apart from the element type of its storage.
+struct CpuStorageAny { char *data; ptrdiff_t size; int refcount; char flag; void *allocator; void *allocatorContext; void *view; };
+struct CpuTensorAny { long *size; long *stride; int nDimension; CpuStorageAny *storage; ptrdiff_t storageOffset; int refcount; char flag; };
+
+thcb200_tensor describe_cpu(const void *tensor, int dtype) {
+  const CpuTensorAny *t = (const CpuTensorAny *)tensor;
+  if (!t) th_error("null CPU tensor");
+  thcb200_tensor d;
+  memset(&d, 0, sizeof(d));
+  d.dtype = dtype;
+  d.ndim = t->nDimension;
+  if (t->nDimension > THCB200_MAX_DIMS) th_arg_error(2, CUTORCH_DIM_WARNING);
+  for (int i = 0; i < t->nDimension; ++i) { d.sizes[i] = t->size[i]; d.strides[i] = t->stride[i]; }
+  static const size_t esz[8] = {1, 1, 2, 4, 8, 2, 4, 8};
+  d.data = (t->storage && t->storage->data) ? (void *)(t->storage->data + t->storageOffset * (ptrdiff_t)esz[dtype]) : nullptr;
+  return d;
+}
+ptrdiff_t cpu_nelement(const void *tensor) {
+  const CpuTensorAny *t = (const CpuTensorAny *)tensor;
+  if (!t || t->nDimension == 0) return 0;
+  ptrdiff_t n = 1;
+  for (int i = 0; i < t->nDimension; ++i) n *= t->size[i];
+  return n;
+}
+bool cpu_contiguous(const void *tensor) {
+  const CpuTensorAny *t = (const CpuTensorAny *)tensor;
+  long run = 1;
+  for (int d = t->nDimension - 1; d >= 0; --d) {
+    if (t->size[d] != 1 && t->stride[d] != run) return false;
+    run *= t->size[d];
+  }
+  return true;
+}
+
+template <typename R>
+void copy_from_cpu(THCState *state, TensorT<R> *self, const void *src, int src_dtype) {
+  check_gpu<R>(state, {self});
+  THArgCheck(tensor_nelement<R>(self) == cpu_nelement(src), 2, "sizes do not match");
+  if (cpu_nelement(src) == 0) return;
+  thcb200_tensor dd = describe<R>(self), ds = describe_cpu(src, src_dtype);
+  check_core(thcb200_copy_from_host(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
+}
+template <typename R>
+void copy_to_cpu(THCState *state, void *self, int self_dtype, TensorT<R> *src) {
+  check_gpu<R>(state, {src});
+  THArgCheck(cpu_nelement(self) == tensor_nelement<R>(src), 2, "sizes do not match");
+  if (cpu_nelement(self) == 0) return;
+  thcb200_tensor dd = describe_cpu(self, self_dtype), ds = describe<R>(src);
+  check_core(thcb200_copy_to_host(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
+}
+// The asynchronous forms (lib/THC/generic/THCTensorCopy.c:112-164): same sizes, both contiguous,
+// one cudaMemcpyAsync on the current stream of the GPU tensor's device.
+template <typename R>
+void copy_async(THCState *state, TensorT<R> *gpu, void *cpu, bool to_gpu) {
+  check_gpu<R>(state, {gpu});
+  THArgCheck(tensor_nelement<R>(gpu) == cpu_nelement(cpu), 2, "sizes do not match");
+  THArgCheck(tensor_is_contiguous<R>(gpu), to_gpu ? 2 : 3, "Target tensor must be contiguous");
+  THArgCheck(cpu_contiguous(cpu), to_gpu ? 3 : 2, "Source tensor must be contiguous");
+  const ptrdiff_t n = tensor_nelement<R>(gpu);
+  if (n == 0) return;
+  thcb200_tensor dg = describe<R>(gpu), dc = describe_cpu(cpu, RealTraits<R>::dtype);
+  DeviceGuard guard(gpu->storage->device);
+  const cudaStream_t st = THCState_getCurrentStreamOnDevice(state, gpu->storage->device);
+  if (to_gpu) THCudaCheck(cudaMemcpyAsync(dg.data, dc.data, (size_t)n * sizeof(R), cudaMemcpyHostToDevice, st));
+  else THCudaCheck(cudaMemcpyAsync(dc.data, dg.data, (size_t)n * sizeof(R), cudaMemcpyDeviceToHost, st));
+}
+
 // ---- indexed moves (lib/THC/generic/THCTensorIndex.cu, THCTensorScatterGather.cu) --------
 using LongT = TensorT<long>;
 template <typename R> R zero_real() { return R(); }
@@ -1290,6 +1358,7 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
 #define real unsigned char
 #define accreal long
 #define CReal CudaByte
+#define Real Byte
 #define THC_T_FLOATING 0
 #define THC_T_SIGNED 0
 #define THC_T_HALF 0
@@ -1297,42 +1366,51 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_SIGNED
 
 #define real char
 #define accreal long
 #define CReal CudaChar
+#define Real Char
 #define THC_T_SIGNED 0
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_SIGNED
 #define THC_T_SIGNED 1
 
 #define real short
 #define accreal long
 #define CReal CudaShort
+#define Real Short
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 #define real int
 #define accreal long
 #define CReal CudaInt
+#define Real Int
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 #define real long
 #define accreal long
 #define CReal CudaLong
+#define Real Long
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 #undef THC_T_FLOATING
 #define THC_T_FLOATING 1
@@ -1340,6 +1418,7 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
 #define real half
 #define accreal float
 #define CReal CudaHalf
+#define Real Half
 #undef THC_T_HALF
 #define THC_T_HALF 1
 #include "thc_compat_type.inc"
@@ -1348,22 +1427,27 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 #define real float
 #define accreal float
 #define CReal Cuda
+#define Real Float
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 #define real double
 #define accreal double
 #define CReal CudaDouble
+#define Real Double
 #include "thc_compat_type.inc"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 
 extern "C" {
 int THCudaByteTensor_logicalall(THCState *state, THCudaByteTensor *self) {

@@ -35,6 +35,41 @@ KINDS = {
     "Double": ("CudaDouble", np.float64, C.c_double, C.c_double, _lib.F64),
 }
 KIND_OF_DTYPE = {np.dtype(v[1]): k for k, v in KINDS.items()}
+
+
+class _THStorage(C.Structure):
+    """torch7's CPU storage (lib/TH/generic/THStorage.h): the same fields for every element type."""
+    _fields_ = [("data", C.c_void_p), ("size", C.c_ssize_t), ("refcount", C.c_int), ("flag", C.c_char),
+                ("allocator", C.c_void_p), ("allocatorContext", C.c_void_p), ("view", C.c_void_p)]
+
+
+class _THTensor(C.Structure):
+    """torch7's CPU tensor (lib/TH/generic/THTensor.h)."""
+    _fields_ = [("size", C.POINTER(C.c_long)), ("stride", C.POINTER(C.c_long)), ("nDimension", C.c_int),
+                ("storage", C.POINTER(_THStorage)), ("storageOffset", C.c_ssize_t), ("refcount", C.c_int), ("flag", C.c_char)]
+
+
+class CpuTensor:
+    """A numpy array seen as a TH CPU tensor (TH<Type>Tensor): the argument of the copies between
+    CPU and GPU tensors.  Any non-negative strides that are whole elements; the array is not copied."""
+
+    def __init__(self, array: np.ndarray):
+        if array.dtype not in KIND_OF_DTYPE:
+            raise TypeError(f"no tensor type for {array.dtype}")
+        if any(s < 0 or s % array.itemsize for s in array.strides):
+            raise ValueError("strides must be non-negative multiples of the element size")
+        self.array = array
+        self.kind = KIND_OF_DTYPE[array.dtype]
+        nd = array.ndim
+        self._size = (C.c_long * max(nd, 1))(*array.shape)
+        self._stride = (C.c_long * max(nd, 1))(*[s // array.itemsize for s in array.strides])
+        extent = 1 + sum((n - 1) * (s // array.itemsize) for n, s in zip(array.shape, array.strides)) if array.size else 0
+        self._storage = _THStorage(array.ctypes.data, extent, 1, b"\x00", None, None, None)
+        self._tensor = _THTensor(self._size, self._stride, nd, C.pointer(self._storage), 0, 1, b"\x01")
+
+    @property
+    def ptr(self):
+        return C.byref(self._tensor)
 FLOATING = ("Half", "Float", "Double")
 
 # Argument codes: T tensor of the receiver's type, L LongTensor, r real, l long, i int.
@@ -408,6 +443,22 @@ class Tensor:
         f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         f.restype = None
         f(self.state.ptr, self.ptr, src.ptr)
+        self.state.check()
+
+    def copy_from_cpu(self, cpu: "CpuTensor"):
+        """self:copy(cpuTensor): THCuda<T>Tensor_copy<CpuType> (lib/THC/generic/THCTensorCopy.c:33-62)."""
+        f = self.state.fn(self.kind, "copy" + cpu.kind)
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        f.restype = None
+        f(self.state.ptr, self.ptr, cpu.ptr)
+        self.state.check()
+
+    def copy_to_cpu(self, cpu: "CpuTensor"):
+        """cpuTensor:copy(self): TH<CpuType>Tensor_copyCuda<T> (lib/THC/generic/THCTensorCopy.c:66-110)."""
+        f = getattr(self.state.lib, f"TH{cpu.kind}Tensor_copyCuda{self.kind}")
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        f.restype = None
+        f(self.state.ptr, cpu.ptr, self.ptr)
         self.state.check()
 
     def sumall_to_device(self, result_dev_ptr: int):

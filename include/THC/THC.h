@@ -131,6 +131,49 @@ THC_API float THC_half2float(half a);
 #define TH_STORAGE_FREEMEM 4
 #define TH_TENSOR_REFCOUNTED 1
 
+/* torch7's CPU storages and tensors as the copies between CPU and GPU tensors see them
+ * (lib/TH/generic/THStorage.h, THTensor.h: the same field order for every element type; the
+ * sources of TH are not part of cutorch, a build inside torch7 uses TH's own headers instead). */
+#ifndef THCB200_HAVE_TH
+#define THCB200_DECLARE_TH_STORAGE(Name, ctype)                                        \
+  typedef struct TH##Name##Storage {                                                   \
+    ctype *data;                                                                       \
+    ptrdiff_t size;                                                                    \
+    int refcount;                                                                      \
+    char flag;                                                                         \
+    void *allocator;                                                                   \
+    void *allocatorContext;                                                            \
+    struct TH##Name##Storage *view;                                                    \
+  } TH##Name##Storage;
+#define THCB200_DECLARE_TH_TENSOR(Name)                                                \
+  typedef struct TH##Name##Tensor {                                                    \
+    long *size;                                                                        \
+    long *stride;                                                                      \
+    int nDimension;                                                                    \
+    TH##Name##Storage *storage;                                                        \
+    ptrdiff_t storageOffset;                                                           \
+    int refcount;                                                                      \
+    char flag;                                                                         \
+  } TH##Name##Tensor;
+THCB200_DECLARE_TH_STORAGE(Byte, unsigned char)
+THCB200_DECLARE_TH_STORAGE(Char, char)
+THCB200_DECLARE_TH_STORAGE(Short, short)
+THCB200_DECLARE_TH_STORAGE(Int, int)
+THCB200_DECLARE_TH_STORAGE(Half, half)
+THCB200_DECLARE_TH_STORAGE(Float, float)
+THCB200_DECLARE_TH_STORAGE(Double, double)
+THCB200_DECLARE_TH_TENSOR(Byte)
+THCB200_DECLARE_TH_TENSOR(Char)
+THCB200_DECLARE_TH_TENSOR(Short)
+THCB200_DECLARE_TH_TENSOR(Int)
+THCB200_DECLARE_TH_TENSOR(Long)   /* THLongStorage is declared above */
+THCB200_DECLARE_TH_TENSOR(Half)
+THCB200_DECLARE_TH_TENSOR(Float)
+THCB200_DECLARE_TH_TENSOR(Double)
+#undef THCB200_DECLARE_TH_STORAGE
+#undef THCB200_DECLARE_TH_TENSOR
+#endif
+
 /* ---- per-type storage, tensor and math API ------------------------------------------- */
 #define THC_B200_DECLARE_STRUCTS
 #include "THCForEachType.h"

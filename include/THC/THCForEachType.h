@@ -6,6 +6,7 @@
 #define real unsigned char
 #define accreal long
 #define CReal CudaByte
+#define Real Byte
 #define THC_T_DTYPE 0
 #undef THC_T_SIGNED
 #define THC_T_SIGNED 0
@@ -15,11 +16,13 @@
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real char
 #define accreal long
 #define CReal CudaChar
+#define Real Char
 #define THC_T_DTYPE 1
 #undef THC_T_SIGNED
 #define THC_T_SIGNED 0 /* neg is not defined for Char (lib/THC/generic/THCTensorMathPointwise.h:37-42) */
@@ -29,36 +32,43 @@
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real short
 #define accreal long
 #define CReal CudaShort
+#define Real Short
 #define THC_T_DTYPE 2
 #include "THCTypeAPI.h"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real int
 #define accreal long
 #define CReal CudaInt
+#define Real Int
 #define THC_T_DTYPE 3
 #include "THCTypeAPI.h"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real long
 #define accreal long
 #define CReal CudaLong
+#define Real Long
 #define THC_T_DTYPE 4
 #include "THCTypeAPI.h"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #undef THC_T_FLOATING
@@ -67,6 +77,7 @@
 #define real half
 #define accreal float
 #define CReal CudaHalf
+#define Real Half
 #define THC_T_DTYPE 5
 #undef THC_T_HALF
 #define THC_T_HALF 1
@@ -76,26 +87,31 @@
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real float
 #define accreal float
 #define CReal Cuda
+#define Real Float
 #define THC_T_DTYPE 6
 #include "THCTypeAPI.h"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #define real double
 #define accreal double
 #define CReal CudaDouble
+#define Real Double
 #define THC_T_DTYPE 7
 #include "THCTypeAPI.h"
 #undef real
 #undef accreal
 #undef CReal
+#undef Real
 #undef THC_T_DTYPE
 
 #undef THC_T_FLOATING

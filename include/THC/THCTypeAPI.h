@@ -120,6 +120,30 @@ THC_API void THCTensor_(copyCudaHalf)(THCState *state, THCTensor *dst, struct TH
 THC_API void THCTensor_(copyCudaFloat)(THCState *state, THCTensor *dst, struct THCudaTensor *src);
 THC_API void THCTensor_(copyCudaDouble)(THCState *state, THCTensor *dst, struct THCudaDoubleTensor *src);
 THC_API void THCTensor_(copyCuda)(THCState *state, THCTensor *self, THCTensor *src);
+/* between CPU and GPU tensors, any strides and element types on both sides; blocking
+ * (lib/THC/generic/THCTensorCopy.h:7-14,26-39, generic/THCTensorCopy.c:7-164) */
+THC_API void THCTensor_(copyByte)(THCState *state, THCTensor *self, struct THByteTensor *src);
+THC_API void THCTensor_(copyChar)(THCState *state, THCTensor *self, struct THCharTensor *src);
+THC_API void THCTensor_(copyShort)(THCState *state, THCTensor *self, struct THShortTensor *src);
+THC_API void THCTensor_(copyInt)(THCState *state, THCTensor *self, struct THIntTensor *src);
+THC_API void THCTensor_(copyLong)(THCState *state, THCTensor *self, struct THLongTensor *src);
+THC_API void THCTensor_(copyFloat)(THCState *state, THCTensor *self, struct THFloatTensor *src);
+THC_API void THCTensor_(copyDouble)(THCState *state, THCTensor *self, struct THDoubleTensor *src);
+THC_API void THCTensor_(copyHalf)(THCState *state, THCTensor *self, struct THHalfTensor *src);
+THC_API void TH_CONCAT_2(THByteTensor_copyCuda, Real)(THCState *state, struct THByteTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THCharTensor_copyCuda, Real)(THCState *state, struct THCharTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THShortTensor_copyCuda, Real)(THCState *state, struct THShortTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THIntTensor_copyCuda, Real)(THCState *state, struct THIntTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THLongTensor_copyCuda, Real)(THCState *state, struct THLongTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THFloatTensor_copyCuda, Real)(THCState *state, struct THFloatTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THDoubleTensor_copyCuda, Real)(THCState *state, struct THDoubleTensor *self, THCTensor *src);
+THC_API void TH_CONCAT_2(THHalfTensor_copyCuda, Real)(THCState *state, struct THHalfTensor *self, THCTensor *src);
+/* same element type on both sides */
+THC_API void THCTensor_(copyCPU)(THCState *state, THCTensor *self, struct TH_CONCAT_3(TH, Real, Tensor) *src);
+THC_API void TH_CONCAT_3(TH, Real, Tensor_copyCuda)(THCState *state, struct TH_CONCAT_3(TH, Real, Tensor) *self, THCTensor *src);
+/* asynchronous on the current stream: both sides contiguous, the CPU side in pinned memory */
+THC_API void THCTensor_(copyAsyncCPU)(THCState *state, THCTensor *self, struct TH_CONCAT_3(TH, Real, Tensor) *src);
+THC_API void TH_CONCAT_3(TH, Real, Tensor_copyAsyncCuda)(THCState *state, struct TH_CONCAT_3(TH, Real, Tensor) *self, THCTensor *src);
 
 /* ---- pointwise math (lib/THC/generic/THCTensorMathPointwise.h) ---- */
 #if THC_T_FLOATING

@@ -300,6 +300,17 @@ THCB200_API int thcb200_renorm_factor(thcb200_ctx *ctx, const thcb200_tensor *fa
 THCB200_API int thcb200_renorm_rows(thcb200_ctx *ctx, const thcb200_tensor *out, const thcb200_tensor *in,
                         int dim, double p, double maxnorm, void *stream);
 
+/* Copies between a view in HOST memory (`src_host` / `dst_host`: the data pointer is a host
+ * address, pageable or pinned; no negative strides) and a view in device memory, converting the
+ * element type like thcb200_copy_convert and walking both sides in logical order.  A dense host
+ * side crosses the bus as it is; otherwise its runs are packed on the host first.  Striding on the
+ * device side and the conversion run on the GPU.  Both return when the copy is complete.
+ * THCTensor_(copy<Type>) / TH<Type>Tensor_copyCuda<Real>: lib/THC/generic/THCTensorCopy.c:7-164. */
+THCB200_API int thcb200_copy_from_host(thcb200_ctx *ctx, const thcb200_tensor *dst,
+                           const thcb200_tensor *src_host, void *stream);
+THCB200_API int thcb200_copy_to_host(thcb200_ctx *ctx, const thcb200_tensor *dst_host,
+                         const thcb200_tensor *src, void *stream);
+
 /* ---- indexed moves along one dim ------------------------------------------------------- */
 
 /* For every coordinate tuple c of the iteration space, p = index value (1-based), and c' = c with

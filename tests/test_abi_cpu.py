@@ -71,6 +71,18 @@ def test_thc_api_symbols_are_exported():
         assert name in syms
 
 
+def test_cpu_gpu_copy_entry_points():
+    """The copies between CPU and GPU tensors: THCTensor_(copy<Type>) is covered by the header walk
+    above; the names that start with the CPU tensor's type (lib/THC/generic/THCTensorCopy.h:26-39)
+    are listed here."""
+    syms = exported()
+    names = ["Byte", "Char", "Short", "Int", "Long", "Half", "Float", "Double"]
+    missing = [f"TH{cpu}Tensor_copyCuda{real}" for cpu in names for real in names if f"TH{cpu}Tensor_copyCuda{real}" not in syms]
+    missing += [f"TH{real}Tensor_{n}" for real in names for n in ("copyCuda", "copyAsyncCuda") if f"TH{real}Tensor_{n}" not in syms]
+    assert not missing, missing[:10]
+    assert "thcb200_copy_from_host" in syms and "thcb200_copy_to_host" in syms
+
+
 def test_configs_minimum_entry_points():
     syms = exported()
     need = ["THCudaTensor_cadd", "THCudaTensor_sumall", "THCudaTensor_addcmul", "THCudaTensor_copy", "THCudaTensor_sum",

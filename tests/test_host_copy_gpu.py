@@ -1,0 +1,67 @@
+"""Copies between CPU tensors and GPU tensors (cutorch's :cuda(), :float(), tensor:copy(other) across
+the two kinds; lib/THC/generic/THCTensorCopy.c:7-164) for every pair of element types and strided
+views on both sides.  cutorch's tests: test/test.lua:495-640 (copyRandomizedTest: random type pairs,
+contiguous and transposed / narrowed on either side).  The expected result is the C conversion of
+every element in logical order (half through float), which numpy's astype gives for values that fit
+the target type: bit-exact."""
+import numpy as np
+import pytest
+
+from cutorch_b200 import thc
+from common import ALL_KINDS, NP_OF_KIND, assert_bit_equal, make_view, rng, to_device
+
+pytestmark = pytest.mark.gpu
+
+def small_values(r, kind, shape, layout):
+    """Values every element type holds exactly (0..100), so that each conversion is exact."""
+    x = make_view(r, kind, shape, layout)
+    x[...] = r.integers(0, 101, size=shape).astype(x.dtype)
+    return x
+
+
+@pytest.mark.parametrize("gpu_kind", ALL_KINDS)
+def test_copy_between_cpu_and_gpu_tensors(state, gpu_kind):
+    r = rng("hostcopy", gpu_kind)
+    shape = (13, 22)
+    for cpu_kind in ALL_KINDS:
+        for cpu_layout, gpu_layout in [("contiguous", "contiguous"), ("transposed", "contiguous"), ("contiguous", "strided"),
+                                       ("holes", "transposed")]:
+            # CPU -> GPU
+            src = small_values(r, cpu_kind, shape, cpu_layout)
+            dst = to_device(state, make_view(r, gpu_kind, shape, gpu_layout))
+            dst.copy_from_cpu(thc.CpuTensor(src))
+            assert_bit_equal(dst.numpy(), np.asarray(src).astype(NP_OF_KIND[gpu_kind]),
+                             f"{cpu_kind} CPU ({cpu_layout}) -> {gpu_kind} GPU ({gpu_layout})")
+            # GPU -> CPU
+            gsrc_host = small_values(r, gpu_kind, shape, gpu_layout)
+            gsrc = to_device(state, gsrc_host)
+            back = make_view(r, cpu_kind, shape, cpu_layout)
+            gsrc.copy_to_cpu(thc.CpuTensor(back))
+            assert_bit_equal(np.asarray(back), np.asarray(gsrc_host).astype(NP_OF_KIND[cpu_kind]),
+                             f"{gpu_kind} GPU ({gpu_layout}) -> {cpu_kind} CPU ({cpu_layout})")
+
+
+def test_element_counts_not_shapes_and_errors(state):
+    r = rng("hostcopy-errors")
+    src = small_values(r, "Float", (6, 10), "contiguous")
+    dst = thc.Tensor.new(state, "Double", 60)
+    dst.copy_from_cpu(thc.CpuTensor(src))           # same element count, different shapes: logical order
+    assert_bit_equal(dst.numpy(), np.asarray(src).reshape(60).astype(np.float64), "6x10 CPU -> 60 GPU")
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        thc.Tensor.new(state, "Float", 59).copy_from_cpu(thc.CpuTensor(src))
+    with pytest.raises(thc.THCError, match="sizes do not match"):
+        dst.copy_to_cpu(thc.CpuTensor(np.zeros(61, np.float32)))
+    empty = thc.Tensor.new(state, "Float")
+    empty.copy_from_cpu(thc.CpuTensor(np.zeros(0, np.float32)))   # nothing to do
+
+
+def test_large_transfer_both_ways(state):
+    """64 MiB of fp32 up as halves into a transposed GPU tensor and back down as doubles."""
+    r = rng("hostcopy-large")
+    host = (r.integers(-1000, 1001, size=(4096, 4096)) / 8).astype(np.float32)     # exact in half
+    gpu = to_device(state, np.zeros((4096, 4096), np.float16)).transpose(0, 1)
+    gpu.copy_from_cpu(thc.CpuTensor(host))
+    assert_bit_equal(gpu.numpy(), host.astype(np.float16), "fp32 CPU -> transposed half GPU")
+    down = np.zeros((4096, 4096), np.float64)
+    gpu.copy_to_cpu(thc.CpuTensor(down))
+    assert_bit_equal(down, host.astype(np.float64), "transposed half GPU -> double CPU")
