@@ -293,8 +293,42 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         out["xdev_copy_f32_transposed_source_1GiB"] = timed_x(lambda: tdst2.copy(tsrc_t), 4 * n)
         out["xdev_copy_f16_to_f32_2pow28"] = timed_x(lambda: tdst.copy_from(tsrc_h), 4 * n)
 
-    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("generic", generic), ("xdev", xdev)):
-        if name == "xdev" and (only is None or "xdev" not in only):
+    def host():
+        """Copies between CPU and GPU tensors (wall-clock: the calls block).  The CPU side is pinned
+        memory (what cutorch's pinned host allocator gives); bytes = what crosses the bus."""
+        import time
+        import numpy as np
+        n = 1 << 28
+        hp = torch.empty(n, dtype=torch.float32).pin_memory()
+        hp.uniform_(-1, 1)
+        host32 = hp.numpy()
+        host_t = host32.reshape(16384, 16384).T              # a transposed CPU view: packed on the host
+        g32 = torch.empty(n, device=dev)
+        g16t = torch.empty(16384, 16384, dtype=torch.float16, device=dev).t()
+        t32, t16t = W(g32, "Float"), W(g16t, "Half")
+        c32, ct = thc.CpuTensor(host32), thc.CpuTensor(host_t)
+
+        def wall(fn, nbytes, reps=3):
+            fn()
+            ts = []
+            for _ in range(reps):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                ts.append(time.perf_counter() - t0)
+            ts.sort()
+            med = ts[len(ts) // 2]
+            return {"gbs": round(nbytes / med / 1e9, 1), "median_ms": round(med * 1e3, 2), "bytes": nbytes}
+
+        out["host_to_gpu_f32_dense_1GiB"] = wall(lambda: t32.copy_from_cpu(c32), 4 * n)
+        out["host_to_gpu_f32_dense_into_f16_transposed"] = wall(lambda: t16t.copy_from_cpu(c32), 4 * n)
+        out["gpu_to_host_f32_dense_1GiB"] = wall(lambda: t32.copy_to_cpu(c32), 4 * n)
+        out["gpu_f16_transposed_to_host_f32_dense"] = wall(lambda: t16t.copy_to_cpu(c32), 4 * n)
+        out["host_f32_transposed_view_to_gpu_dense"] = wall(lambda: t32.copy_from_cpu(ct), 4 * n, reps=1)
+
+    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("generic", generic), ("xdev", xdev),
+                     ("host", host)):
+        if name in ("xdev", "host") and (only is None or name not in only):
             continue
         if only is None or name in only:
             fn()

@@ -65,3 +65,22 @@ def test_large_transfer_both_ways(state):
     down = np.zeros((4096, 4096), np.float64)
     gpu.copy_to_cpu(thc.CpuTensor(down))
     assert_bit_equal(down, host.astype(np.float64), "transposed half GPU -> double CPU")
+
+
+@pytest.mark.parametrize("cols,step", [(64, 2), (70000, 35000)])
+def test_strided_cpu_views_keep_their_gaps(state, cols, step):
+    """A CPU view with gaps in its span: shipped as its span and strided on the GPU when the span is
+    close to the view's size, packed on the host when the view is sparse in it (second case).  Either
+    way the elements between the view's elements stay as they were."""
+    r = rng("hostcopy-gaps", str(cols))
+    base = r.integers(0, 100, size=(64, cols)).astype(np.float32)
+    view = base[:, ::step]
+    dev = thc.Tensor.new(state, "Double", *view.shape)
+    dev.copy_from_cpu(thc.CpuTensor(view))
+    assert_bit_equal(dev.numpy(), view.astype(np.float64), "strided CPU view -> GPU")
+    dev.add(dev, 1000)
+    before = base.copy()
+    dev.copy_to_cpu(thc.CpuTensor(view))
+    want = before.copy()
+    want[:, ::step] = before[:, ::step] + 1000
+    assert_bit_equal(base, want, "GPU -> strided CPU view, gaps untouched")
