@@ -1350,6 +1350,23 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
   check_core(thcb200_masked_select(state_ctx(state), &dt, &ds, &dm, (void *)state_stream(state), THCB200_FLAG_MASK_COUNTED));
 }
 
+// The index* calls with a CPU LongTensor of positions (lib/THC/generic/THCTensorIndex.cu:5-15,
+// 133-143,261-272,383-394): the positions go up into a temporary CudaLongTensor, then the call
+// with device indices runs.
+struct UploadedIndex {
+  THCState *state;
+  LongT *gpu;
+  UploadedIndex(THCState *st, const void *cpu_long_tensor) : state(st), gpu(nullptr) {
+    const CpuTensorAny *t = (const CpuTensorAny *)cpu_long_tensor;
+    THArgCheck(t && t->nDimension == 1, 3, "expecting vector of indices");
+    gpu = tensor_alloc<long>();
+    long n = t->size[0];
+    tensor_raw_resize<long>(state, gpu, 1, &n, nullptr);
+    copy_from_cpu<long>(state, gpu, cpu_long_tensor, THCB200_I64);
+  }
+  ~UploadedIndex() { if (gpu) tensor_free<long>(state, gpu); }
+};
+
 }  // namespace
 
 // ======================================================================================

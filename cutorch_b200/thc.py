@@ -72,7 +72,7 @@ class CpuTensor:
         return C.byref(self._tensor)
 FLOATING = ("Half", "Float", "Double")
 
-# Argument codes: T tensor of the receiver's type, L LongTensor, r real, l long, i int.
+# Argument codes: T tensor of the receiver's type, L LongTensor, C CPU LongTensor (CpuTensor), r real, l long, i int.
 # Return codes: v void, a accreal, R real, n int.
 _UNARY = ["sigmoid", "log", "lgamma", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan",
           "tanh", "sqrt", "rsqrt", "ceil", "floor", "round", "trunc", "frac", "cinv", "neg", "abs", "sign"]
@@ -99,6 +99,9 @@ SIGNATURES.update({
     "resizeAs": ("v", "TT"),
     "tril": ("v", "TTl"), "triu": ("v", "TTl"), "renorm": ("v", "TTrlr"),
     "indexSelect": ("v", "TTiL"), "indexCopy": ("v", "TiLT"), "indexAdd": ("v", "TiLT"), "indexFill": ("v", "TiLr"),
+    # the same with a CPU LongTensor of positions (code C)
+    "indexSelect_long": ("v", "TTiC"), "indexCopy_long": ("v", "TiCT"), "indexAdd_long": ("v", "TiCT"),
+    "indexFill_long": ("v", "TiCr"),
     "gather": ("v", "TTiL"), "scatter": ("v", "TiLT"), "scatterAdd": ("v", "TiLT"), "scatterFill": ("v", "TiLr"),
     "cumsum": ("v", "TTl"), "cumprod": ("v", "TTl"),
     "maskedFill": ("v", "TBr"), "maskedCopy": ("v", "TBT"), "maskedSelect": ("v", "TTB"),
@@ -416,6 +419,11 @@ class Tensor:
                 want = {"L": "Long", "B": "Byte"}.get(code, self.kind)
                 if a.kind != want:
                     raise TypeError(f"{name}: expected a {want} tensor, got {a.kind}")
+                argtypes.append(C.c_void_p)
+                cargs.append(a.ptr)
+            elif code == "C":
+                if not isinstance(a, CpuTensor) or a.kind != "Long":
+                    raise TypeError(f"{name}: expected a CPU Long tensor")
                 argtypes.append(C.c_void_p)
                 cargs.append(a.ptr)
             elif code == "r":

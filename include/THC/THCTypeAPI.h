@@ -241,6 +241,11 @@ THC_API void THCTensor_(indexSelect)(THCState *state, THCTensor *tensor, THCTens
 THC_API void THCTensor_(indexCopy)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
 THC_API void THCTensor_(indexAdd)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
 THC_API void THCTensor_(indexFill)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, real val);
+/* positions in a CPU LongTensor (lib/THC/generic/THCTensorIndex.h:10-13) */
+THC_API void THCTensor_(indexSelect_long)(THCState *state, THCTensor *tensor, THCTensor *src, int dim, struct THLongTensor *index);
+THC_API void THCTensor_(indexCopy_long)(THCState *state, THCTensor *res_, int dim, struct THLongTensor *indices, THCTensor *src);
+THC_API void THCTensor_(indexAdd_long)(THCState *state, THCTensor *res_, int dim, struct THLongTensor *indices, THCTensor *src);
+THC_API void THCTensor_(indexFill_long)(THCState *state, THCTensor *tensor, int dim, struct THLongTensor *index, real val);
 THC_API void THCTensor_(gather)(THCState *state, THCTensor *tensor, THCTensor *src, int dim, struct THCudaLongTensor *index);
 THC_API void THCTensor_(scatter)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, THCTensor *src);
 THC_API void THCTensor_(scatterAdd)(THCState *state, THCTensor *tensor, int dim, struct THCudaLongTensor *index, THCTensor *src);

@@ -194,3 +194,33 @@ def test_gather_scatter_four_neighbours_per_thread(state, kind):
             assert_bit_equal(dout.numpy(), want, f"{kind} gather with positions out of range {shape} dim {dim}")
             lib.thcb200_take_index_errors(C.c_void_p(state.context), C.byref(count), C.c_void_p(state.stream))
             assert count.value == 37
+
+
+@pytest.mark.parametrize("kind", ["Float", "Long", "Half"])
+def test_index_calls_with_positions_in_a_cpu_tensor(state, kind):
+    """index*_long: the positions come in a CPU LongTensor (lib/THC/generic/THCTensorIndex.h:10-13)."""
+    r = rng("index-long", kind)
+    src = exact_values(r, kind, (40, 50), "contiguous")
+    dsrc = to_device(state, src)
+    for dim in (0, 1):
+        n = src.shape[dim]
+        idx = r.integers(1, n + 1, size=17).astype(np.int64)
+        out = thc.Tensor.new(state, kind)
+        out.indexSelect_long(dsrc, dim, thc.CpuTensor(idx))
+        assert_bit_equal(out.numpy(), io.index_select(src, dim, idx), f"{kind} indexSelect_long dim {dim}")
+        perm = (r.permutation(n)[:9] + 1).astype(np.int64)
+        shape = list(src.shape)
+        shape[dim] = 9
+        part = exact_values(r, kind, tuple(shape), "contiguous")
+        dst = exact_values(r, kind, src.shape, "contiguous")
+        ddst = to_device(state, dst)
+        ddst.indexCopy_long(dim, thc.CpuTensor(perm), to_device(state, part))
+        assert_bit_equal(ddst.numpy(), io.index_copy(dst, dim, perm, part), f"{kind} indexCopy_long dim {dim}")
+        ddst = to_device(state, dst)
+        ddst.indexAdd_long(dim, thc.CpuTensor(perm), to_device(state, part))
+        assert_bit_equal(ddst.numpy(), io.index_add(dst, dim, perm, part), f"{kind} indexAdd_long dim {dim}")
+        ddst = to_device(state, dst)
+        ddst.indexFill_long(dim, thc.CpuTensor(perm[::2].copy()), 3)
+        assert_bit_equal(ddst.numpy(), io.index_fill(dst, dim, perm[::2], 3), f"{kind} indexFill_long dim {dim}")
+    with pytest.raises(thc.THCError, match="expecting vector of indices"):
+        thc.Tensor.new(state, kind).indexSelect_long(dsrc, 0, thc.CpuTensor(np.ones((2, 2), np.int64)))
