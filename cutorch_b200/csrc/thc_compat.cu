@@ -1144,6 +1144,37 @@ void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half
   tensor_free<float>(state, wide);
 }
 
+// ---- single elements (lib/THC/generic/THCStorage.c:20-34, generic/THCTensor.c:840-900) ------
+// One element crosses in the order of the current stream of the storage's device, and the call
+// waits for it (the reference uses a plain cudaMemcpy, which is not ordered with non-blocking streams).
+template <typename R> void storage_set(THCState *state, StorageT<R> *s, ptrdiff_t index, R value) {
+  THArgCheck(s && index >= 0 && index < s->size, 2, "index out of bounds");
+  DeviceGuard guard(s->device);
+  const cudaStream_t st = THCState_getCurrentStreamOnDevice(state, s->device);
+  THCudaCheck(cudaMemcpyAsync(s->data + index, &value, sizeof(R), cudaMemcpyHostToDevice, st));
+  THCudaCheck(cudaStreamSynchronize(st));
+}
+template <typename R> R storage_get(THCState *state, const StorageT<R> *s, ptrdiff_t index) {
+  THArgCheck(s && index >= 0 && index < s->size, 2, "index out of bounds");
+  DeviceGuard guard(s->device);
+  const cudaStream_t st = THCState_getCurrentStreamOnDevice(state, s->device);
+  R value;
+  THCudaCheck(cudaMemcpyAsync(&value, s->data + index, sizeof(R), cudaMemcpyDeviceToHost, st));
+  THCudaCheck(cudaStreamSynchronize(st));
+  return value;
+}
+template <typename R> ptrdiff_t element_index(const TensorT<R> *t, int nd, const long *x) {
+  static const char *const kCount[5] = {"", "tensor must have one dimension", "tensor must have two dimensions",
+                                        "tensor must have three dimensions", "tensor must have four dimensions"};
+  THArgCheck(t->nDimension == nd, 1, kCount[nd]);
+  ptrdiff_t off = t->storageOffset;
+  for (int d = 0; d < nd; ++d) {
+    THArgCheck(x[d] >= 0 && x[d] < t->size[d], 2, "out of range");
+    off += x[d] * t->stride[d];
+  }
+  return off;
+}
+
 // ---- CPU <-> GPU tensors (lib/THC/generic/THCTensorCopy.c:7-164) --------------------------
 // Every TH CPU tensor has the same layout apart from the element type of its storage.
 struct CpuStorageAny { char *data; ptrdiff_t size; int refcount; char flag; void *allocator; void *allocatorContext; void *view; };
@@ -1365,6 +1396,20 @@ struct UploadedIndex {
     copy_from_cpu<long>(state, gpu, cpu_long_tensor, THCB200_I64);
   }
   ~UploadedIndex() { if (gpu) tensor_free<long>(state, gpu); }
+};
+// A CPU ByteTensor mask as a CudaByteTensor of the same sizes (lib/THC/generic/THCTensorMasked.cu:
+// the ...Byte variants).
+struct UploadedMask {
+  THCState *state;
+  ByteT *gpu;
+  UploadedMask(THCState *st, const void *cpu_byte_tensor) : state(st), gpu(nullptr) {
+    const CpuTensorAny *t = (const CpuTensorAny *)cpu_byte_tensor;
+    if (!t) th_error("null mask");
+    gpu = tensor_alloc<unsigned char>();
+    tensor_raw_resize<unsigned char>(state, gpu, t->nDimension, t->size, nullptr);
+    copy_from_cpu<unsigned char>(state, gpu, cpu_byte_tensor, THCB200_U8);
+  }
+  ~UploadedMask() { if (gpu) tensor_free<unsigned char>(state, gpu); }
 };
 
 }  // namespace

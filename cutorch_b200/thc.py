@@ -72,7 +72,7 @@ class CpuTensor:
         return C.byref(self._tensor)
 FLOATING = ("Half", "Float", "Double")
 
-# Argument codes: T tensor of the receiver's type, L LongTensor, C CPU LongTensor (CpuTensor), r real, l long, i int.
+# Argument codes: T tensor of the receiver's type, L LongTensor, C / M CPU Long / Byte tensor (CpuTensor), r real, l long, i int.
 # Return codes: v void, a accreal, R real, n int.
 _UNARY = ["sigmoid", "log", "lgamma", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan",
           "tanh", "sqrt", "rsqrt", "ceil", "floor", "round", "trunc", "frac", "cinv", "neg", "abs", "sign"]
@@ -99,6 +99,8 @@ SIGNATURES.update({
     "resizeAs": ("v", "TT"),
     "tril": ("v", "TTl"), "triu": ("v", "TTl"), "renorm": ("v", "TTrlr"),
     "indexSelect": ("v", "TTiL"), "indexCopy": ("v", "TiLT"), "indexAdd": ("v", "TiLT"), "indexFill": ("v", "TiLr"),
+    # masks in a CPU ByteTensor (code M)
+    "maskedFillByte": ("v", "TMr"), "maskedCopyByte": ("v", "TMT"), "maskedSelectByte": ("v", "TTM"),
     # the same with a CPU LongTensor of positions (code C)
     "indexSelect_long": ("v", "TTiC"), "indexCopy_long": ("v", "TiCT"), "indexAdd_long": ("v", "TiCT"),
     "indexFill_long": ("v", "TiCr"),
@@ -421,9 +423,10 @@ class Tensor:
                     raise TypeError(f"{name}: expected a {want} tensor, got {a.kind}")
                 argtypes.append(C.c_void_p)
                 cargs.append(a.ptr)
-            elif code == "C":
-                if not isinstance(a, CpuTensor) or a.kind != "Long":
-                    raise TypeError(f"{name}: expected a CPU Long tensor")
+            elif code in "CM":
+                want = "Long" if code == "C" else "Byte"
+                if not isinstance(a, CpuTensor) or a.kind != want:
+                    raise TypeError(f"{name}: expected a CPU {want} tensor")
                 argtypes.append(C.c_void_p)
                 cargs.append(a.ptr)
             elif code == "r":

@@ -48,6 +48,9 @@ THC_API void THCStorage_(retain)(THCState *state, THCStorage *storage);
 THC_API void THCStorage_(free)(THCState *state, THCStorage *storage);
 THC_API void THCStorage_(resize)(THCState *state, THCStorage *storage, ptrdiff_t size);
 THC_API int THCStorage_(getDevice)(THCState *state, const THCStorage *storage);
+/* one element, blocking (lib/THC/generic/THCStorage.h:22-23) */
+THC_API void THCStorage_(set)(THCState *state, THCStorage *self, ptrdiff_t index, real value);
+THC_API real THCStorage_(get)(THCState *state, const THCStorage *self, ptrdiff_t index);
 
 /* ---- tensor (lib/THC/generic/THCTensor.h) ---- */
 THC_API THCStorage *THCTensor_(storage)(THCState *state, const THCTensor *self);
@@ -104,6 +107,15 @@ THC_API void THCTensor_(retain)(THCState *state, THCTensor *self);
 THC_API void THCTensor_(free)(THCState *state, THCTensor *self);
 THC_API void THCTensor_(freeCopyTo)(THCState *state, THCTensor *self, THCTensor *dst);
 THC_API int THCTensor_(getDevice)(THCState *state, const THCTensor *self);
+/* one element by its coordinates, blocking (lib/THC/generic/THCTensor.h:115-124) */
+THC_API void THCTensor_(set1d)(THCState *state, THCTensor *tensor, long x0, real value);
+THC_API void THCTensor_(set2d)(THCState *state, THCTensor *tensor, long x0, long x1, real value);
+THC_API void THCTensor_(set3d)(THCState *state, THCTensor *tensor, long x0, long x1, long x2, real value);
+THC_API void THCTensor_(set4d)(THCState *state, THCTensor *tensor, long x0, long x1, long x2, long x3, real value);
+THC_API real THCTensor_(get1d)(THCState *state, const THCTensor *tensor, long x0);
+THC_API real THCTensor_(get2d)(THCState *state, const THCTensor *tensor, long x0, long x1);
+THC_API real THCTensor_(get3d)(THCState *state, const THCTensor *tensor, long x0, long x1, long x2);
+THC_API real THCTensor_(get4d)(THCState *state, const THCTensor *tensor, long x0, long x1, long x2, long x3);
 THC_API int THCTensor_(checkGPU)(THCState *state, unsigned int nTensors, ...);
 
 /* ---- fill / copy (lib/THC/generic/THCTensorMath.h:5-6, THCTensorCopy.h) ---- */
@@ -235,8 +247,7 @@ THC_API void THCTensor_(cumsum)(THCState *state, THCTensor *self, THCTensor *src
 THC_API void THCTensor_(cumprod)(THCState *state, THCTensor *self, THCTensor *src, long dim);
 
 /* ---- indexed moves; positions are 1-based (lib/THC/generic/THCTensorIndex.h:5-8,
- * THCTensorScatterGather.h:5-8).  The ..._long variants, which take a torch7 CPU index tensor,
- * need TH and are not provided ---- */
+ * THCTensorScatterGather.h:5-8) ---- */
 THC_API void THCTensor_(indexSelect)(THCState *state, THCTensor *tensor, THCTensor *src, int dim, struct THCudaLongTensor *index);
 THC_API void THCTensor_(indexCopy)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
 THC_API void THCTensor_(indexAdd)(THCState *state, THCTensor *res_, int dim, struct THCudaLongTensor *indices, THCTensor *src);
@@ -255,11 +266,14 @@ THC_API void THCTensor_(scatterFill)(THCState *state, THCTensor *tensor, int dim
 THC_API void THCTensor_(tril)(THCState *state, THCTensor *self, THCTensor *src, long k);
 THC_API void THCTensor_(triu)(THCState *state, THCTensor *self, THCTensor *src, long k);
 
-/* ---- Byte masks (lib/THC/generic/THCTensorMasked.h:5-36; the variants that take a host
- * THByteTensor mask need torch7's TH and are not provided) ---- */
+/* ---- Byte masks (lib/THC/generic/THCTensorMasked.h:5-36); the ...Byte variants take the mask as a
+ * CPU ByteTensor, which is uploaded first ---- */
 THC_API void THCTensor_(maskedFill)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, real value);
 THC_API void THCTensor_(maskedCopy)(THCState *state, THCTensor *tensor, struct THCudaByteTensor *mask, THCTensor *src);
 THC_API void THCTensor_(maskedSelect)(THCState *state, THCTensor *tensor, THCTensor *src, struct THCudaByteTensor *mask);
+THC_API void THCTensor_(maskedFillByte)(THCState *state, THCTensor *tensor, struct THByteTensor *mask, real value);
+THC_API void THCTensor_(maskedCopyByte)(THCState *state, THCTensor *tensor, struct THByteTensor *mask, THCTensor *src);
+THC_API void THCTensor_(maskedSelectByte)(THCState *state, THCTensor *tensor, THCTensor *src, struct THByteTensor *mask);
 
 /* ---- reductions (lib/THC/generic/THCTensorMathReduce.h) ---- */
 #if THC_T_FLOATING

@@ -189,3 +189,24 @@ def test_masked_select_many_tiles(state, n):
     back = dt_.numpy()
     assert_bit_equal(back[mask != 0], want, "maskedCopy puts the selected elements back")
     assert not back[mask == 0].any()
+
+
+@pytest.mark.parametrize("kind", ["Float", "Int", "Half"])
+def test_masked_calls_with_the_mask_in_a_cpu_tensor(state, kind):
+    """maskedFillByte / maskedCopyByte / maskedSelectByte: the mask is a CPU ByteTensor
+    (lib/THC/generic/THCTensorMasked.h: the ...Byte variants), here a transposed view of one."""
+    r = rng("masked-byte", kind)
+    shape = (37, 53)
+    src = make_view(r, kind, shape, "contiguous")
+    mask = (r.uniform(size=shape[::-1]) < 0.4).astype(np.uint8).T      # transposed CPU view
+    cm = thc.CpuTensor(mask)
+    t = to_device(state, src)
+    t.maskedFillByte(cm, 3)
+    assert_bit_equal(t.numpy(), mo.masked_fill(src, mask, 3), f"{kind} maskedFillByte")
+    out = thc.Tensor.new(state, kind)
+    out.maskedSelectByte(to_device(state, src), cm)
+    assert_bit_equal(out.numpy(), mo.masked_select(src, mask), f"{kind} maskedSelectByte")
+    packed = make_view(r, kind, (int(mask.sum()),), "contiguous")
+    t = to_device(state, src)
+    t.maskedCopyByte(cm, to_device(state, packed))
+    assert_bit_equal(t.numpy(), mo.masked_copy(src, mask, packed), f"{kind} maskedCopyByte")

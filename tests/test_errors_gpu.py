@@ -213,3 +213,47 @@ def test_state_services(state):
     assert lib.THCState_getPeerToPeerAccess(state.ptr, 0, 99) == 0
     with pytest.raises(thc.THCError, match="is not a device"):
         state.check()
+
+
+@pytest.mark.parametrize("kind", ["Byte", "Long", "Half", "Double"])
+def test_single_element_accessors(state, kind):
+    """THCStorage_(set/get) and THCTensor_(set1d..4d / get1d..4d) (lib/THC/generic/THCStorage.c:20-34,
+    generic/THCTensor.c:840-900): one element by storage index or by coordinates of a strided view."""
+    import ctypes as C
+    from common import make_view, rng, to_device
+    r = rng("accessors", kind)
+    creal = thc.KINDS[kind][2]
+
+    def as_c(v):
+        return thc._half_from_float(v) if kind == "Half" else v
+
+    def from_c(v):
+        return thc._half_to_float(v) if kind == "Half" else v
+
+    for shape, layout in (((7,), "strided"), ((4, 5), "transposed"), ((3, 4, 5), "permuted"), ((2, 3, 4, 5), "holes")):
+        host = make_view(r, kind, shape, layout)
+        host[...] = r.integers(0, 50, size=shape).astype(host.dtype)
+        t = to_device(state, host)
+        nd = len(shape)
+        get = state.fn(kind, f"get{nd}d")
+        get.restype = creal
+        get.argtypes = [C.c_void_p, C.c_void_p] + [C.c_long] * nd
+        setf = state.fn(kind, f"set{nd}d")
+        setf.restype = None
+        setf.argtypes = [C.c_void_p, C.c_void_p] + [C.c_long] * nd + [creal]
+        for _ in range(5):
+            x = tuple(int(r.integers(0, n)) for n in shape)
+            assert from_c(get(state.ptr, t.ptr, *x)) == host[x]
+            setf(state.ptr, t.ptr, *x, as_c(77))
+            state.check()
+            host[x] = 77
+        assert (t.numpy() == np.asarray(host)).all()
+        get(state.ptr, t.ptr, *([0] * (nd - 1) + [shape[-1]]))
+        with pytest.raises(thc.THCError, match="out of range"):
+            state.check()
+    wrong = state.fn(kind, "get2d")
+    wrong.restype = creal
+    wrong.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_long]
+    wrong(state.ptr, to_device(state, np.zeros(3, thc.KINDS[kind][1])).ptr, 0, 0)
+    with pytest.raises(thc.THCError, match="two dimensions"):
+        state.check()
