@@ -10,6 +10,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 #include <mutex>
 #include <new>
@@ -1144,6 +1145,65 @@ void renorm<half>(THCState *state, TensorT<half> *self, TensorT<half> *src, half
   tensor_free<float>(state, wide);
 }
 
+// ---- construction calls that are thin callers of fill / copy / sumall ------------------------
+// (lib/THC/generic/THCTensorMath.cu:36-82,358-422).  A diagonal is a 1-D view with stride
+// stride0 + stride1, so diag / eye / trace need no kernels of their own.
+thcb200_scalar one_scalar() { thcb200_scalar s; s.f = 1.0; s.i = 1; return s; }
+
+template <typename R> void fill_with(THCState *state, TensorT<R> *t, thcb200_scalar v) {
+  pointwise<R>(state, THCB200_OP_FILL, t, nullptr, nullptr, nullptr, v, kZero);
+}
+// the k-th diagonal of a matrix as a 1-D view of `len` elements (k > 0 above the main diagonal)
+template <typename R> TensorT<R> *diagonal_view(THCState *state, TensorT<R> *m, long k, long len) {
+  TensorT<R> *d = tensor_alloc<R>();
+  const long start = k >= 0 ? k * m->stride[1] : -k * m->stride[0];
+  const long stride = m->stride[0] + m->stride[1];
+  tensor_raw_set<R>(state, d, m->storage, m->storageOffset + start, 1, &len, &stride);
+  return d;
+}
+template <typename R> void diag(THCState *state, TensorT<R> *self, TensorT<R> *src, long k) {
+  check_gpu<R>(state, {self, src});
+  THArgCheck(src->nDimension == 2 || src->nDimension == 1, 1, "expected a matrix or a vector");
+  if (src->nDimension == 2) {
+    const long size0 = src->size[0], size1 = src->size[1];
+    long len = k > 0 ? std::min(size0, size1 - k) : std::min(size0 + k, size1);
+    if (len < 0) len = 0;
+    tensor_raw_resize<R>(state, self, 1, &len, nullptr);
+    if (len == 0) return;
+    TensorT<R> *d = diagonal_view<R>(state, src, k, len);
+    try { tensor_copy<R>(state, self, d); } catch (...) { tensor_free<R>(state, d); throw; }
+    tensor_free<R>(state, d);
+  } else {
+    const long n = (long)tensor_nelement<R>(src);
+    const long side = k > 0 ? n + k : n - k;
+    const long sizes[2] = {side, side};
+    TensorT<R> *keep = src;
+    __sync_fetch_and_add(&keep->refcount, 1);            // src may be self
+    TensorT<R> *from = src;
+    if (self == src) { from = tensor_alloc<R>(); tensor_raw_resize<R>(state, from, 1, &n, nullptr); tensor_copy<R>(state, from, src); }
+    tensor_raw_resize<R>(state, self, 2, sizes, nullptr);
+    fill_with<R>(state, self, kZero);
+    if (n > 0) {
+      TensorT<R> *d = diagonal_view<R>(state, self, k, n);
+      try { tensor_copy<R>(state, d, from); } catch (...) { tensor_free<R>(state, d); throw; }
+      tensor_free<R>(state, d);
+    }
+    if (from != src) tensor_free<R>(state, from);
+    tensor_free<R>(state, keep);
+  }
+}
+template <typename R> void eye(THCState *state, TensorT<R> *self, long n, long m) {
+  check_gpu<R>(state, {self});
+  THArgCheck(n > 0, 1, "invalid argument");
+  if (m <= 0) m = n;
+  const long sizes[2] = {n, m};
+  tensor_raw_resize<R>(state, self, 2, sizes, nullptr);
+  fill_with<R>(state, self, kZero);
+  TensorT<R> *d = diagonal_view<R>(state, self, 0, std::min(n, m));
+  try { fill_with<R>(state, d, one_scalar()); } catch (...) { tensor_free<R>(state, d); throw; }
+  tensor_free<R>(state, d);
+}
+
 // ---- single elements (lib/THC/generic/THCStorage.c:20-34, generic/THCTensor.c:840-900) ------
 // One element crosses in the order of the current stream of the storage's device, and the call
 // waits for it (the reference uses a plain cudaMemcpy, which is not ordered with non-blocking streams).
@@ -1241,6 +1301,54 @@ void copy_async(THCState *state, TensorT<R> *gpu, void *cpu, bool to_gpu) {
   const cudaStream_t st = THCState_getCurrentStreamOnDevice(state, gpu->storage->device);
   if (to_gpu) THCudaCheck(cudaMemcpyAsync(dg.data, dc.data, (size_t)n * sizeof(R), cudaMemcpyHostToDevice, st));
   else THCudaCheck(cudaMemcpyAsync(dc.data, dg.data, (size_t)n * sizeof(R), cudaMemcpyDeviceToHost, st));
+}
+
+// ---- storage copies (lib/THC/generic/THCStorageCopy.h): a storage is copied as the 1-D tensor
+// over all of it, through the tensor copies above ------------------------------------------
+template <typename R> TensorT<R> *storage_as_tensor(THCState *state, StorageT<R> *s) {
+  TensorT<R> *t = tensor_alloc<R>();
+  const long n = (long)s->size, one = 1;
+  tensor_raw_set<R>(state, t, s, 0, 1, &n, &one);
+  return t;
+}
+// a CPU storage (same fields for every element type) as a 1-D CPU tensor on the caller's stack
+struct CpuStorageView {
+  long size, stride;
+  CpuTensorAny t;
+  explicit CpuStorageView(const void *storage) {
+    CpuStorageAny *s = (CpuStorageAny *)storage;
+    if (!s) th_error("null CPU storage");
+    size = (long)s->size;
+    stride = 1;
+    t.size = &size; t.stride = &stride; t.nDimension = 1; t.storage = s; t.storageOffset = 0; t.refcount = 1; t.flag = 0;
+  }
+};
+template <typename RD, typename RS> void storage_copy_convert(THCState *state, StorageT<RD> *self, StorageT<RS> *src) {
+  THArgCheck(self->size == src->size, 2, "size does not match");
+  if (self->size == 0) return;
+  TensorT<RD> *d = storage_as_tensor<RD>(state, self);
+  TensorT<RS> *f = storage_as_tensor<RS>(state, src);
+  try {
+    if constexpr (std::is_same<RD, RS>::value) tensor_copy<RD>(state, d, f); else tensor_copy_convert<RD, RS>(state, d, f);
+  } catch (...) { tensor_free<RD>(state, d); tensor_free<RS>(state, f); throw; }
+  tensor_free<RD>(state, d);
+  tensor_free<RS>(state, f);
+}
+template <typename R> void storage_from_cpu(THCState *state, StorageT<R> *self, const void *cpu_storage, int cpu_dtype) {
+  CpuStorageView v(cpu_storage);
+  THArgCheck(self->size == v.size, 2, "size does not match");
+  if (self->size == 0) return;
+  TensorT<R> *d = storage_as_tensor<R>(state, self);
+  try { copy_from_cpu<R>(state, d, &v.t, cpu_dtype); } catch (...) { tensor_free<R>(state, d); throw; }
+  tensor_free<R>(state, d);
+}
+template <typename R> void storage_to_cpu(THCState *state, void *cpu_storage, int cpu_dtype, StorageT<R> *src) {
+  CpuStorageView v(cpu_storage);
+  THArgCheck(v.size == src->size, 2, "size does not match");
+  if (src->size == 0) return;
+  TensorT<R> *f = storage_as_tensor<R>(state, src);
+  try { copy_to_cpu<R>(state, &v.t, cpu_dtype, f); } catch (...) { tensor_free<R>(state, f); throw; }
+  tensor_free<R>(state, f);
 }
 
 // ---- indexed moves (lib/THC/generic/THCTensorIndex.cu, THCTensorScatterGather.cu) --------

@@ -72,7 +72,7 @@ class CpuTensor:
         return C.byref(self._tensor)
 FLOATING = ("Half", "Float", "Double")
 
-# Argument codes: T tensor of the receiver's type, L LongTensor, C / M CPU Long / Byte tensor (CpuTensor), r real, l long, i int.
+# Argument codes: T tensor of the receiver's type, L LongTensor, C / M CPU Long / Byte tensor (CpuTensor), r real, l long, i int, S sizes.
 # Return codes: v void, a accreal, R real, n int.
 _UNARY = ["sigmoid", "log", "lgamma", "log1p", "exp", "cos", "acos", "cosh", "sin", "asin", "sinh", "tan", "atan",
           "tanh", "sqrt", "rsqrt", "ceil", "floor", "round", "trunc", "frac", "cinv", "neg", "abs", "sign"]
@@ -99,6 +99,9 @@ SIGNATURES.update({
     "resizeAs": ("v", "TT"),
     "tril": ("v", "TTl"), "triu": ("v", "TTl"), "renorm": ("v", "TTrlr"),
     "indexSelect": ("v", "TTiL"), "indexCopy": ("v", "TiLT"), "indexAdd": ("v", "TiLT"), "indexFill": ("v", "TiLr"),
+    # thin callers of fill / copy / sumall; code S: a tuple of sizes passed as a THLongStorage
+    "zeros": ("v", "TS"), "ones": ("v", "TS"), "zerosLike": ("v", "TT"), "onesLike": ("v", "TT"), "reshape": ("v", "TTS"),
+    "numel": ("p", "T"), "diag": ("v", "TTl"), "eye": ("v", "Tll"), "trace": ("a", "T"),
     # masks in a CPU ByteTensor (code M)
     "maskedFillByte": ("v", "TMr"), "maskedCopyByte": ("v", "TMT"), "maskedSelectByte": ("v", "TTM"),
     # the same with a CPU LongTensor of positions (code C)
@@ -414,7 +417,14 @@ class Tensor:
         f = self.state.fn(self.kind, name)
         creal, cacc = KINDS[self.kind][2], KINDS[self.kind][3]
         argtypes, cargs = [C.c_void_p], [self.state.ptr]
+        storages = []
         for code, a in zip(spec, args):
+            if code == "S":
+                sz = self._long_storage(tuple(a))
+                storages.append(sz)
+                argtypes.append(C.c_void_p)
+                cargs.append(sz)
+                continue
             if code in "TLB":
                 if not isinstance(a, Tensor):
                     raise TypeError(f"{name}: expected a tensor")
@@ -439,8 +449,10 @@ class Tensor:
                 argtypes.append(C.c_int)
                 cargs.append(int(a))
         f.argtypes = argtypes
-        f.restype = {"v": None, "a": cacc, "R": creal, "n": C.c_int}[ret]
+        f.restype = {"v": None, "a": cacc, "R": creal, "n": C.c_int, "p": C.c_ssize_t}[ret]
         r = f(*cargs)
+        for sz in storages:
+            self.state.lib.THLongStorage_free(sz)
         self.state.check()
         if ret == "R" and self.kind == "Half":
             return _half_to_float(r)

@@ -48,6 +48,37 @@ THC_API void THCStorage_(retain)(THCState *state, THCStorage *storage);
 THC_API void THCStorage_(free)(THCState *state, THCStorage *storage);
 THC_API void THCStorage_(resize)(THCState *state, THCStorage *storage, ptrdiff_t size);
 THC_API int THCStorage_(getDevice)(THCState *state, const THCStorage *storage);
+/* whole storages: between storages of any two element types on the GPU, and between CPU and
+ * GPU storages (lib/THC/generic/THCStorageCopy.h); sizes must match */
+THC_API void THCStorage_(rawCopy)(THCState *state, THCStorage *storage, real *src);
+THC_API void THCStorage_(copy)(THCState *state, THCStorage *storage, THCStorage *src);
+THC_API void THCStorage_(copyCuda)(THCState *state, THCStorage *self, THCStorage *src);
+THC_API void THCStorage_(copyCudaByte)(THCState *state, THCStorage *storage, struct THCudaByteStorage *src);
+THC_API void THCStorage_(copyCudaChar)(THCState *state, THCStorage *storage, struct THCudaCharStorage *src);
+THC_API void THCStorage_(copyCudaShort)(THCState *state, THCStorage *storage, struct THCudaShortStorage *src);
+THC_API void THCStorage_(copyCudaInt)(THCState *state, THCStorage *storage, struct THCudaIntStorage *src);
+THC_API void THCStorage_(copyCudaLong)(THCState *state, THCStorage *storage, struct THCudaLongStorage *src);
+THC_API void THCStorage_(copyCudaHalf)(THCState *state, THCStorage *storage, struct THCudaHalfStorage *src);
+THC_API void THCStorage_(copyCudaFloat)(THCState *state, THCStorage *storage, struct THCudaStorage *src);
+THC_API void THCStorage_(copyCudaDouble)(THCState *state, THCStorage *storage, struct THCudaDoubleStorage *src);
+THC_API void THCStorage_(copyByte)(THCState *state, THCStorage *storage, struct THByteStorage *src);
+THC_API void THCStorage_(copyChar)(THCState *state, THCStorage *storage, struct THCharStorage *src);
+THC_API void THCStorage_(copyShort)(THCState *state, THCStorage *storage, struct THShortStorage *src);
+THC_API void THCStorage_(copyInt)(THCState *state, THCStorage *storage, struct THIntStorage *src);
+THC_API void THCStorage_(copyLong)(THCState *state, THCStorage *storage, struct THLongStorage *src);
+THC_API void THCStorage_(copyHalf)(THCState *state, THCStorage *storage, struct THHalfStorage *src);
+THC_API void THCStorage_(copyFloat)(THCState *state, THCStorage *storage, struct THFloatStorage *src);
+THC_API void THCStorage_(copyDouble)(THCState *state, THCStorage *storage, struct THDoubleStorage *src);
+THC_API void TH_CONCAT_2(THByteStorage_copyCuda, Real)(THCState *state, struct THByteStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THCharStorage_copyCuda, Real)(THCState *state, struct THCharStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THShortStorage_copyCuda, Real)(THCState *state, struct THShortStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THIntStorage_copyCuda, Real)(THCState *state, struct THIntStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THLongStorage_copyCuda, Real)(THCState *state, struct THLongStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THHalfStorage_copyCuda, Real)(THCState *state, struct THHalfStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THFloatStorage_copyCuda, Real)(THCState *state, struct THFloatStorage *self, THCStorage *src);
+THC_API void TH_CONCAT_2(THDoubleStorage_copyCuda, Real)(THCState *state, struct THDoubleStorage *self, THCStorage *src);
+THC_API void THCStorage_(copyCPU)(THCState *state, THCStorage *self, struct TH_CONCAT_3(TH, Real, Storage) *src);
+THC_API void TH_CONCAT_3(TH, Real, Storage_copyCuda)(THCState *state, struct TH_CONCAT_3(TH, Real, Storage) *self, THCStorage *src);
 /* one element, blocking (lib/THC/generic/THCStorage.h:22-23) */
 THC_API void THCStorage_(set)(THCState *state, THCStorage *self, ptrdiff_t index, real value);
 THC_API real THCStorage_(get)(THCState *state, const THCStorage *self, ptrdiff_t index);
@@ -121,6 +152,16 @@ THC_API int THCTensor_(checkGPU)(THCState *state, unsigned int nTensors, ...);
 /* ---- fill / copy (lib/THC/generic/THCTensorMath.h:5-6, THCTensorCopy.h) ---- */
 THC_API void THCTensor_(fill)(THCState *state, THCTensor *self, real value);
 THC_API void THCTensor_(zero)(THCState *state, THCTensor *self);
+/* thin callers of fill / copy / sumall (lib/THC/generic/THCTensorMath.h:7-12,20-22) */
+THC_API void THCTensor_(zeros)(THCState *state, THCTensor *r_, THLongStorage *size);
+THC_API void THCTensor_(zerosLike)(THCState *state, THCTensor *r_, THCTensor *input);
+THC_API void THCTensor_(ones)(THCState *state, THCTensor *r_, THLongStorage *size);
+THC_API void THCTensor_(onesLike)(THCState *state, THCTensor *r_, THCTensor *input);
+THC_API void THCTensor_(reshape)(THCState *state, THCTensor *r_, THCTensor *t, THLongStorage *size);
+THC_API ptrdiff_t THCTensor_(numel)(THCState *state, THCTensor *t);
+THC_API void THCTensor_(diag)(THCState *state, THCTensor *self, THCTensor *src, long k);
+THC_API void THCTensor_(eye)(THCState *state, THCTensor *self, long n, long m);
+THC_API accreal THCTensor_(trace)(THCState *state, THCTensor *self);
 THC_API void THCTensor_(copy)(THCState *state, THCTensor *self, THCTensor *src);
 THC_API void THCTensor_(copyIgnoringOverlaps)(THCState *state, THCTensor *self, THCTensor *src);
 THC_API void THCTensor_(copyCudaByte)(THCState *state, THCTensor *dst, struct THCudaByteTensor *src);

@@ -84,3 +84,39 @@ def test_strided_cpu_views_keep_their_gaps(state, cols, step):
     want = before.copy()
     want[:, ::step] = before[:, ::step] + 1000
     assert_bit_equal(base, want, "GPU -> strided CPU view, gaps untouched")
+
+
+def test_storage_copies(state):
+    """Whole storages (lib/THC/generic/THCStorageCopy.h): CPU -> GPU with conversion, GPU -> GPU with
+    conversion, GPU -> CPU, and the size check."""
+    import ctypes as C
+    lib = state.lib
+    host = np.arange(1000, dtype=np.float32) / 4
+    cpu = thc.CpuTensor(host)
+    g16 = thc.Tensor.new(state, "Half", 1000)
+    g64 = thc.Tensor.new(state, "Double", 1000)
+
+    def storage_of(t):
+        f = state.fn(t.kind, "storage")
+        f.restype = C.c_void_p
+        f.argtypes = [C.c_void_p, C.c_void_p]
+        return C.c_void_p(f(state.ptr, t.ptr))
+
+    for name in ("THCudaHalfStorage_copyFloat", "THCudaDoubleStorage_copyCudaHalf", "THFloatStorage_copyCudaDouble"):
+        getattr(lib, name).argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        getattr(lib, name).restype = None
+    lib.THCudaHalfStorage_copyFloat(state.ptr, storage_of(g16), C.byref(cpu._storage))
+    state.check()
+    assert_bit_equal(g16.numpy(), host.astype(np.float16), "CPU float storage -> GPU half storage")
+    lib.THCudaDoubleStorage_copyCudaHalf(state.ptr, storage_of(g64), storage_of(g16))
+    state.check()
+    assert_bit_equal(g64.numpy(), host.astype(np.float16).astype(np.float64), "GPU half storage -> GPU double storage")
+    back = np.zeros(1000, np.float32)
+    cb = thc.CpuTensor(back)
+    lib.THFloatStorage_copyCudaDouble(state.ptr, C.byref(cb._storage), storage_of(g64))
+    state.check()
+    assert_bit_equal(back, host.astype(np.float16).astype(np.float32), "GPU double storage -> CPU float storage")
+    short = thc.CpuTensor(np.zeros(999, np.float32))
+    lib.THFloatStorage_copyCudaDouble(state.ptr, C.byref(short._storage), storage_of(g64))
+    with pytest.raises(thc.THCError, match="size does not match"):
+        state.check()

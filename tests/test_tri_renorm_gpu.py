@@ -121,3 +121,53 @@ def test_renorm_one_pass_and_composed_forms_agree(state, kind):
     assert lib.thcb200_last_plan() == b"renorm_rows"
     want = mx.renorm(base.T, 2, 1, 1.0)
     assert np.allclose(view.numpy().astype(np.float64), want.astype(np.float64), rtol=REL[kind], atol=0)
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_zeros_ones_reshape_diag_eye_trace(state, kind):
+    """The construction calls that are thin callers of fill / copy / sumall
+    (lib/THC/generic/THCTensorMath.cu:36-82,358-422; cutorch's tests: test/test.lua:236-330 zeros, ones,
+    reshape; :3000-3050 diag, eye, trace)."""
+    r = rng("construct", kind)
+    dt = NP_OF_KIND[kind]
+    t = thc.Tensor.new(state, kind)
+    t.zeros((3, 5, 2))
+    assert t.sizes == [3, 5, 2] and not t.numpy().any()
+    t.ones((4, 7))
+    assert_bit_equal(t.numpy(), np.ones((4, 7), dt), "ones")
+    src = make_view(r, kind, (6, 10), "transposed")
+    if src.dtype.kind != "f":
+        src[...] = r.integers(0, 9, size=src.shape).astype(dt)
+    else:
+        src[...] = (r.integers(-16, 17, size=src.shape) / 4).astype(dt)
+    dsrc = to_device(state, src)
+    t.onesLike(dsrc)
+    assert_bit_equal(t.numpy(), np.ones((6, 10), dt), "onesLike")
+    t.zerosLike(dsrc)
+    assert t.sizes == [6, 10] and not t.numpy().any()
+    t.reshape(dsrc, (4, 15))
+    assert_bit_equal(t.numpy(), np.asarray(src).reshape(4, 15), "reshape walks the source in logical order")
+    assert dsrc.numel() == 60
+    for k in (0, 2, -3, 9, -5, 12):
+        d = thc.Tensor.new(state, kind)
+        d.diag(dsrc, k)
+        assert_bit_equal(d.numpy(), np.diag(np.asarray(src), k), f"diag of a matrix, k={k}")
+    vec = np.asarray(src)[2].copy()
+    dv = to_device(state, vec)
+    for k in (0, 3, -2):
+        d = thc.Tensor.new(state, kind)
+        d.diag(dv, k)
+        assert_bit_equal(d.numpy(), np.diag(vec, k), f"diag of a vector, k={k}")
+    dv.diag(dv, 1)                                   # in place: the vector becomes the matrix
+    assert_bit_equal(dv.numpy(), np.diag(vec, 1), "diag in place")
+    e = thc.Tensor.new(state, kind)
+    e.eye(5, 8)
+    assert_bit_equal(e.numpy(), np.eye(5, 8, dtype=dt), "eye")
+    e.eye(6, 0)
+    assert_bit_equal(e.numpy(), np.eye(6, dtype=dt), "eye, square by default")
+    want = np.trace(np.asarray(src).astype(np.float64 if src.dtype.kind == "f" else np.int64))
+    assert float(dsrc.trace()) == float(want)
+    with pytest.raises(thc.THCError, match="expected a matrix"):
+        to_device(state, vec).trace()
+    with pytest.raises(thc.THCError, match="matrix or a vector"):
+        thc.Tensor.new(state, kind).diag(to_device(state, make_view(r, kind, (2, 3, 4), "contiguous")), 0)
