@@ -1204,6 +1204,60 @@ template <typename R> void eye(THCState *state, TensorT<R> *self, long n, long m
   tensor_free<R>(state, d);
 }
 
+// cat (lib/THC/generic/THCTensorMath.cu:84-260): the result is sized from the inputs (missing
+// trailing dims count as 1, empty inputs are skipped, a dimension of -1 in cutorch's 1-based
+// convention means the last one) and every input is copied into its narrowed slice of the result.
+// The reference batches many small contiguous inputs into one launch; here each input is one copy.
+template <typename R> void cat_array(THCState *state, TensorT<R> *result, TensorT<R> **inputs, int num, int dimension) {
+  auto dim_size = [](const TensorT<R> *t, int i) -> long { return i < t->nDimension ? t->size[i] : std::min(t->nDimension, 1); };
+  int max_dim = dimension + 1;
+  for (int i = 0; i < num; ++i) max_dim = std::max(max_dim, inputs[i]->nDimension);
+  int cat_dim = dimension;
+  if (dimension + TH_INDEX_BASE == -1) cat_dim = max_dim ? max_dim - 1 : 0;
+  if (num <= 0) th_arg_error(3, "invalid number of inputs");
+  if (cat_dim < 0) th_arg_error(4, "invalid dimension");
+  if (max_dim > THCB200_MAX_DIMS) th_arg_error(2, CUTORCH_DIM_WARNING);
+  for (int i = 0; i < num; ++i) check_gpu<R>(state, {result, inputs[i]});
+  long size[THCB200_MAX_DIMS];
+  for (int i = 0; i < max_dim; ++i) {
+    long d = dim_size(inputs[0], i);
+    for (int j = 1; j < num; ++j) {
+      const long sz = dim_size(inputs[j], i);
+      if (i == cat_dim) d += sz;
+      else if (d != sz && d && sz) th_error("inconsistent tensor sizes");
+      else if (!d) d = sz;
+    }
+    size[i] = d;
+  }
+  // an input may be the result itself: keep the inputs alive and unchanged while the result is resized
+  bool aliased = false;
+  for (int i = 0; i < num; ++i) aliased = aliased || inputs[i] == result || (inputs[i]->storage && inputs[i]->storage == result->storage);
+  TensorT<R> *out = result;
+  if (aliased) out = tensor_alloc<R>();
+  tensor_raw_resize<R>(state, out, max_dim, size, nullptr);
+  long offset = 0;
+  TensorT<R> *slice = tensor_alloc<R>();
+  try {
+    for (int j = 0; j < num; ++j) {
+      const long len = dim_size(inputs[j], cat_dim);
+      if (inputs[j]->nDimension == 0 || len == 0) continue;
+      tensor_narrow<R>(state, slice, out, cat_dim, offset, len);
+      tensor_copy<R>(state, slice, inputs[j]);
+      offset += len;
+    }
+    if (aliased) {
+      tensor_raw_resize<R>(state, result, max_dim, size, nullptr);
+      tensor_copy<R>(state, result, out);
+    }
+  } catch (...) {
+    tensor_free<R>(state, slice);
+    if (aliased) tensor_free<R>(state, out);
+    throw;
+  }
+  tensor_free<R>(state, slice);
+  if (aliased) tensor_free<R>(state, out);
+}
+
 // ---- single elements (lib/THC/generic/THCStorage.c:20-34, generic/THCTensor.c:840-900) ------
 // One element crosses in the order of the current stream of the storage's device, and the call
 // waits for it (the reference uses a plain cudaMemcpy, which is not ordered with non-blocking streams).

@@ -484,6 +484,15 @@ class Tensor:
         f(self.state.ptr, cpu.ptr, self.ptr)
         self.state.check()
 
+    def cat(self, inputs, dimension: int):
+        """result:cat(inputs, dimension): THCTensor_(catArray) (lib/THC/generic/THCTensorMath.cu:84-260)."""
+        f = self.state.fn(self.kind, "catArray")
+        arr = (C.c_void_p * len(inputs))(*[t.ptr for t in inputs])
+        f.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int]
+        f.restype = None
+        f(self.state.ptr, self.ptr, arr, len(inputs), dimension)
+        self.state.check()
+
     def sumall_to_device(self, result_dev_ptr: int):
         f = self.state.fn(self.kind, "sumallToDevice")
         f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]

@@ -159,6 +159,10 @@ THC_API void THCTensor_(ones)(THCState *state, THCTensor *r_, THLongStorage *siz
 THC_API void THCTensor_(onesLike)(THCState *state, THCTensor *r_, THCTensor *input);
 THC_API void THCTensor_(reshape)(THCState *state, THCTensor *r_, THCTensor *t, THLongStorage *size);
 THC_API ptrdiff_t THCTensor_(numel)(THCState *state, THCTensor *t);
+/* concatenation along `dimension` (0-based; -2 = the last dim, cutorch's -1 in 1-based counting):
+ * every input is copied into its slice of the result (lib/THC/generic/THCTensorMath.h:13-14) */
+THC_API void THCTensor_(cat)(THCState *state, THCTensor *result, THCTensor *ta, THCTensor *tb, int dimension);
+THC_API void THCTensor_(catArray)(THCState *state, THCTensor *result, THCTensor **inputs, int numInputs, int dimension);
 THC_API void THCTensor_(diag)(THCState *state, THCTensor *self, THCTensor *src, long k);
 THC_API void THCTensor_(eye)(THCState *state, THCTensor *self, long n, long m);
 THC_API accreal THCTensor_(trace)(THCState *state, THCTensor *self);

@@ -171,3 +171,40 @@ def test_zeros_ones_reshape_diag_eye_trace(state, kind):
         to_device(state, vec).trace()
     with pytest.raises(thc.THCError, match="matrix or a vector"):
         thc.Tensor.new(state, kind).diag(to_device(state, make_view(r, kind, (2, 3, 4), "contiguous")), 0)
+
+
+@pytest.mark.parametrize("kind", ["Byte", "Float", "Half", "Long"])
+def test_cat(state, kind):
+    """cat / catArray (lib/THC/generic/THCTensorMath.cu:84-260; cutorch's tests: test/test.lua:3250-3330):
+    every dim, strided inputs, an empty input, the last dim chosen with -2 (cutorch's -1), an input
+    that is the result itself, and the size check."""
+    r = rng("cat", kind)
+    dt = NP_OF_KIND[kind]
+
+    def rand(shape, layout="contiguous"):
+        x = make_view(r, kind, shape, layout)
+        x[...] = r.integers(0, 9, size=shape).astype(dt)
+        return x
+
+    for dim in range(3):
+        shapes = []
+        for n in (2, 5, 3):
+            s = [4, 6, 5]
+            s[dim] = n
+            shapes.append(tuple(s))
+        parts = [rand(shapes[0]), rand(shapes[1], "transposed"), rand(shapes[2], "strided")]
+        out = thc.Tensor.new(state, kind)
+        out.cat([to_device(state, p) for p in parts], dim)
+        assert_bit_equal(out.numpy(), np.concatenate([np.asarray(p) for p in parts], axis=dim), f"{kind} cat dim {dim}")
+    a, b = rand((3, 4)), rand((3, 2))
+    out = thc.Tensor.new(state, kind)
+    out.cat([to_device(state, a), thc.Tensor.new(state, kind), to_device(state, b)], -2)
+    assert_bit_equal(out.numpy(), np.concatenate([a, b], axis=1), "empty input skipped, last dim by -2")
+    da = to_device(state, a)
+    da.cat([da, to_device(state, rand((2, 4)))], 0)
+    assert da.sizes == [5, 4] and (da.numpy()[:3] == a).all()
+    v1, v2 = rand((4,)), rand((3,))
+    out.cat([to_device(state, v1), to_device(state, v2)], 0)
+    assert_bit_equal(out.numpy(), np.concatenate([v1, v2]), "vectors")
+    with pytest.raises(thc.THCError, match="inconsistent tensor sizes"):
+        out.cat([to_device(state, a), to_device(state, rand((4, 5)))], 0)
