@@ -1326,17 +1326,17 @@ bool cpu_contiguous(const void *tensor) {
 
 template <typename R>
 void copy_from_cpu(THCState *state, TensorT<R> *self, const void *src, int src_dtype) {
-  check_gpu<R>(state, {self});
   THArgCheck(tensor_nelement<R>(self) == cpu_nelement(src), 2, "sizes do not match");
   if (cpu_nelement(src) == 0) return;
+  DeviceGuard guard(tensor_device<R>(self, current_device()));   // the GPU tensor may live on another device than the current one
   thcb200_tensor dd = describe<R>(self), ds = describe_cpu(src, src_dtype);
   check_core(thcb200_copy_from_host(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
 }
 template <typename R>
 void copy_to_cpu(THCState *state, void *self, int self_dtype, TensorT<R> *src) {
-  check_gpu<R>(state, {src});
   THArgCheck(cpu_nelement(self) == tensor_nelement<R>(src), 2, "sizes do not match");
   if (cpu_nelement(self) == 0) return;
+  DeviceGuard guard(tensor_device<R>(src, current_device()));
   thcb200_tensor dd = describe_cpu(self, self_dtype), ds = describe<R>(src);
   check_core(thcb200_copy_to_host(state_ctx(state), &dd, &ds, (void *)state_stream(state)));
 }
@@ -1344,7 +1344,6 @@ void copy_to_cpu(THCState *state, void *self, int self_dtype, TensorT<R> *src) {
 // one cudaMemcpyAsync on the current stream of the GPU tensor's device.
 template <typename R>
 void copy_async(THCState *state, TensorT<R> *gpu, void *cpu, bool to_gpu) {
-  check_gpu<R>(state, {gpu});
   THArgCheck(tensor_nelement<R>(gpu) == cpu_nelement(cpu), 2, "sizes do not match");
   THArgCheck(tensor_is_contiguous<R>(gpu), to_gpu ? 2 : 3, "Target tensor must be contiguous");
   THArgCheck(cpu_contiguous(cpu), to_gpu ? 3 : 2, "Source tensor must be contiguous");

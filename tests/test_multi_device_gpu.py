@@ -102,3 +102,17 @@ def test_copy_without_peer_access_goes_through_dense_temporaries(state, two_devi
     finally:
         lib.THCState_setPeerToPeerAccess(state.ptr, 1, 0, 1)
     assert lib.THCState_getPeerToPeerAccess(state.ptr, 1, 0) == 1
+
+
+def test_cpu_tensor_copies_reach_a_tensor_on_another_device(state, two_devices):
+    """copy between a CPU tensor and a GPU tensor that lives on device 1 while device 0 is current
+    (cutorch's cudaMemcpy does not care which device is current either)."""
+    torch = two_devices
+    r = rng("xdev-host")
+    host = make_view(r, "Float", (40, 33), "transposed")
+    on1 = on_device(torch, 1, lambda: to_device(state, np.zeros((40, 33), np.float64)))
+    on1.copy_from_cpu(thc.CpuTensor(host))                       # device 0 is current here
+    assert_bit_equal(on_device(torch, 1, lambda: on1.numpy()), np.asarray(host).astype(np.float64), "CPU -> GPU 1")
+    back = np.zeros((40, 33), np.float32)
+    on1.copy_to_cpu(thc.CpuTensor(back))
+    assert_bit_equal(back, np.ascontiguousarray(host), "GPU 1 -> CPU")
