@@ -175,6 +175,11 @@ masked_fill_strided_kernel(W *t, StridedView<IndexT> vt, const uint8_t *mask, St
 //   2. tile_scan_kernel (one CTA): exclusive prefix of the tile counts, and the total.
 //   3. masked_move_kernel: recomputes the ballots of its tile and moves the elements.
 // ---------------------------------------------------------------------------------
+// a / b with the 32-bit divide when both fit
+__device__ __forceinline__ uint64_t div_by_u32_or_64(uint64_t a, uint64_t b) {
+  if (((a | b) >> 32) == 0) return (uint32_t)a / (uint32_t)b;
+  return a / b;
+}
 constexpr int kSteps = 16;
 constexpr int kWarpSpan = 32 * kSteps;            // 512
 constexpr int kTile = (kThreads / 32) * kWarpSpan;  // 4096
@@ -698,6 +703,50 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   return 0;
 }
 
+// nonzero: for every set element of a dense mask, in order, the 1-based coordinates it has in a
+// tensor of the given sizes, one row of `nd` int64 per element.  Same tiles, ranks and tile offsets
+// as the select kernel; a lane owns 16 consecutive mask bytes.
+struct CoordShape {
+  int nd;
+  uint64_t size[kMaxDims];
+};
+__global__ void __launch_bounds__(kThreads)
+mask_coords_kernel(const uint8_t *mask, uint64_t n, const uint64_t *offsets, CoordShape shape, int64_t *out) {
+  __shared__ uint32_t wsum[kThreads / 32];
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
+  uint64_t pos = offsets[blockIdx.x];
+  uint32_t bits = 0;
+  if (ebase + 16 <= n) {
+    bits = nonzero_bits16(ld16_stream(mask + ebase));
+  } else {
+    for (int j = 0; j < 16; ++j)
+      if (ebase + j < n && mask[ebase + j]) bits |= 1u << j;
+  }
+  const uint32_t cnt = __popc(bits);
+  uint32_t incl = cnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= (unsigned)d) incl += y;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  for (unsigned w = 0; w < warp; ++w) pos += wsum[w];
+  pos += incl - cnt;
+  for (int j = 0; j < 16; ++j) {
+    if (!((bits >> j) & 1u)) continue;
+    uint64_t rem = ebase + j;
+    int64_t *row = out + pos * (uint64_t)shape.nd;
+    for (int d = shape.nd - 1; d >= 0; --d) {
+      const uint64_t q = d == 0 ? 0 : div_by_u32_or_64(rem, shape.size[d]);
+      row[d] = (int64_t)(rem - q * shape.size[d]) + 1;
+      rem = q;
+    }
+    ++pos;
+  }
+}
+
 template <typename W, bool SELECT>
 int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView &vpacked, const HostView &vm,
                       bool reuse, cudaStream_t st) {
@@ -850,6 +899,36 @@ static int masked_move(thcb200_ctx *ctx, bool select, const thcb200_tensor *stri
     default: return THCB_MOVE(uint64_t);
   }
 #undef THCB_MOVE
+}
+
+int thcb200_mask_coords(thcb200_ctx *ctx, const thcb200_tensor *out_i64, const thcb200_tensor *mask_u8, const int64_t *sizes,
+                        int nd, void *stream, int flags) {
+  if (!ctx || !sizes) { set_error("mask_coords: null argument"); return THCB200_ERR_ARG; }
+  if (nd < 1 || nd > THCB200_MAX_DIMS) { set_error("mask_coords: %d dims", nd); return THCB200_ERR_DIMS; }
+  HostView vo, vm;
+  int rc = to_host_view(out_i64, &vo, "mask_coords output");
+  if (!rc) rc = check_mask(mask_u8, &vm, "mask_coords");
+  if (rc) return rc;
+  if (vo.dtype != THCB200_I64) { set_error("mask_coords: the output must be an I64 view"); return THCB200_ERR_ARG; }
+  int64_t total = 1;
+  CoordShape shape;
+  shape.nd = nd;
+  for (int d = 0; d < nd; ++d) { shape.size[d] = (uint64_t)sizes[d]; total *= sizes[d]; }
+  if (total != vm.numel) { set_error("mask_coords: the sizes do not multiply to the mask's element count"); return THCB200_ERR_SIZE; }
+  if (vm.numel == 0 || vo.numel == 0) return THCB200_OK;
+  THCB_CTX_LOCK(ctx);
+  cudaStream_t st = (cudaStream_t)stream;
+  MaskPrep mp;
+  rc = prepare_mask(ctx, vm, (flags & THCB200_FLAG_MASK_COUNTED) != 0, st, &mp);
+  if (rc) return rc;
+  Collapsed co;
+  if (!mp.cm.unit || !collapse_view(vo, &co) || !co.unit) { set_error("mask_coords: the mask and the output must be dense"); return THCB200_ERR_ARG; }
+  set_plan_name("mask_coords");
+  mask_coords_kernel<<<(unsigned)mp.ntiles, kThreads, 0, st>>>(reinterpret_cast<const uint8_t *>(vm.data), (uint64_t)vm.numel, mp.offsets,
+                                                              shape, reinterpret_cast<int64_t *>(vo.data));
+  count_launch();
+  THCB_CUDA_TRY(cudaGetLastError());
+  return THCB200_OK;
 }
 
 int thcb200_masked_copy(thcb200_ctx *ctx, const thcb200_tensor *t, const thcb200_tensor *mask_u8,

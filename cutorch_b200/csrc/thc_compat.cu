@@ -1542,6 +1542,33 @@ template <typename R> void masked_select(THCState *state, TensorT<R> *tensor, Te
   check_core(thcb200_masked_select(state_ctx(state), &dt, &ds, &dm, (void *)state_stream(state), THCB200_FLAG_MASK_COUNTED));
 }
 
+// nonzero (lib/THC/generic/THCTensorMath.cu:262-356): a comparison with zero into a dense byte
+// mask, the count of its set bytes, then one row of 1-based coordinates per set element.  The
+// reference copies the tensor to a contiguous clone and runs thrust copy_if over linear indices.
+template <typename R> void nonzero(THCState *state, LongT *out, TensorT<R> *self) {
+  check_gpu<R>(state, {self});
+  check_gpu<long>(state, {out});
+  const int nd = self->nDimension;
+  long shape[2] = {0, (long)nd};
+  if (tensor_nelement<R>(self) == 0) { tensor_raw_resize<long>(state, out, 2, shape, nullptr); return; }
+  ByteT *mask = tensor_alloc<unsigned char>();
+  try {
+    compare_to_byte<R>(state, THCB200_OP_NE_S, mask, self, nullptr, kZero);
+    thcb200_tensor dm = describe<unsigned char>(mask);
+    int64_t total = 0;
+    check_core(thcb200_masked_count(state_ctx(state), &dm, &total, (void *)state_stream(state)));
+    shape[0] = (long)total;
+    tensor_raw_resize<long>(state, out, 2, shape, nullptr);
+    if (total > 0) {
+      int64_t sizes[THCB200_MAX_DIMS];
+      for (int d = 0; d < nd; ++d) sizes[d] = self->size[d];
+      thcb200_tensor dout = describe<long>(out);
+      check_core(thcb200_mask_coords(state_ctx(state), &dout, &dm, sizes, nd, (void *)state_stream(state), THCB200_FLAG_MASK_COUNTED));
+    }
+  } catch (...) { tensor_free<unsigned char>(state, mask); throw; }
+  tensor_free<unsigned char>(state, mask);
+}
+
 // The index* calls with a CPU LongTensor of positions (lib/THC/generic/THCTensorIndex.cu:5-15,
 // 133-143,261-272,383-394): the positions go up into a temporary CudaLongTensor, then the call
 // with device indices runs.

@@ -101,7 +101,7 @@ SIGNATURES.update({
     "indexSelect": ("v", "TTiL"), "indexCopy": ("v", "TiLT"), "indexAdd": ("v", "TiLT"), "indexFill": ("v", "TiLr"),
     # thin callers of fill / copy / sumall; code S: a tuple of sizes passed as a THLongStorage
     "zeros": ("v", "TS"), "ones": ("v", "TS"), "zerosLike": ("v", "TT"), "onesLike": ("v", "TT"), "reshape": ("v", "TTS"),
-    "numel": ("p", "T"), "diag": ("v", "TTl"), "eye": ("v", "Tll"), "trace": ("a", "T"),
+    "numel": ("p", "T"), "nonzero": ("v", "LT"), "diag": ("v", "TTl"), "eye": ("v", "Tll"), "trace": ("a", "T"),
     # masks in a CPU ByteTensor (code M)
     "maskedFillByte": ("v", "TMr"), "maskedCopyByte": ("v", "TMT"), "maskedSelectByte": ("v", "TTM"),
     # the same with a CPU LongTensor of positions (code C)

@@ -161,6 +161,8 @@ THC_API void THCTensor_(reshape)(THCState *state, THCTensor *r_, THCTensor *t, T
 THC_API ptrdiff_t THCTensor_(numel)(THCState *state, THCTensor *t);
 /* concatenation along `dimension` (0-based; -2 = the last dim, cutorch's -1 in 1-based counting):
  * every input is copied into its slice of the result (lib/THC/generic/THCTensorMath.h:13-14) */
+/* rows of 1-based coordinates of the non-zero elements, in order (lib/THC/generic/THCTensorMath.h:15) */
+THC_API void THCTensor_(nonzero)(THCState *state, struct THCudaLongTensor *tensor, THCTensor *self);
 THC_API void THCTensor_(cat)(THCState *state, THCTensor *result, THCTensor *ta, THCTensor *tb, int dimension);
 THC_API void THCTensor_(catArray)(THCState *state, THCTensor *result, THCTensor **inputs, int numInputs, int dimension);
 THC_API void THCTensor_(diag)(THCState *state, THCTensor *self, THCTensor *src, long k);

@@ -381,6 +381,15 @@ THCB200_API int thcb200_masked_select(thcb200_ctx *ctx, const thcb200_tensor *ou
                           const thcb200_tensor *src, const thcb200_tensor *mask_u8, void *stream,
                           int flags);
 
+/* For every set element of a dense mask, in order, its 1-based coordinates in a tensor of the given
+ * sizes (their product is the mask's element count): row r of the dense I64 output [count, nd]
+ * holds the coordinates of the r-th set element.  The count comes from thcb200_masked_count; with
+ * THCB200_FLAG_MASK_COUNTED the tile offsets of that call are reused.  This is the second half of
+ * nonzero (lib/THC/generic/THCTensorMath.cu:262-356); the first half is a comparison with zero. */
+THCB200_API int thcb200_mask_coords(thcb200_ctx *ctx, const thcb200_tensor *out_i64,
+                        const thcb200_tensor *mask_u8, const int64_t *sizes, int nd,
+                        void *stream, int flags);
+
 #ifdef __cplusplus
 }
 #endif

@@ -210,3 +210,25 @@ def test_masked_calls_with_the_mask_in_a_cpu_tensor(state, kind):
     t = to_device(state, src)
     t.maskedCopyByte(cm, to_device(state, packed))
     assert_bit_equal(t.numpy(), mo.masked_copy(src, mask, packed), f"{kind} maskedCopyByte")
+
+
+@pytest.mark.parametrize("kind", ALL_KINDS)
+def test_nonzero(state, kind):
+    """nonzero (lib/THC/generic/THCTensorMath.cu:262-356; cutorch's test: test/test.lua:2260-2300): rows of
+    1-based coordinates of the non-zero elements in logical order, for 1-D to 4-D strided inputs, an
+    all-zero input and one with more than a tile of elements."""
+    r = rng("nonzero", kind)
+    for shape, layout in [((1000,), "contiguous"), ((37, 53), "transposed"), ((6, 7, 8), "permuted"), ((3, 5, 4, 6), "holes"),
+                          ((70, 300), "strided")]:
+        x = make_view(r, kind, shape, layout)
+        x[...] = (r.integers(0, 3, size=shape) * (r.uniform(size=shape) < 0.4)).astype(x.dtype)
+        dx = to_device(state, x)
+        out = thc.Tensor.new(state, "Long")
+        dx.call("nonzero", out, dx)
+        want = np.argwhere(np.asarray(x) != 0).astype(np.int64) + 1
+        assert out.sizes == [want.shape[0], len(shape)]
+        assert_bit_equal(out.numpy(), want, f"{kind} nonzero {shape} {layout}")
+    zero = to_device(state, np.zeros((4, 5), NP_OF_KIND[kind]))
+    out = thc.Tensor.new(state, "Long")
+    zero.call("nonzero", out, zero)
+    assert out.sizes == [0, 2]
