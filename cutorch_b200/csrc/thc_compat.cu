@@ -694,6 +694,34 @@ template <typename R> void tensor_resize_as(THCState *state, TensorT<R> *self, T
   if (!tensor_same_size<R>(self, src)) tensor_raw_resize<R>(state, self, src->nDimension, src->size, nullptr);
 }
 
+// expand (lib/THC/generic/THCTensor.c:297-330; the geometry rule is TH's inferExpandGeometry): the
+// tensor's dims are matched to the last dims of `sizes`; a dim of size 1 (or a new leading dim) is
+// repeated with stride 0, any other dim must already have the requested size (-1 keeps it).
+template <typename R> void tensor_expand(THCState *state, TensorT<R> *r, TensorT<R> *t, const long *sizes, int nsizes) {
+  THArgCheck(t->nDimension > 0, 0, "can't expand an empty tensor");
+  THArgCheck(nsizes >= t->nDimension, 1, "the number of sizes provided must be greater or equal to the number of dimensions in the tensor");
+  if (nsizes > THCB200_MAX_DIMS) th_arg_error(1, CUTORCH_DIM_WARNING);
+  long esize[THCB200_MAX_DIMS], estride[THCB200_MAX_DIMS];
+  for (int i = nsizes - 1; i >= 0; --i) {
+    const int d = i - (nsizes - t->nDimension);     // the tensor's dim under position i, or negative
+    long size = d >= 0 ? t->size[d] : 1;
+    long stride = d >= 0 ? t->stride[d] : 0;
+    long want = sizes[i];
+    if (want == -1) {
+      if (d < 0) th_error("The expanded size of the tensor (-1) isn't allowed in a leading, non-existing dimension %d", i);
+      want = size;
+    }
+    if (size != want) {
+      if (size != 1) th_error("The expanded size of the tensor (%ld) must match the existing size (%ld) at non-singleton dimension %d.", want, size, i);
+      size = want;
+      stride = 0;
+    }
+    esize[i] = size;
+    estride[i] = stride;
+  }
+  tensor_raw_set<R>(state, r, t->storage, t->storageOffset, nsizes, esize, estride);
+}
+
 // ---- descriptors and the math layer ----------------------------------------------------
 template <typename R> thcb200_tensor describe(const TensorT<R> *t) {
   thcb200_tensor d;

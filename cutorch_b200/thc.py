@@ -316,6 +316,17 @@ class Tensor:
         self.state.check()
         return t
 
+    def expand(self, *sizes) -> "Tensor":
+        """tensor:expand(sizes): a broadcast view (THCTensor_(newExpand))."""
+        f = self.state.fn(self.kind, "newExpand")
+        f.restype = C.c_void_p
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        sz = self._long_storage(sizes)
+        p = f(self.state.ptr, self.ptr, sz)
+        self.state.lib.THLongStorage_free(sz)
+        self.state.check()
+        return Tensor(self.state, self.kind, p)
+
     def narrow(self, dim, first, size) -> "Tensor":
         f = self.state.fn(self.kind, "newNarrow")
         f.restype = C.c_void_p

@@ -138,6 +138,9 @@ THC_API void THCTensor_(retain)(THCState *state, THCTensor *self);
 THC_API void THCTensor_(free)(THCState *state, THCTensor *self);
 THC_API void THCTensor_(freeCopyTo)(THCState *state, THCTensor *self, THCTensor *dst);
 THC_API int THCTensor_(getDevice)(THCState *state, const THCTensor *self);
+/* broadcast views: dims of size 1 and new leading dims repeat with stride 0 (lib/THC/generic/THCTensor.h:78-80) */
+THC_API void THCTensor_(expand)(THCState *state, THCTensor *r, THCTensor *tensor, THLongStorage *sizes);
+THC_API THCTensor *THCTensor_(newExpand)(THCState *state, THCTensor *tensor, THLongStorage *sizes);
 /* one element by its coordinates, blocking (lib/THC/generic/THCTensor.h:115-124) */
 THC_API void THCTensor_(set1d)(THCState *state, THCTensor *tensor, long x0, real value);
 THC_API void THCTensor_(set2d)(THCState *state, THCTensor *tensor, long x0, long x1, real value);

@@ -462,3 +462,31 @@ def test_half_unary_math_over_every_bit_pattern(state, oracle):
             assert_ulp(got[fin], want[fin], 1, f"Half.{name} over all inputs")
             differing = int((got[fin].view(np.uint16) != want[fin].view(np.uint16)).sum())
             assert differing <= 0.02 * fin.sum(), f"Half.{name}: {differing} of {int(fin.sum())} results off by one ulp"
+
+
+def test_expand_gives_broadcast_views_that_take_the_rows_kernel(state, oracle):
+    """tensor:expand (lib/THC/generic/THCTensor.c:297-330): size-1 dims and new leading dims repeat with
+    stride 0; a per-row factor and a bias row expanded to the matrix go through cmul / cadd like full
+    tensors (rows plan), and the geometry errors are TH's."""
+    from cutorch_b200 import _lib
+    lib = _lib.load_library()
+    r = rng("expand")
+    x = r.standard_normal((300, 256)).astype(np.float32)
+    scale = r.standard_normal((300, 1)).astype(np.float32)
+    bias = r.standard_normal((256,)).astype(np.float32)
+    dx, ds, db = to_device(state, x), to_device(state, scale), to_device(state, bias)
+    es, eb = ds.expand(300, 256), db.expand(300, 256)
+    assert es.sizes == [300, 256] and es.strides == [1, 0]
+    assert eb.sizes == [300, 256] and eb.strides == [0, 1]
+    out = thc.Tensor.new(state, "Float")
+    out.cmul(dx, es)
+    assert lib.thcb200_last_plan() == b"rows"
+    assert_bit_equal(out.numpy(), x * scale, "cmul with an expanded per-row factor")
+    out.cadd(out, 1.0, eb)
+    assert_bit_equal(out.numpy(), x * scale + bias, "cadd with an expanded bias row")
+    assert db.expand(2, 3, 256).sizes == [2, 3, 256]
+    assert ds.expand(-1, 4).sizes == [300, 4]
+    with pytest.raises(thc.THCError, match="must match the existing size"):
+        ds.expand(299, 256)
+    with pytest.raises(thc.THCError, match="greater or equal"):
+        ds.expand(300)
