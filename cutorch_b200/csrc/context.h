@@ -38,6 +38,7 @@ struct thcb200_ctx {
   int64_t prep_numel;
   void *prep_stream;
   int prep_valid;
+  int prep_count_known;   // the host has read the count of that mask from the pinned slot
 };
 
 #define THCB_CTX_LOCK(ctx) std::lock_guard<std::recursive_mutex> thcb_ctx_guard((ctx)->lock)

@@ -630,7 +630,22 @@ struct MaskPrep {
   uint64_t *offsets;   // device, ntiles entries
   int64_t *total;      // device
   Collapsed cm;
+  bool hit;            // the offsets were found in the context and thcb200_masked_count has read their total
 };
+
+// When the tile offsets of a mask are found in the context, thcb200_masked_count ran on it before and
+// the number of set elements sits in the pinned slot (that call synchronised to read it).  True, with *rc set, when an output of `have` elements cannot hold
+// count * per_element of them.
+bool counted_on_host(thcb200_ctx *ctx, int *rc, int64_t have, int64_t per_element, const char *what) {
+  int64_t count = 0;
+  memcpy(&count, (char *)ctx->host_slot + kHostCountOffset, 8);
+  if (count < 0 || have >= count * per_element) return false;
+  set_error("%s: the output holds %lld elements, the mask selects %lld x %lld", what, (long long)have, (long long)count,
+            (long long)per_element);
+  *rc = THCB200_ERR_SIZE;
+  return true;
+}
+
 
 // Fills the context's tile offsets for this mask view (or finds them there when `reuse`).
 int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t st, MaskPrep *mp) {
@@ -668,8 +683,10 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   mp->total = reinterpret_cast<int64_t *>(base);
   mp->offsets = reinterpret_cast<uint64_t *>(base + 256);
   uint32_t *counts = reinterpret_cast<uint32_t *>(base + 256 + mp->ntiles * 8);
+  mp->hit = hit && ctx->prep_count_known;
   if (hit) return 0;
   ctx->prep_valid = 0;
+  ctx->prep_count_known = 0;
   const uint8_t *mask = reinterpret_cast<const uint8_t *>(vm.data);
   const bool mask_vec = mp->cm.unit && aligned16(mask);
   // whole tiles of a unit-stride aligned mask go through the vector count; the rest (a ragged last
@@ -711,15 +728,17 @@ struct CoordShape {
   uint64_t size[kMaxDims];
 };
 __global__ void __launch_bounds__(kThreads)
-mask_coords_kernel(const uint8_t *mask, uint64_t n, const uint64_t *offsets, CoordShape shape, int64_t *out) {
+mask_coords_kernel(const uint8_t *mask, uint64_t n, bool vec /* mask base is 16-byte aligned */, const uint64_t *offsets,
+                   CoordShape shape, int64_t *out) {
   __shared__ uint32_t wsum[kThreads / 32];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
   uint64_t pos = offsets[blockIdx.x];
   uint32_t bits = 0;
-  if (ebase + 16 <= n) {
+  if (vec && ebase + 16 <= n) {
     bits = nonzero_bits16(ld16_stream(mask + ebase));
   } else {
+    // a ragged end, or a dense mask that starts off a 16-byte boundary (a narrowed ByteTensor)
     for (int j = 0; j < 16; ++j)
       if (ebase + j < n && mask[ebase + j]) bits |= 1u << j;
   }
@@ -753,6 +772,8 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
   MaskPrep mp;
   int rc = prepare_mask(ctx, vm, reuse, st, &mp);
   if (rc) return rc;
+  // with the count already on the host a packed side that is too short is refused instead of overrun
+  if (mp.hit && counted_on_host(ctx, &rc, vpacked.numel, 1, SELECT ? "masked_select" : "masked_copy")) return rc;
   Collapsed cs, cp;
   if (!collapse_view(vstrided, &cs) || !collapse_view(vpacked, &cp)) {
     set_error("masked: a view keeps more than %d dims after collapsing", kGenericDims);
@@ -874,6 +895,7 @@ int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8, int64_
   if (rc) return rc;
   THCB_CUDA_TRY(cudaStreamSynchronize(st));
   memcpy(count_host, (char *)ctx->host_slot + kHostCountOffset, 8);
+  ctx->prep_count_known = 1;   // the pinned slot now holds the count of exactly this mask
   return THCB200_OK;
 }
 
@@ -923,8 +945,11 @@ int thcb200_mask_coords(thcb200_ctx *ctx, const thcb200_tensor *out_i64, const t
   if (rc) return rc;
   Collapsed co;
   if (!mp.cm.unit || !collapse_view(vo, &co) || !co.unit) { set_error("mask_coords: the mask and the output must be dense"); return THCB200_ERR_ARG; }
-  set_plan_name("mask_coords");
-  mask_coords_kernel<<<(unsigned)mp.ntiles, kThreads, 0, st>>>(reinterpret_cast<const uint8_t *>(vm.data), (uint64_t)vm.numel, mp.offsets,
+  // with the count already on the host (the caller counted this mask and said so) a short output is refused
+  if (mp.hit && counted_on_host(ctx, &rc, vo.numel, (int64_t)nd, "mask_coords")) return rc;
+  const bool mvec = aligned16(vm.data);
+  set_plan_name(mvec ? "mask_coords" : "mask_coords_bytes");
+  mask_coords_kernel<<<(unsigned)mp.ntiles, kThreads, 0, st>>>(reinterpret_cast<const uint8_t *>(vm.data), (uint64_t)vm.numel, mvec, mp.offsets,
                                                               shape, reinterpret_cast<int64_t *>(vo.data));
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());

@@ -12,6 +12,8 @@
 // The price: every GPU on which this library is loaded holds THCB200_STATIC_SCRATCH_BYTES for
 // the life of the process, a reduction whose partials do not fit is refused, and all calls on
 // one device share the one array.
+#include <mutex>
+
 #include "context.h"
 #include "plan.h"
 #include "reduce_launch.cuh"
@@ -26,10 +28,13 @@ static __device__ __align__(256) unsigned char g_static_scratch[THCB200_STATIC_S
 constexpr int kMaxDevices = 64;
 void *g_scratch_dev[kMaxDevices];  // device address of g_static_scratch, per device
 int g_num_sms[kMaxDevices];
-bool g_ready[kMaxDevices];
+int g_setup_rc[kMaxDevices];
+// The first call on a device, from whichever host thread, runs the set-up; every other caller
+// waits for it and then sees what it published (std::call_once allocates nothing).
+std::once_flag g_once[kMaxDevices];
 
 // Once per device, with that device current.
-int setup_device(int device) {
+int setup_device_once(int device) {
   void *p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
   if (e != cudaSuccess || !p) {
@@ -46,8 +51,13 @@ int setup_device(int device) {
   }
   g_scratch_dev[device] = p;
   g_num_sms[device] = sms;
-  g_ready[device] = true;
   return 0;
+}
+
+int setup_device(int device) {
+  std::call_once(g_once[device], [device] { g_setup_rc[device] = setup_device_once(device); });
+  if (g_setup_rc[device]) thcb::set_error("reduce_dim_static: the set-up of device %d failed on its first call", device);
+  return g_setup_rc[device];
 }
 
 }  // namespace
@@ -75,6 +85,8 @@ extern "C" THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_s
   if (vin.dtype != vout.dtype) { set_error("reduce_dim_static: input and output dtypes differ"); return THCB200_ERR_ARG; }
   const int mode = reduce_mode(rop, pre);
   if (mode < 0) { set_error("reduce_dim_static: unknown reduce op %d / pre op %d", rop, pre); return THCB200_ERR_ARG; }
+  // the running sums of var / std need the post step that only thcb200_reduce_dim_post takes
+  if (pre == THCB200_PRE_MOMENTS) { set_error("reduce_dim_static: THCB200_PRE_MOMENTS needs a var/std post step; use thcb200_reduce_dim_post"); return THCB200_ERR_ARG; }
   if (dim < 0 || dim >= vin.ndim) { set_error("reduce_dim_static: dimension %d out of range", dim); return THCB200_ERR_ARG; }
   if (vout.ndim != vin.ndim) { set_error("reduce_dim_static: output must have the input's dimension count"); return THCB200_ERR_ARG; }
   for (int i = 0; i < vin.ndim; ++i) {
@@ -86,10 +98,8 @@ extern "C" THCB200_API int thcb200_reduce_dim_static(int rop, int pre, thcb200_s
   int device = 0;
   THCB_CUDA_TRY(cudaGetDevice(&device));
   if (device < 0 || device >= kMaxDevices) { set_error("reduce_dim_static: device index %d not supported", device); return THCB200_ERR_LIMIT; }
-  if (!g_ready[device]) {
-    rc = setup_device(device);
-    if (rc) return rc;
-  }
+  rc = setup_device(device);
+  if (rc) return rc;
 
   // A stand-in context whose workspace is the static array: the shared launch code then finds
   // its partials buffer large enough and never grows it.

@@ -500,6 +500,17 @@ template <> half from_double<half>(double v) { return THC_float2half((float)v); 
 template <typename R> double real_to_double(R v) { return (double)v; }
 template <> double real_to_double<half>(half v) { return (double)THC_half2float(v); }
 
+// Makes device `d` current for a scope.
+struct DeviceGuard {
+  int prev;
+  bool changed;
+  explicit DeviceGuard(int d) : prev(0), changed(false) {
+    THCudaCheck(cudaGetDevice(&prev));
+    if (d >= 0 && d != prev) { THCudaCheck(cudaSetDevice(d)); changed = true; }
+  }
+  ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
+};
+
 // ---- storage -------------------------------------------------------------------------
 template <typename R> StorageT<R> *storage_new(THCState *state, ptrdiff_t size) {
   THArgCheck(size >= 0, 2, "invalid size");
@@ -525,7 +536,12 @@ template <typename R> void storage_free(THCState *, StorageT<R> *s) {
   if (!s) return;
   if (!(s->flag & TH_STORAGE_REFCOUNTED)) return;
   if (__sync_sub_and_fetch(&s->refcount, 1) > 0) return;
-  if ((s->flag & TH_STORAGE_FREEMEM) && s->data) s->allocator->free(s->allocatorContext, s->data);
+  if ((s->flag & TH_STORAGE_FREEMEM) && s->data) {
+    // with the storage's own device current, the block goes back in the order of THAT device's
+    // current stream, whatever device the caller is working on
+    DeviceGuard g(s->device);
+    s->allocator->free(s->allocatorContext, s->data);
+  }
   if ((s->flag & TH_STORAGE_FREEMEM) == 0 && s->view) storage_free<R>(nullptr, s->view);
   free(s);
 }
@@ -534,6 +550,9 @@ template <typename R> void storage_resize(THCState *state, StorageT<R> *s, ptrdi
   THArgCheck(size >= 0, 2, "invalid size");
   if (!(s->flag & TH_STORAGE_RESIZABLE)) th_error("Trying to resize storage that is not resizable");
   if (size == s->size) return;
+  // a storage lives on one device: it is reallocated and its old block freed with that device current
+  DeviceGuard g(s->data ? s->device : -1);
+  if (!s->data) s->device = current_device();
   R *nd = nullptr;
   if (size > 0) {
     cudaError_t e = s->allocator->malloc(s->allocatorContext, (void **)&nd, (size_t)size * sizeof(R), state_stream(state));
@@ -801,15 +820,6 @@ template <typename R> bool may_alias(const TensorT<R> *a, const TensorT<R> *b) {
 }
 
 // ---- copies, same device or across devices (THC_copyTensor, lib/THC/THCTensorCopy.cu:24-205) ----
-struct DeviceGuard {
-  int prev;
-  bool changed;
-  explicit DeviceGuard(int d) : prev(0), changed(false) {
-    THCudaCheck(cudaGetDevice(&prev));
-    if (d >= 0 && d != prev) { THCudaCheck(cudaSetDevice(d)); changed = true; }
-  }
-  ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
-};
 
 template <typename R> int tensor_device(const TensorT<R> *t, int fallback) {
   return (t->storage && t->storage->data) ? t->storage->device : fallback;

@@ -361,7 +361,9 @@ THCB200_API int thcb200_masked_fill(thcb200_ctx *ctx, const thcb200_tensor *t,
  * lib/THC/generic/THCTensorMasked.cu:52,128).  The per-tile positions computed on the way stay
  * in the context; a following masked_copy / masked_select on the same mask view and stream may
  * reuse them by passing THCB200_FLAG_MASK_COUNTED, which asserts that the mask's contents have
- * not changed in between. */
+ * not changed in between.  On such a reuse the count is known on the host, and a packed side
+ * (the output of masked_select / mask_coords, the source of masked_copy) that is too short for it
+ * is refused with THCB200_ERR_SIZE; without the reuse sizing that operand is the caller's job. */
 #define THCB200_FLAG_MASK_COUNTED 2
 THCB200_API int thcb200_masked_count(thcb200_ctx *ctx, const thcb200_tensor *mask_u8,
                          int64_t *count_host, void *stream);

@@ -232,3 +232,39 @@ def test_nonzero(state, kind):
     out = thc.Tensor.new(state, "Long")
     zero.call("nonzero", out, zero)
     assert out.sizes == [0, 2]
+
+
+@pytest.mark.parametrize("shift", [1, 3, 8, 16])
+def test_mask_coords_of_a_mask_that_starts_off_a_16_byte_boundary(state, shift):
+    """A narrowed ByteTensor is a dense mask whose first byte sits anywhere: the coordinates kernel must
+    read it byte by byte then (its 16-byte loads need an aligned base).  Also: an output too short for
+    the counted mask is refused instead of overrun."""
+    import ctypes as C
+    from cutorch_b200 import _lib
+    lib = _lib.load_library()
+    r = rng("coords-shift", shift)
+    n = 3 * 4096 + 123
+    base = (r.uniform(size=n + shift) < 0.3).astype(np.uint8)
+    dbase = to_device(state, base)
+    dmask = dbase.narrow(0, shift, n)
+    assert dmask.data_ptr() % 16 == shift % 16
+    mask = base[shift:]
+    want = np.argwhere(mask.reshape(-1) != 0).astype(np.int64) + 1
+    ctx, stream = C.c_void_p(state.context), C.c_void_p(state.stream)
+    P, vp = C.POINTER, C.c_void_p
+    lib.thcb200_masked_count.argtypes = [vp, P(_lib.TensorDesc), P(C.c_int64), vp]
+    lib.thcb200_mask_coords.argtypes = [vp, P(_lib.TensorDesc), P(_lib.TensorDesc), P(C.c_int64), C.c_int, vp, C.c_int]
+    dm = dmask.descriptor()
+    count = C.c_int64(-1)
+    _lib.check(lib.thcb200_masked_count(ctx, C.byref(dm), C.byref(count), stream))
+    assert count.value == want.shape[0]
+    out = thc.Tensor.new(state, "Long", want.shape[0], 1)
+    do = out.descriptor()
+    sizes = (C.c_int64 * 1)(n)
+    _lib.check(lib.thcb200_mask_coords(ctx, C.byref(do), C.byref(dm), sizes, 1, stream, 2))
+    assert_bit_equal(out.numpy(), want, f"coordinates of a mask shifted by {shift}")
+    short = thc.Tensor.new(state, "Long", want.shape[0] - 1, 1)
+    ds = short.descriptor()
+    _lib.check(lib.thcb200_masked_count(ctx, C.byref(dm), C.byref(count), stream))
+    rc = lib.thcb200_mask_coords(ctx, C.byref(ds), C.byref(dm), sizes, 1, stream, 2)
+    assert rc == -3, rc   # THCB200_ERR_SIZE
