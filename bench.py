@@ -176,10 +176,13 @@ def reference_main(args):
     rows = 32768  # bounded sample: 1/16 of the rows per step, 1 GiB per tensor (about 0.3 s of host work per step)
     steps, warmup = max(1, args.steps), max(0, args.warmup)
     gbs, dt, nthreads = run_cpu(rows, steps, warmup, None)
-    sample = f"{rows} of {ROWS_TOTAL} rows x {COLS} per step ({steps} steps), scaled by bytes"
+    sample = f"{rows} of {ROWS_TOTAL} rows x {COLS} per step ({steps} steps); GB/s is measured on the sample"
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": dt * 1e3 * (ROWS_TOTAL / rows), "higher_is_better": True, "scaling": "strong",
+        # measured: one step of the arm is one pass over the row sample; the full-size figure is a
+        # separate, extrapolated key
+        "warmup": warmup, "ms_per_step": dt * 1e3, "ms_per_step_full_size_extrapolated": dt * 1e3 * (ROWS_TOTAL / rows),
+        "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "c5: cmul, add 1, row max+argmax, sum-all on fp32 524288x8192 (row sample on the host)",
                    "impl_note": "TH CPU semantics restated in oracle/th_oracle.cpp (torch7's TH is not in the cutorch tree)"},
@@ -200,7 +203,7 @@ def ours_main(args):
     import torch
     import torch.distributed as dist
     from cutorch_b200 import thc, _lib
-    from cutorch_b200.shard import combine_partials, shard_rows
+    from cutorch_b200.shard import Comm, shard_rows
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -220,6 +223,10 @@ def ours_main(args):
     stream = torch.cuda.current_stream()
     state.set_stream(stream.cuda_stream, local)
     lib = _lib.load_library()
+    # N > 1: the exchange runs inside the C library (NCCL bound by libthcb200); torch.distributed only
+    # hands the NCCL id round and provides the barriers of the timing protocol
+    comm = Comm.from_process_group(state) if world > 1 else None
+    checks = multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream) if world > 1 else {}
 
     # synthetic inputs, generated on the device per shard from seed + rank
     g = torch.Generator(device=dev)
@@ -245,8 +252,12 @@ def ours_main(args):
         tz.cmul(tx, ty)
         tz.add(tz, 1.0)
         tv.max(ti, tz, 1, 1)
-        tz.sumall_to_device(partial.data_ptr())
-        combine_partials(partial, "sum")   # NCCL all-reduce of the 8-byte partials (no-op at N=1)
+        if comm is None:
+            tz.sumall_to_device(partial.data_ptr())
+        else:
+            # the finishing CTA leaves this rank's double in `partial`; ncclAllReduce runs on that slot,
+            # on the same stream, inside thcb200_sharded_reduce_all
+            comm.reduce_all(tz, partial.data_ptr(), "SUM")
 
     def barrier():
         if world > 1:
@@ -314,15 +325,20 @@ def ours_main(args):
     roofline = {"bound": "hbm", "kernel": "apply_contig_vec_kernel<MUL,float,2> (THCudaTensor_cmul)",
                 "achieved": dom["gbs"], "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": dom["gbs"] / peak, "frac_of_nominal_8000": dom["gbs"] / 8000.0,
-                # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture summarised in
-                # profiles/c5_rows16384_contig_vec_row_argmax_reduce_all.md (11.71 B/element on a 16384-row slice;
-                # traffic grows with the element count), scaled to the elements of one launch here
-                "traffic": int(CMUL_TRAFFIC_BYTES_PER_ELEM * n), "traffic_source": "ncu capture of a 16384-row slice, scaled by elements",
-                "per_kernel": {k: {"gbs": round(vv["gbs"], 1), "frac": round(vv["gbs"] / peak, 4), "avg_ms": round(vv["avg_ms"], 4)}
-                               for k, vv in kernels.items()}}
+                # dram__bytes_read + dram__bytes_write of this kernel from an ncu capture of a 16384-row
+                # slice (11.71 B/element; traffic grows with the element count), scaled to the elements
+                # of one launch here
+                "traffic": int(CMUL_TRAFFIC_BYTES_PER_ELEM * n), "traffic_source": "ncu capture of a 16384-row slice, scaled by elements"}
+    # flat scalar keys: per-kernel average duration and fraction of the peak for the four calls of a step
+    for key, name in (("cmul", "cmul contig_vec"), ("add", "add_scalar contig_vec (in place)"),
+                      ("max_dim1", "max+argmax dim1 row_warp"), ("sumall", "sumall reduce_all")):
+        roofline[key + "_avg_ms"] = round(kernels[name]["avg_ms"], 4)
+        roofline[key + "_frac"] = round(kernels[name]["gbs"] / peak, 4)
+    roofline["kernels_sum_ms"] = round(sum(k["avg_ms"] for k in kernels.values()), 4)
+    roofline["step_minus_kernels_us"] = round((ms_per_step - sum(k["avg_ms"] for k in kernels.values())) * 1e3, 2)
 
     # end to end: host (pinned) inputs -> device -> THC calls -> results back on the host
-    e2e = None if args.no_e2e else run_e2e(args, torch, thc, state, stream, dev, rows, world, rank)
+    e2e = None if args.no_e2e else run_e2e(args, torch, thc, state, stream, dev, rows, world, rank, comm, local)
 
     extra = {}
     cpu_baseline = None
@@ -334,7 +350,20 @@ def ours_main(args):
                         "one_thread": one_thread_baseline(), "host": host_description()}
     if rank == 0 and world == 1 and args.configs:
         from bench_configs import run_small_configs
-        extra["per_config"] = run_small_configs(torch, thc, state, stream, dev, peak)
+        per_config = run_small_configs(torch, thc, state, stream, dev, peak)
+        extra["per_config"] = per_config
+        # the c1-c4 figures as flat scalar keys of `roofline`: fraction of the measured peak of the
+        # flushed single call, its median, and the per-call time of a back-to-back train over rotating buffers
+        for name, r in per_config.items():
+            if not name.startswith(("c1_", "c2_", "c3_", "c4_")):
+                continue
+            short = name.replace("_f32_16M", "").replace("_f32_transposed_strided", "").replace("_128M", "").replace("_f16", "")
+            roofline[short + "_frac"] = r["frac"]
+            roofline[short + "_us"] = r["median_us"]
+            if "back_to_back_us" in r:
+                roofline[short + "_b2b_us"] = r["back_to_back_us"]
+                roofline[short + "_b2b_frac"] = r["back_to_back_frac"]
+    extra.update(checks)
 
     if rank == 0:
         line = {
@@ -345,20 +374,162 @@ def ours_main(args):
                                    f"{ROWS_TOTAL}x{COLS} split by rows over {world} GPU(s)",
                        "rows_per_gpu": rows, "cols": COLS, "bytes_per_step": total_bytes,
                        "l2": "inputs (16 GiB per tensor at N=1) are far larger than the 126 MB L2; no flush needed",
+                       "collective": ("none (one GPU)" if comm is None else
+                                      "ncclAllReduce(sum, 1 x f64) on the compute stream, issued by thcb200_sharded_reduce_all "
+                                      f"on the slot the finishing CTA wrote (NCCL {comm.nccl_version()} bound by libthcb200.so)"),
                        "elements_per_s": rows * COLS * world / (ms_per_step * 1e-3)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks, "checksum": total_sum,
         }
         line.update(extra)
         print(json.dumps(line))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.destroy_process_group()
     return 0
 
 
-def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
+def multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream):
+    """Run before the timed region when there are two or more ranks (a one-GPU box cannot):
+    copies between two GPUs of one process, and reductions along the SHARDED dim through the C
+    library's communicator, each compared bit for bit with the unsharded result; then the time of the
+    two sharded-dim reductions at the benchmark's shape."""
+    import torch.distributed as dist
+    out = {}
+    T = thc.Tensor
+
+    def wrap(t, kind):
+        w = T.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
+        w._owner = t
+        return w
+
+    # ---- copies from cuda:1 into cuda:0, driven by rank 0 (THCTensor_(copy) across devices) ----
+    if rank == 0:
+        try:
+            verdict = "ok"
+            if torch.cuda.device_count() < 2:
+                verdict = "skipped: one visible device"
+            else:
+                r = np.random.default_rng(77)
+                a = r.standard_normal((1024, 1536)).astype(np.float32)
+                h = r.standard_normal((777, 333)).astype(np.float16)
+                other = torch.device("cuda", 1 if dev.index == 0 else 0)
+                src = torch.from_numpy(a).to(other)
+                src_t = torch.from_numpy(np.ascontiguousarray(a.T)).to(other).t()     # a transposed view on the other GPU
+                src_h = torch.from_numpy(h).to(other)
+                torch.cuda.synchronize(other)
+                for label, s_, kind, want in (("contiguous f32", src, "Float", a), ("transposed source f32", src_t, "Float", a),
+                                              ("f16 -> f32", src_h, "Half", h.astype(np.float32))):
+                    dst = torch.zeros(want.shape, dtype=torch.float32, device=dev)
+                    td, ts = wrap(dst, "Float"), wrap(s_, kind)
+                    if kind == "Float":
+                        td.copy(ts)
+                    else:
+                        td.copy_from(ts)
+                    torch.cuda.synchronize(dev)
+                    got = dst.cpu().numpy()
+                    if not np.array_equal(got.view(np.uint32), want.view(np.uint32)):
+                        bad = np.argwhere(got != want)
+                        verdict = f"{label}: {len(bad)} elements differ, first at {tuple(bad[0])}"
+                        break
+            out["xdev_check"] = verdict
+        except Exception as e:   # the check reports, it does not end the benchmark
+            out["xdev_check"] = f"error: {e}"
+    dist.barrier()
+
+    # ---- reductions along the sharded dim: a replicated-seed matrix split by rows ----
+    try:
+        rows_total, cols = 4096 + 3 * world, 2048
+        r = np.random.default_rng(4242)
+        full = (r.integers(-1000, 1001, (rows_total, cols)) / 8).astype(np.float32)   # exact sums, many ties
+        full[rows_total // 2, 5] = np.nan
+        from cutorch_b200.shard import shard_rows
+        start, cnt = shard_rows(rows_total, world, rank)
+        mine = torch.from_numpy(full[start:start + cnt]).to(dev)
+        tm = wrap(mine, "Float")
+        osum = torch.empty(1, cols, dtype=torch.float32, device=dev)
+        omax = torch.empty(1, cols, dtype=torch.float32, device=dev)
+        oidx = torch.empty(1, cols, dtype=torch.int64, device=dev)
+        slot = torch.zeros(1, dtype=torch.float64, device=dev)
+        comm.reduce_dim(wrap(osum, "Float"), tm, 0, "SUM")
+        comm.reduce_dim_index(wrap(omax, "Float"), wrap(oidx, "Long"), tm, 0, start, "MAX")
+        comm.reduce_all(tm, slot.data_ptr(), "MAX")     # a floating max over all ranks: the gather + fold path
+        torch.cuda.synchronize(dev)
+        verdict = "ok"
+        if rank == 0:
+            whole = torch.from_numpy(full).to(dev)
+            tw = wrap(whole, "Float")
+            wsum = torch.empty(1, cols, dtype=torch.float32, device=dev)
+            wmax = torch.empty(1, cols, dtype=torch.float32, device=dev)
+            widx = torch.empty(1, cols, dtype=torch.int64, device=dev)
+            wslot = torch.zeros(1, dtype=torch.float64, device=dev)
+            wrap(wsum, "Float").sum(tw, 0, 1)
+            wrap(wmax, "Float").max(wrap(widx, "Long"), tw, 0, 1)
+            lib = state.lib
+            import ctypes as C
+            from cutorch_b200 import _lib
+            d = tw.descriptor()
+            _lib.check(lib.thcb200_reduce_all(C.c_void_p(state.context), _lib.RED["MAX"], 0, _lib.scalar(0), C.byref(d),
+                                              C.c_void_p(wslot.data_ptr()), C.c_void_p(state.stream)))
+            torch.cuda.synchronize(dev)
+            eq = lambda x, y: np.array_equal(x.cpu().numpy().view(np.uint8), y.cpu().numpy().view(np.uint8))
+            if not eq(osum, wsum):
+                verdict = "sum along the sharded dim differs from the unsharded call"
+            elif not eq(omax, wmax) or not eq(oidx, widx):
+                verdict = "max / positions along the sharded dim differ from the unsharded call"
+            elif not eq(slot, wslot):
+                verdict = "sharded full max differs from the unsharded call"
+        out["sharded_check"] = verdict
+    except Exception as e:
+        out["sharded_check"] = f"error: {e}"
+    dist.barrier()
+
+    # ---- the same two calls at the benchmark's shape: this rank's rows of 524288 x 8192 ----
+    try:
+        from cutorch_b200.shard import shard_rows
+        start, cnt = shard_rows(ROWS_TOTAL, world, rank)
+        big = torch.empty(cnt, COLS, dtype=torch.float32, device=dev).normal_()
+        tb = wrap(big, "Float")
+        osum = torch.empty(1, COLS, dtype=torch.float32, device=dev)
+        oidx = torch.empty(1, COLS, dtype=torch.int64, device=dev)
+        tsum, tidx = wrap(osum, "Float"), wrap(oidx, "Long")
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(5):
+                fn()
+            b.record(stream)
+            torch.cuda.synchronize(dev)
+            t = torch.tensor([a.elapsed_time(b) / 5], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return round(float(t.item()), 4)
+
+        out["sharded_sum_dim0_ms"] = timed(lambda: comm.reduce_dim(tsum, tb, 0, "SUM"))
+        out["sharded_sum_dim0_local_only_ms"] = timed(lambda: tsum.sum(tb, 0, 1))
+        out["sharded_max_dim0_ms"] = timed(lambda: comm.reduce_dim_index(tsum, tidx, tb, 0, start, "MAX"))
+        out["sharded_max_dim0_local_only_ms"] = timed(lambda: tsum.max(tidx, tb, 0, 1))
+        out["sharded_note"] = ("dim 0 of the row-sharded 524288 x 8192 tensor: local column reduction of this rank's rows, then "
+                               "ncclAllReduce of 8192 floats (sum) or ncclAllGather of 8192 (value, position) pairs + combine (max)")
+        del big
+        torch.cuda.empty_cache()
+    except Exception as e:
+        out["sharded_timing_error"] = str(e)
+    dist.barrier()
+    return out
+
+
+def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank, comm, local):
     """Same step with HOST inputs: per row chunk, pinned host -> device copies, the four THC
-    calls, and the row results plus the sum copied back, all inside the timed region."""
+    calls, and the row results plus the sum copied back, all inside the timed region.  The bytes
+    cross through the library's own CPU <-> GPU tensor copies (THCudaTensor_copyAsyncCPU and
+    TH<Type>Tensor_copyAsyncCuda, the calls under cutorch's :cuda() / :float()), issued on a copy
+    stream that is made current for them; torch only allocates the buffers and records the events."""
     import torch.distributed as dist
     chunk = min(8192, rows)
     nchunks = rows // chunk
@@ -388,6 +559,10 @@ def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
     hv = torch.empty(rows, 1, dtype=torch.float32, pin_memory=True)
     hi = torch.empty(rows, 1, dtype=torch.int64, pin_memory=True)
     hs = torch.empty(1, dtype=torch.float64, pin_memory=True)
+    # the pinned arrays as TH CPU tensors (one per chunk of the inputs)
+    cx = [thc.CpuTensor(hx[r0:r0 + chunk].numpy()) for r0 in range(0, host_rows, chunk)]
+    cy = [thc.CpuTensor(hy[r0:r0 + chunk].numpy()) for r0 in range(0, host_rows, chunk)]
+    chv, chi, chs = thc.CpuTensor(hv.numpy()), thc.CpuTensor(hi.numpy()), thc.CpuTensor(hs.numpy())
     nslots = 2
     dx = [torch.empty(chunk, COLS, dtype=torch.float32, device=dev) for _ in range(nslots)]
     dy = [torch.empty(chunk, COLS, dtype=torch.float32, device=dev) for _ in range(nslots)]
@@ -400,43 +575,46 @@ def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
     tx = [W(t, "Float", (chunk, COLS)) for t in dx]
     ty = [W(t, "Float", (chunk, COLS)) for t in dy]
     tz = [W(t, "Float", (chunk, COLS)) for t in dz]
+    tvs = [W(dv[c * chunk:], "Float", (chunk, 1)) for c in range(nchunks)]
+    tis = [W(di[c * chunk:], "Long", (chunk, 1)) for c in range(nchunks)]
+    tdv, tdi, ttotal = W(dv, "Float", (rows, 1)), W(di, "Long", (rows, 1)), W(total, "Double", (1,))
     tparts = W(parts, "Double", (nchunks,))
     copy_stream = torch.cuda.Stream(device=dev)
     ready = [torch.cuda.Event() for _ in range(nslots)]
     freed = [torch.cuda.Event() for _ in range(nslots)]
+    nhost = len(cx)
 
     def e2e_step():
         for c in range(nchunks):
             s = c % nslots
-            h0 = (c * chunk) % host_rows
-            with torch.cuda.stream(copy_stream):
-                if c >= nslots:
-                    copy_stream.wait_event(freed[s])
-                dx[s].copy_(hx[h0:h0 + chunk], non_blocking=True)
-                dy[s].copy_(hy[h0:h0 + chunk], non_blocking=True)
-                ready[s].record(copy_stream)
+            if c >= nslots:
+                copy_stream.wait_event(freed[s])
+            # host -> device through the library, in the order of the copy stream
+            state.set_stream(copy_stream.cuda_stream, local)
+            tx[s].copy_async_from_cpu(cx[c % nhost])
+            ty[s].copy_async_from_cpu(cy[c % nhost])
+            state.set_stream(stream.cuda_stream, local)
+            ready[s].record(copy_stream)
             stream.wait_event(ready[s])
             tz[s].cmul(tx[s], ty[s])
             tz[s].add(tz[s], 1.0)
-            tv = thc.Tensor.wrap(state, "Float", dv[c * chunk:].data_ptr(), (chunk, 1))
-            ti = thc.Tensor.wrap(state, "Long", di[c * chunk:].data_ptr(), (chunk, 1))
-            tv.max(ti, tz[s], 1, 1)
+            tvs[c].max(tis[c], tz[s], 1, 1)
             tz[s].sumall_to_device(parts[c:].data_ptr())
             freed[s].record(stream)
-            tv.free()
-            ti.free()
-        tparts.sumall_to_device(total.data_ptr())
-        if world > 1:
-            dist.all_reduce(total)
-        hv.copy_(dv, non_blocking=True)
-        hi.copy_(di, non_blocking=True)
-        hs.copy_(total, non_blocking=True)
+        if comm is None:
+            tparts.sumall_to_device(total.data_ptr())
+        else:
+            comm.reduce_all(tparts, total.data_ptr(), "SUM")
+        # device -> host through the library, in the order of the compute stream
+        tdv.copy_async_to_cpu(chv)
+        tdi.copy_async_to_cpu(chi)
+        ttotal.copy_async_to_cpu(chs)
 
     e2e_step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    steps = max(1, min(args.steps, 3))
+    steps = max(5, min(args.steps, 8))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record(stream)
@@ -453,6 +631,9 @@ def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank):
     d2h = rows * 12 + 8
     return {"value": step_bytes(rows) * world / (ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
             "d2h_bytes_per_step": d2h * world, "ms_per_step": ms, "steps": steps,
+            "bound": f"pcie h2d, {h2d / (ms * 1e-3) / 1e9:.1f} GB/s per GPU: the step moves {h2d >> 20} MiB per GPU from host memory, "
+                     "which takes longer than the kernels; the host link of the box, not the library, sets this number",
+            "copies": "THCudaTensor_copyAsyncCPU / TH<Type>Tensor_copyAsyncCuda (the library's CPU <-> GPU tensor copies)",
             "host_rows_resident": host_rows, "note": "pinned host chunks of 8192 rows, double-buffered H2D overlapped with the kernels"
             + ("" if host_rows == rows else f"; host array of {host_rows} rows cycled (box cannot pin {need >> 30} GiB)")}
 

@@ -1,24 +1,28 @@
 """Device-time measurements of the baseline configs c1-c4 (full size, one GPU), used by bench.py.
 
-Each entry is one THC call timed with CUDA events on the launching stream; a 512 MiB memset runs
-between timed iterations so that tensors that would fit the 126 MB L2 are read from HBM.
-The flush writes 512 MiB and then reads 256 MiB so no dirty lines are left.
+Each entry is one THC call timed with CUDA events on the launching stream; a read of a 512 MiB
+buffer runs between timed iterations so that tensors that would fit the 126 MB L2 are read from
+HBM (a read, not a memset: dirty lines of a written flush buffer would be written back during
+the timed call).
 `python bench.py --only c2,c3` runs a subset (that is also the small case the ncu captures use).
 """
 from __future__ import annotations
 
 
 def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_override=None):
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
-
     def W(t, kind):
         w = thc.Tensor.wrap(state, kind, t.data_ptr(), tuple(t.shape), tuple(t.stride()))
         w._owner = t   # the wrapper holds a raw pointer: keep the torch tensor alive with it
         return w
 
-    clean = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    # The L2 is flushed by READING a buffer four times its size.  Writing one instead (a memset) leaves
+    # up to 126 MB of dirty lines behind, and the timed call then pays for their write-back: measured
+    # here, a 1 GiB fp64 sum-all read 175 us after a 512 MiB memset followed by a 256 MiB read, 156 us
+    # after a read-only flush and 151 us in a back-to-back train.
+    flush = torch.zeros(512 << 20, dtype=torch.uint8, device=dev)
     res_flush = torch.zeros(1, dtype=torch.int64, device=dev)
-    tclean = W(clean, "Byte")
+    tflush = W(flush, "Byte")
+    torch.cuda.synchronize()
 
     def timed(fn, nbytes, reps=10, rot=None):
         reps = reps_override or reps
@@ -26,10 +30,8 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         for _ in range(3):
             fn()
         for _ in range(reps):
-            # write 512 MiB (evicts the operands), then read 256 MiB so that the lines left in L2 are
-            # clean: otherwise the timed kernel would also pay for writing back the flush's dirty lines
-            flush.zero_()
-            tclean.sumall_to_device(res_flush.data_ptr())
+            # read 512 MiB (four times the L2) so that the operands of the timed call come from HBM
+            tflush.sumall_to_device(res_flush.data_ptr())
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
             fn()
@@ -47,7 +49,7 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
             # the cost of an event pair and an idle GPU around each launch.
             for f in rot:
                 f()
-            rounds = 6
+            rounds = max(6, 24 // len(rot))
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             a.record(stream)
@@ -128,10 +130,12 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         i1 = torch.empty(32768, 1, dtype=torch.int64, device=dev)
         i0 = torch.empty(1, 8192, dtype=torch.int64, device=dev)
         tr1, tr0, ti1, ti0 = W(r1, "Float"), W(r0, "Float"), W(i1, "Long"), W(i0, "Long")
-        out["c3_sum_dim1"] = timed(lambda: tr1.sum(tm, 1, 1), 4 * n + 4 * 32768)
-        out["c3_sum_dim0"] = timed(lambda: tr0.sum(tm, 0, 1), 4 * n + 4 * 8192)
-        out["c3_max_dim1"] = timed(lambda: tr1.max(ti1, tm, 1, 1), 4 * n + 12 * 32768)
-        out["c3_max_dim0"] = timed(lambda: tr0.max(ti0, tm, 0, 1), 4 * n + 12 * 8192)
+        tm2 = W(m.clone(), "Float")    # second buffer set of the back-to-back trains (2 GiB together)
+        both = (tm, tm2)
+        out["c3_sum_dim1"] = timed(lambda: tr1.sum(tm, 1, 1), 4 * n + 4 * 32768, rot=[(lambda t=t: tr1.sum(t, 1, 1)) for t in both])
+        out["c3_sum_dim0"] = timed(lambda: tr0.sum(tm, 0, 1), 4 * n + 4 * 8192, rot=[(lambda t=t: tr0.sum(t, 0, 1)) for t in both])
+        out["c3_max_dim1"] = timed(lambda: tr1.max(ti1, tm, 1, 1), 4 * n + 12 * 32768, rot=[(lambda t=t: tr1.max(ti1, t, 1, 1)) for t in both])
+        out["c3_max_dim0"] = timed(lambda: tr0.max(ti0, tm, 0, 1), 4 * n + 12 * 8192, rot=[(lambda t=t: tr0.max(ti0, t, 0, 1)) for t in both])
 
     def c4():
         h = (torch.empty(8192, 8192, device=dev).normal_(0, 2, generator=g)).half()
@@ -154,11 +158,14 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         c = torch.empty_like(a)
         ta, tb, tc = W(a, "Int"), W(b, "Int"), W(c, "Int")
         out["c4_cmul_i32_128M"] = timed(lambda: tc.cmul(ta, tb), 12 * n, reps=5)
-        out["c4_sumall_i32_128M"] = timed(lambda: tc.sumall_to_device(res.data_ptr()), 4 * n, reps=5)
-        del a, b, c
+        # the three 512 MiB tensors serve as the rotating sets of the back-to-back train (1.5 GiB together)
+        out["c4_sumall_i32_128M"] = timed(lambda: tc.sumall_to_device(res.data_ptr()), 4 * n, reps=5,
+                                          rot=[(lambda t=t: t.sumall_to_device(res.data_ptr())) for t in (tc, ta, tb)])
+        del a, b, c, ta, tb, tc
         d = torch.empty(n, dtype=torch.float64, device=dev).uniform_(0, 1, generator=g)
-        td = W(d, "Double")
-        out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5)
+        td, td2 = W(d, "Double"), W(d.clone(), "Double")
+        out["c4_sumall_f64_128M"] = timed(lambda: td.sumall_to_device(res.data_ptr()), 8 * n, reps=5,
+                                          rot=[(lambda t=t: t.sumall_to_device(res.data_ptr())) for t in (td, td2)])
 
     def nxt():
         """The callers either side of the path (comparisons into bytes, masks, scans, indexed moves,
@@ -326,9 +333,34 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         out["gpu_f16_transposed_to_host_f32_dense"] = wall(lambda: t16t.copy_to_cpu(c32), 4 * n)
         out["host_f32_transposed_view_to_gpu_dense"] = wall(lambda: t32.copy_from_cpu(ct), 4 * n, reps=1)
 
-    for name, fn in (("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4), ("next", nxt), ("generic", generic), ("xdev", xdev),
-                     ("host", host)):
-        if name in ("xdev", "host") and (only is None or name not in only):
+    def template():
+        """The C++ template face (include/THC/THCApply.cuh, THCReduce.cuh) with user functors, through
+        the test library built from tests/csrc/user_apply_test.cu: a scale functor on a contiguous and
+        on a transposed 2^27-element fp32 tensor, and a user sum along each dim."""
+        import ctypes as C
+        from cutorch_b200.build import USERTEST_LIB
+        if not USERTEST_LIB.exists():
+            out["template"] = {"skipped": "the user-functor test library is not built"}
+            return
+        ulib = C.CDLL(str(USERTEST_LIB))
+        ulib.usertest_scale.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float]
+        ulib.usertest_scale.restype = C.c_int
+        n = 1 << 27
+        x = torch.empty(n, device=dev).normal_(generator=g)
+        y = torch.empty(n, device=dev)
+        tx, ty = W(x, "Float"), W(y, "Float")
+        out["b_template_apply2_scale_f32_contiguous_128M"] = timed(
+            lambda: ulib.usertest_scale(state.ptr, ty.ptr, tx.ptr, 1.5), 8 * n, reps=5)
+        xt = x.view(8192, 16384).t()
+        yt = y.view(16384, 8192)
+        txt, tyt = W(xt, "Float"), W(yt, "Float")
+        out["b_template_apply2_scale_f32_transposed_source_16384x8192"] = timed(
+            lambda: ulib.usertest_scale(state.ptr, tyt.ptr, txt.ptr, 1.5), 8 * n, reps=5)
+
+    # c1-c4 come last so that they are the end of the printed line
+    for name, fn in (("next", nxt), ("generic", generic), ("xdev", xdev), ("host", host), ("template", template),
+                     ("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4)):
+        if name in ("xdev", "host", "template") and (only is None or name not in only):
             continue
         if only is None or name in only:
             fn()

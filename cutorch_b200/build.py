@@ -72,6 +72,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
                     print(f"--- {name}\n{log}", file=sys.stderr)
     if todo or not LIB.exists():
         cmd = [nvcc, "-shared", "-cudart", "shared", "-o", str(LIB), *map(str, objs),
+               "-ldl",   # NCCL is bound with dlopen when a communicator is first asked for
                "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

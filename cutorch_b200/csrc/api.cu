@@ -48,6 +48,7 @@ template <> struct ElemOf<8> { using type = uint64_t; };
 
 template <int B, bool GATHER>
 __global__ void __launch_bounds__(256) deep_copy_kernel(void *dense_raw, void *strided_raw, DeepView v, uint64_t n) {
+  pdl_prologue();
   using E = typename ElemOf<B>::type;
   E *dense = reinterpret_cast<E *>(dense_raw);
   E *strided = reinterpret_cast<E *>(strided_raw);
@@ -71,8 +72,8 @@ int deep_copy(bool gather, void *dense, const HostView &v, size_t esz, cudaStrea
   uint64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
 #define THCB_DC(B)                                                                                   \
-  if (gather) deep_copy_kernel<B, true><<<(unsigned)blocks, 256, 0, st>>>(dense, v.data, dv, n);     \
-  else deep_copy_kernel<B, false><<<(unsigned)blocks, 256, 0, st>>>(dense, v.data, dv, n);
+  if (gather) launch_pdl(deep_copy_kernel<B, true>, (unsigned)blocks, 256, 0, st, dense, v.data, dv, n);     \
+  else launch_pdl(deep_copy_kernel<B, false>, (unsigned)blocks, 256, 0, st, dense, v.data, dv, n);
   switch (esz) {
     case 1: THCB_DC(1) break;
     case 2: THCB_DC(2) break;

@@ -37,6 +37,7 @@ template <int OP, typename T, int NIN, int VB>
 __global__ void __launch_bounds__(kApplyThreads)
 apply_contig_vec_kernel(T *out, const T *a, const T *b, const T *c, uint64_t n,
                         OpParams<T> p) {
+  pdl_prologue();
   constexpr int V = VB / sizeof(T);                       // elements per vector
   constexpr int U = contig_unroll<VB>();
   constexpr uint64_t kTile = contig_tile<T, VB>();
@@ -121,6 +122,7 @@ struct RowsPlan {
 template <int OP, typename T, int NIN, int V>
 __global__ void __launch_bounds__(kApplyThreads)
 apply_rows_kernel(T *out, const T *a, const T *b, const T *c, RowsPlan pl, OpParams<T> p) {
+  pdl_prologue();
   constexpr int U = kRowsUnroll;
   constexpr int UC = V == 1 ? kRowsScalarCols : 1;
   struct alignas(V * sizeof(T)) Unit { T v[V]; };
@@ -183,6 +185,7 @@ __global__ void __launch_bounds__(kApplyThreads)
 apply_generic_kernel(T *out, StridedView<IndexT> vo, const T *a, StridedView<IndexT> va,
                      const T *b, StridedView<IndexT> vb, const T *c, StridedView<IndexT> vc,
                      IndexT n, OpParams<T> p) {
+  pdl_prologue();
   constexpr int U = kApplyUnroll;
   const IndexT tile = (IndexT)kApplyThreads * U;
   // grid is sized so that blockIdx.x * tile never wraps; one tile per CTA
@@ -266,6 +269,7 @@ template <typename T> constexpr size_t tiled_smem_bytes(int slots) {
 template <int OP, typename T, int NIN>
 __global__ void __launch_bounds__(kTiledThreads)
 apply_tiled_kernel(T *out, const T *a, const T *b, const T *c, TiledPlan P, OpParams<T> p, int slots) {
+  pdl_prologue();
   constexpr int TC = tiled_tc<T>();
   constexpr int LD = TC + tiled_pad<T>();    // padded row length in shared memory
   constexpr int NW = kTiledThreads / 32;

@@ -42,10 +42,10 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       if (blocks >= (1ULL << 31)) { set_error("pointwise: tensor too large"); return THCB200_ERR_DIMS; }
       if (wide) {
         set_plan_name("contig_vec");
-        apply_contig_vec_kernel<OP, T, NIN, 32><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, n, p);
+        launch_pdl(apply_contig_vec_kernel<OP, T, NIN, 32>, (unsigned)blocks, kApplyThreads, 0, st, out, a, b, c, n, p);
       } else {
         set_plan_name("contig_vec16");
-        apply_contig_vec_kernel<OP, T, NIN, 16><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, n, p);
+        launch_pdl(apply_contig_vec_kernel<OP, T, NIN, 16>, (unsigned)blocks, kApplyThreads, 0, st, out, a, b, c, n, p);
       }
       break;
     }
@@ -62,7 +62,7 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
         smem_set_for_device = ctx->device;
       }
       set_plan_name("tiled");
-      apply_tiled_kernel<OP, T, NIN><<<(unsigned)blocks, kTiledThreads, smem, st>>>(out, a, b, c, t, p, plan.tiled_slots);
+      launch_pdl(apply_tiled_kernel<OP, T, NIN>, (unsigned)blocks, kTiledThreads, smem, st, out, a, b, c, t, p, plan.tiled_slots);
       break;
     }
     case kApplyRows: {
@@ -71,10 +71,10 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       const uint64_t blocks = (uint64_t)r.tiles_c * (((uint64_t)r.R + rows_per_cta - 1) / rows_per_cta);
       if (r.vec) {
         set_plan_name("rows");
-        apply_rows_kernel<OP, T, NIN, 16 / (int)sizeof(T)><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+        launch_pdl(apply_rows_kernel<OP, T, NIN, 16 / (int)sizeof(T)>, (unsigned)blocks, kApplyThreads, 0, st, out, a, b, c, r, p);
       } else {
         set_plan_name("rows_scalar");
-        apply_rows_kernel<OP, T, NIN, 1><<<(unsigned)blocks, kApplyThreads, 0, st>>>(out, a, b, c, r, p);
+        launch_pdl(apply_rows_kernel<OP, T, NIN, 1>, (unsigned)blocks, kApplyThreads, 0, st, out, a, b, c, r, p);
       }
       break;
     }
@@ -84,12 +84,12 @@ int launch_apply(thcb200_ctx *ctx, const ApplyPlan &plan, char *const data[4], O
       if (blocks >= (1ULL << 31)) { set_error("pointwise: tensor too large"); return THCB200_ERR_DIMS; }
       if (!plan.index64) {
         set_plan_name("generic32");
-        apply_generic_kernel<OP, T, NIN, uint32_t><<<(unsigned)blocks, kApplyThreads, 0, st>>>(
+        launch_pdl(apply_generic_kernel<OP, T, NIN, uint32_t>, (unsigned)blocks, kApplyThreads, 0, st, 
             out, to_strided_view<uint32_t>(plan, 0), a, to_strided_view<uint32_t>(plan, 1), b,
             to_strided_view<uint32_t>(plan, 2), c, to_strided_view<uint32_t>(plan, 3), (uint32_t)n, p);
       } else {
         set_plan_name("generic64");
-        apply_generic_kernel<OP, T, NIN, uint64_t><<<(unsigned)blocks, kApplyThreads, 0, st>>>(
+        launch_pdl(apply_generic_kernel<OP, T, NIN, uint64_t>, (unsigned)blocks, kApplyThreads, 0, st, 
             out, to_strided_view<uint64_t>(plan, 0), a, to_strided_view<uint64_t>(plan, 1), b,
             to_strided_view<uint64_t>(plan, 2), c, to_strided_view<uint64_t>(plan, 3), (uint64_t)n, p);
       }

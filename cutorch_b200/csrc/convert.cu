@@ -21,6 +21,7 @@ template <typename TO, typename TI> __device__ __forceinline__ TO convert_elem(T
 template <typename TO, typename TI, typename IndexT>
 __global__ void __launch_bounds__(kApplyThreads)
 convert_kernel(TO *out, StridedView<IndexT> vo, const TI *in, StridedView<IndexT> vi, IndexT n) {
+  pdl_prologue();
   constexpr int U = kApplyUnroll;
   const IndexT base = (IndexT)blockIdx.x * (IndexT)(kApplyThreads * U) + threadIdx.x;
   TI x[U];
@@ -43,10 +44,10 @@ int launch_convert(const ApplyPlan &plan, void *out, const void *in, cudaStream_
   const uint64_t blocks = (n + tile - 1) / tile;
   if (blocks >= (1ULL << 31)) { set_error("copy: tensor too large"); return THCB200_ERR_DIMS; }
   if (!plan.index64) {
-    convert_kernel<TO, TI, uint32_t><<<(unsigned)blocks, kApplyThreads, 0, st>>>(
+    launch_pdl(convert_kernel<TO, TI, uint32_t>, (unsigned)blocks, kApplyThreads, 0, st, 
         (TO *)out, to_strided_view<uint32_t>(plan, 0), (const TI *)in, to_strided_view<uint32_t>(plan, 1), (uint32_t)n);
   } else {
-    convert_kernel<TO, TI, uint64_t><<<(unsigned)blocks, kApplyThreads, 0, st>>>(
+    launch_pdl(convert_kernel<TO, TI, uint64_t>, (unsigned)blocks, kApplyThreads, 0, st, 
         (TO *)out, to_strided_view<uint64_t>(plan, 0), (const TI *)in, to_strided_view<uint64_t>(plan, 1), (uint64_t)n);
   }
   count_launch();

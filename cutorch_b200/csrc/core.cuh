@@ -190,4 +190,37 @@ template <int VB> __device__ __forceinline__ void stv(void *p, const typename Ve
   if constexpr (VB == 16) st16(p, v); else st32(p, v);
 }
 
+// ---------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the library starts with pdl_prologue() and is
+// launched through launch_pdl(): the launch carries the programmatic-stream-serialization
+// attribute, so the GPU may make the kernel's CTAs resident while the previous kernel of the stream
+// is still running its tail, and the launch latency and ramp of one call overlap the end of the
+// one before.  griddepcontrol.launch_dependents lets the NEXT kernel's CTAs come in as soon as all of
+// this kernel's CTAs have started; griddepcontrol.wait returns once every earlier kernel of the
+// stream has completed and its writes are visible, so it stands before the first access to global
+// memory (arguments arrive with the launch and need no wait).  Under a plain launch both are no-ops.
+// THCB200_PDL=0 in the environment turns the attribute off (plain stream order).
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+bool pdl_enabled();   // plan.cu: reads THCB200_PDL once
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace thcb

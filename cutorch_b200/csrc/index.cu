@@ -72,6 +72,7 @@ template <> __device__ __forceinline__ void atomic_add_elem<int16_t>(int16_t *p,
 template <typename T, int MODE, bool REDIRECT_DST, typename IndexT>
 __global__ void __launch_bounds__(kIdxThreads)
 indexed_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, IndexT n, T value, unsigned int *errors) {
+  pdl_prologue();
   // Offsets are kept in IndexT: with 32-bit indices every tensor's largest offset fits 32 bits, so
   // sums taken modulo 2^32 are exact.
   const IndexT base = (IndexT)blockIdx.x * (IndexT)(kIdxThreads * kIdxUnroll) + threadIdx.x;
@@ -133,6 +134,7 @@ template <typename T> struct alignas(4 * sizeof(T)) Quad { T e[4]; };
 template <typename T, int MODE, bool REDIRECT_DST, typename IndexT>
 __global__ void __launch_bounds__(kIdxThreads)
 indexed_quad_kernel(T *dst, const T *src, const int64_t *index, IdxPlan<IndexT> p, IndexT nquads, T value, unsigned int *errors) {
+  pdl_prologue();
   const IndexT quad = (IndexT)blockIdx.x * (IndexT)kIdxThreads + threadIdx.x;
   if (quad >= nquads) return;
   const int L = p.nd - 1;
@@ -229,11 +231,11 @@ int launch_indexed(thcb200_ctx *ctx, const HostIdxPlan &h, void *dst, const void
       const uint64_t qblocks = (h.n + kIdxThreads - 1) / kIdxThreads;
       if (h.fits32) {
         set_plan_name("indexed_quad32");
-        indexed_quad_kernel<T, MODE, REDIRECT_DST, uint32_t><<<(unsigned)qblocks, kIdxThreads, 0, st>>>(
+        launch_pdl(indexed_quad_kernel<T, MODE, REDIRECT_DST, uint32_t>, (unsigned)qblocks, kIdxThreads, 0, st, 
             (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint32_t>(h), (uint32_t)h.n, value, errors);
       } else {
         set_plan_name("indexed_quad64");
-        indexed_quad_kernel<T, MODE, REDIRECT_DST, uint64_t><<<(unsigned)qblocks, kIdxThreads, 0, st>>>(
+        launch_pdl(indexed_quad_kernel<T, MODE, REDIRECT_DST, uint64_t>, (unsigned)qblocks, kIdxThreads, 0, st, 
             (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint64_t>(h), (uint64_t)h.n, value, errors);
       }
       count_launch();
@@ -243,11 +245,11 @@ int launch_indexed(thcb200_ctx *ctx, const HostIdxPlan &h, void *dst, const void
   }
   if (h.fits32 && h.n < (1ull << 32) - per_cta) {
     set_plan_name("indexed32");
-    indexed_kernel<T, MODE, REDIRECT_DST, uint32_t><<<(unsigned)blocks, kIdxThreads, 0, st>>>(
+    launch_pdl(indexed_kernel<T, MODE, REDIRECT_DST, uint32_t>, (unsigned)blocks, kIdxThreads, 0, st, 
         (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint32_t>(h), (uint32_t)h.n, value, errors);
   } else {
     set_plan_name("indexed64");
-    indexed_kernel<T, MODE, REDIRECT_DST, uint64_t><<<(unsigned)blocks, kIdxThreads, 0, st>>>(
+    launch_pdl(indexed_kernel<T, MODE, REDIRECT_DST, uint64_t>, (unsigned)blocks, kIdxThreads, 0, st, 
         (T *)dst, (const T *)src, (const int64_t *)index, to_device_plan<uint64_t>(h), (uint64_t)h.n, value, errors);
   }
   count_launch();

@@ -44,6 +44,7 @@ template <> struct Word<16> { using type = Bytes16; };
 template <typename T, bool HAS_B>
 __global__ void __launch_bounds__(kThreads)
 compare_contig_kernel(uint8_t *out, const T *a, const T *b, uint64_t n, int cmp, typename TypeTraits<T>::Math s) {
+  pdl_prologue();
   using M = typename TypeTraits<T>::Math;
   constexpr int EV = 16 / (int)sizeof(T);
   using OutW = typename Word<EV>::type;
@@ -85,6 +86,7 @@ template <typename T, bool HAS_B, typename IndexT>
 __global__ void __launch_bounds__(kThreads)
 compare_strided_kernel(uint8_t *out, StridedView<IndexT> vo, const T *a, StridedView<IndexT> va, const T *b,
                        StridedView<IndexT> vb, IndexT n, int cmp, typename TypeTraits<T>::Math s) {
+  pdl_prologue();
   using M = typename TypeTraits<T>::Math;
   const IndexT base = (IndexT)blockIdx.x * (IndexT)(kThreads * kUnroll) + threadIdx.x;
   T x[kUnroll], y[kUnroll];
@@ -114,6 +116,7 @@ compare_strided_kernel(uint8_t *out, StridedView<IndexT> vo, const T *a, Strided
 template <typename W>
 __global__ void __launch_bounds__(kThreads)
 masked_fill_contig_kernel(W *t, const uint8_t *mask, uint64_t n, W value) {
+  pdl_prologue();
   constexpr int EV = 16 / (int)sizeof(W);
   using MaskW = typename Word<EV>::type;
   const uint64_t nvec = n / EV;
@@ -151,6 +154,7 @@ masked_fill_contig_kernel(W *t, const uint8_t *mask, uint64_t n, W value) {
 template <typename W, typename IndexT>
 __global__ void __launch_bounds__(kThreads)
 masked_fill_strided_kernel(W *t, StridedView<IndexT> vt, const uint8_t *mask, StridedView<IndexT> vm, IndexT n, W value) {
+  pdl_prologue();
   const IndexT base = (IndexT)blockIdx.x * (IndexT)(kThreads * kUnroll) + threadIdx.x;
   uint8_t m[kUnroll];
 #pragma unroll
@@ -244,6 +248,7 @@ __device__ __forceinline__ uint32_t nonzero_bits16(const Bytes16 &v) {
 // bit arithmetic; a CTA takes kCountTiles consecutive tiles, all loads first.
 constexpr int kCountTiles = 4;
 __global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint64_t full_tiles, uint32_t *counts) {
+  pdl_prologue();
   __shared__ uint32_t wsum[kCountTiles][kThreads / 32];
   const uint64_t tile0 = (uint64_t)blockIdx.x * kCountTiles;
   Bytes16 v[kCountTiles];
@@ -278,6 +283,7 @@ __global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uin
 template <typename W, typename IndexT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
 masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const uint8_t *mask, const uint64_t *offsets) {
+  pdl_prologue();
   __shared__ uint32_t wsum[kThreads / 32];
   __shared__ W stage[kThreads / 32][kWarpSpan];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,6 +325,7 @@ masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const 
 template <typename IndexT>
 __global__ void __launch_bounds__(kThreads)
 mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, bool vec, uint32_t *counts, uint32_t tile0) {
+  pdl_prologue();
   __shared__ uint32_t wsum[kThreads / 32];
   const unsigned warp = threadIdx.x >> 5;
   const uint64_t tile = (uint64_t)blockIdx.x + tile0;
@@ -340,6 +347,7 @@ mask_tile_count_kernel(const uint8_t *mask, StridedView<IndexT> vm, uint64_t n, 
 // add its span up, then, once the 32 span totals are scanned, to write the offsets).
 __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts, uint64_t *offsets, uint64_t ntiles,
                                                          int64_t *total, int64_t *total_host) {
+  pdl_prologue();
   __shared__ uint64_t span_total[32];
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint64_t steps = (ntiles + 1023) / 1024;          // 32-tile steps per warp
@@ -397,6 +405,7 @@ __global__ void __launch_bounds__(1024) tile_scan_kernel(const uint32_t *counts,
 // 17 us issuing instructions for 32768 tiles; spread over 32 SMs the scan takes a few.
 __global__ void __launch_bounds__(1024) tile_scan_spread_kernel(const uint32_t *counts, uint64_t *offsets, uint32_t ntiles,
                                                                 int64_t *total, int64_t *total_host) {
+  pdl_prologue();
   __shared__ uint64_t before_part[32];
   __shared__ uint32_t warp_total[32];
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -439,6 +448,7 @@ template <typename W, typename IndexT, bool SELECT>
 __global__ void __launch_bounds__(kThreads)
 masked_move_kernel(W *strided, StridedView<IndexT> vs, W *packed, StridedView<IndexT> vp, const uint8_t *mask,
                    StridedView<IndexT> vm, uint64_t n, bool vec, const uint64_t *offsets, uint32_t tile0) {
+  pdl_prologue();
   __shared__ uint32_t wsum[kThreads / 32];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t tile = (uint64_t)blockIdx.x + tile0;
@@ -542,15 +552,15 @@ int compare_typed(int cmp, bool has_b, const HostView &vo, const HostView &va, c
     int rc = grid_for(n / EV, (uint64_t)kThreads * kUnroll, &grid, "compare");
     if (rc) return rc;
     set_plan_name("compare_contig_vec");
-    if (has_b) compare_contig_kernel<T, true><<<grid, kThreads, 0, st>>>(out, a, b, n, cmp, sv);
-    else compare_contig_kernel<T, false><<<grid, kThreads, 0, st>>>(out, a, b, n, cmp, sv);
+    if (has_b) launch_pdl(compare_contig_kernel<T, true>, grid, kThreads, 0, st, out, a, b, n, cmp, sv);
+    else launch_pdl(compare_contig_kernel<T, false>, grid, kThreads, 0, st, out, a, b, n, cmp, sv);
   } else {
     int rc = grid_for(n, (uint64_t)kThreads * kUnroll, &grid, "compare");
     if (rc) return rc;
     const bool i32 = co.fits32 && ca.fits32 && (!has_b || cb.fits32);
     set_plan_name(i32 ? "compare_strided32" : "compare_strided64");
 #define THCB_CMP_LAUNCH(HB, IDX)                                                                          \
-  compare_strided_kernel<T, HB, IDX><<<grid, kThreads, 0, st>>>(out, make_view<IDX>(co), a, make_view<IDX>(ca), b, \
+  launch_pdl(compare_strided_kernel<T, HB, IDX>, grid, kThreads, 0, st, out, make_view<IDX>(co), a, make_view<IDX>(ca), b, \
                                                                 make_view<IDX>(cb), (IDX)n, cmp, sv)
     if (i32) { if (has_b) THCB_CMP_LAUNCH(true, uint32_t); else THCB_CMP_LAUNCH(false, uint32_t); }
     else { if (has_b) THCB_CMP_LAUNCH(true, uint64_t); else THCB_CMP_LAUNCH(false, uint64_t); }
@@ -594,17 +604,17 @@ int masked_fill_sized(const HostView &vt, const HostView &vm, uint64_t bits, cud
     int rc = grid_for(n / EV, (uint64_t)kThreads * kUnroll, &grid, "masked_fill");
     if (rc) return rc;
     set_plan_name("masked_fill_contig_vec");
-    masked_fill_contig_kernel<W><<<grid, kThreads, 0, st>>>(t, mask, n, value);
+    launch_pdl(masked_fill_contig_kernel<W>, grid, kThreads, 0, st, t, mask, n, value);
   } else {
     int rc = grid_for(n, (uint64_t)kThreads * kUnroll, &grid, "masked_fill");
     if (rc) return rc;
     if (ct.fits32 && cm.fits32) {
       set_plan_name("masked_fill_strided32");
-      masked_fill_strided_kernel<W, uint32_t><<<grid, kThreads, 0, st>>>(t, make_view<uint32_t>(ct), mask,
+      launch_pdl(masked_fill_strided_kernel<W, uint32_t>, grid, kThreads, 0, st, t, make_view<uint32_t>(ct), mask,
                                                                          make_view<uint32_t>(cm), (uint32_t)n, value);
     } else {
       set_plan_name("masked_fill_strided64");
-      masked_fill_strided_kernel<W, uint64_t><<<grid, kThreads, 0, st>>>(t, make_view<uint64_t>(ct), mask,
+      launch_pdl(masked_fill_strided_kernel<W, uint64_t>, grid, kThreads, 0, st, t, make_view<uint64_t>(ct), mask,
                                                                          make_view<uint64_t>(cm), (uint64_t)n, value);
     }
   }
@@ -694,22 +704,22 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   const uint64_t full = mask_vec ? n / kTile : 0;
   int launches = 1;
   if (full > 0) {
-    mask_tile_count_vec_kernel<<<(unsigned)((full + kCountTiles - 1) / kCountTiles), kThreads, 0, st>>>(mask, full, counts);
+    launch_pdl(mask_tile_count_vec_kernel, (unsigned)((full + kCountTiles - 1) / kCountTiles), kThreads, 0, st, mask, full, counts);
     ++launches;
   }
   if (full < mp->ntiles) {
     const unsigned rest = (unsigned)(mp->ntiles - full);
     if (mp->cm.fits32)
-      mask_tile_count_kernel<uint32_t><<<rest, kThreads, 0, st>>>(mask, make_view<uint32_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
+      launch_pdl(mask_tile_count_kernel<uint32_t>, rest, kThreads, 0, st, mask, make_view<uint32_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
     else
-      mask_tile_count_kernel<uint64_t><<<rest, kThreads, 0, st>>>(mask, make_view<uint64_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
+      launch_pdl(mask_tile_count_kernel<uint64_t>, rest, kThreads, 0, st, mask, make_view<uint64_t>(mp->cm), n, mask_vec, counts, (uint32_t)full);
     ++launches;
   }
   int64_t *total_host = reinterpret_cast<int64_t *>((char *)ctx->host_slot_dev + kHostCountOffset);
   if (mp->ntiles > 1024 && mp->ntiles <= (1u << 18))
-    tile_scan_spread_kernel<<<(unsigned)((mp->ntiles + 1023) / 1024), 1024, 0, st>>>(counts, mp->offsets, (uint32_t)mp->ntiles, mp->total, total_host);
+    launch_pdl(tile_scan_spread_kernel, (unsigned)((mp->ntiles + 1023) / 1024), 1024, 0, st, counts, mp->offsets, (uint32_t)mp->ntiles, mp->total, total_host);
   else
-    tile_scan_kernel<<<1, 1024, 0, st>>>(counts, mp->offsets, mp->ntiles, mp->total, total_host);
+    launch_pdl(tile_scan_kernel, 1, 1024, 0, st, counts, mp->offsets, mp->ntiles, mp->total, total_host);
   count_launch(launches);
   THCB_CUDA_TRY(cudaGetLastError());
   ctx->prep_mask = vm.data;
@@ -730,6 +740,7 @@ struct CoordShape {
 __global__ void __launch_bounds__(kThreads)
 mask_coords_kernel(const uint8_t *mask, uint64_t n, bool vec /* mask base is 16-byte aligned */, const uint64_t *offsets,
                    CoordShape shape, int64_t *out) {
+  pdl_prologue();
   __shared__ uint32_t wsum[kThreads / 32];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
@@ -793,10 +804,10 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
     if (full > 0) {
       set_plan_name(i32 ? "masked_select_vec32" : "masked_select_vec64");
       const bool wide = ((uintptr_t)strided) % 32 == 0;
-      if (i32 && wide) masked_select_vec_kernel<W, uint32_t, true><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
-      else if (i32) masked_select_vec_kernel<W, uint32_t, false><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
-      else if (wide) masked_select_vec_kernel<W, uint64_t, true><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
-      else masked_select_vec_kernel<W, uint64_t, false><<<(unsigned)full, kThreads, 0, st>>>(strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      if (i32 && wide) launch_pdl(masked_select_vec_kernel<W, uint32_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
+      else if (i32) launch_pdl(masked_select_vec_kernel<W, uint32_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
+      else if (wide) launch_pdl(masked_select_vec_kernel<W, uint64_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      else launch_pdl(masked_select_vec_kernel<W, uint64_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
       ++launches;
     }
   }
@@ -804,10 +815,10 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
     const unsigned rest = (unsigned)(mp.ntiles - full);
     if (full == 0) set_plan_name(SELECT ? (i32 ? "masked_select32" : "masked_select64") : (i32 ? "masked_copy32" : "masked_copy64"));
     if (i32)
-      masked_move_kernel<W, uint32_t, SELECT><<<rest, kThreads, 0, st>>>(strided, make_view<uint32_t>(cs), packed, make_view<uint32_t>(cp), mask,
+      launch_pdl(masked_move_kernel<W, uint32_t, SELECT>, rest, kThreads, 0, st, strided, make_view<uint32_t>(cs), packed, make_view<uint32_t>(cp), mask,
                                                                        make_view<uint32_t>(mp.cm), n, mask_vec, mp.offsets, (uint32_t)full);
     else
-      masked_move_kernel<W, uint64_t, SELECT><<<rest, kThreads, 0, st>>>(strided, make_view<uint64_t>(cs), packed, make_view<uint64_t>(cp), mask,
+      launch_pdl(masked_move_kernel<W, uint64_t, SELECT>, rest, kThreads, 0, st, strided, make_view<uint64_t>(cs), packed, make_view<uint64_t>(cp), mask,
                                                                        make_view<uint64_t>(mp.cm), n, mask_vec, mp.offsets, (uint32_t)full);
     ++launches;
   }
@@ -949,7 +960,7 @@ int thcb200_mask_coords(thcb200_ctx *ctx, const thcb200_tensor *out_i64, const t
   if (mp.hit && counted_on_host(ctx, &rc, vo.numel, (int64_t)nd, "mask_coords")) return rc;
   const bool mvec = aligned16(vm.data);
   set_plan_name(mvec ? "mask_coords" : "mask_coords_bytes");
-  mask_coords_kernel<<<(unsigned)mp.ntiles, kThreads, 0, st>>>(reinterpret_cast<const uint8_t *>(vm.data), (uint64_t)vm.numel, mvec, mp.offsets,
+  launch_pdl(mask_coords_kernel, (unsigned)mp.ntiles, kThreads, 0, st, reinterpret_cast<const uint8_t *>(vm.data), (uint64_t)vm.numel, mvec, mp.offsets,
                                                               shape, reinterpret_cast<int64_t *>(vo.data));
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());

@@ -27,6 +27,14 @@ const char *get_plan_name() { return g_plan; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("THCB200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int64_t view_numel(const thcb200_tensor *t) {
   if (t->ndim <= 0) return 0;
   int64_t n = 1;

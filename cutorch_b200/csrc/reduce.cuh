@@ -310,6 +310,28 @@ constexpr int kRedThreads = 256;
 constexpr int kRedWarps = kRedThreads / 32;
 constexpr int kRedUnroll = 4;
 
+// Ticket draw that publishes this CTA's earlier stores and, in the CTA that draws the last ticket,
+// makes the other CTAs' stores visible: one acquire-release atomic at GPU scope in place of a fence,
+// an atomic and a second fence.  Call from one thread after a __syncthreads() that follows the
+// CTA's stores; the stores of the CTA's other threads are covered through that barrier.
+__device__ __forceinline__ unsigned int draw_ticket(unsigned int *ticket) {
+  unsigned int old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(ticket) : "memory");
+  return old;
+}
+
+// Loads a partial that another CTA stored, from the L2 (never from a line an earlier kernel may
+// have left in this SM's L1).
+template <typename P> __device__ __forceinline__ P load_partial(const P *p) {
+  static_assert(sizeof(P) % 4 == 0, "partials are made of 32-bit words");
+  P r;
+  const unsigned int *src = reinterpret_cast<const unsigned int *>(p);
+  unsigned int *dst = reinterpret_cast<unsigned int *>(&r);
+#pragma unroll
+  for (int i = 0; i < (int)(sizeof(P) / 4); ++i) dst[i] = __ldcg(src + i);
+  return r;
+}
+
 // ====================================================================================
 // Tail shared by the full-reduction kernels: fold the CTA's accumulators, store the CTA's
 // partial, and let the CTA that draws the last ticket fold all partials in index order.
@@ -326,35 +348,39 @@ __device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) { sm[warp].v = acc.v; sm[warp].has = acc.has; }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (warp == 0) {
+    // the 8 warp results fold as a butterfly over the first lanes (fixed order)
     Opt<F> b = Opt<F>::start();
-    for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = sm[w].v; o.has = sm[w].has; b.merge(o); }
-    partials[blockIdx.x].v = b.v;
-    partials[blockIdx.x].has = b.has;
-    __threadfence();
-    const unsigned int done = atomicAdd(ticket, 1u);
-    is_last = (done == gridDim.x - 1);
+    if (lane < kRedWarps) { b.v = sm[lane].v; b.has = sm[lane].has; }
+    b = warp_fold_opt<F>(b);
+    if (lane == 0) {
+      partials[blockIdx.x].v = b.v;
+      partials[blockIdx.x].has = b.has;
+      is_last = (draw_ticket(ticket) == gridDim.x - 1);
+    }
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence();
   Opt<F> f = Opt<F>::start();
   for (unsigned int i = threadIdx.x; i < gridDim.x; i += kRedThreads) {
+    const Partial p = load_partial(partials + i);
     Opt<F> o;
-    o.v = partials[i].v; o.has = partials[i].has;
+    o.v = p.v; o.has = p.has;
     f.merge(o);
   }
   f = warp_fold_opt<F>(f);
-  __syncthreads();
   if (lane == 0) { sm[warp].v = f.v; sm[warp].has = f.has; }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (warp == 0) {
     Opt<F> b = Opt<F>::start();
-    for (int w = 0; w < kRedWarps; ++w) { Opt<F> o; o.v = sm[w].v; o.has = sm[w].has; b.merge(o); }
-    // result slot: double for floating element types, int64 for integer ones
-    if constexpr (TypeTraits<T>::is_fp) *reinterpret_cast<double *>(result) = (double)b.v;
-    else *reinterpret_cast<int64_t *>(result) = (int64_t)b.v;
-    *ticket = 0;  // ready for the next launch on this stream
+    if (lane < kRedWarps) { b.v = sm[lane].v; b.has = sm[lane].has; }
+    b = warp_fold_opt<F>(b);
+    if (lane == 0) {
+      // result slot: double for floating element types, int64 for integer ones
+      if constexpr (TypeTraits<T>::is_fp) *reinterpret_cast<double *>(result) = (double)b.v;
+      else *reinterpret_cast<int64_t *>(result) = (int64_t)b.v;
+      *ticket = 0;  // ready for the next launch on this stream
+    }
   }
 }
 
@@ -398,6 +424,7 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Folder<T, MODE>::Params prm,
                        void *partials_raw, unsigned int *ticket, void *result) {
+  pdl_prologue();
   using F = Folder<T, MODE>;
   constexpr int V = 16 / (int)sizeof(T);
   constexpr int W = kRedRowsSlots;
@@ -447,6 +474,7 @@ template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided w
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
                   void *partials_raw, unsigned int *ticket, void *result, const T *edge, uint32_t nedge) {
+  pdl_prologue();
   using F = Folder<T, MODE>;
   constexpr bool VEC = VB != 0;
   constexpr int V = VEC ? VB / (int)sizeof(T) : 1;
@@ -543,6 +571,8 @@ template <typename T, typename Acc> __device__ __forceinline__ T finalize_out(Ac
 // Partial accumulators of split reductions, kept in the workspace between the two stages.
 template <typename Acc> struct PartialVal { Acc v; int has; };
 
+constexpr int kFinishBatch = 16;
+
 // Folds the nsplit partials of output `o` in split order and writes the result: the second
 // stage of a split reduction, run either by reduce_finish_kernel or by the last CTA of a tile.
 template <typename T, int MODE, bool INDEX, bool IS_MAX>
@@ -551,16 +581,29 @@ __device__ __forceinline__ void finish_output(T *out_elem, int64_t *idx_elem, ui
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   if constexpr (INDEX) {
+    // the partials are loaded kFinishBatch at a time (independent loads in flight) and folded in split order
     const typename IF::Acc *pp = reinterpret_cast<const typename IF::Acc *>(partials_raw) + o * nsplit;
-    typename IF::Acc r = pp[0];
-    for (uint32_t s = 1; s < nsplit; ++s) r = IF::combine(r, pp[s]);
+    typename IF::Acc r = IF::empty();
+    for (uint32_t s0 = 0; s0 < nsplit; s0 += kFinishBatch) {
+      typename IF::Acc b[kFinishBatch];
+#pragma unroll
+      for (int u = 0; u < kFinishBatch; ++u) if (s0 + u < nsplit) b[u] = load_partial(pp + s0 + u);
+#pragma unroll
+      for (int u = 0; u < kFinishBatch; ++u) if (s0 + u < nsplit) r = IF::combine(r, b[u]);
+    }
     r = FastIdx<T, IS_MAX>::resolve(r);
     *out_elem = from_math<T>(r.v);
     *idx_elem = r.i + 1;  // TH_INDEX_BASE
   } else {
     const PartialVal<typename F::Acc> *pp = reinterpret_cast<const PartialVal<typename F::Acc> *>(partials_raw) + o * nsplit;
     Opt<F> r = Opt<F>::start();
-    for (uint32_t s = 0; s < nsplit; ++s) { Opt<F> x; x.v = pp[s].v; x.has = pp[s].has; r.merge(x); }
+    for (uint32_t s0 = 0; s0 < nsplit; s0 += kFinishBatch) {
+      PartialVal<typename F::Acc> b[kFinishBatch];
+#pragma unroll
+      for (int u = 0; u < kFinishBatch; ++u) if (s0 + u < nsplit) b[u] = load_partial(pp + s0 + u);
+#pragma unroll
+      for (int u = 0; u < kFinishBatch; ++u) if (s0 + u < nsplit) { Opt<F> x; x.v = b[u].v; x.has = b[u].has; r.merge(x); }
+    }
     *out_elem = finalize_out<T, typename F::Acc>(r.v, post);
   }
 }
@@ -569,11 +612,9 @@ __device__ __forceinline__ void finish_output(T *out_elem, int64_t *idx_elem, ui
 // the tile are then visible to it).  Call with every thread of the CTA, after the partial stores.
 __device__ __forceinline__ bool last_cta_of_tile(unsigned int *tickets, uint64_t tile, uint32_t count) {
   __shared__ bool s_last;
-  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&tickets[tile], 1u) == count - 1);
+  if (threadIdx.x == 0) s_last = (draw_ticket(&tickets[tile]) == count - 1);
   __syncthreads();
-  if (s_last) __threadfence();
   return s_last;
 }
 
@@ -587,6 +628,7 @@ __global__ void __launch_bounds__(kRedThreads, 4)
 reduce_row_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
                   uint32_t nsplit, uint64_t split_len, typename Folder<T, MODE>::Params prm, void *partials_raw,
                   unsigned int *tickets, PostOp post) {
+  pdl_prologue();
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   constexpr int V = 16 / sizeof(T);
@@ -743,12 +785,13 @@ template <typename T> constexpr int col_vec_elems() { return sizeof(T) == 1 ? 4 
 // take the rows of the split round-robin, kRedUnroll row loads in flight per thread, and are
 // merged through shared memory in warp order.
 // ====================================================================================
-template <typename T, int MODE, bool INDEX, bool IS_MAX, int V>
+template <typename T, int MODE, bool INDEX, bool IS_MAX, int V, int U /* row loads in flight per thread */>
 __global__ void __launch_bounds__(kRedThreads, 4)
 reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims other than K and inner */,
                   uint64_t nouter, uint64_t K, int64_t strideK, uint64_t I, int64_t out_inner_stride,
                   int64_t idx_inner_stride, uint32_t nsplit, uint64_t split_len, uint32_t tiles_i,
                   typename Folder<T, MODE>::Params prm, void *partials_raw, unsigned int *tickets, PostOp post) {
+  pdl_prologue();
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   using VecT = typename ColVec<V * sizeof(T), T>::type;
@@ -772,15 +815,15 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
   for (int j = 0; j < V; ++j) { acc[j] = Opt<F>::start(); fast[j].reset(); }
   if (col_ok) {
     uint64_t k = k0 + warp;
-    for (; k + (uint64_t)(kRedUnroll - 1) * kRedWarps < k1; k += (uint64_t)kRedUnroll * kRedWarps) {
-      VecT v[kRedUnroll];
+    for (; k + (uint64_t)(U - 1) * kRedWarps < k1; k += (uint64_t)U * kRedWarps) {
+      VecT v[U];
 #pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
+      for (int u = 0; u < U; ++u) {
         const T *p = col + (int64_t)(k + (uint64_t)u * kRedWarps) * strideK;
         v[u] = ColVec<V * sizeof(T), T>::load(p);
       }
 #pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
+      for (int u = 0; u < U; ++u) {
         const T *e = reinterpret_cast<const T *>(&v[u]);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
@@ -789,15 +832,25 @@ reduce_col_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map /* dims ot
         }
       }
     }
-    for (; k < k1; k += kRedWarps) {
-      VecT v;
-      const T *p = col + (int64_t)k * strideK;
-      v = ColVec<V * sizeof(T), T>::load(p);
-      const T *e = reinterpret_cast<const T *>(&v);
+    // the last rows of the split: one more batch, each load guarded (a single round trip)
+    if (k < k1) {
+      VecT v[U];
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        if constexpr (INDEX) fast[j].feed(e[j], (uint32_t)(k - k0));
-        else acc[j].feed(F::pre(e[j], prm));
+      for (int u = 0; u < U; ++u) {
+        const uint64_t kk = k + (uint64_t)u * kRedWarps;
+        if (kk < k1) v[u] = ColVec<V * sizeof(T), T>::load(col + (int64_t)kk * strideK);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t kk = k + (uint64_t)u * kRedWarps;
+        if (kk < k1) {
+          const T *e = reinterpret_cast<const T *>(&v[u]);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            if constexpr (INDEX) fast[j].feed(e[j], (uint32_t)(kk - k0));
+            else acc[j].feed(F::pre(e[j], prm));
+          }
+        }
       }
     }
   }
@@ -859,6 +912,7 @@ __global__ void __launch_bounds__(kRedThreads)
 reduce_finish_kernel(T *out, int64_t *idx_out, SliceMap map, uint64_t nouter, uint64_t I,
                      int64_t out_inner_stride, int64_t idx_inner_stride, uint32_t nsplit,
                      const void *partials_raw, PostOp post) {
+  pdl_prologue();
   const uint64_t o = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;
   if (o >= nouter * I) return;
   const uint64_t outer = o / I, i = o - outer * I;
@@ -875,6 +929,7 @@ template <typename T, int MODE, bool INDEX, bool IS_MAX>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_strided_kernel(const T *in, T *out, int64_t *idx_out, SliceMap map, uint64_t nslices, uint64_t K,
                       int64_t strideK, typename Folder<T, MODE>::Params prm, PostOp post) {
+  pdl_prologue();
   using F = Folder<T, MODE>;
   using IF = IndexFolder<T, IS_MAX>;
   const uint64_t s = (uint64_t)blockIdx.x * kRedThreads + threadIdx.x;

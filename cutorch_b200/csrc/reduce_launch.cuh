@@ -79,7 +79,7 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
         void *partials = ctx_workspace(ctx, grid * 16);
         if (!partials) return THCB200_ERR_NOMEM;
         set_plan_name("reduce_all_rows");
-        reduce_all_rows_kernel<T, MODE><<<(unsigned)grid, kRedThreads, 0, st>>>(p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
+        launch_pdl(reduce_all_rows_kernel<T, MODE>, (unsigned)grid, kRedThreads, 0, st, p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
         count_launch();
         THCB_CUDA_TRY(cudaGetLastError());
         return 0;
@@ -106,11 +106,12 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   const uint64_t tile = (uint64_t)kRedThreads * kRedUnroll * (vb ? vb / sizeof(T) : 1);
   uint64_t ntiles = (nbody + tile - 1) / tile;
   if (ntiles < 1) ntiles = 1;
-  // at most 4 CTAs per SM, all resident at once (measured on B200: more CTAs in flight lower the
-  // read bandwidth), sized so that every CTA gets the same number of tiles to within one: a
-  // function of n and the SM count only
-  const uint64_t per_cta = (ntiles + max_grid - 1) / max_grid;
-  uint64_t grid = per_cta ? (ntiles + per_cta - 1) / per_cta : 1;
+  // 4 CTAs per SM, all resident at once (measured on B200: more CTAs in flight lower the read
+  // bandwidth), walking the tiles block-cyclically: every CTA gets the same number of tiles to
+  // within one and, with the CTAs dealt round the SMs, so does every SM (a grid cut down to whole
+  // tiles per CTA left some SMs with 16 tiles and others with 12 on a 64 MiB tensor).  A function
+  // of n and the SM count only.
+  uint64_t grid = ntiles < max_grid ? ntiles : max_grid;
   if (grid < 1) grid = 1;
   void *partials = ctx_workspace(ctx, grid * 16);
   if (!partials) return THCB200_ERR_NOMEM;
@@ -122,10 +123,10 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   }
   if (vb == 32) {
     set_plan_name(nedge ? "reduce_all_vec_peeled" : "reduce_all_vec");
-    reduce_all_kernel<T, MODE, 32><<<(unsigned)grid, kRedThreads, 0, st>>>(body, view, nbody, prm, partials, ctx->tickets, result, p, nedge);
+    launch_pdl(reduce_all_kernel<T, MODE, 32>, (unsigned)grid, kRedThreads, 0, st, body, view, nbody, prm, partials, ctx->tickets, result, p, nedge);
   } else {
     set_plan_name("reduce_all_strided");
-    reduce_all_kernel<T, MODE, 0><<<(unsigned)grid, kRedThreads, 0, st>>>(p, view, n, prm, partials, ctx->tickets, result, p, 0u);
+    launch_pdl(reduce_all_kernel<T, MODE, 0>, (unsigned)grid, kRedThreads, 0, st, p, view, n, prm, partials, ctx->tickets, result, p, 0u);
   }
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());
@@ -284,8 +285,10 @@ inline int plan_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView 
       uint64_t maxs = pl->K / (2 * step);
       if (want > maxs) want = maxs;
       if (want > 1) {
+        // equal splits, each warp the same number of rows: rounding the length up to a whole number
+        // of iterations instead left 8192 rows as 17 splits of 480 and one of 32
         uint64_t len = (pl->K + want - 1) / want;
-        len = (len + step - 1) / step * step;
+        len = (len + kRedWarps - 1) / kRedWarps * kRedWarps;
         pl->split_len = len;
         pl->nsplit = (uint32_t)((pl->K + len - 1) / len);
       }
@@ -339,30 +342,30 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
       const uint64_t blocks = (pl.nslices + kRedWarps - 1) / kRedWarps;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name(pl.vec ? "row_warp_vec" : "row_warp");
-      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
-      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, true><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
+      if (pl.vec) launch_pdl(reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, true>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
+      else launch_pdl(reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, true>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, 1, pl.K, prm, nullptr, nullptr, post);
       break;
     }
     case kRedRowBlock: {
       const uint64_t blocks = pl.nslices * pl.nsplit;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name(pl.nsplit > 1 ? "row_block_split" : "row_block");
-      if (pl.vec) reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
-      else reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, false><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
+      if (pl.vec) launch_pdl(reduce_row_kernel<T, MODE, INDEX, IS_MAX, true, false>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
+      else launch_pdl(reduce_row_kernel<T, MODE, INDEX, IS_MAX, false, false>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.nsplit, pl.split_len, prm, partials, tickets, post);
       break;
     }
     case kRedCol: {
       const uint64_t blocks = pl.nslices * pl.tiles_i * pl.nsplit;
       set_plan_name(pl.nsplit > 1 ? "col_tile_split" : "col_tile");
-      if (pl.vec) reduce_col_kernel<T, MODE, INDEX, IS_MAX, CV><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
-      else reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
+      if (pl.vec) launch_pdl(reduce_col_kernel<T, MODE, INDEX, IS_MAX, CV, kRedUnroll>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
+      else launch_pdl(reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1, kRedUnroll>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
       break;
     }
     case kRedStrided: {
       const uint64_t blocks = (pl.nslices + kRedThreads - 1) / kRedThreads;
       if (blocks >= (1ull << 31)) { set_error("reduce_dim: too many slices"); return THCB200_ERR_DIMS; }
       set_plan_name("strided");
-      reduce_strided_kernel<T, MODE, INDEX, IS_MAX><<<(unsigned)blocks, kRedThreads, 0, st>>>(ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, prm, post);
+      launch_pdl(reduce_strided_kernel<T, MODE, INDEX, IS_MAX>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, prm, post);
       break;
     }
   }
@@ -370,7 +373,7 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
   if (pl.nsplit > 1 && !tickets) {
     const uint64_t blocks = (noutputs + kRedThreads - 1) / kRedThreads;
     const uint64_t I = pl.kind == kRedCol ? pl.I : 1;
-    reduce_finish_kernel<T, MODE, INDEX, IS_MAX><<<(unsigned)blocks, kRedThreads, 0, st>>>(
+    launch_pdl(reduce_finish_kernel<T, MODE, INDEX, IS_MAX>, (unsigned)blocks, kRedThreads, 0, st, 
         op, xp, pl.map, pl.nslices, I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, partials, post);
     THCB_CUDA_TRY(cudaGetLastError());
     ++launches;

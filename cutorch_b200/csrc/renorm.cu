@@ -18,6 +18,7 @@ namespace {
 
 template <typename T>
 __global__ void __launch_bounds__(256) renorm_factor_kernel(T *factors, const T *sums, uint64_t n, double p, T maxnorm) {
+  pdl_prologue();
   const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
   if (i >= n) return;
   const T norm = (T)pow((double)sums[i], 1.0 / p);
@@ -33,6 +34,7 @@ template <typename T, int NV, int G, int PMODE, int R>
 __global__ void __launch_bounds__(256) renorm_rows_kernel(T *out, const T *in, uint64_t nrows, uint32_t nvec,
                                                           int64_t in_pitch, int64_t out_pitch, double p,
                                                           typename TypeTraits<T>::Math maxnorm) {
+  pdl_prologue();
   using M = typename TypeTraits<T>::Math;  // half slices are computed as float slices and rounded once
   constexpr int V = 16 / (int)sizeof(T);
   constexpr int GPC = 256 / G;  // groups per CTA
@@ -118,9 +120,9 @@ void launch_renorm_rows_r(T *out, const T *in, uint64_t nrows, uint32_t nvec, in
   using M = typename TypeTraits<T>::Math;
   constexpr uint64_t rows_per_cta = (uint64_t)(256 / G) * R;
   const unsigned blocks = (unsigned)((nrows + rows_per_cta - 1) / rows_per_cta);
-  if (p == 1.0) renorm_rows_kernel<T, NV, G, 1, R><<<blocks, 256, 0, st>>>(out, in, nrows, nvec, ip, op, p, (M)maxnorm);
-  else if (p == 2.0) renorm_rows_kernel<T, NV, G, 2, R><<<blocks, 256, 0, st>>>(out, in, nrows, nvec, ip, op, p, (M)maxnorm);
-  else renorm_rows_kernel<T, NV, G, 0, R><<<blocks, 256, 0, st>>>(out, in, nrows, nvec, ip, op, p, (M)maxnorm);
+  if (p == 1.0) launch_pdl(renorm_rows_kernel<T, NV, G, 1, R>, blocks, 256, 0, st, out, in, nrows, nvec, ip, op, p, (M)maxnorm);
+  else if (p == 2.0) launch_pdl(renorm_rows_kernel<T, NV, G, 2, R>, blocks, 256, 0, st, out, in, nrows, nvec, ip, op, p, (M)maxnorm);
+  else launch_pdl(renorm_rows_kernel<T, NV, G, 0, R>, blocks, 256, 0, st, out, in, nrows, nvec, ip, op, p, (M)maxnorm);
 }
 
 template <typename T, int NV, int G>
@@ -198,9 +200,9 @@ extern "C" int thcb200_renorm_factor(thcb200_ctx *ctx, const thcb200_tensor *fac
   if (blocks >= (1ull << 31)) { set_error("renorm_factor: too many slices"); return THCB200_ERR_DIMS; }
   cudaStream_t st = (cudaStream_t)stream;
   if (vf.dtype == THCB200_F32)
-    renorm_factor_kernel<float><<<(unsigned)blocks, 256, 0, st>>>((float *)vf.data, (const float *)vs.data, n, p, (float)maxnorm);
+    launch_pdl(renorm_factor_kernel<float>, (unsigned)blocks, 256, 0, st, (float *)vf.data, (const float *)vs.data, n, p, (float)maxnorm);
   else
-    renorm_factor_kernel<double><<<(unsigned)blocks, 256, 0, st>>>((double *)vf.data, (const double *)vs.data, n, p, maxnorm);
+    launch_pdl(renorm_factor_kernel<double>, (unsigned)blocks, 256, 0, st, (double *)vf.data, (const double *)vs.data, n, p, maxnorm);
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());
   return THCB200_OK;

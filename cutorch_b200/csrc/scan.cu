@@ -70,6 +70,7 @@ template <typename T, bool PROD, bool VEC, bool TOTAL_ONLY>
 __global__ void __launch_bounds__(kScanThreads)
 scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, uint32_t S, uint64_t chunk_len,
                 typename TypeTraits<T>::Acc *carries) {
+  pdl_prologue();
   using A = typename TypeTraits<T>::Acc;
   constexpr int V = VEC ? 16 / (int)sizeof(T) : 1;
   constexpr int U = kScanUnroll;
@@ -185,6 +186,7 @@ scan_row_kernel(const T *in, T *out, ScanMap map, uint64_t nrows, uint64_t K, ui
 // chunk totals -> exclusive carries, in place; a CTA per row, threads own consecutive segments
 template <typename A, bool PROD>
 __global__ void __launch_bounds__(kScanThreads) scan_row_carry_kernel(A *carries, uint64_t nrows, uint32_t S) {
+  pdl_prologue();
   __shared__ A wtot[kScanWarps];
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   A *c = carries + (uint64_t)blockIdx.x * S;
@@ -220,6 +222,7 @@ template <typename T, bool PROD, int V, bool TOTAL_ONLY>
 __global__ void __launch_bounds__(kScanThreads)
 scan_col_kernel(const T *in, T *out, ScanMap map, uint64_t nouter, uint64_t K, int64_t sKi, int64_t sKo, uint64_t I,
                 uint32_t tiles_i, uint32_t S, uint64_t chunk_len, typename TypeTraits<T>::Acc *carries) {
+  pdl_prologue();
   using A = typename TypeTraits<T>::Acc;
   constexpr int U = kScanUnroll;
   const unsigned lane = threadIdx.x & 31;
@@ -273,6 +276,7 @@ scan_col_kernel(const T *in, T *out, ScanMap map, uint64_t nouter, uint64_t K, i
 // chunk totals -> exclusive carries along the chunk index; a thread per (outer, column)
 template <typename A, bool PROD>
 __global__ void __launch_bounds__(kScanThreads) scan_col_carry_kernel(A *carries, uint64_t nouter, uint64_t I, uint32_t S) {
+  pdl_prologue();
   const uint64_t t = (uint64_t)blockIdx.x * kScanThreads + threadIdx.x;
   if (t >= nouter * I) return;
   const uint64_t o = t / I, col = t - o * I;
@@ -300,6 +304,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_col_carry_kernel(A *carries
 template <typename T, bool PROD>
 __global__ void __launch_bounds__(kScanThreads)
 scan_strided_kernel(const T *in, T *out, ScanMap map, uint64_t nslices, uint64_t K, int64_t sKi, int64_t sKo) {
+  pdl_prologue();
   using A = typename TypeTraits<T>::Acc;
   const uint64_t s = (uint64_t)blockIdx.x * kScanThreads + threadIdx.x;
   if (s >= nslices) return;
@@ -474,36 +479,36 @@ int launch_scan(thcb200_ctx *ctx, const HostView &in, const HostView &out, int d
       if ((rc = blocks_for(pl.nslices * pl.S, kScanWarps, &grid))) return rc;
       set_plan_name(pl.S > 1 ? (pl.vec ? "scan_row_vec_chunked" : "scan_row_chunked") : (pl.vec ? "scan_row_vec" : "scan_row"));
       if (pl.S > 1) {
-        if (pl.vec) scan_row_kernel<T, PROD, true, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
-        else scan_row_kernel<T, PROD, false, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
+        if (pl.vec) launch_pdl(scan_row_kernel<T, PROD, true, true>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
+        else launch_pdl(scan_row_kernel<T, PROD, false, true>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
         unsigned g2;
         if ((rc = blocks_for(pl.nslices, 1, &g2))) return rc;
-        scan_row_carry_kernel<A, PROD><<<g2, kScanThreads, 0, st>>>(carries, pl.nslices, pl.S);
+        launch_pdl(scan_row_carry_kernel<A, PROD>, g2, kScanThreads, 0, st, carries, pl.nslices, pl.S);
         launches += 2;
       }
-      if (pl.vec) scan_row_kernel<T, PROD, true, false><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
-      else scan_row_kernel<T, PROD, false, false><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
+      if (pl.vec) launch_pdl(scan_row_kernel<T, PROD, true, false>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
+      else launch_pdl(scan_row_kernel<T, PROD, false, false>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.S, pl.chunk_len, carries);
       break;
     }
     case kScanCol: {
       if ((rc = blocks_for(pl.nslices * pl.S * pl.tiles_i, kScanWarps, &grid))) return rc;
       set_plan_name(pl.S > 1 ? (pl.vec ? "scan_col_vec_chunked" : "scan_col_chunked") : (pl.vec ? "scan_col_vec" : "scan_col"));
       if (pl.S > 1) {
-        if (pl.vec) scan_col_kernel<T, PROD, VC, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
-        else scan_col_kernel<T, PROD, 1, true><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
+        if (pl.vec) launch_pdl(scan_col_kernel<T, PROD, VC, true>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
+        else launch_pdl(scan_col_kernel<T, PROD, 1, true>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
         unsigned g2;
         if ((rc = blocks_for(pl.nslices * pl.I, kScanThreads, &g2))) return rc;
-        scan_col_carry_kernel<A, PROD><<<g2, kScanThreads, 0, st>>>(carries, pl.nslices, pl.I, pl.S);
+        launch_pdl(scan_col_carry_kernel<A, PROD>, g2, kScanThreads, 0, st, carries, pl.nslices, pl.I, pl.S);
         launches += 2;
       }
-      if (pl.vec) scan_col_kernel<T, PROD, VC, false><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
-      else scan_col_kernel<T, PROD, 1, false><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
+      if (pl.vec) launch_pdl(scan_col_kernel<T, PROD, VC, false>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
+      else launch_pdl(scan_col_kernel<T, PROD, 1, false>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo, pl.I, pl.tiles_i, pl.S, pl.chunk_len, carries);
       break;
     }
     default: {
       if ((rc = blocks_for(pl.nslices, kScanThreads, &grid))) return rc;
       set_plan_name("scan_strided");
-      scan_strided_kernel<T, PROD><<<grid, kScanThreads, 0, st>>>(ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo);
+      launch_pdl(scan_strided_kernel<T, PROD>, grid, kScanThreads, 0, st, ip, op, pl.map, pl.nslices, pl.K, pl.sKi, pl.sKo);
       break;
     }
   }

@@ -66,8 +66,11 @@ using namespace thcb;
 
 // Same contract and results as thcb200_reduce_dim (the same kernels run), but without a
 // context and without any allocation.
-//  * The first call on a device looks up the device address of the scratch array; make that
-//    first call outside any stream capture.
+//  * The first call on a device looks up the device address of the scratch array (and, with
+//    CUDA's lazy module loading, is the moment the runtime places the library's device code and
+//    this array on that GPU: the free memory cudaMemGetInfo reports drops by the array's size
+//    then, once).  Make that first call at start-up, outside any stream capture; every later
+//    call leaves the device's memory as it found it.
 //  * A reduction that needs more than THCB200_STATIC_SCRATCH_BYTES of partials is refused with
 //    THCB200_ERR_LIMIT (only reductions that are split along the reduced dim need partials at
 //    all; the others always pass).

@@ -24,6 +24,7 @@ template <typename W>
 __global__ void __launch_bounds__(kTriThreads)
 tri_kernel(W *out, const W *in, uint64_t nfast, uint64_t nslow, int64_t of, int64_t os, int64_t inf, int64_t ins,
            int64_t k, int upper, int row_is_fast, uint32_t tiles_f) {
+  pdl_prologue();
   const uint64_t stile = blockIdx.x / tiles_f;
   const uint64_t f0 = (uint64_t)(blockIdx.x - stile * tiles_f) * (kTriThreads * kTriUnroll) + threadIdx.x;
   // two lines at a time: all of their loads are issued before the first store (out may be in)
@@ -60,6 +61,7 @@ template <typename W>
 __global__ void __launch_bounds__(kTriThreads)
 tri_vec_kernel(W *out, const W *in, uint64_t ncols, uint64_t nrows, int64_t orow, int64_t irow, int64_t k, int upper,
                uint32_t tiles_f) {
+  pdl_prologue();
   constexpr int V = 16 / (int)sizeof(W);
   const uint64_t nvec = ncols / V;   // ncols is a multiple of V
   const uint64_t stile = blockIdx.x / tiles_f;
@@ -116,7 +118,7 @@ int launch_tri(const HostView &vo, const HostView &vi, int64_t k, int upper, cud
     const uint64_t blocks = tiles_f * (((uint64_t)vo.sizes[0] + kTriRows - 1) / kTriRows);
     if (blocks >= (1ull << 31)) { set_error("tri: matrix too large"); return THCB200_ERR_DIMS; }
     set_plan_name("tri_rows_vec");
-    tri_vec_kernel<W><<<(unsigned)blocks, kTriThreads, 0, st>>>(op, ip, (uint64_t)vo.sizes[1], (uint64_t)vo.sizes[0],
+    launch_pdl(tri_vec_kernel<W>, (unsigned)blocks, kTriThreads, 0, st, op, ip, (uint64_t)vo.sizes[1], (uint64_t)vo.sizes[0],
                                                                 vo.strides[0], vi.strides[0], k, upper, (uint32_t)tiles_f);
     count_launch();
     THCB_CUDA_TRY(cudaGetLastError());
@@ -131,7 +133,7 @@ int launch_tri(const HostView &vo, const HostView &vi, int64_t k, int upper, cud
   const uint64_t blocks = tiles_f * ((nslow + kTriRows - 1) / kTriRows);
   if (blocks >= (1ull << 31) || tiles_f >= (1ull << 31)) { set_error("tri: matrix too large"); return THCB200_ERR_DIMS; }
   set_plan_name(fast == 1 ? "tri_rows" : "tri_cols");
-  tri_kernel<W><<<(unsigned)blocks, kTriThreads, 0, st>>>(op, ip, nfast, nslow, vo.strides[fast], vo.strides[slow],
+  launch_pdl(tri_kernel<W>, (unsigned)blocks, kTriThreads, 0, st, op, ip, nfast, nslow, vo.strides[fast], vo.strides[slow],
                                                           vi.strides[fast], vi.strides[slow], k, upper, fast == 0 ? 1 : 0,
                                                           (uint32_t)tiles_f);
   count_launch();

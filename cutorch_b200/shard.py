@@ -12,11 +12,108 @@ tiny and goes through ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests
 
 cutorch itself has no multi-process layer (it drives several devices from one process,
 lib/THC/THCGeneral.h.in:57-123); this module exists for the sharded benchmark configuration.
+
+On GPUs the exchange itself lives in the C library (`Comm`: thcb200_comm_* / thcb200_sharded_* in
+include/thcb200.h, NCCL bound by the library); torch.distributed only carries the 128-byte NCCL id
+from rank 0 to the others.  The torch.distributed functions below are the same rules on any
+backend: the CPU double of the C layer, which the gloo tests run.
 """
 from __future__ import annotations
 
 import torch
 import torch.distributed as dist
+
+
+class Comm:
+    """A communicator of the C library: one rank per GPU, this process's device current.
+
+    `Comm.from_process_group(state)` bootstraps it over an initialised torch.distributed group (rank 0
+    draws the NCCL id, a broadcast hands it round); `Comm(state, 1, 0)` is the single-rank form."""
+
+    def __init__(self, state, nranks: int, rank: int, comm_id: bytes | None = None):
+        import ctypes as C
+        from . import _lib
+        self.state, self.nranks, self.rank = state, nranks, rank
+        self._C, self._lib_mod = C, _lib
+        lib = self.lib = _lib.load_library()
+        P, vp = C.POINTER, C.c_void_p
+        lib.thcb200_comm_unique_id.argtypes = [vp, C.c_size_t]
+        lib.thcb200_comm_create.argtypes = [P(vp), C.c_int, C.c_int, vp, C.c_size_t]
+        lib.thcb200_comm_destroy.argtypes = [vp]
+        lib.thcb200_comm_destroy.restype = None
+        lib.thcb200_comm_info.argtypes = [vp, P(C.c_int), P(C.c_int), P(C.c_int)]
+        lib.thcb200_comm_all_reduce.argtypes = [vp, vp, C.c_int64, C.c_int, C.c_int, vp]
+        lib.thcb200_comm_all_gather.argtypes = [vp, vp, vp, C.c_int64, vp]
+        TD, SC = _lib.TensorDesc, _lib.Scalar
+        lib.thcb200_sharded_reduce_all.argtypes = [vp, vp, C.c_int, C.c_int, SC, P(TD), vp, vp]
+        lib.thcb200_sharded_reduce_dim.argtypes = [vp, vp, C.c_int, C.c_int, SC, P(TD), P(TD), C.c_int, vp]
+        lib.thcb200_sharded_reduce_dim_index.argtypes = [vp, vp, C.c_int, P(TD), P(TD), P(TD), C.c_int, C.c_int64, vp]
+        if comm_id is None:
+            comm_id = self.new_id()
+        self._id = C.create_string_buffer(comm_id, 128)
+        handle = vp()
+        _lib.check(lib.thcb200_comm_create(C.byref(handle), nranks, rank, self._id, 128))
+        self.handle = handle
+
+    @staticmethod
+    def new_id() -> bytes:
+        import ctypes as C
+        from . import _lib
+        lib = _lib.load_library()
+        lib.thcb200_comm_unique_id.argtypes = [C.c_void_p, C.c_size_t]
+        buf = C.create_string_buffer(128)
+        _lib.check(lib.thcb200_comm_unique_id(buf, 128))
+        return buf.raw
+
+    @classmethod
+    def from_process_group(cls, state, group=None) -> "Comm":
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        box = [cls.new_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0, group=group)
+        return cls(state, world, rank, box[0])
+
+    def nccl_version(self) -> int:
+        C = self._C
+        v = C.c_int(0)
+        self._lib_mod.check(self.lib.thcb200_comm_info(self.handle, None, None, C.byref(v)))
+        return v.value
+
+    def _ctx_stream(self):
+        C = self._C
+        return C.c_void_p(self.state.context), C.c_void_p(self.state.stream)
+
+    def reduce_all(self, t, result_dev_ptr: int, rop: str = "SUM", pre: str = "IDENTITY", s=0):
+        """Full reduction of a row-sharded tensor; the global accumulator (double / int64) lands at
+        `result_dev_ptr` on every rank."""
+        C, L = self._C, self._lib_mod
+        ctx, st = self._ctx_stream()
+        d = t.descriptor()
+        L.check(self.lib.thcb200_sharded_reduce_all(ctx, self.handle, L.RED[rop], L.PRE[pre], L.scalar(s), C.byref(d),
+                                                    C.c_void_p(result_dev_ptr), st))
+
+    def reduce_dim(self, out, t, dim: int, rop: str = "SUM", pre: str = "IDENTITY", s=0):
+        """Reduction along the sharded dim `dim`; `out` (dense, size 1 there) holds the global result on every rank."""
+        C, L = self._C, self._lib_mod
+        ctx, st = self._ctx_stream()
+        do, di = out.descriptor(), t.descriptor()
+        L.check(self.lib.thcb200_sharded_reduce_dim(ctx, self.handle, L.RED[rop], L.PRE[pre], L.scalar(s), C.byref(do), C.byref(di), dim, st))
+
+    def reduce_dim_index(self, values, indices, t, dim: int, shard_start: int, rop: str = "MAX"):
+        """max / min with global 1-based positions along the sharded dim."""
+        C, L = self._C, self._lib_mod
+        ctx, st = self._ctx_stream()
+        dv, dx, di = values.descriptor(), indices.descriptor(), t.descriptor()
+        L.check(self.lib.thcb200_sharded_reduce_dim_index(ctx, self.handle, L.RED[rop], C.byref(dv), C.byref(dx), C.byref(di), dim,
+                                                          shard_start, st))
+
+    def all_reduce(self, dev_ptr: int, count: int, dtype: int, rop: str = "SUM"):
+        C, L = self._C, self._lib_mod
+        L.check(self.lib.thcb200_comm_all_reduce(self.handle, C.c_void_p(dev_ptr), count, dtype, L.RED[rop], C.c_void_p(self.state.stream)))
+
+    def close(self):
+        if self.handle:
+            self.lib.thcb200_comm_destroy(self.handle)
+            self.handle = None
 
 
 def shard_rows(total_rows: int, world: int, rank: int) -> tuple[int, int]:

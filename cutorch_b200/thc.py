@@ -495,6 +495,23 @@ class Tensor:
         f(self.state.ptr, cpu.ptr, self.ptr)
         self.state.check()
 
+    def copy_async_from_cpu(self, cpu: "CpuTensor"):
+        """THCuda<T>Tensor_copyAsyncCPU (lib/THC/generic/THCTensorCopy.c:112-137): same element type, both
+        contiguous, one asynchronous copy in the order of the current stream; the CPU side should be pinned."""
+        f = self.state.fn(self.kind, "copyAsyncCPU")
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        f.restype = None
+        f(self.state.ptr, self.ptr, cpu.ptr)
+        self.state.check()
+
+    def copy_async_to_cpu(self, cpu: "CpuTensor"):
+        """TH<T>Tensor_copyAsyncCuda (lib/THC/generic/THCTensorCopy.c:139-164): the way back."""
+        f = getattr(self.state.lib, f"TH{self.kind}Tensor_copyAsyncCuda")
+        f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        f.restype = None
+        f(self.state.ptr, cpu.ptr, self.ptr)
+        self.state.check()
+
     def cat(self, inputs, dimension: int):
         """result:cat(inputs, dimension): THCTensor_(catArray) (lib/THC/generic/THCTensorMath.cu:84-260)."""
         f = self.state.fn(self.kind, "catArray")

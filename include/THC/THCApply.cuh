@@ -16,7 +16,12 @@
  * dimensions is a no-op returning true; a ReadWrite / WriteOnly operand whose index tuples alias is
  * replaced by a contiguous copy and copied back (copyIgnoringOverlaps); the launch goes to the
  * THCState's current stream.  Layout planning (collapseDims, overlap test, 32- vs 64-bit indices)
- * is done by the host functions exported from libthcb200 (thcb200.h).
+ * is done by the host functions exported from libthcb200 (thcb200.h).  The kernels decode offsets
+ * with multiply-high divisions, take four elements per thread, and are compiled with non-aliasing
+ * pointers when the operands sit in storages that do not overlap (so the loads of the four
+ * elements can be in flight together); the memory pattern itself is the functor's: a transposed
+ * operand is read the way its strides say, since pointer-taking functors cannot be staged through
+ * shared memory.
  *
  * Include this header from a .cu file compiled for sm_100a and link libthcb200.
  */
@@ -53,18 +58,37 @@ THCB_USER_ACCESS(THCudaTensor, float, THCB200_F32)
 THCB_USER_ACCESS(THCudaDoubleTensor, double, THCB200_F64)
 #undef THCB_USER_ACCESS
 
-// Collapsed view of one operand as the kernel sees it.
+// Collapsed view of one operand as the kernel sees it.  With 32-bit indices the per-dim division
+// is a multiply-high by a constant worked out on the host (n / d = (umulhi(n, mul) + n) >> shift for
+// n < 2^32, round-up method of Granlund and Montgomery) instead of a hardware divide.
+template <typename IndexT> struct Divisor;
+template <> struct Divisor<uint32_t> {
+  uint32_t d, mul, shift;
+  void set(uint64_t div) {
+    d = (uint32_t)div;
+    for (shift = 0; shift < 32; ++shift)
+      if ((1ULL << shift) >= div) break;
+    mul = (uint32_t)((((uint64_t)1 << 32) * (((uint64_t)1 << shift) - div)) / div + 1);
+  }
+  __device__ __forceinline__ uint32_t quotient(uint32_t n) const { return (uint32_t)(((uint64_t)__umulhi(n, mul) + n) >> shift); }
+};
+template <> struct Divisor<uint64_t> {
+  uint64_t d;
+  void set(uint64_t div) { d = div; }
+  __device__ __forceinline__ uint64_t quotient(uint64_t n) const { return n / d; }
+};
+
 template <typename IndexT>
 struct View {
   int dims;
-  IndexT sizes[THCB200_MAX_DIMS];
+  Divisor<IndexT> sizes[THCB200_MAX_DIMS];
   IndexT strides[THCB200_MAX_DIMS];
   __device__ __forceinline__ IndexT offset(IndexT linear) const {
     if (dims == 1) return linear * strides[0];
     IndexT off = 0;
     for (int d = dims - 1; d > 0; --d) {
-      const IndexT q = linear / sizes[d];
-      off += (linear - q * sizes[d]) * strides[d];
+      const IndexT q = sizes[d].quotient(linear);
+      off += (linear - q * sizes[d].d) * strides[d];
       linear = q;
     }
     return off + linear * strides[0];
@@ -89,7 +113,7 @@ inline View<IndexT> collapse(const thcb200_tensor &d) {
   thcb200_collapse_dims(sz, st, &nd, -1);
   View<IndexT> v;
   v.dims = nd;
-  for (int i = 0; i < nd; ++i) { v.sizes[i] = (IndexT)sz[i]; v.strides[i] = (IndexT)st[i]; }
+  for (int i = 0; i < nd; ++i) { v.sizes[i].set((uint64_t)sz[i]); v.strides[i] = (IndexT)st[i]; }
   return v;
 }
 
@@ -101,29 +125,97 @@ inline int64_t numel(const thcb200_tensor &d) {
 }
 
 constexpr int kThreads = 256;
+constexpr int kPerThread = 4;   // elements per thread and step: their offsets are decoded together
+
+// A thread takes kPerThread elements, kThreads apart (neighbouring lanes on neighbouring elements),
+// decodes all their offsets first and then runs the functor on each.  NOALIAS (picked on the host
+// when the operands' memory ranges are disjoint) lets the compiler start the loads of all four
+// before the first store; otherwise a store through one pointer orders every later load.
+#define THCB_USER_PTR(T, NOALIAS) typename PtrOf<T, NOALIAS>::type
+template <typename T, bool NOALIAS> struct PtrOf { typedef T *type; };
+template <typename T> struct PtrOf<T, true> { typedef T *__restrict__ type; };
 
 template <typename Op, typename Ta, typename IndexT>
 __global__ void __launch_bounds__(kThreads) apply1_kernel(Ta *a, View<IndexT> va, IndexT n, Op op) {
-  for (IndexT i = (IndexT)blockIdx.x * kThreads + threadIdx.x; i < n; i += (IndexT)gridDim.x * kThreads)
-    op(&a[va.offset(i)]);
+  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
+  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+    IndexT oa[kPerThread];
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      oa[u] = (i < n && i >= base) ? va.offset(i) : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      if (i < n && i >= base) op(&a[oa[u]]);
+    }
+    if (base + step < base) break;   // the index type would wrap
+  }
 }
-template <typename Op, typename Ta, typename Tb, typename IndexT>
-__global__ void __launch_bounds__(kThreads) apply2_kernel(Ta *a, View<IndexT> va, Tb *b, View<IndexT> vb, IndexT n, Op op) {
-  for (IndexT i = (IndexT)blockIdx.x * kThreads + threadIdx.x; i < n; i += (IndexT)gridDim.x * kThreads)
-    op(&a[va.offset(i)], &b[vb.offset(i)]);
-}
-template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT>
+template <typename Op, typename Ta, typename Tb, typename IndexT, bool NOALIAS>
 __global__ void __launch_bounds__(kThreads)
-apply3_kernel(Ta *a, View<IndexT> va, Tb *b, View<IndexT> vb, Tc *c, View<IndexT> vc, IndexT n, Op op) {
-  for (IndexT i = (IndexT)blockIdx.x * kThreads + threadIdx.x; i < n; i += (IndexT)gridDim.x * kThreads)
-    op(&a[va.offset(i)], &b[vb.offset(i)], &c[vc.offset(i)]);
+apply2_kernel(THCB_USER_PTR(Ta, NOALIAS) a, View<IndexT> va, THCB_USER_PTR(Tb, NOALIAS) b, View<IndexT> vb, IndexT n, Op op) {
+  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
+  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+    IndexT oa[kPerThread], ob[kPerThread];
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      const bool ok = i < n && i >= base;
+      oa[u] = ok ? va.offset(i) : 0;
+      ob[u] = ok ? vb.offset(i) : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      if (i < n && i >= base) op(&a[oa[u]], &b[ob[u]]);
+    }
+    if (base + step < base) break;
+  }
 }
+template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT, bool NOALIAS>
+__global__ void __launch_bounds__(kThreads)
+apply3_kernel(THCB_USER_PTR(Ta, NOALIAS) a, View<IndexT> va, THCB_USER_PTR(Tb, NOALIAS) b, View<IndexT> vb,
+              THCB_USER_PTR(Tc, NOALIAS) c, View<IndexT> vc, IndexT n, Op op) {
+  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
+  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+    IndexT oa[kPerThread], ob[kPerThread], oc[kPerThread];
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      const bool ok = i < n && i >= base;
+      oa[u] = ok ? va.offset(i) : 0;
+      ob[u] = ok ? vb.offset(i) : 0;
+      oc[u] = ok ? vc.offset(i) : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+      const IndexT i = base + (IndexT)u * kThreads;
+      if (i < n && i >= base) op(&a[oa[u]], &b[ob[u]], &c[oc[u]]);
+    }
+    if (base + step < base) break;
+  }
+}
+#undef THCB_USER_PTR
 
 inline unsigned grid_for(int64_t n) {
   // enough CTAs to fill a B200 several times over; the kernels stride over the rest
-  int64_t blocks = (n + kThreads - 1) / kThreads;
-  const int64_t cap = 148 * 16;  // keeps i + gridDim.x * kThreads inside 32 bits for every n the 32-bit path accepts
+  int64_t blocks = (n + kThreads * kPerThread - 1) / (kThreads * kPerThread);
+  const int64_t cap = 148 * 16;  // keeps the loop's step inside 32 bits for every n the 32-bit path accepts
   return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+// True when the two tensors live in storages whose memory does not overlap: the kernels may then
+// be told that their pointers do not alias.  Storages, not views: a functor may reach neighbours of
+// its element through the pointer, but never leaves the tensor's storage.
+template <typename TensorTypeA, typename TensorTypeB>
+inline bool storages_apart(TensorTypeA *a, TensorTypeB *b) {
+  if (!a->storage || !b->storage || !a->storage->data || !b->storage->data) return false;
+  const uintptr_t al = (uintptr_t)a->storage->data, bl = (uintptr_t)b->storage->data;
+  const uintptr_t ah = al + (size_t)a->storage->size * sizeof(typename TensorAccess<TensorTypeA>::DataType);
+  const uintptr_t bh = bl + (size_t)b->storage->size * sizeof(typename TensorAccess<TensorTypeB>::DataType);
+  return ah <= bl || bh <= al;
 }
 
 // Replaces an aliasing ReadWrite operand by a contiguous copy; `orig` remembers the original.
@@ -185,12 +277,14 @@ bool THC_pointwiseApply2(THCState *state, TensorTypeA *a, TensorTypeB *b, const 
   typedef typename TensorAccess<TensorTypeA>::DataType Ta;
   typedef typename TensorAccess<TensorTypeB>::DataType Tb;
   if (n > 0) {
-    if (thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db))
-      apply2_kernel<Op, Ta, Tb, uint32_t><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<uint32_t>(da), (Tb *)db.data,
-                                                                          collapse<uint32_t>(db), (uint32_t)n, op);
-    else
-      apply2_kernel<Op, Ta, Tb, uint64_t><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<uint64_t>(da), (Tb *)db.data,
-                                                                          collapse<uint64_t>(db), (uint64_t)n, op);
+    const bool apart = storages_apart(a, b);
+    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db);
+#define THCB_USER_LAUNCH2(IDX, NA)                                                                                   \
+  apply2_kernel<Op, Ta, Tb, IDX, NA><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, \
+                                                                       collapse<IDX>(db), (IDX)n, op)
+    if (i32) { if (apart) THCB_USER_LAUNCH2(uint32_t, true); else THCB_USER_LAUNCH2(uint32_t, false); }
+    else { if (apart) THCB_USER_LAUNCH2(uint64_t, true); else THCB_USER_LAUNCH2(uint64_t, false); }
+#undef THCB_USER_LAUNCH2
   }
   restore_overlap(state, a, oa);
   restore_overlap(state, b, ob);
@@ -218,14 +312,14 @@ bool THC_pointwiseApply3(THCState *state, TensorTypeA *a, TensorTypeB *b, Tensor
   typedef typename TensorAccess<TensorTypeB>::DataType Tb;
   typedef typename TensorAccess<TensorTypeC>::DataType Tc;
   if (n > 0) {
-    if (thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db) && thcb200_can_use_32bit(&dc))
-      apply3_kernel<Op, Ta, Tb, Tc, uint32_t><<<grid_for(n), kThreads, 0, st>>>(
-          (Ta *)da.data, collapse<uint32_t>(da), (Tb *)db.data, collapse<uint32_t>(db), (Tc *)dc.data, collapse<uint32_t>(dc),
-          (uint32_t)n, op);
-    else
-      apply3_kernel<Op, Ta, Tb, Tc, uint64_t><<<grid_for(n), kThreads, 0, st>>>(
-          (Ta *)da.data, collapse<uint64_t>(da), (Tb *)db.data, collapse<uint64_t>(db), (Tc *)dc.data, collapse<uint64_t>(dc),
-          (uint64_t)n, op);
+    const bool apart = storages_apart(a, b) && storages_apart(a, c) && storages_apart(b, c);
+    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db) && thcb200_can_use_32bit(&dc);
+#define THCB_USER_LAUNCH3(IDX, NA)                                                                                       \
+  apply3_kernel<Op, Ta, Tb, Tc, IDX, NA><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, \
+                                                                           collapse<IDX>(db), (Tc *)dc.data, collapse<IDX>(dc), (IDX)n, op)
+    if (i32) { if (apart) THCB_USER_LAUNCH3(uint32_t, true); else THCB_USER_LAUNCH3(uint32_t, false); }
+    else { if (apart) THCB_USER_LAUNCH3(uint64_t, true); else THCB_USER_LAUNCH3(uint64_t, false); }
+#undef THCB_USER_LAUNCH3
   }
   restore_overlap(state, a, oa);
   restore_overlap(state, b, ob);

@@ -392,6 +392,50 @@ THCB200_API int thcb200_mask_coords(thcb200_ctx *ctx, const thcb200_tensor *out_
                         const thcb200_tensor *mask_u8, const int64_t *sizes, int nd,
                         void *stream, int flags);
 
+/* ---- sharded reductions: one rank per GPU of a box, NCCL over NVLink ---------------------
+ *
+ * cutorch drives several GPUs from one process and has no collective layer
+ * (lib/THC/THCGeneral.h.in:57-123); these calls are what a tensor split by rows over several
+ * GPUs needs on top of the per-device ones.  A communicator is NCCL's: one rank calls
+ * thcb200_comm_unique_id and hands the THCB200_COMM_ID_BYTES to the others by any means (MPI, a
+ * file, torch.distributed ...), then every rank, with its own device current, calls
+ * thcb200_comm_create (collective: it returns when all ranks have joined).  NCCL is looked up at
+ * run time (libnccl.so.2, or the path in the environment variable THCB200_NCCL_LIB); without it
+ * these calls return THCB200_ERR_UNSUPPORTED and the rest of the library works as before.
+ * Every rank must make the same sequence of sharded calls.  All work is asynchronous on `stream`. */
+typedef struct thcb200_comm thcb200_comm;
+#define THCB200_COMM_ID_BYTES 128
+THCB200_API int thcb200_comm_unique_id(void *id, size_t bytes);
+THCB200_API int thcb200_comm_create(thcb200_comm **out, int nranks, int rank, const void *id, size_t bytes);
+THCB200_API void thcb200_comm_destroy(thcb200_comm *comm);
+THCB200_API int thcb200_comm_info(const thcb200_comm *comm, int *nranks, int *rank, int *nccl_version);
+/* ncclAllReduce in place over `count` elements (rop: THCB200_RED_SUM / PROD / MIN / MAX); dtypes NCCL has. */
+THCB200_API int thcb200_comm_all_reduce(thcb200_comm *comm, void *buf_dev, int64_t count, int dtype, int rop, void *stream);
+/* ncclAllGather of `bytes_per_rank` bytes from every rank into recv_dev[rank * bytes_per_rank ...]. */
+THCB200_API int thcb200_comm_all_gather(thcb200_comm *comm, const void *send_dev, void *recv_dev, int64_t bytes_per_rank, void *stream);
+
+/* thcb200_reduce_all over a tensor whose rows are split over the ranks: each rank folds its block,
+ * the accumulators (double / int64, in the 8-byte slot `result_dev` on each rank) are combined, and
+ * every rank ends with the global result in its slot.  Sums, products and integer min / max are one
+ * ncclAllReduce on the slot; floating min / max gather the slots and fold them in rank order with
+ * the library's kernel, so that a NaN wins as in the unsharded call. */
+THCB200_API int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, int pre, thcb200_scalar s,
+                               const thcb200_tensor *in, void *result_dev, void *stream);
+/* thcb200_reduce_dim along the dim the tensor is split on: each rank reduces its rows into `out`
+ * (dense), then the ranks' outputs are folded and every rank holds the result in `out`.  float /
+ * double / int32 / int64 sums and products and integer min / max use ncclAllReduce on the element
+ * type (each rank's partial is rounded to the element type first); every other case gathers the
+ * ranks' vectors and folds them in rank order with thcb200_reduce_dim. */
+THCB200_API int thcb200_sharded_reduce_dim(thcb200_ctx *ctx, thcb200_comm *comm, int rop, int pre, thcb200_scalar s,
+                               const thcb200_tensor *out, const thcb200_tensor *in, int dim, void *stream);
+/* thcb200_reduce_dim_index along the split dim: `shard_start` is the number of rows in front of
+ * this rank's block.  (value, global position) pairs are all-gathered and combined with the rule of
+ * the unsharded call: the largest (smallest) value, a NaN first, the lowest global position among
+ * equals.  `values` and `indices` (1-based, global) are dense and end up identical on every rank. */
+THCB200_API int thcb200_sharded_reduce_dim_index(thcb200_ctx *ctx, thcb200_comm *comm, int rop,
+                                     const thcb200_tensor *values, const thcb200_tensor *indices,
+                                     const thcb200_tensor *in, int dim, int64_t shard_start, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

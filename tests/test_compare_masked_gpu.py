@@ -247,7 +247,7 @@ def test_mask_coords_of_a_mask_that_starts_off_a_16_byte_boundary(state, shift):
     base = (r.uniform(size=n + shift) < 0.3).astype(np.uint8)
     dbase = to_device(state, base)
     dmask = dbase.narrow(0, shift, n)
-    assert dmask.data_ptr() % 16 == shift % 16
+    assert dmask.data_ptr % 16 == shift % 16
     mask = base[shift:]
     want = np.argwhere(mask.reshape(-1) != 0).astype(np.int64) + 1
     ctx, stream = C.c_void_p(state.context), C.c_void_p(state.stream)
