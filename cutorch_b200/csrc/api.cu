@@ -10,6 +10,7 @@
 
 namespace thcb {
 int64_t launch_count();
+void arm_allocation_failure(int nth);
 
 void *ctx_workspace(thcb200_ctx *ctx, size_t bytes) {
   if (bytes <= ctx->ws_bytes) return ctx->ws;
@@ -21,7 +22,7 @@ void *ctx_workspace(thcb200_ctx *ctx, size_t bytes) {
   size_t want = 1 << 20;
   while (want < bytes) want <<= 1;
   void *p = nullptr;
-  if (cudaMalloc(&p, want) != cudaSuccess) {
+  if (device_alloc(&p, want) != cudaSuccess) {
     cudaGetLastError();
     set_error("workspace: cannot allocate %zu bytes", want);
     return nullptr;
@@ -125,7 +126,7 @@ int run_pointwise(thcb200_ctx *ctx, int op, HostView *v, int nops, thcb200_scala
     // Views that stay deeper than kGenericDims after collapsing go through dense copies.
     for (int o = 0; o < nops && rc == 0; ++o) {
       if (plan.gdims[o] <= kGenericDims) continue;
-      if (cudaMallocAsync(&temps[o], (size_t)v[o].numel * esz, st) != cudaSuccess) {
+      if (device_alloc_async(&temps[o], (size_t)v[o].numel * esz, st) != cudaSuccess) {
         cudaGetLastError();
         set_error("pointwise: cannot allocate a dense temporary");
         rc = THCB200_ERR_NOMEM;
@@ -210,6 +211,7 @@ void *thcb200_ctx_workspace(thcb200_ctx *ctx, size_t min_bytes, size_t *bytes) {
   return p;
 }
 
+void thcb200_debug_fail_allocation(int nth) { arm_allocation_failure(nth); }
 const char *thcb200_last_error(void) { return get_error(); }
 int64_t thcb200_launch_count(void) { return launch_count(); }
 const char *thcb200_last_plan(void) { return get_plan_name(); }
@@ -243,6 +245,29 @@ int thcb200_can_use_32bit(const thcb200_tensor *t) {
   HostView v;
   if (to_host_view(t, &v, "can_use_32bit")) return 0;
   return can_use_32bit(v) ? 1 : 0;
+}
+
+int thcb200_view_extent(const thcb200_tensor *t, int64_t *min_offset, int64_t *max_offset) {
+  HostView v;
+  if (to_host_view(t, &v, "view_extent")) return THCB200_ERR_ARG;
+  if (v.numel == 0) return 0;
+  int64_t lo = 0, hi = 0;
+  offset_range(v, &lo, &hi);
+  if (min_offset) *min_offset = lo;
+  if (max_offset) *max_offset = hi;
+  return 1;
+}
+
+int thcb200_check_extent(const thcb200_tensor *t, int64_t elements_before, int64_t elements_after) {
+  int64_t lo = 0, hi = 0;
+  const int rc = thcb200_view_extent(t, &lo, &hi);
+  if (rc <= 0) return rc;
+  if (lo < -elements_before || hi > elements_after) {
+    set_error("the view reaches offsets %lld..%lld; the allocation allows %lld..%lld", (long long)lo, (long long)hi,
+              (long long)-elements_before, (long long)elements_after);
+    return THCB200_ERR_SIZE;
+  }
+  return THCB200_OK;
 }
 
 int64_t thcb200_index_to_offset(const thcb200_tensor *t, int64_t linear) {
@@ -310,7 +335,7 @@ int thcb200_pointwise_ex(thcb200_ctx *ctx, int op, const thcb200_tensor *out, co
     // temporary and written back element by element; which duplicate lands last is not
     // defined (lib/THC/THCApply.cuh:288-302,401-417).
     void *tmp = nullptr;
-    if (cudaMallocAsync(&tmp, (size_t)v[0].numel * esz, st) != cudaSuccess) {
+    if (device_alloc_async(&tmp, (size_t)v[0].numel * esz, st) != cudaSuccess) {
       cudaGetLastError();
       set_error("pointwise: cannot allocate a dense temporary");
       return THCB200_ERR_NOMEM;

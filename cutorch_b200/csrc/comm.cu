@@ -157,7 +157,7 @@ void *comm_buffer(thcb200_comm *comm, size_t bytes) {
   comm->buf_bytes = 0;
   size_t want = 1 << 16;
   while (want < bytes) want <<= 1;
-  if (cudaMalloc(&comm->buf, want) != cudaSuccess) {
+  if (device_alloc(&comm->buf, want) != cudaSuccess) {
     cudaGetLastError();
     comm->buf = nullptr;
     set_error("comm buffer: cannot allocate %zu bytes", want);

@@ -49,6 +49,12 @@ namespace thcb {
 // that asks for more.  Growing synchronises the device; nullptr on allocation failure.
 void *ctx_workspace(thcb200_ctx *ctx, size_t bytes);
 
+// Every device allocation the library makes for itself (workspaces, dense temporaries) goes through
+// these two, so that a test can make the n-th one fail the way an exhausted GPU would, without
+// exhausting a GPU: see thcb200_debug_fail_allocation in thcb200.h.
+cudaError_t device_alloc(void **p, size_t bytes);
+cudaError_t device_alloc_async(void **p, size_t bytes, cudaStream_t st);
+
 #define THCB_CUDA_TRY(expr)                                                              \
   do {                                                                                   \
     cudaError_t _e = (expr);                                                             \

@@ -135,7 +135,7 @@ extern "C" THCB200_API int thcb200_copy_from_host(thcb200_ctx *ctx, const thcb20
     // the span the view covers goes up as it is; the device walks it with the view's strides
     const size_t span_bytes = (size_t)span_elems(vs) * esz;
     void *tmp = nullptr;
-    cudaError_t e = cudaMallocAsync(&tmp, span_bytes, st);
+    cudaError_t e = device_alloc_async(&tmp, span_bytes, st);
     if (e == cudaSuccess) e = cudaMemcpyAsync(tmp, vs.data, span_bytes, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) {
       thcb200_tensor up = span_desc(tmp, vs);
@@ -160,7 +160,7 @@ extern "C" THCB200_API int thcb200_copy_from_host(thcb200_ctx *ctx, const thcb20
     e = cudaMemcpyAsync(vd.data, wire, bytes, cudaMemcpyHostToDevice, st);
   } else {
     void *tmp = nullptr;
-    e = cudaMallocAsync(&tmp, bytes, st);
+    e = device_alloc_async(&tmp, bytes, st);
     if (e == cudaSuccess) e = cudaMemcpyAsync(tmp, wire, bytes, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) {
       thcb200_tensor dense = dense_desc(tmp, vs.dtype, vs.numel);
@@ -195,7 +195,7 @@ extern "C" THCB200_API int thcb200_copy_to_host(thcb200_ctx *ctx, const thcb200_
     const int64_t span = span_elems(vd);
     const size_t span_bytes = (size_t)span * esz;
     void *tmp = nullptr;
-    cudaError_t e = cudaMallocAsync(&tmp, span_bytes, st);
+    cudaError_t e = device_alloc_async(&tmp, span_bytes, st);
     if (e == cudaSuccess && span != vd.numel) e = cudaMemcpyAsync(tmp, vd.data, span_bytes, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) {
       thcb200_tensor down = span_desc(tmp, vd);
@@ -220,7 +220,7 @@ extern "C" THCB200_API int thcb200_copy_to_host(thcb200_ctx *ctx, const thcb200_
     e = cudaMemcpyAsync(wire, vs.data, bytes, cudaMemcpyDeviceToHost, st);
   } else {
     // the device packs (and converts) into a dense temporary of the host side's type
-    e = cudaMallocAsync(&tmp, bytes, st);
+    e = device_alloc_async(&tmp, bytes, st);
     if (e == cudaSuccess) {
       thcb200_tensor dense = dense_desc(tmp, vd.dtype, vd.numel);
       rc = device_copy(ctx, &dense, src, stream);

@@ -681,7 +681,7 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
     }
     size_t want = 1 << 20;
     while (want < need) want <<= 1;
-    if (cudaMalloc(&ctx->mask_ws, want) != cudaSuccess) {
+    if (device_alloc(&ctx->mask_ws, want) != cudaSuccess) {
       cudaGetLastError();
       ctx->mask_ws = nullptr;
       set_error("masked: cannot allocate %zu bytes of tile offsets", want);

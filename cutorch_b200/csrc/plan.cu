@@ -1,5 +1,6 @@
 // Host-side layout analysis for the apply / reduce planners (no device code).
 #include "plan.h"
+#include "context.h"
 
 #include <stdarg.h>
 #include <stdio.h>
@@ -26,6 +27,25 @@ void set_plan_name(const char *name) { g_plan = name; }
 const char *get_plan_name() { return g_plan; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+// countdown to an injected allocation failure: 0 = off, n = the n-th allocation from now fails
+static std::atomic<int> g_fail_alloc_in{0};
+static bool injected_failure() {
+  int n = g_fail_alloc_in.load(std::memory_order_relaxed);
+  while (n > 0) {
+    if (g_fail_alloc_in.compare_exchange_weak(n, n - 1, std::memory_order_relaxed)) return n == 1;
+  }
+  return false;
+}
+void arm_allocation_failure(int nth) { g_fail_alloc_in.store(nth > 0 ? nth : 0, std::memory_order_relaxed); }
+cudaError_t device_alloc(void **p, size_t bytes) {
+  if (injected_failure()) { *p = nullptr; return cudaErrorMemoryAllocation; }
+  return cudaMalloc(p, bytes);
+}
+cudaError_t device_alloc_async(void **p, size_t bytes, cudaStream_t st) {
+  if (injected_failure()) { *p = nullptr; return cudaErrorMemoryAllocation; }
+  return cudaMallocAsync(p, bytes, st);
+}
 
 bool pdl_enabled() {
   static const bool on = [] {

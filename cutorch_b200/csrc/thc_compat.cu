@@ -104,6 +104,8 @@ struct THCState {
   unsigned char *p2pOff;      // numDevices x numDevices: 1 = direct access switched off by the caller
   cudaDeviceProp *props;      // per device, filled on first request
   unsigned char *propsValid;
+  void (*gcFunction)(void *); // called once when a device allocation fails, before one retry
+  void *gcData;
 };
 
 namespace {
@@ -117,6 +119,19 @@ cudaStream_t state_stream(THCState *state);
 // current when it is freed, so a storage has to be freed while the stream that last used it is
 // current (or after that stream was synchronised).
 cudaError_t default_malloc(void *, void **p, size_t n, cudaStream_t st) { return cudaMallocAsync(p, n, st); }
+
+// Device allocation as cutorch's THCudaMalloc does it (lib/THC/THCGeneral.c:842-854): when the
+// allocator fails and the host language registered a garbage-collection callback, run it (it frees
+// tensors nobody refers to any more) and try once more.  The failed attempt's error is cleared.
+cudaError_t malloc_with_gc_retry(THCState *state, THCDeviceAllocator *a, void *actx, void **p, size_t n, cudaStream_t st) {
+  cudaError_t e = a->malloc(actx, p, n, st);
+  if (e != cudaSuccess && state && state->gcFunction) {
+    cudaGetLastError();
+    state->gcFunction(state->gcData);
+    e = a->malloc(actx, p, n, st);
+  }
+  return e;
+}
 
 // States that are initialised right now: a storage may outlive its THCState, and must not follow a
 // dangling pointer when it is finally freed (it is then released in the order of the null stream).
@@ -392,7 +407,11 @@ void __THCudaCheck(cudaError_t err, const char *file, const int line) {
   API_END
 }
 cudaError_t THCudaMalloc(THCState *state, void **ptr, size_t size) {
-  return state->allocator->malloc(state->allocator->state, ptr, size, state_stream(state));
+  return malloc_with_gc_retry(state, state->allocator, state->allocator->state, ptr, size, state_stream(state));
+}
+void THCSetGCHandler(THCState *state, void (*gc_function)(void *data), void *data) {
+  state->gcFunction = gc_function;
+  state->gcData = data;
 }
 cudaError_t THCudaFree(THCState *state, void *ptr) { return state->allocator->free(state->allocator->state, ptr); }
 
@@ -522,7 +541,7 @@ template <typename R> StorageT<R> *storage_new(THCState *state, ptrdiff_t size) 
   s->device = current_device();
   s->size = size;
   if (size > 0) {
-    cudaError_t e = s->allocator->malloc(s->allocatorContext, (void **)&s->data, (size_t)size * sizeof(R), state_stream(state));
+    cudaError_t e = malloc_with_gc_retry(state, s->allocator, s->allocatorContext, (void **)&s->data, (size_t)size * sizeof(R), state_stream(state));
     if (e != cudaSuccess) {
       cudaGetLastError();
       free(s);
@@ -555,7 +574,7 @@ template <typename R> void storage_resize(THCState *state, StorageT<R> *s, ptrdi
   if (!s->data) s->device = current_device();
   R *nd = nullptr;
   if (size > 0) {
-    cudaError_t e = s->allocator->malloc(s->allocatorContext, (void **)&nd, (size_t)size * sizeof(R), state_stream(state));
+    cudaError_t e = malloc_with_gc_retry(state, s->allocator, s->allocatorContext, (void **)&nd, (size_t)size * sizeof(R), state_stream(state));
     if (e != cudaSuccess) { cudaGetLastError(); th_error("cuda runtime error (%d) : %s", (int)e, cudaGetErrorString(e)); }
     if (s->data && s->size > 0) {
       const ptrdiff_t keep = size < s->size ? size : s->size;
@@ -616,22 +635,26 @@ template <typename R> void tensor_raw_resize(THCState *state, TensorT<R> *t, int
   }
   if (same) return;
   if (nd <= 0) { t->nDimension = 0; return; }
-  if (nd != t->nDimension) {
-    t->size = (long *)realloc(t->size, sizeof(long) * nd);
-    t->stride = (long *)realloc(t->stride, sizeof(long) * nd);
-    t->nDimension = nd;
-  }
+  // the new strides and the extent they need are worked out first and the storage is grown before
+  // the tensor's own fields change: if the allocation fails the tensor is left as it was
+  long new_stride[THCB200_MAX_DIMS > 32 ? THCB200_MAX_DIMS : 32];
+  if (nd > (int)(sizeof(new_stride) / sizeof(new_stride[0]))) th_arg_error(1, CUTORCH_DIM_WARNING);
   ptrdiff_t extent = 1;
   for (int d = nd - 1; d >= 0; --d) {
-    t->size[d] = size[d];
-    if (stride && stride[d] >= 0) t->stride[d] = stride[d];
-    else t->stride[d] = (d == nd - 1) ? 1 : t->size[d + 1] * t->stride[d + 1];
-    extent += (ptrdiff_t)(t->size[d] - 1) * t->stride[d];
+    if (stride && stride[d] >= 0) new_stride[d] = stride[d];
+    else new_stride[d] = (d == nd - 1) ? 1 : size[d + 1] * new_stride[d + 1];
+    extent += (ptrdiff_t)(size[d] - 1) * new_stride[d];
   }
   if (extent + t->storageOffset > 0) {
     if (!t->storage) t->storage = storage_new<R>(state, 0);
     if (extent + t->storageOffset > t->storage->size) storage_resize<R>(state, t->storage, extent + t->storageOffset);
   }
+  if (nd != t->nDimension) {
+    t->size = (long *)realloc(t->size, sizeof(long) * nd);
+    t->stride = (long *)realloc(t->stride, sizeof(long) * nd);
+    t->nDimension = nd;
+  }
+  for (int d = 0; d < nd; ++d) { t->size[d] = size[d]; t->stride[d] = new_stride[d]; }
 }
 
 template <typename R> void tensor_raw_set(THCState *state, TensorT<R> *t, StorageT<R> *storage, ptrdiff_t offset, int nd,
@@ -750,6 +773,19 @@ template <typename R> thcb200_tensor describe(const TensorT<R> *t) {
   if (t->nDimension > THCB200_MAX_DIMS) th_arg_error(2, CUTORCH_DIM_WARNING);
   for (int i = 0; i < t->nDimension; ++i) { d.sizes[i] = t->size[i]; d.strides[i] = t->stride[i]; }
   d.data = (t->storage && t->storage->data) ? (void *)(t->storage->data + t->storageOffset) : nullptr;
+  // Every kernel trusts the view: the smallest and the largest element offset it can reach (as
+  // canUse32BitIndexMath works out the largest, lib/THC/THCTensorTypeUtils.cu:220-245) have to lie
+  // inside the storage.  cutorch's kernels assert on their offsets in debug builds
+  // (lib/THC/THCTensorInfo.cuh:228-278); here the view is refused on the host, before any launch.
+  if (t->storage && t->nDimension > 0) {
+    int64_t lo = 0, hi = 0;
+    if (thcb200_view_extent(&d, &lo, &hi) == 1) {
+      const int64_t first = (int64_t)t->storageOffset + lo, last = (int64_t)t->storageOffset + hi;
+      if (first < 0 || last >= (int64_t)t->storage->size)
+        th_error("tensor view reaches elements %lld..%lld of a storage of %lld elements", (long long)first, (long long)last,
+                 (long long)t->storage->size);
+    }
+  }
   return d;
 }
 

@@ -112,6 +112,9 @@ THC_API struct cudaDeviceProp *THCState_getCurrentDeviceProperties(THCState *sta
 THC_API void *THCState_getCurrentDeviceScratchSpace(THCState *state);
 THC_API size_t THCState_getCurrentDeviceScratchSpaceSize(THCState *state);
 THC_API void __THCudaCheck(cudaError_t err, const char *file, const int line);
+/* Registers the callback THCudaMalloc and the storage allocations run once, before one retry, when
+ * the device allocator fails (lib/THC/THCGeneral.c:836-854: cutorch hands Lua's collector here). */
+THC_API void THCSetGCHandler(THCState *state, void (*cutorchGCFunction_)(void *data), void *data);
 THC_API cudaError_t THCudaMalloc(THCState *state, void **ptr, size_t size);
 THC_API cudaError_t THCudaFree(THCState *state, void *ptr);
 THC_API THCStream *THCStream_new(int flags);

@@ -157,6 +157,12 @@ THCB200_API void thcb200_ctx_destroy(thcb200_ctx *ctx);
  * THCState_getCurrentDeviceScratchSpace (lib/THC/THCGeneral.c:677-712). */
 THCB200_API void *thcb200_ctx_workspace(thcb200_ctx *ctx, size_t min_bytes, size_t *bytes);
 THCB200_API const char *thcb200_last_error(void);
+/* Failure injection for tests: the nth device allocation the library makes for itself from now on
+ * (workspace growth, mask offsets, dense temporaries, gather buffers) fails as if the GPU were out
+ * of memory, without any CUDA call; 0 disarms.  The call that hits it returns THCB200_ERR_NOMEM and
+ * leaves its context usable.  cutorch reports a failed allocation through THCudaCheck / THError
+ * (lib/THC/THCGeneral.c:714-726, 842-854); nothing in its tree injects one. */
+THCB200_API void thcb200_debug_fail_allocation(int nth);
 /* Number of kernels this library has launched in this process (all contexts). */
 THCB200_API int64_t thcb200_launch_count(void);
 /* Name of the kernel family picked by the most recent pointwise / reduce call of this
@@ -176,6 +182,17 @@ THCB200_API int thcb200_collapse_dims(int64_t *sizes, int64_t *strides, int *ndi
 /* 1 if two distinct index tuples of the view address the same element. */
 THCB200_API int thcb200_overlapping(const thcb200_tensor *t);
 /* 1 if element count and largest offset both fit 32-bit unsigned arithmetic. */
+/* The smallest and largest element offset (relative to `data`) that the view can reach: the sums
+ * of (size - 1) * stride over the dims with negative and with positive strides, as
+ * TensorUtils::canUse32BitIndexMath computes the largest (lib/THC/THCTensorTypeUtils.cu:220-245).
+ * Returns 1 and fills the outputs, 0 for a view without elements, a negative status for a bad
+ * descriptor.  thcb200_check_extent refuses (THCB200_ERR_SIZE) a view that reaches more than
+ * `elements_before` elements in front of `data` or more than `elements_after` behind it: the check
+ * a caller who knows the allocation runs before handing the view to a kernel (the THC layer runs
+ * it against the storage's size on every call; cutorch asserts inside its kernels instead,
+ * lib/THC/THCTensorInfo.cuh:228-278). */
+THCB200_API int thcb200_view_extent(const thcb200_tensor *t, int64_t *min_offset, int64_t *max_offset);
+THCB200_API int thcb200_check_extent(const thcb200_tensor *t, int64_t elements_before, int64_t elements_after);
 THCB200_API int thcb200_can_use_32bit(const thcb200_tensor *t);
 /* Element offset of logical (row-major) index `linear` in the view. */
 THCB200_API int64_t thcb200_index_to_offset(const thcb200_tensor *t, int64_t linear);

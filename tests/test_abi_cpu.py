@@ -146,3 +146,29 @@ def test_library_reports_missing_cuda_cleanly():
     ctx = C.c_void_p()
     rc = lib.thcb200_ctx_create(C.byref(ctx), 0)
     assert rc == -4 and lib.thcb200_last_error()
+
+
+def test_view_extent_and_the_check_against_an_allocation():
+    """The host-side bound check that stands in for cutorch's device-side asserts
+    (lib/THC/THCTensorInfo.cuh:228-278): the smallest and largest offset a view reaches, as
+    canUse32BitIndexMath sums them (lib/THC/THCTensorTypeUtils.cu:220-245), against what the
+    caller says the allocation holds."""
+    lib = _lib.load_library()
+    P = C.POINTER
+    lib.thcb200_view_extent.argtypes = [P(_lib.TensorDesc), P(C.c_int64), P(C.c_int64)]
+    lib.thcb200_check_extent.argtypes = [P(_lib.TensorDesc), C.c_int64, C.c_int64]
+    lo, hi = C.c_int64(7), C.c_int64(7)
+    cases = [(((4, 5), (5, 1)), 0, 19), (((4, 5), (1, 4)), 0, 19), (((3, 4), (8, 2)), 0, 22), (((10,), (0,)), 0, 0),
+             (((3, 4), (-4, 1)), -8, 3), (((2, 3, 4), (100, -10, 3)), -20, 109)]
+    for (sizes, strides), wlo, whi in cases:
+        d = _lib.make_desc(0x1000, 6, sizes, strides)
+        assert lib.thcb200_view_extent(C.byref(d), C.byref(lo), C.byref(hi)) == 1
+        assert (lo.value, hi.value) == (wlo, whi), (sizes, strides)
+        assert lib.thcb200_check_extent(C.byref(d), -wlo, whi) == 0
+        assert lib.thcb200_check_extent(C.byref(d), -wlo, whi - 1) == (-3 if whi > 0 else 0) or whi == 0
+        if wlo < 0:
+            assert lib.thcb200_check_extent(C.byref(d), -wlo - 1, whi) == -3
+            assert b"reaches offsets" in lib.thcb200_last_error()
+    empty = _lib.make_desc(0x1000, 6, (3, 0), (1, 1))
+    assert lib.thcb200_view_extent(C.byref(empty), C.byref(lo), C.byref(hi)) == 0
+    assert lib.thcb200_check_extent(C.byref(empty), 0, 0) == 0

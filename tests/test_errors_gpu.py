@@ -257,3 +257,23 @@ def test_single_element_accessors(state, kind):
     wrong(state.ptr, to_device(state, np.zeros(3, thc.KINDS[kind][1])).ptr, 0, 0)
     with pytest.raises(thc.THCError, match="two dimensions"):
         state.check()
+
+
+def test_a_view_that_leaves_its_storage_is_refused_before_any_launch(state):
+    """cutorch asserts on offsets inside its kernels in debug builds (lib/THC/THCTensorInfo.cuh:228-278);
+    here every call checks on the host that the view's smallest and largest offset lie inside the
+    storage, so a bad view costs an error message, not a stray write."""
+    buf = to_device(state, np.arange(100, dtype=np.float32))
+    launches = state.lib.thcb200_launch_count()
+    inside = thc.Tensor.wrap(state, "Float", buf.data_ptr, (10, 10), (10, 1), storage_elems=100)
+    inside.add(inside, 1.0)
+    assert state.lib.thcb200_launch_count() == launches + 1
+    for sizes, strides in [((10, 11), (10, 1)), ((101,), (1,)), ((2, 2), (99, 1))]:
+        bad = thc.Tensor.wrap(state, "Float", buf.data_ptr, sizes, strides, storage_elems=100)
+        with pytest.raises(thc.THCError, match="storage of 100 elements"):
+            bad.add(bad, 1.0)
+        with pytest.raises(thc.THCError, match="storage of 100 elements"):
+            bad.sumall()
+    assert state.lib.thcb200_launch_count() == launches + 1     # nothing was launched for the bad views
+    want = np.arange(100, dtype=np.float32) + 1
+    assert np.array_equal(buf.numpy(), want)

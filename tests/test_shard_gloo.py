@@ -115,3 +115,50 @@ def test_single_process_combine_is_identity():
     assert combine_partials(t, "sum").item() == 3.5
     v, p = combine_index_partials(torch.tensor([1.0, 2.0]), torch.tensor([4, 1]), 10)
     assert v.tolist() == [1.0, 2.0] and p.tolist() == [14, 11]
+
+
+def _worker_with_a_failing_rank(rank, world, port, results):
+    """Rank 1 fails on the host between steps (an exception before its collective) and leaves; rank 0
+    must come out of its collective with an error inside the process group's timeout, not wait for ever."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    partial = torch.tensor([float(rank + 1)], dtype=torch.float64)
+    combine_partials(partial, "sum")          # a first step that works: 1 + 2
+    assert partial.item() == 3.0
+    if rank == 1:
+        results.put(("rank1", "leaving"))
+        results.close()
+        results.join_thread()                 # the message is on its way before the process goes
+        os._exit(17)                          # the rank dies without joining the next collective
+    t0 = time.time()
+    try:
+        combine_partials(torch.tensor([1.0], dtype=torch.float64), "sum")
+        results.put(("rank0", "no error", time.time() - t0))
+    except Exception as e:                    # gloo reports the lost peer (or the timeout) as a RuntimeError
+        results.put(("rank0", "error", time.time() - t0, type(e).__name__))
+    results.close()
+    results.join_thread()
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_gives_the_others_an_error_not_a_hang():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() % 90)
+    procs = [ctx.Process(target=_worker_with_a_failing_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=90)
+        assert p.exitcode is not None, "a rank is still waiting: the collective hung"
+    got = {}
+    while not q.empty():
+        item = q.get(timeout=5)
+        got[item[0]] = item[1:]
+    assert got.get("rank1") == ("leaving",)
+    assert got["rank0"][0] == "error", got
+    assert got["rank0"][1] < 60, f"rank 0 needed {got['rank0'][1]:.0f} s to notice"
+    assert procs[1].exitcode == 17 and procs[0].exitcode == 0
