@@ -268,8 +268,12 @@ def test_a_view_that_leaves_its_storage_is_refused_before_any_launch(state):
     inside = thc.Tensor.wrap(state, "Float", buf.data_ptr, (10, 10), (10, 1), storage_elems=100)
     inside.add(inside, 1.0)
     assert state.lib.thcb200_launch_count() == launches + 1
-    for sizes, strides in [((10, 11), (10, 1)), ((101,), (1,)), ((2, 2), (99, 1))]:
-        bad = thc.Tensor.wrap(state, "Float", buf.data_ptr, sizes, strides, storage_elems=100)
+    # setStorage itself never builds such a view (it grows the storage or refuses); a view goes bad
+    # when something writes the tensor's fields directly, as FFI callers of cutorch can
+    for field, index, value in [("size", 1, 11), ("stride", 0, 12), ("size", 0, 11)]:
+        bad = thc.Tensor.wrap(state, "Float", buf.data_ptr, (10, 10), (10, 1), storage_elems=100)
+        raw = C.cast(bad.ptr, C.POINTER(thc._THTensor)).contents
+        getattr(raw, field)[index] = value
         with pytest.raises(thc.THCError, match="storage of 100 elements"):
             bad.add(bad, 1.0)
         with pytest.raises(thc.THCError, match="storage of 100 elements"):

@@ -62,7 +62,7 @@ class Guarded:
 
     def check_result(self, want: np.ndarray, what, rel=None, abs_sum=None):
         after = self.buf.numpy()
-        got = np.array(self._on(after), copy=True)
+        got = np.array(self._on(after), copy=True, order="C")
         if rel is None:
             same = got.view(np.uint8) == np.ascontiguousarray(want).view(np.uint8) if got.size else np.ones(0, bool)
             if not np.all(same):
@@ -186,7 +186,10 @@ def test_reduce_rows(state, oracle, shift):
 def test_reduce_columns(state, oracle, shift):
     r = rng("guard-redcol", shift)
     for kind, shape, layout in [("Float", (3001, 96), "contiguous"),     # split along K, 3001 rows
-                                ("Float", (515, 33), "contiguous"),      # odd width: one column per lane
+                                ("Float", (515, 33), "contiguous"),      # odd narrow width: one column per lane
+                                ("Float", (700, 131), "contiguous"),
+                                ("Int", (300, 257), "holes"), ("Long", (200, 75), "contiguous"),
+                                ("Float", (4000, 125), "contiguous"),    # the same with the rows split over CTAs
                                 ("Byte", (300, 64), "contiguous"),       # 4-byte column words
                                 ("Half", (1000, 72), "holes"), ("Short", (64, 5, 40), "contiguous"),
                                 ("Double", (70, 130), "offset")]:
