@@ -167,6 +167,7 @@ int reduce_all_typed(thcb200_ctx *ctx, int mode, const HostView &in, thcb200_sca
 // ------------------------------------------------------------------------------------
 // workspace bytes per partial accumulator (the largest is two doubles and a flag)
 constexpr size_t kPartialSlotBytes = 32;
+constexpr int kRedColScalarUnroll = 16;
 
 enum RedDimKind { kRedRowWarp, kRedRowBlock, kRedCol, kRedStrided };
 
@@ -358,7 +359,8 @@ int launch_reduce_dim(thcb200_ctx *ctx, const HostView &in, const HostView &out,
       const uint64_t blocks = pl.nslices * pl.tiles_i * pl.nsplit;
       set_plan_name(pl.nsplit > 1 ? "col_tile_split" : "col_tile");
       if (pl.vec) launch_pdl(reduce_col_kernel<T, MODE, INDEX, IS_MAX, CV, kRedUnroll>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
-      else launch_pdl(reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1, kRedUnroll>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
+      // one column per lane moves 4 bytes a load: more row loads in flight per thread make up for it
+      else launch_pdl(reduce_col_kernel<T, MODE, INDEX, IS_MAX, 1, kRedColScalarUnroll>, (unsigned)blocks, kRedThreads, 0, st, ip, op, xp, pl.map, pl.nslices, pl.K, pl.strideK, pl.I, pl.out_inner_stride, pl.idx_inner_stride, pl.nsplit, pl.split_len, pl.tiles_i, prm, partials, tickets, post);
       break;
     }
     case kRedStrided: {
