@@ -4,6 +4,9 @@
 #define THCStorage TH_CONCAT_3(TH, CReal, Storage)
 #define THCTensor_(NAME) TH_CONCAT_4(TH, CReal, Tensor_, NAME)
 #define THCStorage_(NAME) TH_CONCAT_4(TH, CReal, Storage_, NAME)
+/* torch7's names for the CPU tensor of the same element type (lib/TH/THTensor.h) */
+#define THTensor TH_CONCAT_3(TH, Real, Tensor)
+#define THTensor_(NAME) TH_CONCAT_4(TH, Real, Tensor_, NAME)
 
 #ifdef THC_B200_DECLARE_STRUCTS
 
@@ -201,11 +204,11 @@ THC_API void TH_CONCAT_2(THFloatTensor_copyCuda, Real)(THCState *state, struct T
 THC_API void TH_CONCAT_2(THDoubleTensor_copyCuda, Real)(THCState *state, struct THDoubleTensor *self, THCTensor *src);
 THC_API void TH_CONCAT_2(THHalfTensor_copyCuda, Real)(THCState *state, struct THHalfTensor *self, THCTensor *src);
 /* same element type on both sides */
-THC_API void THCTensor_(copyCPU)(THCState *state, THCTensor *self, struct TH_CONCAT_3(TH, Real, Tensor) *src);
-THC_API void TH_CONCAT_3(TH, Real, Tensor_copyCuda)(THCState *state, struct TH_CONCAT_3(TH, Real, Tensor) *self, THCTensor *src);
+THC_API void THCTensor_(copyCPU)(THCState *state, THCTensor *self, struct THTensor *src);
+THC_API void THTensor_(copyCuda)(THCState *state, struct THTensor *self, THCTensor *src);
 /* asynchronous on the current stream: both sides contiguous, the CPU side in pinned memory */
-THC_API void THCTensor_(copyAsyncCPU)(THCState *state, THCTensor *self, struct TH_CONCAT_3(TH, Real, Tensor) *src);
-THC_API void TH_CONCAT_3(TH, Real, Tensor_copyAsyncCuda)(THCState *state, struct TH_CONCAT_3(TH, Real, Tensor) *self, THCTensor *src);
+THC_API void THCTensor_(copyAsyncCPU)(THCState *state, THCTensor *self, struct THTensor *src);
+THC_API void THTensor_(copyAsyncCuda)(THCState *state, struct THTensor *self, THCTensor *src);
 
 /* ---- pointwise math (lib/THC/generic/THCTensorMathPointwise.h) ---- */
 #if THC_T_FLOATING
@@ -279,18 +282,30 @@ THC_API int THCTensor_(equal)(THCState *state, THCTensor *self, THCTensor *src);
 /* ---- comparisons (lib/THC/generic/THCTensorMathCompare.h:5-18, THCTensorMathCompareT.h:5-18):
  * <op>Value / <op>Tensor write 0/1 into a ByteTensor resized to src's shape, the ...T forms
  * into a tensor of the operands' own type ---- */
-#define THC_B200_DECLARE_COMPARE(NAME)                                                                                          \
-  THC_API void THCTensor_(TH_CONCAT_2(NAME, Value))(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value); \
-  THC_API void THCTensor_(TH_CONCAT_2(NAME, ValueT))(THCState *state, THCTensor *self_, THCTensor *src, real value);            \
-  THC_API void THCTensor_(TH_CONCAT_2(NAME, Tensor))(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2); \
-  THC_API void THCTensor_(TH_CONCAT_2(NAME, TensorT))(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
-THC_B200_DECLARE_COMPARE(lt)
-THC_B200_DECLARE_COMPARE(gt)
-THC_B200_DECLARE_COMPARE(le)
-THC_B200_DECLARE_COMPARE(ge)
-THC_B200_DECLARE_COMPARE(eq)
-THC_B200_DECLARE_COMPARE(ne)
-#undef THC_B200_DECLARE_COMPARE
+THC_API void THCTensor_(ltValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(ltValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(ltTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(ltTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(gtValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(gtValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(gtTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(gtTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(leValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(leValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(leTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(leTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(geValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(geValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(geTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(geTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(eqValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(eqValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(eqTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(eqTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(neValue)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(neValueT)(THCState *state, THCTensor *self_, THCTensor *src, real value);
+THC_API void THCTensor_(neTensor)(THCState *state, struct THCudaByteTensor *self_, THCTensor *src1, THCTensor *src2);
+THC_API void THCTensor_(neTensorT)(THCState *state, THCTensor *self_, THCTensor *src1, THCTensor *src2);
 
 /* ---- scans (lib/THC/generic/THCTensorMathScan.h:5-6) ---- */
 THC_API void THCTensor_(cumsum)(THCState *state, THCTensor *self, THCTensor *src, long dim);
@@ -358,3 +373,5 @@ THC_API void THCTensor_(sumallToDevice)(THCState *state, THCTensor *self, void *
 #undef THCStorage
 #undef THCTensor_
 #undef THCStorage_
+#undef THTensor
+#undef THTensor_

@@ -22,10 +22,24 @@ def ref_path() -> Path:
     return HERE / "_ref" / "libref_check.so"
 
 
+def cutorch_tree():
+    """Where a cutorch checkout lies, if anywhere: the environment variable CUTORCH_TREE, else a
+    directory named `reference` beside the repository."""
+    import os
+    for cand in (os.environ.get("CUTORCH_TREE"), str(HERE.parent.parent / "reference")):
+        if cand and (Path(cand) / "lib" / "THC").is_dir():
+            return cand
+    return None
+
+
 def build_oracle() -> None:
-    """make -C oracle: the restatement always, the reference-derived library when the
-    cutorch tree is mounted."""
-    r = subprocess.run(["make", "-C", str(HERE)], capture_output=True, text=True)
+    """make -C oracle: the restatement always, the reference-derived library when a cutorch
+    tree is at hand (see cutorch_tree)."""
+    cmd = ["make", "-C", str(HERE)]
+    tree = cutorch_tree()
+    if tree:
+        cmd.append(f"REF={tree}")
+    r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"building the oracle failed:\n{r.stdout}\n{r.stderr}")
 
@@ -150,6 +164,45 @@ class RefCheck:
         self.lib.ref_index_to_offset.restype = C.c_int64
         self.lib.ref_apply_functor.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_void_p, C.c_double, C.c_double, C.c_int64, C.c_int64]
+
+        self.lib.ref_compare.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_double, C.c_int64]
+        self.lib.ref_masked.argtypes = [C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_double, C.c_int64]
+
+    CMP = {"lt": 0, "gt": 1, "le": 2, "ge": 3, "eq": 4, "ne": 5}
+
+    def compare(self, name: str, a: np.ndarray, b, same_type: bool = False) -> np.ndarray:
+        """TensorLTValueOp ... TensorNEOp (lib/THC/THCTensorMathCompare.cuh, THCTensorMathCompareT.cuh) on
+        dense arrays; b is an array of a's dtype or a scalar; the result is uint8, or a's dtype with same_type."""
+        a = np.ascontiguousarray(a)
+        out = np.zeros(a.shape, a.dtype if same_type else np.uint8)
+        if isinstance(b, np.ndarray):
+            bb = np.ascontiguousarray(b)
+            rc = self.lib.ref_compare(self.CMP[name], int(same_type), DTYPE_ID[a.dtype], a.size, out.ctypes.data, a.ctypes.data,
+                                      bb.ctypes.data, 0.0, 0)
+        else:
+            rc = self.lib.ref_compare(self.CMP[name], int(same_type), DTYPE_ID[a.dtype], a.size, out.ctypes.data, a.ctypes.data,
+                                      None, float(b), int(b) if a.dtype.kind != "f" else 0)
+        assert rc == 0
+        return out
+
+    def masked(self, which: str, t: np.ndarray, mask: np.ndarray, other=None, value=0) -> np.ndarray:
+        """TensorMaskedFillOp / CopyOp / SelectOp (lib/THC/THCTensorMasked.cuh:16-56) over the exclusive prefix
+        sum of the mask.  fill / copy return t's new contents, select returns the packed elements."""
+        t = np.array(t, copy=True, order="C")
+        m = np.ascontiguousarray(mask, dtype=np.uint8)
+        fp = t.dtype.kind == "f"
+        if which == "fill":
+            rc = self.lib.ref_masked(0, DTYPE_ID[t.dtype], t.size, t.ctypes.data, m.ctypes.data, None, float(value), 0 if fp else int(value))
+            res = t
+        elif which == "copy":
+            src = np.ascontiguousarray(other)
+            rc = self.lib.ref_masked(1, DTYPE_ID[t.dtype], t.size, t.ctypes.data, m.ctypes.data, src.ctypes.data, 0.0, 0)
+            res = t
+        else:
+            res = np.zeros(int((m != 0).sum()), t.dtype)
+            rc = self.lib.ref_masked(2, DTYPE_ID[t.dtype], t.size, t.ctypes.data, m.ctypes.data, res.ctypes.data, 0.0, 0)
+        assert rc == 0
+        return res
 
     def collapse_dims(self, sizes, strides, exclude_dim=-1):
         n = len(sizes)

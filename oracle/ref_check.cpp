@@ -3,6 +3,8 @@
 //   * TensorInfo::collapseDims / IndexToOffset      (lib/THC/THCTensorInfo.cuh:74-278)
 //   * the pointwise functor bodies                   (lib/THC/THCTensorMathPointwise.cuh:12-772)
 //   * THCNumerics<T> math                            (lib/THC/THCNumerics.cuh:12-666)
+//   * the comparison functors into Byte and into T   (lib/THC/THCTensorMathCompare.cuh:9-67, THCTensorMathCompareT.cuh:11-51)
+//   * the Byte-masked fill / copy / select functors  (lib/THC/THCTensorMasked.cuh:16-56)
 // through a C ABI, so that the tests can pin the CPU restatement (th_oracle.cpp) and the
 // product's planner against the reference's own code, and so that golden vectors can be
 // generated (tests/golden/make_golden.py).  The output goes to oracle/_ref/ and is never
@@ -10,6 +12,9 @@
 #include "THCTensorInfo.cuh"
 #include "THCNumerics.cuh"
 #include "THCTensorMathPointwise.cuh"
+#include "THCTensorMathCompare.cuh"
+#include "THCTensorMathCompareT.cuh"
+#include "THCTensorMasked.cuh"
 
 #include <stdint.h>
 #include <string.h>
@@ -173,6 +178,92 @@ int ref_apply_functor(int fid, int dtype, int64_t n, void *out, void *a, void *b
             if (rc) rc = run_fp_only<double>(fid, n, (double *)out, (double *)a, (double *)b, sf0); break;
   }
   return rc;
+}
+
+}  // extern "C"
+
+namespace {
+
+// out[i] = a[i] CMP (b ? b[i] : value), TOut the result type: the ...Value functors of
+// THCTensorMathCompare.cuh with a scalar, the tensor functors of THCTensorMathCompareT.cuh otherwise
+template <typename T, typename TOut> int run_compare(int cmp, int64_t n, TOut *out, T *a, T *b, T value) {
+  for (int64_t i = 0; i < n; ++i) {
+    if (b) {
+      switch (cmp) {
+        case 0: { TensorLTOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        case 1: { TensorGTOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        case 2: { TensorLEOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        case 3: { TensorGEOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        case 4: { TensorEQOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        case 5: { TensorNEOp<T, TOut> f; f(out + i, a + i, b + i); break; }
+        default: return -1;
+      }
+    } else {
+      switch (cmp) {
+        case 0: { TensorLTValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        case 1: { TensorGTValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        case 2: { TensorLEValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        case 3: { TensorGEValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        case 4: { TensorEQValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        case 5: { TensorNEValueOp<T, TOut> f(value); f(out + i, a + i); break; }
+        default: return -1;
+      }
+    }
+  }
+  return 0;
+}
+
+template <typename T> int run_compare_both(int cmp, int same_type, int64_t n, void *out, T *a, T *b, T value) {
+  return same_type ? run_compare<T, T>(cmp, n, (T *)out, a, b, value)
+                   : run_compare<T, unsigned char>(cmp, n, (unsigned char *)out, a, b, value);
+}
+
+// The masked functors take the exclusive prefix sum of the mask (cutorch computes it with a thrust
+// exclusive_scan over a Long copy of the mask, lib/THC/generic/THCTensorMasked.cu:75-93,150-168).
+template <typename T> int run_masked(int which, int64_t n, T *t, unsigned char *mask, T *other, T value) {
+  long *prefix = (long *)malloc(sizeof(long) * (size_t)(n > 0 ? n : 1));
+  long run = 0;
+  for (int64_t i = 0; i < n; ++i) { prefix[i] = run; run += mask[i] ? 1 : 0; }
+  int rc = 0;
+  if (which == 0) { TensorMaskedFillOp<T, unsigned char> f(value); for (int64_t i = 0; i < n; ++i) f(t + i, mask + i); }
+  else if (which == 1) { TensorMaskedCopyOp<T, unsigned char, long> f(other); for (int64_t i = 0; i < n; ++i) f(t + i, mask + i, prefix + i); }
+  else if (which == 2) { TensorMaskedSelectOp<T, unsigned char, long> f(other); for (int64_t i = 0; i < n; ++i) f(mask + i, prefix + i, t + i); }
+  else rc = -1;
+  free(prefix);
+  return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+// cmp: 0 lt, 1 gt, 2 le, 3 ge, 4 eq, 5 ne.  b == NULL compares with the scalar.  same_type: the
+// result has the operands' type (the ...T entry points), else unsigned char.
+int ref_compare(int cmp, int same_type, int dtype, int64_t n, void *out, void *a, void *b, double sf, int64_t si) {
+  switch (dtype) {
+    case 0: return run_compare_both<unsigned char>(cmp, same_type, n, out, (unsigned char *)a, (unsigned char *)b, (unsigned char)si);
+    case 1: return run_compare_both<char>(cmp, same_type, n, out, (char *)a, (char *)b, (char)si);
+    case 2: return run_compare_both<short>(cmp, same_type, n, out, (short *)a, (short *)b, (short)si);
+    case 3: return run_compare_both<int>(cmp, same_type, n, out, (int *)a, (int *)b, (int)si);
+    case 4: return run_compare_both<long>(cmp, same_type, n, out, (long *)a, (long *)b, (long)si);
+    case 6: return run_compare_both<float>(cmp, same_type, n, out, (float *)a, (float *)b, (float)sf);
+    case 7: return run_compare_both<double>(cmp, same_type, n, out, (double *)a, (double *)b, sf);
+  }
+  return -1;
+}
+
+// which: 0 fill t where mask (value), 1 copy: t[i] = other[rank of i] where mask, 2 select: other[rank of i] = t[i] where mask
+int ref_masked(int which, int dtype, int64_t n, void *t, unsigned char *mask, void *other, double sf, int64_t si) {
+  switch (dtype) {
+    case 0: return run_masked<unsigned char>(which, n, (unsigned char *)t, mask, (unsigned char *)other, (unsigned char)si);
+    case 1: return run_masked<char>(which, n, (char *)t, mask, (char *)other, (char)si);
+    case 2: return run_masked<short>(which, n, (short *)t, mask, (short *)other, (short)si);
+    case 3: return run_masked<int>(which, n, (int *)t, mask, (int *)other, (int)si);
+    case 4: return run_masked<long>(which, n, (long *)t, mask, (long *)other, (long)si);
+    case 6: return run_masked<float>(which, n, (float *)t, mask, (float *)other, (float)sf);
+    case 7: return run_masked<double>(which, n, (double *)t, mask, (double *)other, sf);
+  }
+  return -1;
 }
 
 }  // extern "C"

@@ -10,6 +10,12 @@ absent:
   functors.json       outputs of the pointwise functor bodies (lib/THC/THCTensorMathPointwise.cuh,
                       lib/THC/THCNumerics.cuh) on fixed inputs, as hex bit patterns
 
+  compare_masked.json outputs of the comparison functors into Byte and into the operands' type
+                      (lib/THC/THCTensorMathCompare.cuh, THCTensorMathCompareT.cuh) and of the Byte-masked
+                      fill / copy / select functors (lib/THC/THCTensorMasked.cuh) on fixed inputs
+  thc_prototypes.json the C prototypes of lib/THC/generic/*.h (and the two non-generic Byte entry
+                      points), normalised to one line each, per header
+
     python tests/golden/make_golden.py
 """
 import json
@@ -124,6 +130,79 @@ def main():
                                                "out": res.tobytes().hex()}
     (HERE / "functors.json").write_text(json.dumps(fx, separators=(",", ":")))
     print(f"wrote {len(out)} collapse cases and {len(fx)} functor vectors")
+
+    # comparison and mask functors
+    cm = {}
+    n = 96
+    rc = np.random.default_rng(11)
+    for dt in (np.uint8, np.int8, np.int16, np.int32, np.int64, np.float32, np.float64):
+        if np.dtype(dt).kind == "f":
+            a = rc.integers(-3, 4, n).astype(dt)
+            b = rc.integers(-3, 4, n).astype(dt)
+            a[5], b[9], a[20], b[20] = np.nan, np.nan, np.nan, np.nan      # comparisons with NaN are false, ne is true
+            a[7], b[7] = 0.0, -0.0
+        else:
+            lo = 0 if np.dtype(dt).kind == "u" else -3
+            a = rc.integers(lo, 4, n).astype(dt)
+            b = rc.integers(lo, 4, n).astype(dt)
+        mask = (rc.uniform(size=n) < 0.45).astype(np.uint8)
+        mask[rc.integers(0, n, 5)] = 7          # any non-zero byte is "set"
+        packed = rc.integers(10, 100, int((mask != 0).sum())).astype(dt)
+        key = np.dtype(dt).name
+        entry = {"a": a.tobytes().hex(), "b": b.tobytes().hex(), "mask": mask.tobytes().hex(), "packed": packed.tobytes().hex(),
+                 "scalar": 1, "fill": 9}
+        for name in ("lt", "gt", "le", "ge", "eq", "ne"):
+            entry[name + "Tensor"] = ref.compare(name, a, b).tobytes().hex()
+            entry[name + "Value"] = ref.compare(name, a, 1).tobytes().hex()
+            entry[name + "TensorT"] = ref.compare(name, a, b, same_type=True).tobytes().hex()
+            entry[name + "ValueT"] = ref.compare(name, a, 1, same_type=True).tobytes().hex()
+        entry["maskedFill"] = ref.masked("fill", a, mask, value=9).tobytes().hex()
+        entry["maskedCopy"] = ref.masked("copy", a, mask, other=packed).tobytes().hex()
+        entry["maskedSelect"] = ref.masked("select", a, mask).tobytes().hex()
+        cm[key] = entry
+    (HERE / "compare_masked.json").write_text(json.dumps(cm, separators=(",", ":")))
+    print(f"wrote comparison and mask vectors for {len(cm)} element types")
+
+    write_prototypes()
+
+
+PROTOTYPE_HEADERS = ["generic/THCTensorMathPointwise.h", "generic/THCTensorMathPairwise.h", "generic/THCTensorMathReduce.h",
+                     "generic/THCTensorMathCompare.h", "generic/THCTensorMathCompareT.h", "generic/THCTensorMathScan.h",
+                     "generic/THCTensorMath.h", "generic/THCTensorCopy.h", "generic/THCTensorMasked.h",
+                     "generic/THCTensorIndex.h", "generic/THCTensorScatterGather.h"]
+
+
+def normalise_prototype(text: str) -> str:
+    """One prototype as a canonical string: comments and THC_API dropped, whitespace collapsed,
+    no space around punctuation, parameter names kept (they are part of what a reader diffs)."""
+    import re
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"//[^\n]*", " ", text)
+    text = text.replace("THC_API", " ")
+    text = re.sub(r"\s+", " ", text).strip()
+    text = re.sub(r"\s*([(),*])\s*", r"\1", text)
+    return text
+
+
+def prototypes_of(text: str):
+    """The THC_API declarations of a header, each normalised, in file order."""
+    import re
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"//[^\n]*", " ", text)
+    return [normalise_prototype(m.group(0)) for m in re.finditer(r"THC_API[^;]*;", text)]
+
+
+def write_prototypes():
+    from oracle.loader import cutorch_tree
+    tree = cutorch_tree()
+    if not tree:
+        print("no cutorch tree: thc_prototypes.json left as it is")
+        return
+    out = {}
+    for h in PROTOTYPE_HEADERS:
+        out[h] = prototypes_of((Path(tree) / "lib" / "THC" / h).read_text())
+    (HERE / "thc_prototypes.json").write_text(json.dumps(out, indent=0))
+    print(f"wrote {sum(len(v) for v in out.values())} prototypes from {len(out)} headers")
 
 
 if __name__ == "__main__":
