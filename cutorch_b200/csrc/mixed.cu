@@ -247,7 +247,10 @@ __device__ __forceinline__ uint32_t nonzero_bits16(const Bytes16 &v) {
 // Unit-stride, 16-byte aligned mask, whole tiles only: a thread counts its 16 bytes of a tile with
 // bit arithmetic; a CTA takes kCountTiles consecutive tiles, all loads first.
 constexpr int kCountTiles = 4;
-__global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint64_t full_tiles, uint32_t *counts) {
+// It also leaves one bit per mask byte behind (16 bits per thread, 512 bytes per tile): the select
+// and copy kernels that follow read those instead of the mask bytes again (an eighth of the traffic).
+__global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uint8_t *mask, uint64_t full_tiles, uint32_t *counts,
+                                                                       uint16_t *tile_bits) {
   pdl_prologue();
   __shared__ uint32_t wsum[kCountTiles][kThreads / 32];
   const uint64_t tile0 = (uint64_t)blockIdx.x * kCountTiles;
@@ -259,9 +262,9 @@ __global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uin
   }
 #pragma unroll
   for (int t = 0; t < kCountTiles; ++t) {
-    uint32_t c = 0;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) c += __popc(nonzero_bytes(v[t].w[w]));
+    const uint32_t b16 = nonzero_bits16(v[t]);
+    if (tile0 + t < full_tiles) tile_bits[(tile0 + t) * (uint64_t)kThreads + threadIdx.x] = (uint16_t)b16;
+    uint32_t c = __popc(b16);
     c = __reduce_add_sync(0xffffffffu, c);
     if ((threadIdx.x & 31) == 0) wsum[t][threadIdx.x >> 5] = c;
   }
@@ -282,14 +285,15 @@ __global__ void __launch_bounds__(kThreads) mask_tile_count_vec_kernel(const uin
 // coalesced stores (the packed side keeps its own strides).
 template <typename W, typename IndexT, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
-masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const uint8_t *mask, const uint64_t *offsets) {
+masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const uint16_t *tile_bits, const uint64_t *offsets) {
   pdl_prologue();
   __shared__ uint32_t wsum[kThreads / 32];
   __shared__ W stage[kThreads / 32][kWarpSpan];
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint64_t ebase = (uint64_t)blockIdx.x * kTile + (uint64_t)warp * kWarpSpan + (uint64_t)lane * 16;
-  uint64_t pos = offsets[blockIdx.x];   // needed last: in flight together with the mask and the data
-  const Bytes16 mv = ld16_stream(mask + ebase);
+  uint64_t pos = offsets[blockIdx.x];   // needed last: in flight together with the mask bits and the data
+  // the bits the counting pass left for this thread's 16 mask bytes
+  const uint32_t bits = tile_bits[(uint64_t)blockIdx.x * kThreads + threadIdx.x];
   alignas(32) W e[16];
   constexpr int NV = (int)sizeof(W);   // 16-byte vectors holding 16 elements
   if constexpr (WIDE && NV >= 2) {
@@ -303,7 +307,6 @@ masked_select_vec_kernel(const W *src, W *packed, StridedView<IndexT> vp, const 
       *reinterpret_cast<Bytes16 *>(reinterpret_cast<char *>(e) + 16 * v) =
           ld16_stream(reinterpret_cast<const char *>(src + ebase) + 16 * v);
   }
-  const uint32_t bits = nonzero_bits16(mv);
   const uint32_t cnt = __popc(bits);
   uint32_t incl = cnt;
 #pragma unroll
@@ -639,6 +642,7 @@ struct MaskPrep {
   uint64_t ntiles;
   uint64_t *offsets;   // device, ntiles entries
   int64_t *total;      // device
+  uint16_t *tile_bits; // device: one bit per mask byte for the whole tiles of a dense aligned mask (else unused)
   Collapsed cm;
   bool hit;            // the offsets were found in the context and thcb200_masked_count has read their total
 };
@@ -666,8 +670,11 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   const uint64_t n = (uint64_t)vm.numel;
   mp->ntiles = (n + kTile - 1) / kTile;
   if (mp->ntiles >= (1ULL << 31)) { set_error("masked: tensor too large"); return THCB200_ERR_DIMS; }
-  // layout: [total: 8 B, padded to 256][offsets: 8 B x ntiles][counts: 4 B x ntiles]
-  const size_t need = 256 + mp->ntiles * 12;
+  // layout: [total: 8 B, padded to 256][offsets: 8 B x ntiles][counts: 4 B x ntiles][bits: 512 B x ntiles]
+  // (the bits only for a dense 16-byte aligned mask: n / 8 bytes)
+  const bool dense_aligned = mp->cm.unit && aligned16(vm.data);
+  const size_t bits_at = (256 + mp->ntiles * 12 + 255) & ~(size_t)255;
+  const size_t need = bits_at + (dense_aligned ? mp->ntiles * (size_t)kThreads * 2 : 0);
   const uint64_t lh = layout_hash(vm);
   const bool hit = reuse && ctx->prep_valid && ctx->prep_mask == (const void *)vm.data && ctx->prep_numel == vm.numel &&
                    ctx->prep_layout == lh && ctx->prep_stream == (void *)st && ctx->mask_ws_bytes >= need;
@@ -693,6 +700,7 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   mp->total = reinterpret_cast<int64_t *>(base);
   mp->offsets = reinterpret_cast<uint64_t *>(base + 256);
   uint32_t *counts = reinterpret_cast<uint32_t *>(base + 256 + mp->ntiles * 8);
+  mp->tile_bits = reinterpret_cast<uint16_t *>(base + bits_at);
   mp->hit = hit && ctx->prep_count_known;
   if (hit) return 0;
   ctx->prep_valid = 0;
@@ -704,7 +712,7 @@ int prepare_mask(thcb200_ctx *ctx, const HostView &vm, bool reuse, cudaStream_t 
   const uint64_t full = mask_vec ? n / kTile : 0;
   int launches = 1;
   if (full > 0) {
-    launch_pdl(mask_tile_count_vec_kernel, (unsigned)((full + kCountTiles - 1) / kCountTiles), kThreads, 0, st, mask, full, counts);
+    launch_pdl(mask_tile_count_vec_kernel, (unsigned)((full + kCountTiles - 1) / kCountTiles), kThreads, 0, st, mask, full, counts, mp->tile_bits);
     ++launches;
   }
   if (full < mp->ntiles) {
@@ -804,10 +812,10 @@ int masked_move_sized(thcb200_ctx *ctx, const HostView &vstrided, const HostView
     if (full > 0) {
       set_plan_name(i32 ? "masked_select_vec32" : "masked_select_vec64");
       const bool wide = ((uintptr_t)strided) % 32 == 0;
-      if (i32 && wide) launch_pdl(masked_select_vec_kernel<W, uint32_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
-      else if (i32) launch_pdl(masked_select_vec_kernel<W, uint32_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mask, mp.offsets);
-      else if (wide) launch_pdl(masked_select_vec_kernel<W, uint64_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
-      else launch_pdl(masked_select_vec_kernel<W, uint64_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mask, mp.offsets);
+      if (i32 && wide) launch_pdl(masked_select_vec_kernel<W, uint32_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mp.tile_bits, mp.offsets);
+      else if (i32) launch_pdl(masked_select_vec_kernel<W, uint32_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint32_t>(cp), mp.tile_bits, mp.offsets);
+      else if (wide) launch_pdl(masked_select_vec_kernel<W, uint64_t, true>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mp.tile_bits, mp.offsets);
+      else launch_pdl(masked_select_vec_kernel<W, uint64_t, false>, (unsigned)full, kThreads, 0, st, strided, packed, make_view<uint64_t>(cp), mp.tile_bits, mp.offsets);
       ++launches;
     }
   }
