@@ -260,9 +260,14 @@ def ours_main(args):
             comm.reduce_all(tz, partial.data_ptr(), "SUM")
 
     def barrier():
+        torch.cuda.synchronize()       # nothing of the library's communicator is in flight when torch's runs
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if comm is not None and not args.no_overlap:
+        # the 8-byte all-reduce runs on the communicator's stream: the next step's kernels do not wait for it
+        comm.set_overlap(True)
 
     sampler = ClockSampler(local)
     if rank == 0:
@@ -279,6 +284,8 @@ def ours_main(args):
     e0.record(stream)
     for _ in range(args.steps):
         step()
+    if comm is not None:
+        comm.wait()                   # the timed region ends when the last all-reduce has landed
     e1.record(stream)
     barrier()
     launches = lib.thcb200_launch_count() - launches0
@@ -375,8 +382,11 @@ def ours_main(args):
                        "rows_per_gpu": rows, "cols": COLS, "bytes_per_step": total_bytes,
                        "l2": "inputs (16 GiB per tensor at N=1) are far larger than the 126 MB L2; no flush needed",
                        "collective": ("none (one GPU)" if comm is None else
-                                      "ncclAllReduce(sum, 1 x f64) on the compute stream, issued by thcb200_sharded_reduce_all "
-                                      f"on the slot the finishing CTA wrote (NCCL {comm.nccl_version()} bound by libthcb200.so)"),
+                                      "ncclAllReduce(sum, 1 x f64) issued by thcb200_sharded_reduce_all on the slot the finishing CTA wrote, "
+                                      + ("in the compute stream's order" if args.no_overlap else
+                                         "on the communicator's own stream behind an event (the next step's kernels do not wait for it; "
+                                         "the timed region ends after the last one)")
+                                      + f" (NCCL {comm.nccl_version()} bound by libthcb200.so)"),
                        "elements_per_s": rows * COLS * world / (ms_per_step * 1e-3)},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches),
             "clocks": clocks, "checksum": total_sum,
@@ -607,6 +617,7 @@ def run_e2e(args, torch, thc, state, stream, dev, rows, world, rank, comm, local
             tparts.sumall_to_device(total.data_ptr())
         else:
             comm.reduce_all(tparts, total.data_ptr(), "SUM")
+            comm.wait()               # the total is read next
         # device -> host through the library, in the order of the compute stream
         tdv.copy_async_to_cpu(chv)
         tdi.copy_async_to_cpu(chi)
@@ -667,6 +678,7 @@ def main():
     ap.add_argument("--configs", action="store_true", default=True, help="also time the c1-c4 configs at N=1")
     ap.add_argument("--no-configs", dest="configs", action="store_false")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-overlap", action="store_true", help="N > 1: run the all-reduce in the compute stream's order")
     ap.add_argument("--only", default="", help="comma list of c1..c4: time just those configs on one GPU and print them")
     ap.add_argument("--reps", type=int, default=0, help="timed repetitions per entry with --only")
     args = ap.parse_args()

@@ -35,6 +35,12 @@ struct thcb200_comm {
   // the folds that follow a gather may use for their own partials
   void *buf;
   size_t buf_bytes;
+  // overlapped mode: the all-reduce of a full reduction's accumulators runs on `side`, in the order
+  // local fold (caller's stream) -> ev_local -> all-reduce (side) -> ev_done
+  int overlap;
+  int pending;            // an all-reduce has been issued on `side` and nobody has waited for it yet
+  cudaStream_t side;
+  cudaEvent_t ev_local, ev_done;
 };
 
 namespace thcb {
@@ -203,17 +209,37 @@ int thcb200_comm_create(thcb200_comm **out, int nranks, int rank, const void *id
   c->rank = rank;
   cudaError_t e = cudaGetDevice(&c->device);
   if (e != cudaSuccess) { delete c; set_error("comm_create: %s", cudaGetErrorString(e)); return THCB200_ERR_CUDA; }
+  e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_local, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming);
+  if (e != cudaSuccess) { delete c; set_error("comm_create: %s", cudaGetErrorString(e)); return THCB200_ERR_CUDA; }
   ncclResult_t r = n->CommInitRank(&c->comm, nranks, u, rank);
   if (r != ncclSuccess) { delete c; set_error("ncclCommInitRank failed: %s", n->GetErrorString(r)); return THCB200_ERR_CUDA; }
   *out = c;
   return THCB200_OK;
 }
 
+int thcb200_comm_set_overlap(thcb200_comm *comm, int on) {
+  if (!comm) { set_error("comm_set_overlap: null communicator"); return THCB200_ERR_ARG; }
+  comm->overlap = on ? 1 : 0;
+  return THCB200_OK;
+}
+
+int thcb200_comm_wait(thcb200_comm *comm, void *stream) {
+  if (!comm) { set_error("comm_wait: null communicator"); return THCB200_ERR_ARG; }
+  if (comm->pending) THCB_CUDA_TRY(cudaStreamWaitEvent((cudaStream_t)stream, comm->ev_done, 0));
+  return THCB200_OK;
+}
+
 void thcb200_comm_destroy(thcb200_comm *comm) {
   if (!comm) return;
   const NcclApi *n = nccl();
+  if (comm->side) cudaStreamSynchronize(comm->side);
   if (n && comm->comm) n->CommDestroy(comm->comm);
   if (comm->buf) cudaFree(comm->buf);
+  if (comm->ev_local) cudaEventDestroy(comm->ev_local);
+  if (comm->ev_done) cudaEventDestroy(comm->ev_done);
+  if (comm->side) cudaStreamDestroy(comm->side);
   delete comm;
 }
 
@@ -257,6 +283,9 @@ int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, in
   if (rc) return rc;
   if (!in) { set_error("sharded_reduce_all: null tensor"); return THCB200_ERR_ARG; }
   THCB_CTX_LOCK(ctx);
+  cudaStream_t st = (cudaStream_t)stream;
+  // an earlier overlapped all-reduce may still be using a slot: it finishes before this fold writes one
+  if (comm->pending) THCB_CUDA_TRY(cudaStreamWaitEvent(st, comm->ev_done, 0));
   // this rank's accumulator, left in the result slot on the device by the finishing CTA
   rc = thcb200_reduce_all(ctx, rop, pre, s, in, result_dev, stream);
   if (rc || comm->nranks == 1) return rc;
@@ -264,8 +293,21 @@ int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, in
   const int slot_dtype = fp ? THCB200_F64 : THCB200_I64;
   // logical and / or of 0/1 accumulators are their min / max
   const int fold = rop == THCB200_RED_ALL ? THCB200_RED_MIN : rop == THCB200_RED_ANY ? THCB200_RED_MAX : rop;
-  if (all_reduce_keeps_the_rule(slot_dtype, fold))
-    return thcb200_comm_all_reduce(comm, result_dev, 1, slot_dtype, fold, stream);
+  if (all_reduce_keeps_the_rule(slot_dtype, fold)) {
+    if (!comm->overlap) {
+      comm->pending = 0;
+      return thcb200_comm_all_reduce(comm, result_dev, 1, slot_dtype, fold, stream);
+    }
+    // overlapped: the collective leaves the caller's stream free for the kernels that follow
+    THCB_CUDA_TRY(cudaEventRecord(comm->ev_local, st));
+    THCB_CUDA_TRY(cudaStreamWaitEvent(comm->side, comm->ev_local, 0));
+    rc = thcb200_comm_all_reduce(comm, result_dev, 1, slot_dtype, fold, (void *)comm->side);
+    if (rc) return rc;
+    THCB_CUDA_TRY(cudaEventRecord(comm->ev_done, comm->side));
+    comm->pending = 1;
+    return THCB200_OK;
+  }
+  comm->pending = 0;
   // floating min / max: gather the ranks' slots and fold them here in rank order (a NaN wins)
   void *slots_dev = comm_buffer(comm, (size_t)comm->nranks * 8);
   if (!slots_dev) return THCB200_ERR_NOMEM;

@@ -43,6 +43,8 @@ class Comm:
         lib.thcb200_comm_destroy.restype = None
         lib.thcb200_comm_info.argtypes = [vp, P(C.c_int), P(C.c_int), P(C.c_int)]
         lib.thcb200_comm_all_reduce.argtypes = [vp, vp, C.c_int64, C.c_int, C.c_int, vp]
+        lib.thcb200_comm_set_overlap.argtypes = [vp, C.c_int]
+        lib.thcb200_comm_wait.argtypes = [vp, vp]
         lib.thcb200_comm_all_gather.argtypes = [vp, vp, vp, C.c_int64, vp]
         TD, SC = _lib.TensorDesc, _lib.Scalar
         lib.thcb200_sharded_reduce_all.argtypes = [vp, vp, C.c_int, C.c_int, SC, P(TD), vp, vp]
@@ -109,6 +111,14 @@ class Comm:
     def all_reduce(self, dev_ptr: int, count: int, dtype: int, rop: str = "SUM"):
         C, L = self._C, self._lib_mod
         L.check(self.lib.thcb200_comm_all_reduce(self.handle, C.c_void_p(dev_ptr), count, dtype, L.RED[rop], C.c_void_p(self.state.stream)))
+
+    def set_overlap(self, on: bool):
+        """Full reductions all-reduce on the communicator's own stream from now on (see thcb200_comm_set_overlap)."""
+        self._lib_mod.check(self.lib.thcb200_comm_set_overlap(self.handle, int(on)))
+
+    def wait(self):
+        """The current stream waits for the last overlapped all-reduce."""
+        self._lib_mod.check(self.lib.thcb200_comm_wait(self.handle, self._C.c_void_p(self.state.stream)))
 
     def close(self):
         if self.handle:

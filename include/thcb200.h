@@ -438,6 +438,14 @@ THCB200_API int thcb200_comm_all_gather(thcb200_comm *comm, const void *send_dev
  * the library's kernel, so that a NaN wins as in the unsharded call. */
 THCB200_API int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, int pre, thcb200_scalar s,
                                const thcb200_tensor *in, void *result_dev, void *stream);
+/* Overlapped mode (off by default).  With it on, the ncclAllReduce of thcb200_sharded_reduce_all runs on
+ * a stream the communicator owns, ordered after the local fold by an event, so the kernels the caller
+ * enqueues next do not wait for the collective; the slot holds the GLOBAL result only once that
+ * all-reduce is done.  thcb200_comm_wait makes `stream` wait for it: call it before anything reads the
+ * slot (the next thcb200_sharded_reduce_all waits by itself before it reuses a slot).  The folds that
+ * gather and combine (floating min / max) always run in the caller's stream order. */
+THCB200_API int thcb200_comm_set_overlap(thcb200_comm *comm, int on);
+THCB200_API int thcb200_comm_wait(thcb200_comm *comm, void *stream);
 /* thcb200_reduce_dim along the dim the tensor is split on: each rank reduces its rows into `out`
  * (dense), then the ranks' outputs are folded and every rank holds the result in `out`.  float /
  * double / int32 / int64 sums and products and integer min / max use ncclAllReduce on the element

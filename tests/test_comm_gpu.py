@@ -46,6 +46,12 @@ def test_sharded_calls_with_one_rank_equal_the_unsharded_ones(state, comm, oracl
     islot = thc.Tensor.new(state, "Long", 1)
     comm.reduce_all(to_device(state, y), islot.data_ptr, "SUM")
     assert int(islot.numpy()[0]) == int(y.astype(np.int64).sum())
+    # the overlapped mode and its wait are accepted with one rank too (there is nothing to overlap)
+    comm.set_overlap(True)
+    comm.reduce_all(to_device(state, y), islot.data_ptr, "SUM")
+    comm.wait()
+    comm.set_overlap(False)
+    assert int(islot.numpy()[0]) == int(y.astype(np.int64).sum())
 
 
 def test_all_reduce_and_bad_arguments(state, comm):
