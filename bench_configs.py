@@ -109,6 +109,12 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
                                        rot=[(lambda s=s: s[2].cadd(s[0], 2.5, s[1])) for s in sets[:4]])
         out["c1_sumall_f32_16M"] = timed(lambda: tz.sumall_to_device(res.data_ptr()), 4 * n,
                                          rot=[(lambda s=s: s[0].sumall_to_device(res.data_ptr())) for s in sets])
+        # the config as it is stated: z = x + 2.5 y, then the sum of that z (which the cadd has just left
+        # in the L2); bytes of both calls, time of the pair
+        def pair(s):
+            s[2].cadd(s[0], 2.5, s[1])
+            s[2].sumall_to_device(res.data_ptr())
+        out["c1_chain_cadd_then_sumall"] = timed(lambda: pair((tx, ty, tz)), 16 * n, rot=[(lambda s=s: pair(s)) for s in sets[:4]])
 
     def c2():
         shape = (64, 256, 56, 56)
@@ -150,6 +156,13 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
                                         rot=[(lambda s=s: trh.mean(s[0], 0, 1)) for s in hs])
         out["c4_norm2_dim0_f16"] = timed(lambda: trh.norm(th2, 2, 0, 1), 2 * n + 2 * 8192,
                                          rot=[(lambda s=s: trh.norm(s[0], 2, 0, 1)) for s in hs])
+        # the config as it is stated: sigmoid, then mean and 2-norm along dim 0 of its result
+        def chain(s):
+            s[1].sigmoid(s[0])
+            trh.mean(s[1], 0, 1)
+            trh.norm(s[1], 2, 0, 1)
+        out["c4_chain_sigmoid_mean_norm_f16"] = timed(lambda: chain((th, th2)), 4 * n + 2 * (2 * n + 2 * 8192),
+                                                      rot=[(lambda s=s: chain(s)) for s in hs])
         keep.clear()
         del h, h2, hs
         n = 134217728
