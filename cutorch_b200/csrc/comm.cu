@@ -212,9 +212,18 @@ int thcb200_comm_create(thcb200_comm **out, int nranks, int rank, const void *id
   e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_local, cudaEventDisableTiming);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming);
-  if (e != cudaSuccess) { delete c; set_error("comm_create: %s", cudaGetErrorString(e)); return THCB200_ERR_CUDA; }
+  if (e != cudaSuccess) {
+    set_error("comm_create: %s", cudaGetErrorString(e));
+    thcb200_comm_destroy(c);
+    return THCB200_ERR_CUDA;
+  }
   ncclResult_t r = n->CommInitRank(&c->comm, nranks, u, rank);
-  if (r != ncclSuccess) { delete c; set_error("ncclCommInitRank failed: %s", n->GetErrorString(r)); return THCB200_ERR_CUDA; }
+  if (r != ncclSuccess) {
+    c->comm = nullptr;
+    set_error("ncclCommInitRank failed: %s", n->GetErrorString(r));
+    thcb200_comm_destroy(c);
+    return THCB200_ERR_CUDA;
+  }
   *out = c;
   return THCB200_OK;
 }
