@@ -226,7 +226,11 @@ def ours_main(args):
     # N > 1: the exchange runs inside the C library (NCCL bound by libthcb200); torch.distributed only
     # hands the NCCL id round and provides the barriers of the timing protocol
     comm = Comm.from_process_group(state) if world > 1 else None
-    checks = multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream) if world > 1 else {}
+    checks = multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream, args.collective) if world > 1 else {}
+    peer_ok = checks.get("peer_check") == "ok"
+    peer_on = peer_ok and args.collective == "peer"
+    if peer_ok and not peer_on:
+        comm.disable_peer_exchange()      # checked and available; the timed loop uses the collective asked for
 
     # synthetic inputs, generated on the device per shard from seed + rank
     g = torch.Generator(device=dev)
@@ -265,7 +269,7 @@ def ours_main(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    if comm is not None and not args.no_overlap:
+    if comm is not None and not peer_on and not args.no_overlap:
         # the 8-byte all-reduce runs on the communicator's stream: the next step's kernels do not wait for it
         comm.set_overlap(True)
 
@@ -299,7 +303,42 @@ def ours_main(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
+    if peer_on:
+        checks["peer_exchange_timed_out"] = bool(comm.peer_timed_out())     # must be False: a rank's wait never ran out
     total_sum = float(partial.item())
+    if comm is not None and peer_ok:
+        # the same loop with the other way of combining the partials, as an extra figure
+        other = "nccl" if peer_on else "peer"
+        if other == "peer":
+            comm.set_overlap(False)
+            comm.resume_peer_exchange()
+        else:
+            comm.disable_peer_exchange()
+            comm.set_overlap(not args.no_overlap)
+        for _ in range(2):
+            step()
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(args.steps):
+            step()
+        comm.wait()
+        a1.record(stream)
+        barrier()
+        ta = torch.tensor([a0.elapsed_time(a1) / args.steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
+        key = "peer_exchange" if other == "peer" else "nccl_overlapped"
+        checks[key + "_ms_per_step"] = round(float(ta.item()), 4)
+        if other == "peer":
+            checks["peer_exchange_timed_out"] = bool(comm.peer_timed_out())
+        checks["other_checksum_equal"] = bool(float(partial.item()) == total_sum)
+        # back to the mode of the main loop for the legs that follow
+        if other == "peer":
+            comm.disable_peer_exchange()
+            comm.set_overlap(not args.no_overlap)
+        else:
+            comm.set_overlap(False)
+            comm.resume_peer_exchange()
     ms_per_step = ms / args.steps
     total_bytes = step_bytes(rows) * world
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
@@ -382,6 +421,9 @@ def ours_main(args):
                        "rows_per_gpu": rows, "cols": COLS, "bytes_per_step": total_bytes,
                        "l2": "inputs (16 GiB per tensor at N=1) are far larger than the 126 MB L2; no flush needed",
                        "collective": ("none (one GPU)" if comm is None else
+                                      "inside the reducing kernel: the finishing CTA stores the rank's accumulator into every rank's exchange "
+                                      "block over NVLink (peer stores), waits with a bound for the others' and folds them in rank order "
+                                      "(thcb200_sharded_reduce_all with the peer exchange on)" if peer_on else
                                       "ncclAllReduce(sum, 1 x f64) issued by thcb200_sharded_reduce_all on the slot the finishing CTA wrote, "
                                       + ("in the compute stream's order" if args.no_overlap else
                                          "on the communicator's own stream behind an event (the next step's kernels do not wait for it; "
@@ -400,7 +442,7 @@ def ours_main(args):
     return 0
 
 
-def multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream):
+def multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream, collective="nccl"):
     """Run before the timed region when there are two or more ranks (a one-GPU box cannot):
     copies between two GPUs of one process, and reductions along the SHARDED dim through the C
     library's communicator, each compared bit for bit with the unsharded result; then the time of the
@@ -496,6 +538,33 @@ def multi_gpu_checks(np, torch, thc, state, comm, dev, world, rank, stream):
     except Exception as e:
         out["sharded_check"] = f"error: {e}"
     dist.barrier()
+
+    # ---- the exchange through peer memory against NCCL's all-reduce: same data, same bits ----
+    if True:
+        try:
+            vals = torch.from_numpy(np.nan_to_num(full[start:start + cnt])).to(dev)
+            tvv = wrap(vals, "Float")
+            by_nccl = torch.zeros(1, dtype=torch.float64, device=dev)
+            by_peer = torch.zeros(1, dtype=torch.float64, device=dev)
+            comm.reduce_all(tvv, by_nccl.data_ptr(), "SUM")
+            why = comm.enable_peer_exchange()
+            if why:
+                out["peer_check"] = f"unavailable ({why}): the all-reduce stays with NCCL"
+            else:
+                for _ in range(3):       # three calls: both parities of the exchange blocks
+                    comm.reduce_all(tvv, by_peer.data_ptr(), "SUM")
+                torch.cuda.synchronize(dev)
+                same = bool(by_nccl.item() == by_peer.item()) and not comm.peer_timed_out()
+                agree = torch.tensor([1 if same else 0], device=dev)
+                dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+                if int(agree.item()) == 1:
+                    out["peer_check"] = "ok"
+                else:
+                    out["peer_check"] = f"differs from NCCL on some rank (here {by_peer.item()!r} vs {by_nccl.item()!r})"
+                    comm.disable_peer_exchange()
+        except Exception as e:
+            out["peer_check"] = f"error: {e}"
+        dist.barrier()
 
     # ---- the same two calls at the benchmark's shape: this rank's rows of 524288 x 8192 ----
     try:
@@ -679,6 +748,10 @@ def main():
     ap.add_argument("--no-configs", dest="configs", action="store_false")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-overlap", action="store_true", help="N > 1: run the all-reduce in the compute stream's order")
+    ap.add_argument("--collective", default="nccl", choices=["peer", "nccl"],
+                    help="N > 1, the timed loop: ncclAllReduce overlapped on the communicator's stream (default), or the exchange "
+                         "inside the reducing kernel through peer memory (falls back to NCCL when the blocks cannot be mapped); "
+                         "the other one is timed after the main loop and reported as an extra key")
     ap.add_argument("--only", default="", help="comma list of c1..c4: time just those configs on one GPU and print them")
     ap.add_argument("--reps", type=int, default=0, help="timed repetitions per entry with --only")
     args = ap.parse_args()

@@ -27,6 +27,7 @@
 
 #include "context.h"
 #include "plan.h"
+#include "reduce.cuh"
 
 struct thcb200_comm {
   ncclComm_t comm;
@@ -41,6 +42,14 @@ struct thcb200_comm {
   int pending;            // an all-reduce has been issued on `side` and nobody has waited for it yet
   cudaStream_t side;
   cudaEvent_t ev_local, ev_done;
+  // exchange through peer memory (ExchangeBlock in core.cuh): this rank's block, every rank's block as
+  // mapped here, which of them were opened from an IPC handle, the call counter, the poll limit
+  thcb::ExchangeBlock *own_block;
+  thcb::ExchangeBlock *blocks[thcb::kMaxPeers];
+  unsigned char ipc_opened[thcb::kMaxPeers];
+  int peer_ready, peer_on;
+  unsigned int epoch, max_polls;
+  int *peer_status;       // device word the finishing CTA sets when its wait runs out
 };
 
 namespace thcb {
@@ -173,6 +182,12 @@ void *comm_buffer(thcb200_comm *comm, size_t bytes) {
   return comm->buf;
 }
 
+// the exchange alone, for a rank whose block of the tensor is empty: one warp
+__global__ void __launch_bounds__(32) peer_exchange_only_kernel(PeerExchange px, unsigned long long bits, void *result) {
+  pdl_prologue();
+  peer_exchange(px, bits, result);
+}
+
 int check_comm(thcb200_ctx *ctx, thcb200_comm *comm, const char *what) {
   if (!ctx || !comm) { set_error("%s: null context or communicator", what); return THCB200_ERR_ARG; }
   if (ctx->device != comm->device) { set_error("%s: the context and the communicator belong to different devices", what); return THCB200_ERR_ARG; }
@@ -240,10 +255,128 @@ int thcb200_comm_wait(thcb200_comm *comm, void *stream) {
   return THCB200_OK;
 }
 
+int thcb200_comm_create_local(thcb200_comm **out, int nranks, int rank) {
+  if (!out) { set_error("comm_create_local: null output pointer"); return THCB200_ERR_ARG; }
+  if (nranks < 1 || rank < 0 || rank >= nranks) { set_error("comm_create_local: rank %d outside %d ranks", rank, nranks); return THCB200_ERR_ARG; }
+  if (nranks > kMaxPeers) { set_error("comm_create_local: at most %d ranks exchange through peer memory", kMaxPeers); return THCB200_ERR_LIMIT; }
+  thcb200_comm *c = new thcb200_comm();
+  c->nranks = nranks;
+  c->rank = rank;
+  cudaError_t e = cudaGetDevice(&c->device);
+  if (e != cudaSuccess) { delete c; set_error("comm_create_local: %s", cudaGetErrorString(e)); return THCB200_ERR_CUDA; }
+  *out = c;
+  return THCB200_OK;
+}
+
+size_t thcb200_comm_peer_block_bytes(void) { return sizeof(ExchangeBlock); }
+
+static int ensure_own_block(thcb200_comm *comm) {
+  if (comm->own_block) return 0;
+  if (comm->nranks > kMaxPeers) { set_error("peer exchange: at most %d ranks", kMaxPeers); return THCB200_ERR_LIMIT; }
+  // cudaMalloc, not the stream-ordered pool: the block is exported to other processes
+  void *p = nullptr;
+  cudaError_t e = device_alloc(&p, sizeof(ExchangeBlock));
+  if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(ExchangeBlock));
+  void *st = nullptr;
+  if (e == cudaSuccess) e = device_alloc(&st, 64);
+  if (e == cudaSuccess) e = cudaMemset(st, 0, 64);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();   // zeroed before any peer learns the address
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (p) cudaFree(p);
+    if (st) cudaFree(st);
+    set_error("peer exchange: cannot set up this rank's block: %s", cudaGetErrorString(e));
+    return THCB200_ERR_NOMEM;
+  }
+  comm->own_block = (ExchangeBlock *)p;
+  comm->peer_status = (int *)st;
+  comm->blocks[comm->rank] = comm->own_block;
+  comm->max_polls = 1u << 22;   // about a second of polling before a wait gives up
+  return 0;
+}
+
+int thcb200_comm_peer_export(thcb200_comm *comm, void *handle, size_t bytes) {
+  if (!comm || !handle || bytes < sizeof(cudaIpcMemHandle_t)) { set_error("comm_peer_export: null argument or short buffer"); return THCB200_ERR_ARG; }
+  int rc = ensure_own_block(comm);
+  if (rc) return rc;
+  cudaIpcMemHandle_t h;
+  THCB_CUDA_TRY(cudaIpcGetMemHandle(&h, comm->own_block));
+  memcpy(handle, &h, sizeof(h));
+  return THCB200_OK;
+}
+
+int thcb200_comm_peer_attach(thcb200_comm *comm, const void *handles, size_t bytes_each) {
+  if (!comm || !handles || bytes_each < sizeof(cudaIpcMemHandle_t)) { set_error("comm_peer_attach: null argument or short handles"); return THCB200_ERR_ARG; }
+  int rc = ensure_own_block(comm);
+  if (rc) return rc;
+  for (int r = 0; r < comm->nranks; ++r) {
+    if (r == comm->rank || comm->blocks[r]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, (const char *)handles + (size_t)r * bytes_each, sizeof(h));
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      set_error("comm_peer_attach: cannot map rank %d's block: %s", r, cudaGetErrorString(e));
+      return THCB200_ERR_CUDA;
+    }
+    comm->blocks[r] = (ExchangeBlock *)p;
+    comm->ipc_opened[r] = 1;
+  }
+  comm->peer_ready = 1;
+  return THCB200_OK;
+}
+
+int thcb200_comm_peer_attach_local(thcb200_comm *comm, void *const *blocks) {
+  if (!comm || !blocks) { set_error("comm_peer_attach_local: null argument"); return THCB200_ERR_ARG; }
+  if (comm->nranks > kMaxPeers) { set_error("peer exchange: at most %d ranks", kMaxPeers); return THCB200_ERR_LIMIT; }
+  for (int r = 0; r < comm->nranks; ++r) {
+    if (!blocks[r]) { set_error("comm_peer_attach_local: no block for rank %d", r); return THCB200_ERR_ARG; }
+    comm->blocks[r] = (ExchangeBlock *)blocks[r];
+  }
+  if (!comm->peer_status) {
+    void *st = nullptr;
+    if (device_alloc(&st, 64) != cudaSuccess || cudaMemset(st, 0, 64) != cudaSuccess) {
+      cudaGetLastError();
+      if (st) cudaFree(st);
+      set_error("comm_peer_attach_local: cannot allocate the status word");
+      return THCB200_ERR_NOMEM;
+    }
+    comm->peer_status = (int *)st;
+  }
+  if (!comm->max_polls) comm->max_polls = 1u << 22;
+  comm->peer_ready = 1;
+  return THCB200_OK;
+}
+
+int thcb200_comm_set_peer_exchange(thcb200_comm *comm, int on, unsigned int max_polls) {
+  if (!comm) { set_error("comm_set_peer_exchange: null communicator"); return THCB200_ERR_ARG; }
+  if (on && !comm->peer_ready) { set_error("comm_set_peer_exchange: attach the ranks' blocks first"); return THCB200_ERR_ARG; }
+  comm->peer_on = on ? 1 : 0;
+  if (max_polls) comm->max_polls = max_polls;
+  return THCB200_OK;
+}
+
+int thcb200_comm_peer_status(thcb200_comm *comm, int *timed_out, void *stream) {
+  if (!comm || !timed_out) { set_error("comm_peer_status: null argument"); return THCB200_ERR_ARG; }
+  *timed_out = 0;
+  if (!comm->peer_status) return THCB200_OK;
+  THCB_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  int v = 0;
+  THCB_CUDA_TRY(cudaMemcpy(&v, comm->peer_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (v) THCB_CUDA_TRY(cudaMemset(comm->peer_status, 0, sizeof(int)));
+  *timed_out = v;
+  return THCB200_OK;
+}
+
 void thcb200_comm_destroy(thcb200_comm *comm) {
   if (!comm) return;
-  const NcclApi *n = nccl();
+  const NcclApi *n = comm->comm ? nccl() : nullptr;
   if (comm->side) cudaStreamSynchronize(comm->side);
+  for (int r = 0; r < kMaxPeers; ++r)
+    if (comm->ipc_opened[r] && comm->blocks[r]) cudaIpcCloseMemHandle(comm->blocks[r]);
+  if (comm->own_block) cudaFree(comm->own_block);
+  if (comm->peer_status) cudaFree(comm->peer_status);
   if (n && comm->comm) n->CommDestroy(comm->comm);
   if (comm->buf) cudaFree(comm->buf);
   if (comm->ev_local) cudaEventDestroy(comm->ev_local);
@@ -268,6 +401,7 @@ int thcb200_comm_all_reduce(thcb200_comm *comm, void *buf_dev, int64_t count, in
   const NcclApi *n = nccl();
   if (!n) return THCB200_ERR_UNSUPPORTED;
   if (!comm || !buf_dev || count < 0) { set_error("comm_all_reduce: bad argument"); return THCB200_ERR_ARG; }
+  if (!comm->comm) { set_error("comm_all_reduce: this communicator was created without NCCL"); return THCB200_ERR_UNSUPPORTED; }
   if (nccl_type(dtype) == ncclNumTypes || rop < THCB200_RED_SUM || rop > THCB200_RED_MAX) {
     set_error("comm_all_reduce: dtype %d / fold %d has no NCCL form", dtype, rop);
     return THCB200_ERR_UNSUPPORTED;
@@ -281,6 +415,7 @@ int thcb200_comm_all_gather(thcb200_comm *comm, const void *send_dev, void *recv
   const NcclApi *n = nccl();
   if (!n) return THCB200_ERR_UNSUPPORTED;
   if (!comm || !send_dev || !recv_dev || bytes_per_rank < 0) { set_error("comm_all_gather: bad argument"); return THCB200_ERR_ARG; }
+  if (!comm->comm) { set_error("comm_all_gather: this communicator was created without NCCL"); return THCB200_ERR_UNSUPPORTED; }
   if (bytes_per_rank == 0) return THCB200_OK;
   THCB_NCCL_TRY(n, n->AllGather(send_dev, recv_dev, (size_t)bytes_per_rank, ncclUint8, comm->comm, (cudaStream_t)stream));
   return THCB200_OK;
@@ -293,6 +428,38 @@ int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, in
   if (!in) { set_error("sharded_reduce_all: null tensor"); return THCB200_ERR_ARG; }
   THCB_CTX_LOCK(ctx);
   cudaStream_t st = (cudaStream_t)stream;
+  if (comm->peer_on && comm->nranks > 1) {
+    // one kernel: the finishing CTA stores this rank's accumulator into every rank's block, waits (bounded)
+    // for the others' and folds them in rank order
+    const int fold = rop == THCB200_RED_ALL ? THCB200_RED_MIN : rop == THCB200_RED_ANY ? THCB200_RED_MAX : rop;
+    if (fold < THCB200_RED_SUM || fold > THCB200_RED_MAX) { set_error("sharded_reduce_all: unknown reduce op %d", rop); return THCB200_ERR_ARG; }
+    PeerExchange px;
+    memset(&px, 0, sizeof(px));
+    px.nranks = comm->nranks;
+    px.rank = comm->rank;
+    px.epoch = ++comm->epoch;
+    if (px.epoch == 0) px.epoch = ++comm->epoch;
+    px.max_polls = comm->max_polls;
+    px.fold = fold;
+    px.is_fp = in->dtype >= THCB200_F16 ? 1 : 0;
+    px.status = comm->peer_status;
+    for (int r = 0; r < comm->nranks; ++r) px.block[r] = comm->blocks[r];
+    if (view_numel(in) == 0) {
+      // nothing to fold here, but the other ranks wait for this rank's column: send the identity
+      if (fold == THCB200_RED_MIN || fold == THCB200_RED_MAX) { set_error("sharded_reduce_all: min/max over an empty block"); return THCB200_ERR_ARG; }
+      const bool one = (rop == THCB200_RED_PROD || rop == THCB200_RED_ALL);
+      unsigned long long bits;
+      if (px.is_fp) { const double d = one ? 1.0 : 0.0; memcpy(&bits, &d, 8); } else bits = one ? 1ull : 0ull;
+      launch_pdl(peer_exchange_only_kernel, 1, 32, 0, st, px, bits, result_dev);
+      THCB_CUDA_TRY(cudaGetLastError());
+      return THCB200_OK;
+    }
+    ctx->px = &px;
+    rc = thcb200_reduce_all(ctx, rop, pre, s, in, result_dev, stream);
+    ctx->px = nullptr;
+    return rc;
+  }
+  if (comm->nranks > 1 && !comm->comm) { set_error("sharded_reduce_all: this communicator has no NCCL and its peer exchange is off"); return THCB200_ERR_UNSUPPORTED; }
   // an earlier overlapped all-reduce may still be using a slot: it finishes before this fold writes one
   if (comm->pending) THCB_CUDA_TRY(cudaStreamWaitEvent(st, comm->ev_done, 0));
   // this rank's accumulator, left in the result slot on the device by the finishing CTA

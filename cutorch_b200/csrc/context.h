@@ -11,6 +11,7 @@
 
 namespace thcb {
 constexpr int kNumTickets = 4096;
+struct PeerExchange;
 }
 
 // The scratch of a context (workspace, ticket counters, result slots, mask offsets) is reused
@@ -39,6 +40,9 @@ struct thcb200_ctx {
   void *prep_stream;
   int prep_valid;
   int prep_count_known;   // the host has read the count of that mask from the pinned slot
+  // set by a sharded full reduction for the duration of its launch: fold the other GPUs' accumulators
+  // in the finishing CTA (see ExchangeBlock in core.cuh); null otherwise
+  const thcb::PeerExchange *px;
 };
 
 #define THCB_CTX_LOCK(ctx) std::lock_guard<std::recursive_mutex> thcb_ctx_guard((ctx)->lock)

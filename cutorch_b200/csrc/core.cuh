@@ -191,6 +191,33 @@ template <int VB> __device__ __forceinline__ void stv(void *p, const typename Ve
 }
 
 // ---------------------------------------------------------------------------------
+// Exchange of full-reduction accumulators between the GPUs of a box through peer memory.
+// Every rank owns one ExchangeBlock in its device memory, mapped into every other rank
+// (cudaIpc between processes, plain peer access inside one).  The CTA that finishes a rank's
+// full reduction STORES the rank's 8-byte accumulator and then the call's epoch into its
+// column of every rank's block (peer stores over NVLink, no peer loads), waits -- for a
+// bounded number of polls -- until its own block holds this epoch from every rank, and folds
+// the accumulators in rank order: the reduction and its all-reduce are one kernel, and every
+// rank computes the same bits.  Two parities alternate, so a rank that runs ahead by one call
+// does not overwrite what a slower rank is still reading.
+// ---------------------------------------------------------------------------------
+constexpr int kMaxPeers = 16;
+struct ExchangeBlock {
+  unsigned long long slot[2][kMaxPeers];   // [parity][writer rank]: accumulator bits (double or int64)
+  unsigned int flag[2][kMaxPeers];         // [parity][writer rank]: epoch of the call that wrote the slot
+};
+struct PeerExchange {
+  int nranks;                 // 0 or 1: no exchange
+  int rank;
+  unsigned int epoch;         // grows by one per call, never 0
+  unsigned int max_polls;     // per awaited rank; the wait gives up after that and sets *status
+  int fold;                   // THCB200_RED_SUM / PROD / MIN / MAX
+  int is_fp;                  // slots hold doubles (else int64)
+  int *status;                // device word, set to 1 when a wait ran out
+  ExchangeBlock *block[kMaxPeers];   // block[r]: rank r's block as this process addresses it
+};
+
+// ---------------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of the library starts with pdl_prologue() and is
 // launched through launch_pdl(): the launch carries the programmatic-stream-serialization
 // attribute, so the GPU may make the kernel's CTAs resident while the previous kernel of the stream

@@ -333,11 +333,73 @@ template <typename P> __device__ __forceinline__ P load_partial(const P *p) {
 }
 
 // ====================================================================================
+// Cross-GPU part of a full reduction (see ExchangeBlock in core.cuh).  Called by the 32 lanes of
+// warp 0 of the finishing CTA with the rank's accumulator bits; lane 0 stores the folded result.
+// ====================================================================================
+__device__ __forceinline__ unsigned long long slot_fold(int fold, int is_fp, unsigned long long a, unsigned long long b) {
+  if (is_fp) {
+    const double x = __longlong_as_double((long long)a), y = __longlong_as_double((long long)b);
+    double r;
+    switch (fold) {
+      case THCB200_RED_PROD: r = x * y; break;
+      case THCB200_RED_MIN: r = (x != x) ? x : (y != y) ? y : (x < y ? x : y); break;   // a NaN wins, the first one
+      case THCB200_RED_MAX: r = (x != x) ? x : (y != y) ? y : (x > y ? x : y); break;
+      default: r = x + y; break;
+    }
+    return (unsigned long long)__double_as_longlong(r);
+  }
+  const long long x = (long long)a, y = (long long)b;
+  switch (fold) {
+    case THCB200_RED_PROD: return a * b;
+    case THCB200_RED_MIN: return (unsigned long long)(x < y ? x : y);
+    case THCB200_RED_MAX: return (unsigned long long)(x > y ? x : y);
+    default: return a + b;
+  }
+}
+
+__device__ __forceinline__ void peer_exchange(const PeerExchange &px, unsigned long long mine, void *result) {
+  const int lane = threadIdx.x & 31;
+  const int par = (int)(px.epoch & 1u);
+  if (lane < px.nranks) {
+    // my accumulator, then the epoch, into my column of rank `lane`'s block
+    ExchangeBlock *peer = px.block[lane];
+    *reinterpret_cast<volatile unsigned long long *>(&peer->slot[par][px.rank]) = mine;
+    __threadfence_system();
+    *reinterpret_cast<volatile unsigned int *>(&peer->flag[par][px.rank]) = px.epoch;
+  }
+  // every rank's column of my own block must show this epoch; a bounded number of polls each
+  ExchangeBlock *own = px.block[px.rank];
+  bool arrived = true;
+  if (lane < px.nranks) {
+    const volatile unsigned int *f = &own->flag[par][lane];
+    unsigned int polls = 0;
+    while ((int)(*f - px.epoch) < 0) {
+      if (++polls > px.max_polls) { arrived = false; break; }
+      __nanosleep(200);
+    }
+  }
+  arrived = __all_sync(0xffffffffu, arrived);
+  __threadfence_system();
+  if (lane == 0) {
+    unsigned long long r = mine;
+    if (arrived) {
+      r = *reinterpret_cast<volatile unsigned long long *>(&own->slot[par][0]);
+      for (int k = 1; k < px.nranks; ++k)
+        r = slot_fold(px.fold, px.is_fp, r, *reinterpret_cast<volatile unsigned long long *>(&own->slot[par][k]));
+    } else {
+      *px.status = 1;   // the host reads this; the slot keeps this rank's own accumulator
+    }
+    *reinterpret_cast<unsigned long long *>(result) = r;
+  }
+}
+
+// ====================================================================================
 // Tail shared by the full-reduction kernels: fold the CTA's accumulators, store the CTA's
 // partial, and let the CTA that draws the last ticket fold all partials in index order.
 // ====================================================================================
 template <typename T, int MODE>
-__device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void *partials_raw, unsigned int *ticket, void *result) {
+__device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void *partials_raw, unsigned int *ticket, void *result,
+                                                  const PeerExchange &px) {
   using F = Folder<T, MODE>;
   using Acc = typename F::Acc;
   struct Partial { Acc v; int has; };
@@ -375,11 +437,17 @@ __device__ __forceinline__ void reduce_all_finish(Opt<Folder<T, MODE>> acc, void
     Opt<F> b = Opt<F>::start();
     if (lane < kRedWarps) { b.v = sm[lane].v; b.has = sm[lane].has; }
     b = warp_fold_opt<F>(b);
-    if (lane == 0) {
-      // result slot: double for floating element types, int64 for integer ones
+    if (lane == 0) *ticket = 0;  // ready for the next launch on this stream
+    // result slot: double for floating element types, int64 for integer ones
+    if (px.nranks > 1) {
+      // the other GPUs' accumulators are folded in here, by this warp, before the kernel ends
+      unsigned long long bits;
+      if constexpr (TypeTraits<T>::is_fp) bits = (unsigned long long)__double_as_longlong((double)b.v);
+      else bits = (unsigned long long)(int64_t)b.v;
+      peer_exchange(px, bits, result);
+    } else if (lane == 0) {
       if constexpr (TypeTraits<T>::is_fp) *reinterpret_cast<double *>(result) = (double)b.v;
       else *reinterpret_cast<int64_t *>(result) = (int64_t)b.v;
-      *ticket = 0;  // ready for the next launch on this stream
     }
   }
 }
@@ -423,7 +491,7 @@ constexpr int kRedRowsSlots = 8;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Folder<T, MODE>::Params prm,
-                       void *partials_raw, unsigned int *ticket, void *result) {
+                       void *partials_raw, unsigned int *ticket, void *result, PeerExchange px) {
   pdl_prologue();
   using F = Folder<T, MODE>;
   constexpr int V = 16 / (int)sizeof(T);
@@ -463,7 +531,7 @@ reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Fo
     }
     if (eok) acc.feed(F::pre(edge, prm));
   }
-  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
+  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result, px);
 }
 
 // ====================================================================================
@@ -473,7 +541,7 @@ reduce_all_rows_kernel(const T *in, RedRowsView rv, uint32_t ntiles, typename Fo
 template <typename T, int MODE, int VB /* vector bytes: 32, 16, or 0 = strided walk */>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename Folder<T, MODE>::Params prm,
-                  void *partials_raw, unsigned int *ticket, void *result, const T *edge, uint32_t nedge) {
+                  void *partials_raw, unsigned int *ticket, void *result, const T *edge, uint32_t nedge, PeerExchange px) {
   pdl_prologue();
   using F = Folder<T, MODE>;
   constexpr bool VEC = VB != 0;
@@ -512,7 +580,7 @@ reduce_all_kernel(const T *in, StridedView<uint64_t> view, uint64_t n, typename 
       for (int u = 0; u < kRedUnroll; ++u) if (ok[u]) acc.feed(F::pre(x[u], prm));
     }
   }
-  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result);
+  reduce_all_finish<T, MODE>(acc, partials_raw, ticket, result, px);
 }
 
 // ====================================================================================

@@ -2,6 +2,8 @@
 // type instantiates reduce_all_typed<T>, reduce_dim_typed<T> and reduce_dim_index_typed<T>.
 #pragma once
 
+#include <string.h>
+
 #include <algorithm>
 
 #include "context.h"
@@ -37,6 +39,9 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   collapse_dims(sizes, strides, &nd, -1);
   if (nd > kGenericDims) { set_error("reduce_all: more than %d non-collapsible dimensions", kGenericDims); return THCB200_ERR_DIMS; }
   const uint64_t n = (uint64_t)in.numel;
+  // a sharded call hands its exchange description over through the context (which it holds locked)
+  PeerExchange px;
+  if (ctx->px) px = *ctx->px; else memset(&px, 0, sizeof(px));
   const bool unit = nd == 1 && strides[0] == 1;
   const T *p = reinterpret_cast<const T *>(in.data);
   const uint64_t max_grid = (uint64_t)ctx->num_sms * 4;
@@ -79,7 +84,7 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
         void *partials = ctx_workspace(ctx, grid * 16);
         if (!partials) return THCB200_ERR_NOMEM;
         set_plan_name("reduce_all_rows");
-        launch_pdl(reduce_all_rows_kernel<T, MODE>, (unsigned)grid, kRedThreads, 0, st, p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result);
+        launch_pdl(reduce_all_rows_kernel<T, MODE>, (unsigned)grid, kRedThreads, 0, st, p, rv, (uint32_t)ntiles, prm, partials, ctx->tickets, result, px);
         count_launch();
         THCB_CUDA_TRY(cudaGetLastError());
         return 0;
@@ -123,10 +128,10 @@ int launch_reduce_all(thcb200_ctx *ctx, const HostView &in, thcb200_scalar s, vo
   }
   if (vb == 32) {
     set_plan_name(nedge ? "reduce_all_vec_peeled" : "reduce_all_vec");
-    launch_pdl(reduce_all_kernel<T, MODE, 32>, (unsigned)grid, kRedThreads, 0, st, body, view, nbody, prm, partials, ctx->tickets, result, p, nedge);
+    launch_pdl(reduce_all_kernel<T, MODE, 32>, (unsigned)grid, kRedThreads, 0, st, body, view, nbody, prm, partials, ctx->tickets, result, p, nedge, px);
   } else {
     set_plan_name("reduce_all_strided");
-    launch_pdl(reduce_all_kernel<T, MODE, 0>, (unsigned)grid, kRedThreads, 0, st, p, view, n, prm, partials, ctx->tickets, result, p, 0u);
+    launch_pdl(reduce_all_kernel<T, MODE, 0>, (unsigned)grid, kRedThreads, 0, st, p, view, n, prm, partials, ctx->tickets, result, p, 0u, px);
   }
   count_launch();
   THCB_CUDA_TRY(cudaGetLastError());

@@ -43,6 +43,10 @@ class Comm:
         lib.thcb200_comm_destroy.restype = None
         lib.thcb200_comm_info.argtypes = [vp, P(C.c_int), P(C.c_int), P(C.c_int)]
         lib.thcb200_comm_all_reduce.argtypes = [vp, vp, C.c_int64, C.c_int, C.c_int, vp]
+        lib.thcb200_comm_peer_export.argtypes = [vp, vp, C.c_size_t]
+        lib.thcb200_comm_peer_attach.argtypes = [vp, vp, C.c_size_t]
+        lib.thcb200_comm_set_peer_exchange.argtypes = [vp, C.c_int, C.c_uint]
+        lib.thcb200_comm_peer_status.argtypes = [vp, P(C.c_int), vp]
         lib.thcb200_comm_set_overlap.argtypes = [vp, C.c_int]
         lib.thcb200_comm_wait.argtypes = [vp, vp]
         lib.thcb200_comm_all_gather.argtypes = [vp, vp, vp, C.c_int64, vp]
@@ -111,6 +115,48 @@ class Comm:
     def all_reduce(self, dev_ptr: int, count: int, dtype: int, rop: str = "SUM"):
         C, L = self._C, self._lib_mod
         L.check(self.lib.thcb200_comm_all_reduce(self.handle, C.c_void_p(dev_ptr), count, dtype, L.RED[rop], C.c_void_p(self.state.stream)))
+
+    def enable_peer_exchange(self, group=None, max_polls: int = 0) -> str:
+        """Full reductions exchange their accumulators through peer memory from now on, inside the reducing
+        kernel (thcb200_comm_peer_export / _attach / _set_peer_exchange): every rank exports a handle of its
+        exchange block, torch.distributed gathers the handles, every rank maps the others' blocks.  Returns ""
+        when every rank succeeded; otherwise the first rank's reason, with the exchange left off everywhere
+        (all ranks take the same decision)."""
+        C = self._C
+
+        def agree(err):
+            errs = [None] * self.nranks
+            dist.all_gather_object(errs, err, group=group)
+            return next((f"rank {r}: {e}" for r, e in enumerate(errs) if e), "")
+
+        mine = C.create_string_buffer(64)
+        rc = self.lib.thcb200_comm_peer_export(self.handle, mine, 64)
+        why = agree(self.lib.thcb200_last_error().decode() if rc else "")
+        if why:
+            return why
+        handles = [None] * self.nranks
+        dist.all_gather_object(handles, mine.raw, group=group)
+        table = C.create_string_buffer(b"".join(handles), 64 * self.nranks)
+        rc = self.lib.thcb200_comm_peer_attach(self.handle, table, 64)
+        why = agree(self.lib.thcb200_last_error().decode() if rc else "")      # also: every block is mapped everywhere
+        if why:
+            return why
+        self._lib_mod.check(self.lib.thcb200_comm_set_peer_exchange(self.handle, 1, max_polls))
+        return ""
+
+    def disable_peer_exchange(self):
+        self._lib_mod.check(self.lib.thcb200_comm_set_peer_exchange(self.handle, 0, 0))
+
+    def resume_peer_exchange(self):
+        """Switches the exchange back on after disable_peer_exchange (the blocks stay mapped)."""
+        self._lib_mod.check(self.lib.thcb200_comm_set_peer_exchange(self.handle, 1, 0))
+
+    def peer_timed_out(self) -> bool:
+        """Waits for the current stream; True when an exchange gave up waiting for a rank since the last call."""
+        C = self._C
+        v = C.c_int(0)
+        self._lib_mod.check(self.lib.thcb200_comm_peer_status(self.handle, C.byref(v), C.c_void_p(self.state.stream)))
+        return bool(v.value)
 
     def set_overlap(self, on: bool):
         """Full reductions all-reduce on the communicator's own stream from now on (see thcb200_comm_set_overlap)."""

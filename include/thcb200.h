@@ -446,6 +446,28 @@ THCB200_API int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm,
  * gather and combine (floating min / max) always run in the caller's stream order. */
 THCB200_API int thcb200_comm_set_overlap(thcb200_comm *comm, int on);
 THCB200_API int thcb200_comm_wait(thcb200_comm *comm, void *stream);
+/* Exchange through peer memory instead of NCCL, for thcb200_sharded_reduce_all: the CTA that finishes a
+ * rank's reduction stores the rank's accumulator into a small block in every rank's device memory (peer
+ * stores over NVLink), waits until its own block holds every rank's, and folds them in rank order -- the
+ * reduction and its all-reduce are one kernel and every rank gets the same bits.  The wait is bounded:
+ * after `max_polls` polls per awaited rank (0 keeps the default of about a second) the kernel stores the
+ * rank's own accumulator, sets a status word and returns; thcb200_comm_peer_status synchronises `stream`
+ * and reports (and clears) that word.  At most 16 ranks; every rank must make the same calls.
+ *   between processes: every rank calls _peer_export (a cudaIpc handle of THCB200_PEER_HANDLE_BYTES), the
+ *     handles are gathered by any means into one array in rank order, every rank calls _peer_attach;
+ *   inside one process that drives several devices, as cutorch programs do (peer access enabled by the
+ *     caller): allocate _peer_block_bytes() zeroed bytes per rank with cudaMalloc and hand every
+ *     communicator the same array of pointers with _peer_attach_local; such communicators need no NCCL
+ *     (thcb200_comm_create_local).
+ * Then thcb200_comm_set_peer_exchange(comm, 1, 0) on every rank. */
+#define THCB200_PEER_HANDLE_BYTES 64
+THCB200_API int thcb200_comm_create_local(thcb200_comm **out, int nranks, int rank);
+THCB200_API size_t thcb200_comm_peer_block_bytes(void);
+THCB200_API int thcb200_comm_peer_export(thcb200_comm *comm, void *handle, size_t bytes);
+THCB200_API int thcb200_comm_peer_attach(thcb200_comm *comm, const void *handles, size_t bytes_each);
+THCB200_API int thcb200_comm_peer_attach_local(thcb200_comm *comm, void *const *blocks);
+THCB200_API int thcb200_comm_set_peer_exchange(thcb200_comm *comm, int on, unsigned int max_polls);
+THCB200_API int thcb200_comm_peer_status(thcb200_comm *comm, int *timed_out, void *stream);
 /* thcb200_reduce_dim along the dim the tensor is split on: each rank reduces its rows into `out`
  * (dense), then the ranks' outputs are folded and every rank holds the result in `out`.  float /
  * double / int32 / int64 sums and products and integer min / max use ncclAllReduce on the element
