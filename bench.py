@@ -331,7 +331,8 @@ def ours_main(args):
         checks[key + "_ms_per_step"] = round(float(ta.item()), 4)
         if other == "peer":
             checks["peer_exchange_timed_out"] = bool(comm.peer_timed_out())
-        checks["other_checksum_equal"] = bool(float(partial.item()) == total_sum)
+        # NCCL folds the ranks' doubles in its own order, the exchange in rank order: the totals agree to rounding
+        checks["other_checksum_rel_diff"] = abs(float(partial.item()) - total_sum) / max(abs(total_sum), 1e-300)
         # back to the mode of the main loop for the legs that follow
         if other == "peer":
             comm.disable_peer_exchange()
