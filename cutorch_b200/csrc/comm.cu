@@ -437,8 +437,8 @@ int thcb200_sharded_reduce_all(thcb200_ctx *ctx, thcb200_comm *comm, int rop, in
     memset(&px, 0, sizeof(px));
     px.nranks = comm->nranks;
     px.rank = comm->rank;
-    px.epoch = ++comm->epoch;
-    if (px.epoch == 0) px.epoch = ++comm->epoch;
+    if (++comm->epoch == 0) comm->epoch = 2;   // never 0, and the parity keeps alternating across the wrap
+    px.epoch = comm->epoch;
     px.max_polls = comm->max_polls;
     px.fold = fold;
     px.is_fp = in->dtype >= THCB200_F16 ? 1 : 0;
