@@ -132,7 +132,7 @@ def test_thc_type_api_declares_every_prototype_of_cutorchs_generic_headers():
     ours_text = (GOLDEN.parent.parent / "include" / "THC" / "THCTypeAPI.h").read_text()
     ours = {_strip_parameter_names(p) for p in mg.prototypes_of(ours_text)}
     fixture = json.loads((GOLDEN / "thc_prototypes.json").read_text())
-    # what SURVEY scopes out: needs sort (median), thrust tabulate with TH's evaluation order (linspace ...),
+    # outside this library's scope: needs sort (median), thrust tabulate with TH's evaluation order (linspace ...),
     # and cutorch's internal helper for advanced indexing
     out_of_scope = ("median", "medianall", "linspace", "logspace", "range", "arange", "calculateAdvancedIndexingOffsets")
     missing = []
