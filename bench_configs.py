@@ -369,6 +369,19 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
         txt, tyt = W(xt, "Float"), W(yt, "Float")
         out["b_template_apply2_scale_f32_transposed_source_16384x8192"] = timed(
             lambda: ulib.usertest_scale(state.ptr, tyt.ptr, txt.ptr, 1.5), 8 * n, reps=5)
+        # user reductions through THC_reduceDim / THC_reduceAll: a sum of squares along each dim, an absolute maximum
+        ulib.usertest_sumsq_dim.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        ulib.usertest_sumsq_dim.restype = C.c_int
+        ulib.usertest_absmax_all.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
+        ulib.usertest_absmax_all.restype = C.c_int
+        m = x.view(16384, 8192)
+        tm = W(m, "Float")
+        r1, r0 = torch.empty(16384, 1, device=dev), torch.empty(1, 8192, device=dev)
+        tr1, tr0 = W(r1, "Float"), W(r0, "Float")
+        out["b_template_reduceDim_sumsq_f32_16384x8192_dim1"] = timed(lambda: ulib.usertest_sumsq_dim(state.ptr, tr1.ptr, tm.ptr, 1, 1), 4 * n, reps=5)
+        out["b_template_reduceDim_sumsq_f32_16384x8192_dim0"] = timed(lambda: ulib.usertest_sumsq_dim(state.ptr, tr0.ptr, tm.ptr, 0, 1), 4 * n, reps=5)
+        host_max = C.c_float(0)
+        out["b_template_reduceAll_absmax_f32_128M_to_host"] = timed(lambda: ulib.usertest_absmax_all(state.ptr, tx.ptr, C.byref(host_max)), 4 * n, reps=5)
 
     # c1-c4 come last so that they are the end of the printed line
     for name, fn in (("next", nxt), ("generic", generic), ("xdev", xdev), ("host", host), ("template", template),

@@ -38,7 +38,8 @@ def _nvcc() -> str:
 
 
 def _newest_header() -> float:
-    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.rglob("*.h")) + list(CSRC.glob("*.inc"))
+    hs = (list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(INCLUDE.rglob("*.h")) + list(INCLUDE.rglob("*.cuh")) +
+          list(CSRC.glob("*.inc")))
     return max(h.stat().st_mtime for h in hs)
 
 

@@ -17,8 +17,8 @@
  * replaced by a contiguous copy and copied back (copyIgnoringOverlaps); the launch goes to the
  * THCState's current stream.  Layout planning (collapseDims, overlap test, 32- vs 64-bit indices)
  * is done by the host functions exported from libthcb200 (thcb200.h).  The kernels decode offsets
- * with multiply-high divisions, take eight elements per thread, and are compiled with non-aliasing
- * pointers when the operands sit in storages that do not overlap (so the loads of the eight
+ * with multiply-high divisions, take four elements per thread, and are compiled with non-aliasing
+ * pointers when the operands sit in storages that do not overlap (so the loads of the four
  * elements can be in flight together); the memory pattern itself is the functor's: a transposed
  * operand is read the way its strides say, since pointer-taking functors cannot be staged through
  * shared memory.
@@ -125,11 +125,11 @@ inline int64_t numel(const thcb200_tensor &d) {
 }
 
 constexpr int kThreads = 256;
-constexpr int kPerThread = 8;   // elements per thread and step: their offsets are decoded together
+constexpr int kPerThread = 4;   // elements per thread and step: their offsets are decoded together
 
 // A thread takes kPerThread elements, kThreads apart (neighbouring lanes on neighbouring elements),
 // decodes all their offsets first and then runs the functor on each.  NOALIAS (picked on the host
-// when the operands' memory ranges are disjoint) lets the compiler start the loads of all eight
+// when the operands' memory ranges are disjoint) lets the compiler start the loads of all four
 // before the first store; otherwise a store through one pointer orders every later load.
 #define THCB_USER_PTR(T, NOALIAS) typename PtrOf<T, NOALIAS>::type
 template <typename T, bool NOALIAS> struct PtrOf { typedef T *type; };

@@ -63,6 +63,8 @@ __device__ __forceinline__ AccT block_fold(AccT acc, AccT *buf, const ReduceAccO
   return buf[0];
 }
 
+constexpr int kLoadsInFlight = 8;   // elements a thread loads before it folds the first of them
+
 // one CTA per slice; threads stride over the reduced dim
 template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
 __global__ void __launch_bounds__(kReduceThreads)
@@ -74,9 +76,83 @@ reduce_dim_cta_kernel(T *out, const T *in, SliceView sv, uint64_t K, int64_t str
   sv.decode(blockIdx.x, in_off, out_off);
   const T *p = in + in_off;
   AccT acc = init;
-  for (uint64_t k = threadIdx.x; k < K; k += blockDim.x) acc = reduceOp(acc, modifyOp(p[(int64_t)k * strideK]));
+  // kLoadsInFlight elements are loaded before the first is folded (the functors take values, so the
+  // loads do not depend on one another); they are folded in the order a one-at-a-time walk would take
+  for (uint64_t k0 = threadIdx.x; k0 < K; k0 += (uint64_t)blockDim.x * kLoadsInFlight) {
+    T x[kLoadsInFlight];
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u) {
+      const uint64_t k = k0 + (uint64_t)u * blockDim.x;
+      if (k < K) x[u] = p[(int64_t)k * strideK];
+    }
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u)
+      if (k0 + (uint64_t)u * blockDim.x < K) acc = reduceOp(acc, modifyOp(x[u]));
+  }
   acc = block_fold(acc, buf, accOp);
   if (threadIdx.x == 0) out[out_off] = (T)acc;
+}
+
+// The reduced dim is strided and some other dim (`inner` elements, stride 1 in the input) is dense:
+// the 32 lanes of a warp sit on 32 neighbouring slices, so every load of a warp is one 128-byte
+// line, the CTA's warps take the reduced positions round-robin with kLoadsInFlight of them in
+// flight per thread, and the warps' accumulators are merged in warp order through shared memory.
+template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_dim_col_kernel(T *out, const T *in, SliceView sv /* the dims other than the reduced and the inner one */, uint64_t inner,
+                      int64_t out_inner_stride, uint32_t tiles_i, uint64_t K, int64_t strideK, AccT init, ModifyOp modifyOp,
+                      ReduceOp reduceOp, ReduceAccOp accOp, uint32_t nsplit, uint64_t split_len, AccT *partials) {
+  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);     // [warp][lane]
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  // blockIdx.x -> (outer slice, split of the reduced dim, tile of 32 inner positions)
+  uint32_t b = blockIdx.x;
+  const uint32_t ti = b % tiles_i; b /= tiles_i;
+  const uint32_t split = b % nsplit;
+  const uint64_t outer = b / nsplit;
+  const uint64_t i = (uint64_t)ti * 32 + lane;
+  int64_t in_off, out_off;
+  sv.decode(outer, in_off, out_off);
+  const T *p = in + in_off + (int64_t)i;
+  const uint64_t kbeg = (uint64_t)split * split_len, kend = kbeg + split_len < K ? kbeg + split_len : K;
+  AccT acc = init;
+  if (i < inner) {
+    for (uint64_t k0 = kbeg + warp; k0 < kend; k0 += (uint64_t)nwarps * kLoadsInFlight) {
+      T x[kLoadsInFlight];
+#pragma unroll
+      for (int u = 0; u < kLoadsInFlight; ++u) {
+        const uint64_t k = k0 + (uint64_t)u * nwarps;
+        if (k < kend) x[u] = p[(int64_t)k * strideK];
+      }
+#pragma unroll
+      for (int u = 0; u < kLoadsInFlight; ++u)
+        if (k0 + (uint64_t)u * nwarps < kend) acc = reduceOp(acc, modifyOp(x[u]));
+    }
+  }
+  buf[warp * 32 + lane] = acc;
+  __syncthreads();
+  if (warp == 0 && i < inner) {
+    AccT r = buf[lane];
+    for (unsigned w = 1; w < nwarps; ++w) r = accOp(r, buf[w * 32 + lane]);
+    if (nsplit > 1) partials[(outer * nsplit + split) * inner + i] = r;   // [outer][split][inner]
+    else out[out_off + (int64_t)i * out_inner_stride] = (T)r;
+  }
+}
+
+// second stage of a split column reduction: partials [outer][split][inner] folded in split order
+template <typename T, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_dim_col_finish_kernel(T *out, SliceView sv, uint64_t nouter, uint64_t inner, int64_t out_inner_stride, uint32_t nsplit,
+                             const AccT *partials, ReduceAccOp accOp) {
+  const uint64_t o = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x;
+  if (o >= nouter * inner) return;
+  const uint64_t outer = o / inner, i = o - outer * inner;
+  int64_t in_off, out_off;
+  sv.decode(outer, in_off, out_off);
+  const AccT *pp = partials + outer * nsplit * inner + i;
+  AccT r = pp[0];
+  for (uint32_t s2 = 1; s2 < nsplit; ++s2) r = accOp(r, pp[(uint64_t)s2 * inner]);
+  out[out_off + (int64_t)i * out_inner_stride] = (T)r;
 }
 
 // one thread per slice; neighbouring threads take neighbouring slices
@@ -90,7 +166,15 @@ reduce_dim_thread_kernel(T *out, const T *in, SliceView sv, uint64_t nslices, ui
   sv.decode(s, in_off, out_off);
   const T *p = in + in_off;
   AccT acc = init;
-  for (uint64_t k = 0; k < K; ++k) acc = reduceOp(acc, modifyOp(p[(int64_t)k * strideK]));
+  for (uint64_t k0 = 0; k0 < K; k0 += kLoadsInFlight) {
+    T x[kLoadsInFlight];
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u)
+      if (k0 + u < K) x[u] = p[(int64_t)(k0 + u) * strideK];
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u)
+      if (k0 + u < K) acc = reduceOp(acc, modifyOp(x[u]));
+  }
   out[out_off] = (T)acc;
 }
 
@@ -102,8 +186,18 @@ reduce_all_partial_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, 
   extern __shared__ __align__(16) unsigned char thcb_user_smem[];
   AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
   AccT acc = init;
-  for (uint64_t i = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kReduceThreads)
-    acc = reduceOp(acc, modifyOp(in[v.offset(i)]));
+  const uint64_t step = (uint64_t)gridDim.x * kReduceThreads;
+  for (uint64_t i0 = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x; i0 < n; i0 += step * kLoadsInFlight) {
+    T x[kLoadsInFlight];
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u) {
+      const uint64_t i = i0 + (uint64_t)u * step;
+      if (i < n) x[u] = in[v.offset(i)];
+    }
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u)
+      if (i0 + (uint64_t)u * step < n) acc = reduceOp(acc, modifyOp(x[u]));
+  }
   acc = block_fold(acc, buf, accOp);
   if (threadIdx.x == 0) partials[blockIdx.x] = acc;
 }
@@ -168,7 +262,55 @@ bool THC_reduceDim(THCState *state, TensorType *out, TensorType *in, const Modif
   thcb200_tensor din = describe(in), dout = describe(out);
   cudaStream_t st = THCState_getCurrentStream(state);
   bool ok = true;
-  if (nslices > 0 && K > 0) {
+  // a dense dim other than the reduced one (the innermost such): lanes go along it
+  int inner_dim = -1;
+  if (strideK != 1)
+    for (int d = in->nDimension - 1; d >= 0; --d)
+      if (d != dim && in->stride[d] == 1 && in->size[d] >= 32) { inner_dim = d; break; }
+  if (nslices > 0 && K > 0 && inner_dim >= 0 && sizeof(AccT) * kReduceThreads <= 48 * 1024) {
+    SliceView so;
+    so.n = 0;
+    uint64_t nouter = 1;
+    for (int d = 0; d < in->nDimension; ++d) {
+      if (d == dim || d == inner_dim || in->size[d] == 1) continue;
+      so.size[so.n] = (uint64_t)in->size[d];
+      so.in_stride[so.n] = in->stride[d];
+      so.out_stride[so.n] = out->stride[d];
+      nouter *= (uint64_t)in->size[d];
+      ++so.n;
+    }
+    const uint64_t inner = (uint64_t)in->size[inner_dim];
+    const uint64_t tiles_i = (inner + 31) / 32;
+    // few tiles: the reduced dim is cut into splits (one CTA each) whose partials a second small kernel
+    // folds in split order; about eight CTAs per SM in all
+    uint64_t nsplit = 1, split_len = K;
+    const uint64_t ctas = nouter * tiles_i, want_ctas = 148ull * 8;
+    if (ctas < want_ctas && K >= 512) {
+      nsplit = want_ctas / ctas;
+      if (nsplit > K / 256) nsplit = K / 256;
+      if (nsplit < 1) nsplit = 1;
+      split_len = (K + nsplit - 1) / nsplit;
+      nsplit = (K + split_len - 1) / split_len;
+    }
+    AccT *partials = 0;
+    if (ctas * nsplit >= (1ull << 31)) ok = false;
+    if (ok && nsplit > 1 && cudaMallocAsync((void **)&partials, sizeof(AccT) * nouter * nsplit * inner, st) != cudaSuccess) {
+      cudaGetLastError();
+      ok = false;
+    }
+    if (ok) {
+      reduce_dim_col_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)(ctas * nsplit), kReduceThreads,
+                                                                      sizeof(AccT) * kReduceThreads, st>>>(
+          (T *)dout.data, (const T *)din.data, so, inner, out->stride[inner_dim], (uint32_t)tiles_i, K, strideK, init, modifyOp,
+          reduceOp, reduceAccOp, (uint32_t)nsplit, split_len, partials);
+      if (nsplit > 1) {
+        const uint64_t outs = nouter * inner;
+        reduce_dim_col_finish_kernel<T, ReduceAccOp, AccT><<<(unsigned)((outs + kReduceThreads - 1) / kReduceThreads), kReduceThreads, 0, st>>>(
+            (T *)dout.data, so, nouter, inner, out->stride[inner_dim], (uint32_t)nsplit, partials, reduceAccOp);
+        cudaFreeAsync(partials, st);
+      }
+    }
+  } else if (nslices > 0 && K > 0) {
     // lanes along the reduced dim when it is the dense one or when there are too few slices to
     // fill the GPU with a thread each; otherwise a thread per slice
     const bool cta_per_slice = strideK == 1 || nslices < 148ull * 8 * kReduceThreads / 32;

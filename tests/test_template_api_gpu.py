@@ -91,7 +91,8 @@ def test_reduce_dim_user_functors(state, user):
     user.usertest_sumsq_dim.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
     r = rng("user-reduce-dim")
     for shape, layout in [((40, 1000), "contiguous"), ((1000, 40), "transposed"), ((6, 7, 50), "permuted"),
-                          ((3000, 5), "contiguous"), ((9, 2000, 3), "holes")]:
+                          ((3000, 5), "contiguous"), ((9, 2000, 3), "holes"), ((300, 70), "contiguous"), ((17, 33, 65), "offset"),
+                          ((5, 700, 33), "contiguous"), ((3000, 40), "contiguous")]:
         # multiples of 1/4 so that float sums of squares are exact in any order
         x = make_view(r, "Float", shape, layout)
         x[...] = (r.integers(-8, 9, size=shape) / 4).astype(np.float32)
