@@ -401,6 +401,17 @@ def ours_main(args):
         extra["per_config"] = per_config
         # the c1-c4 figures as flat scalar keys of `roofline`: fraction of the measured peak of the
         # flushed single call, its median, and the per-call time of a back-to-back train over rotating buffers
+        # ... and the fractions of the rows around the path that were below 0.85 of the measured peak
+        for name, short in (("f1_maskedSelect_f32_128M_half_set", "maskedSelect"), ("f2_cumsum_f32_1d_128M", "cumsum_1d_chunked"),
+                            ("f2_cumsum_f32_16384x8192_dim0", "cumsum_dim0_chunked"),
+                            ("a7_sum_dim0_f32_16384x8191_odd_columns", "sum_dim0_odd_width"),
+                            ("a8_max_dim0_f32_16384x8191_odd_columns", "max_dim0_odd_width"),
+                            ("b_template_apply2_scale_f32_contiguous_128M", "template_apply_contiguous"),
+                            ("b_template_apply2_scale_f32_transposed_source_16384x8192", "template_apply_transposed"),
+                            ("b_template_reduceDim_sumsq_f32_16384x8192_dim1", "template_reduce_dim1"),
+                            ("b_template_reduceDim_sumsq_f32_16384x8192_dim0", "template_reduce_dim0")):
+            if name in per_config and "frac" in per_config[name]:
+                roofline[short + "_frac"] = per_config[name]["frac"]
         for name, r in per_config.items():
             if not name.startswith(("c1_", "c2_", "c3_", "c4_")):
                 continue

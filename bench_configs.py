@@ -386,7 +386,7 @@ def run_small_configs(torch, thc, state, stream, dev, peak, only=None, reps_over
     # c1-c4 come last so that they are the end of the printed line
     for name, fn in (("next", nxt), ("generic", generic), ("xdev", xdev), ("host", host), ("template", template),
                      ("c1", c1), ("c2", c2), ("c3", c3), ("c4", c4)):
-        if name in ("xdev", "host", "template") and (only is None or name not in only):
+        if name in ("xdev", "host") and (only is None or name not in only):
             continue
         if only is None or name in only:
             fn()
