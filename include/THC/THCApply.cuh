@@ -16,12 +16,19 @@
  * dimensions is a no-op returning true; a ReadWrite / WriteOnly operand whose index tuples alias is
  * replaced by a contiguous copy and copied back (copyIgnoringOverlaps); the launch goes to the
  * THCState's current stream.  Layout planning (collapseDims, overlap test, 32- vs 64-bit indices)
- * is done by the host functions exported from libthcb200 (thcb200.h).  The kernels decode offsets
- * with multiply-high divisions, take four elements per thread, and are compiled with non-aliasing
- * pointers when the operands sit in storages that do not overlap (so the loads of the four
- * elements can be in flight together); the memory pattern itself is the functor's: a transposed
- * operand is read the way its strides say, since pointer-taking functors cannot be staged through
- * shared memory.
+ * is done by the host functions exported from libthcb200 (thcb200.h).  Three walks:
+ *   dense    every operand one stride-1 run on a 16-byte boundary, storages apart: a thread takes
+ *            runs of 16 bytes of consecutive elements, which the compiler merges into 16-byte
+ *            accesses through the functor's pointers;
+ *   patch    some operand is a transposed matrix: threads are assigned to elements patch by patch
+ *            (32 x 32) instead of in index order, so that operands dense along either direction
+ *            are touched in short runs whose lines the CTA finishes out of the L1 (a pointer-taking
+ *            functor cannot be staged through shared memory, but which thread runs it is free);
+ *   plain    anything else: index order, four elements per thread, offsets decoded together.
+ * Views of at most two collapsed dims use a form with one multiply-high division at most (none in
+ * the patch walk); deeper ones decode dim by dim.  The kernels are compiled with non-aliasing
+ * pointers when the operands sit in storages that do not overlap, so that the loads of a thread's
+ * elements can be in flight together.
  *
  * Include this header from a .cu file compiled for sm_100a and link libthcb200.
  */
@@ -93,6 +100,22 @@ struct View {
     }
     return off + linear * strides[0];
   }
+  __device__ __forceinline__ IndexT offset(IndexT linear, IndexT, IndexT) const { return offset(linear); }
+};
+
+// A view of at most two collapsed dims, its sizes known when the kernel is compiled: one division
+// at most, and none when the walk already knows the element's (row, column) in this view's own
+// shape (`by_row_col`: a patch walk whose N is this view's inner size, or any 1-D view).
+template <typename IndexT>
+struct View2 {
+  Divisor<IndexT> inner;   // size of the inner dim (of the whole view if it has one dim)
+  IndexT s0, s1;           // strides of the outer and the inner dim
+  bool by_row_col;
+  __device__ __forceinline__ IndexT offset(IndexT linear, IndexT row, IndexT col) const {
+    if (by_row_col) return row * s0 + col * s1;
+    const IndexT q = inner.quotient(linear);
+    return q * s0 + (linear - q * inner.d) * s1;
+  }
 };
 
 template <typename TensorType>
@@ -126,84 +149,207 @@ inline int64_t numel(const thcb200_tensor &d) {
 
 constexpr int kThreads = 256;
 constexpr int kPerThread = 4;   // elements per thread and step: their offsets are decoded together
+constexpr int kSlotsPerBlock = kThreads * kPerThread;
 
-// A thread takes kPerThread elements, kThreads apart (neighbouring lanes on neighbouring elements),
-// decodes all their offsets first and then runs the functor on each.  NOALIAS (picked on the host
-// when the operands' memory ranges are disjoint) lets the compiler start the loads of all four
-// before the first store; otherwise a store through one pointer orders every later load.
+// Which element a thread takes.  Plain walk: block `blk` covers kSlotsPerBlock consecutive logical
+// indices, neighbouring lanes on neighbouring elements.  Patch walk (N != 0), chosen on the host
+// when some operand is a transposed matrix (its innermost collapsed dim is strided and the next one
+// is dense): the logical index space is seen as rows x N, a block covers a 32 x 32 patch of it, a
+// warp four rows of it and a warp instruction a piece of 4 rows x 8 columns, so that every operand
+// is touched in runs of 16 or 32 bytes and the rest of each line is used by the same CTA out of the
+// L1.  Only the assignment of elements to threads changes: the functor still gets the element's
+// own pointers.  (Measured on a 16384 x 8192 fp32 transposed source: pieces of 8 x 4 instead of
+// 4 x 8, or patches numbered in 8 x 8 clusters instead of row by row, were slower; the kernel is
+// bound by instruction issue, so the index arithmetic is kept as short as it can be.)
+template <typename IndexT>
+struct Walk {
+  IndexT n, nblk;
+  IndexT N, rows;
+  Divisor<IndexT> patches_per_row;
+  __device__ __forceinline__ bool slot(IndexT blk, int u, IndexT &i, IndexT &row, IndexT &col) const {
+    if (N == 0) {
+      i = blk * (IndexT)kSlotsPerBlock + (IndexT)(u * kThreads) + threadIdx.x;
+      row = 0;
+      col = i;
+      return i < n;
+    }
+    const IndexT pr = patches_per_row.quotient(blk), pc = blk - pr * patches_per_row.d;
+    row = pr * 32 + (threadIdx.x >> 3);                        // warp w: rows 4w .. 4w+3 of the patch
+    col = pc * 32 + (IndexT)(u * 8) + (threadIdx.x & 7);
+    i = row * N + col;
+    return row < rows && col < N;
+  }
+};
+static_assert(kThreads == 256 && kPerThread == 4, "a block of the patch walk is 32 rows x (4 x 8) columns");
+
+// N of the patch walk this operand asks for, or 0
+template <typename IndexT>
+inline uint64_t wants_patches(const View<IndexT> &v) {
+  if (v.dims < 2 || v.strides[v.dims - 1] == 1 || v.strides[v.dims - 2] != 1) return 0;
+  return v.sizes[v.dims - 1].d >= 16 ? (uint64_t)v.sizes[v.dims - 1].d : 0;
+}
+template <typename IndexT>
+inline Walk<IndexT> make_walk(uint64_t n, uint64_t patchN) {
+  Walk<IndexT> w;
+  w.n = (IndexT)n;
+  w.N = 0;
+  w.rows = 0;
+  w.patches_per_row.set(1);
+  w.nblk = (IndexT)((n + kSlotsPerBlock - 1) / kSlotsPerBlock);
+  if (patchN && n / patchN >= 16) {
+    const uint64_t rows = n / patchN, ppr = (patchN + 31) / 32, blocks = (rows + 31) / 32 * ppr;
+    if (blocks < (1ull << 31)) {
+      w.N = (IndexT)patchN;
+      w.rows = (IndexT)rows;
+      w.patches_per_row.set(ppr);
+      w.nblk = (IndexT)blocks;
+    }
+  }
+  return w;
+}
+// the two-dim form of a collapsed view of at most two dims, for this walk
+template <typename IndexT>
+inline View2<IndexT> two_dims(const View<uint64_t> &v, const Walk<IndexT> &w, uint64_t n) {
+  View2<IndexT> r;
+  if (v.dims <= 1) {
+    // one run of stride s: element (row, col) of any rows x N reading of the index space sits at (row * N + col) * s
+    const uint64_t st = v.dims == 1 ? v.strides[0] : 0;
+    r.inner.set(n ? n : 1);
+    r.s0 = (IndexT)((w.N ? (uint64_t)w.N : 0) * st);
+    r.s1 = (IndexT)st;
+    r.by_row_col = true;        // plain walk: row = 0, col = the index
+  } else {
+    r.inner.set(v.sizes[1].d);
+    r.s0 = (IndexT)v.strides[0];
+    r.s1 = (IndexT)v.strides[1];
+    r.by_row_col = w.N != 0 && (uint64_t)w.N == v.sizes[1].d;
+  }
+  return r;
+}
+// the 32-bit kernels count slots up to the next multiple of kSlotsPerBlock
+inline bool slots_fit_32bit(int64_t n) { return (uint64_t)n + kSlotsPerBlock < (1ull << 32); }
+
+// A thread takes kPerThread elements, decodes all their offsets first and then runs the functor on
+// each.  NOALIAS (picked on the host when the operands' memory ranges are disjoint) lets the
+// compiler start the loads of all four before the first store; otherwise a store through one
+// pointer orders every later load.
 #define THCB_USER_PTR(T, NOALIAS) typename PtrOf<T, NOALIAS>::type
 template <typename T, bool NOALIAS> struct PtrOf { typedef T *type; };
 template <typename T> struct PtrOf<T, true> { typedef T *__restrict__ type; };
 
-template <typename Op, typename Ta, typename IndexT>
-__global__ void __launch_bounds__(kThreads) apply1_kernel(Ta *a, View<IndexT> va, IndexT n, Op op) {
-  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
-  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+template <typename Op, typename Ta, typename IndexT, typename ViewT>
+__global__ void __launch_bounds__(kThreads) apply1_kernel(Ta *a, ViewT va, Walk<IndexT> w, Op op) {
+  for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
     IndexT oa[kPerThread];
+    bool ok[kPerThread];
 #pragma unroll
     for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      oa[u] = (i < n && i >= base) ? va.offset(i) : 0;
+      IndexT i, row, col;
+      ok[u] = w.slot(blk, u, i, row, col);
+      oa[u] = va.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      if (i < n && i >= base) op(&a[oa[u]]);
-    }
-    if (base + step < base) break;   // the index type would wrap
+    for (int u = 0; u < kPerThread; ++u)
+      if (ok[u]) op(&a[oa[u]]);
   }
 }
-template <typename Op, typename Ta, typename Tb, typename IndexT, bool NOALIAS>
+template <typename Op, typename Ta, typename Tb, typename IndexT, bool NOALIAS, typename ViewT>
 __global__ void __launch_bounds__(kThreads)
-apply2_kernel(THCB_USER_PTR(Ta, NOALIAS) a, View<IndexT> va, THCB_USER_PTR(Tb, NOALIAS) b, View<IndexT> vb, IndexT n, Op op) {
-  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
-  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+apply2_kernel(THCB_USER_PTR(Ta, NOALIAS) a, ViewT va, THCB_USER_PTR(Tb, NOALIAS) b, ViewT vb, Walk<IndexT> w, Op op) {
+  for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
     IndexT oa[kPerThread], ob[kPerThread];
+    bool ok[kPerThread];
 #pragma unroll
     for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      const bool ok = i < n && i >= base;
-      oa[u] = ok ? va.offset(i) : 0;
-      ob[u] = ok ? vb.offset(i) : 0;
+      IndexT i, row, col;
+      ok[u] = w.slot(blk, u, i, row, col);
+      oa[u] = va.offset(i, row, col);
+      ob[u] = vb.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      if (i < n && i >= base) op(&a[oa[u]], &b[ob[u]]);
-    }
-    if (base + step < base) break;
+    for (int u = 0; u < kPerThread; ++u)
+      if (ok[u]) op(&a[oa[u]], &b[ob[u]]);
   }
 }
-template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT, bool NOALIAS>
+template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT, bool NOALIAS, typename ViewT>
 __global__ void __launch_bounds__(kThreads)
-apply3_kernel(THCB_USER_PTR(Ta, NOALIAS) a, View<IndexT> va, THCB_USER_PTR(Tb, NOALIAS) b, View<IndexT> vb,
-              THCB_USER_PTR(Tc, NOALIAS) c, View<IndexT> vc, IndexT n, Op op) {
-  const IndexT step = (IndexT)gridDim.x * (kThreads * kPerThread);
-  for (IndexT base = (IndexT)blockIdx.x * (kThreads * kPerThread) + threadIdx.x; base < n; base += step) {
+apply3_kernel(THCB_USER_PTR(Ta, NOALIAS) a, ViewT va, THCB_USER_PTR(Tb, NOALIAS) b, ViewT vb,
+              THCB_USER_PTR(Tc, NOALIAS) c, ViewT vc, Walk<IndexT> w, Op op) {
+  for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
     IndexT oa[kPerThread], ob[kPerThread], oc[kPerThread];
+    bool ok[kPerThread];
 #pragma unroll
     for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      const bool ok = i < n && i >= base;
-      oa[u] = ok ? va.offset(i) : 0;
-      ob[u] = ok ? vb.offset(i) : 0;
-      oc[u] = ok ? vc.offset(i) : 0;
+      IndexT i, row, col;
+      ok[u] = w.slot(blk, u, i, row, col);
+      oa[u] = va.offset(i, row, col);
+      ob[u] = vb.offset(i, row, col);
+      oc[u] = vc.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-      const IndexT i = base + (IndexT)u * kThreads;
-      if (i < n && i >= base) op(&a[oa[u]], &b[ob[u]], &c[oc[u]]);
+    for (int u = 0; u < kPerThread; ++u)
+      if (ok[u]) op(&a[oa[u]], &b[ob[u]], &c[oc[u]]);
+  }
+}
+
+// Dense operands (every one a single stride-1 run, 16-byte aligned, in storages that do not overlap):
+// a thread takes runs of kRun consecutive elements, so that the compiler can merge the functor's
+// element accesses into 16-byte ones; two runs per step.
+template <int A, int B, int C> struct MinSize { static const int value = A < B ? (A < C ? A : C) : (B < C ? B : C); };
+template <typename Op, typename Ta, int RUN>
+__global__ void __launch_bounds__(kThreads) apply1_dense_kernel(Ta *__restrict__ a, uint64_t n, Op op) {
+  const uint64_t nruns = (n + RUN - 1) / RUN;
+  for (uint64_t r = (uint64_t)blockIdx.x * kThreads + threadIdx.x; r < nruns; r += (uint64_t)gridDim.x * kThreads) {
+    Ta *pa = (Ta *)__builtin_assume_aligned(a + r * RUN, 16);
+    if ((r + 1) * RUN <= n) {
+#pragma unroll
+      for (int j = 0; j < RUN; ++j) op(pa + j);
+    } else {
+      for (uint64_t j = 0; r * RUN + j < n; ++j) op(pa + j);
     }
-    if (base + step < base) break;
+  }
+}
+template <typename Op, typename Ta, typename Tb, int RUN>
+__global__ void __launch_bounds__(kThreads) apply2_dense_kernel(Ta *__restrict__ a, Tb *__restrict__ b, uint64_t n, Op op) {
+  const uint64_t nruns = (n + RUN - 1) / RUN;
+  for (uint64_t r = (uint64_t)blockIdx.x * kThreads + threadIdx.x; r < nruns; r += (uint64_t)gridDim.x * kThreads) {
+    Ta *pa = (Ta *)__builtin_assume_aligned(a + r * RUN, 16);
+    Tb *pb = (Tb *)__builtin_assume_aligned(b + r * RUN, 16);
+    if ((r + 1) * RUN <= n) {
+#pragma unroll
+      for (int j = 0; j < RUN; ++j) op(pa + j, pb + j);
+    } else {
+      for (uint64_t j = 0; r * RUN + j < n; ++j) op(pa + j, pb + j);
+    }
+  }
+}
+template <typename Op, typename Ta, typename Tb, typename Tc, int RUN>
+__global__ void __launch_bounds__(kThreads)
+apply3_dense_kernel(Ta *__restrict__ a, Tb *__restrict__ b, Tc *__restrict__ c, uint64_t n, Op op) {
+  const uint64_t nruns = (n + RUN - 1) / RUN;
+  for (uint64_t r = (uint64_t)blockIdx.x * kThreads + threadIdx.x; r < nruns; r += (uint64_t)gridDim.x * kThreads) {
+    Ta *pa = (Ta *)__builtin_assume_aligned(a + r * RUN, 16);
+    Tb *pb = (Tb *)__builtin_assume_aligned(b + r * RUN, 16);
+    Tc *pc = (Tc *)__builtin_assume_aligned(c + r * RUN, 16);
+    if ((r + 1) * RUN <= n) {
+#pragma unroll
+      for (int j = 0; j < RUN; ++j) op(pa + j, pb + j, pc + j);
+    } else {
+      for (uint64_t j = 0; r * RUN + j < n; ++j) op(pa + j, pb + j, pc + j);
+    }
   }
 }
 #undef THCB_USER_PTR
 
-inline unsigned grid_for(int64_t n) {
+inline unsigned grid_for_blocks(uint64_t blocks) {
   // enough CTAs to fill a B200 several times over; the kernels stride over the rest
-  int64_t blocks = (n + kThreads * kPerThread - 1) / (kThreads * kPerThread);
-  const int64_t cap = 148 * 16;  // keeps the loop's step inside 32 bits for every n the 32-bit path accepts
+  const uint64_t cap = 148 * 16;
   return (unsigned)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+// one stride-1 run starting on a 16-byte boundary
+template <typename IndexT>
+inline bool dense_aligned(const View<IndexT> &v, const void *data) {
+  return v.dims == 1 && v.strides[0] == 1 && ((uintptr_t)data & 15) == 0;
 }
 
 // True when the two tensors live in storages whose memory does not overlap: the kernels may then
@@ -250,10 +396,20 @@ bool THC_pointwiseApply1(THCState *state, TensorTypeA *a, const Op &op, TensorAr
   cudaStream_t st = THCState_getCurrentStream(state);
   typedef typename TensorAccess<TensorTypeA>::DataType Ta;
   if (n > 0) {
-    if (thcb200_can_use_32bit(&da))
-      apply1_kernel<Op, Ta, uint32_t><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<uint32_t>(da), (uint32_t)n, op);
-    else
-      apply1_kernel<Op, Ta, uint64_t><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<uint64_t>(da), (uint64_t)n, op);
+    const View<uint64_t> va = collapse<uint64_t>(da);
+    constexpr int RUN = 16 / (int)sizeof(Ta);
+    if (dense_aligned(va, da.data)) {
+      apply1_dense_kernel<Op, Ta, RUN><<<grid_for_blocks(((uint64_t)n + RUN * kThreads - 1) / (RUN * kThreads)), kThreads, 0, st>>>((Ta *)da.data, (uint64_t)n, op);
+    } else if (thcb200_can_use_32bit(&da) && slots_fit_32bit(n)) {
+      const Walk<uint32_t> w = make_walk<uint32_t>((uint64_t)n, wants_patches(va));
+      if (va.dims <= 2)
+        apply1_kernel<Op, Ta, uint32_t, View2<uint32_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, two_dims(va, w, (uint64_t)n), w, op);
+      else
+        apply1_kernel<Op, Ta, uint32_t, View<uint32_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, collapse<uint32_t>(da), w, op);
+    } else {
+      const Walk<uint64_t> w = make_walk<uint64_t>((uint64_t)n, wants_patches(va));
+      apply1_kernel<Op, Ta, uint64_t, View<uint64_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, va, w, op);
+    }
   }
   restore_overlap(state, a, oa);
   return true;
@@ -278,11 +434,25 @@ bool THC_pointwiseApply2(THCState *state, TensorTypeA *a, TensorTypeB *b, const 
   typedef typename TensorAccess<TensorTypeB>::DataType Tb;
   if (n > 0) {
     const bool apart = storages_apart(a, b);
-    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db);
+    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db) && slots_fit_32bit(n);
+    const View<uint64_t> va = collapse<uint64_t>(da), vb = collapse<uint64_t>(db);
+    uint64_t patchN = wants_patches(va);
+    if (!patchN) patchN = wants_patches(vb);
+    constexpr int RUN = 16 / MinSize<(int)sizeof(Ta), (int)sizeof(Tb), 16>::value;
 #define THCB_USER_LAUNCH2(IDX, NA)                                                                                   \
-  apply2_kernel<Op, Ta, Tb, IDX, NA><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, \
-                                                                       collapse<IDX>(db), (IDX)n, op)
-    if (i32) { if (apart) THCB_USER_LAUNCH2(uint32_t, true); else THCB_USER_LAUNCH2(uint32_t, false); }
+  do {                                                                                                               \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                         \
+    if (sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2)                                                            \
+      apply2_kernel<Op, Ta, Tb, IDX, NA, View2<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                 \
+          (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), w, op);         \
+    else                                                                                                             \
+      apply2_kernel<Op, Ta, Tb, IDX, NA, View<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                  \
+          (Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, collapse<IDX>(db), w, op);                               \
+  } while (0)
+    if (apart && dense_aligned(va, da.data) && dense_aligned(vb, db.data))
+      apply2_dense_kernel<Op, Ta, Tb, RUN><<<grid_for_blocks(((uint64_t)n + 2 * RUN * kThreads - 1) / (2 * RUN * kThreads)), kThreads, 0, st>>>(
+          (Ta *)da.data, (Tb *)db.data, (uint64_t)n, op);
+    else if (i32) { if (apart) THCB_USER_LAUNCH2(uint32_t, true); else THCB_USER_LAUNCH2(uint32_t, false); }
     else { if (apart) THCB_USER_LAUNCH2(uint64_t, true); else THCB_USER_LAUNCH2(uint64_t, false); }
 #undef THCB_USER_LAUNCH2
   }
@@ -313,11 +483,27 @@ bool THC_pointwiseApply3(THCState *state, TensorTypeA *a, TensorTypeB *b, Tensor
   typedef typename TensorAccess<TensorTypeC>::DataType Tc;
   if (n > 0) {
     const bool apart = storages_apart(a, b) && storages_apart(a, c) && storages_apart(b, c);
-    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db) && thcb200_can_use_32bit(&dc);
+    const bool i32 = thcb200_can_use_32bit(&da) && thcb200_can_use_32bit(&db) && thcb200_can_use_32bit(&dc) && slots_fit_32bit(n);
+    const View<uint64_t> va = collapse<uint64_t>(da), vb = collapse<uint64_t>(db), vc = collapse<uint64_t>(dc);
+    uint64_t patchN = wants_patches(va);
+    if (!patchN) patchN = wants_patches(vb);
+    if (!patchN) patchN = wants_patches(vc);
+    constexpr int RUN = 16 / MinSize<(int)sizeof(Ta), (int)sizeof(Tb), (int)sizeof(Tc)>::value;
 #define THCB_USER_LAUNCH3(IDX, NA)                                                                                       \
-  apply3_kernel<Op, Ta, Tb, Tc, IDX, NA><<<grid_for(n), kThreads, 0, st>>>((Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, \
-                                                                           collapse<IDX>(db), (Tc *)dc.data, collapse<IDX>(dc), (IDX)n, op)
-    if (i32) { if (apart) THCB_USER_LAUNCH3(uint32_t, true); else THCB_USER_LAUNCH3(uint32_t, false); }
+  do {                                                                                                                   \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                             \
+    if (sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2 && vc.dims <= 2)                                                \
+      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View2<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                 \
+          (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), (Tc *)dc.data,      \
+          two_dims(vc, w, (uint64_t)n), w, op);                                                                          \
+    else                                                                                                                 \
+      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                  \
+          (Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, collapse<IDX>(db), (Tc *)dc.data, collapse<IDX>(dc), w, op);  \
+  } while (0)
+    if (apart && dense_aligned(va, da.data) && dense_aligned(vb, db.data) && dense_aligned(vc, dc.data))
+      apply3_dense_kernel<Op, Ta, Tb, Tc, RUN><<<grid_for_blocks(((uint64_t)n + 2 * RUN * kThreads - 1) / (2 * RUN * kThreads)), kThreads, 0, st>>>(
+          (Ta *)da.data, (Tb *)db.data, (Tc *)dc.data, (uint64_t)n, op);
+    else if (i32) { if (apart) THCB_USER_LAUNCH3(uint32_t, true); else THCB_USER_LAUNCH3(uint32_t, false); }
     else { if (apart) THCB_USER_LAUNCH3(uint64_t, true); else THCB_USER_LAUNCH3(uint64_t, false); }
 #undef THCB_USER_LAUNCH3
   }

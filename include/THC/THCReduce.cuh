@@ -17,13 +17,19 @@
  * Both return false for more than 25 dims.
  *
  * The built-in reductions (sum, prod, min, max, norm ...) do not come through here: they use the
- * vectorised kernels behind the C API.  These templates serve arbitrary functors and arbitrary
- * trivially-copyable accumulator types, combining partials through shared memory in a fixed order.
+ * kernels behind the C API.  These templates serve arbitrary functors and arbitrary trivially
+ * copyable accumulator types.  The functors take values, so elements are loaded 16 bytes at a time
+ * where the layout allows and eight loads ahead of the first fold; a reduced dim that is dense gets a
+ * warp per slice (many slices) or a CTA per slice, a strided one with a dense neighbour gets lanes
+ * along that neighbour.  Partials are merged by shuffles and through shared memory in a fixed
+ * order, so results repeat bit for bit.
  *
  * Include from a .cu file compiled for sm_100a and link libthcb200.
  */
 #ifndef THCB200_THC_REDUCE_CUH
 #define THCB200_THC_REDUCE_CUH
+
+#include <string.h>
 
 #include "THCApply.cuh"
 
@@ -49,24 +55,51 @@ struct SliceView {
   }
 };
 
-// Folds the accumulators of a CTA in thread order (0 with 1, then with 2 ... as a binary tree over
-// thread numbers), result in thread 0.  `buf` holds blockDim.x accumulators.
+// V elements loaded as one aligned unit (V * sizeof(T) = 16 bytes in the vector kernels)
+template <typename T, int V> struct alignas(V * sizeof(T)) ValuePack { T v[V]; };
+
+// shuffle of any trivially copyable accumulator, 32 bits at a time
+template <typename AccT>
+__device__ __forceinline__ AccT shfl_down_any(const AccT &v, unsigned delta) {
+  constexpr int W = (int)((sizeof(AccT) + 3) / 4);
+  uint32_t w[W];
+  for (int i = 0; i < W; ++i) w[i] = 0;
+  memcpy(w, &v, sizeof(AccT));
+#pragma unroll
+  for (int i = 0; i < W; ++i) w[i] = __shfl_down_sync(0xffffffffu, w[i], delta);
+  AccT r;
+  memcpy(&r, w, sizeof(AccT));
+  return r;
+}
+
+// Folds the accumulators of a CTA in thread order (0 with 1, 2 with 3, then 0-1 with 2-3 ...: a
+// binary tree over thread numbers), result in thread 0 only.  Inside a warp the tree runs on
+// shuffles, across warps thread 0 finishes it from `buf` (one accumulator per warp).  blockDim.x is
+// a power of two of at least 32 and every thread of the CTA calls this.
 template <typename AccT, typename ReduceAccOp>
 __device__ __forceinline__ AccT block_fold(AccT acc, AccT *buf, const ReduceAccOp &accOp) {
-  buf[threadIdx.x] = acc;
-  __syncthreads();
-  for (unsigned s = 1; s < blockDim.x; s <<= 1) {
-    const unsigned i = threadIdx.x * 2 * s;
-    if (i + s < blockDim.x) buf[i] = accOp(buf[i], buf[i + s]);
-    __syncthreads();
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll
+  for (unsigned s = 1; s < 32; s <<= 1) {
+    const AccT other = shfl_down_any(acc, s);
+    if ((lane & (2 * s - 1)) == 0) acc = accOp(acc, other);
   }
-  return buf[0];
+  if (nwarps == 1) return acc;
+  if (lane == 0) buf[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (unsigned s = 1; s < nwarps; s <<= 1)
+      for (unsigned i = 0; i + s < nwarps; i += 2 * s) buf[i] = accOp(buf[i], buf[i + s]);
+    acc = buf[0];
+  }
+  return acc;
 }
 
 constexpr int kLoadsInFlight = 8;   // elements a thread loads before it folds the first of them
 
-// one CTA per slice; threads stride over the reduced dim
-template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+// one CTA per slice; threads stride over the reduced dim.  V > 1 (the reduced dim is dense and every
+// slice starts on a 16-byte boundary): whole 16-byte packs first, then the K % V elements left.
+template <typename T, int V, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
 __global__ void __launch_bounds__(kReduceThreads)
 reduce_dim_cta_kernel(T *out, const T *in, SliceView sv, uint64_t K, int64_t strideK, AccT init, ModifyOp modifyOp,
                       ReduceOp reduceOp, ReduceAccOp accOp) {
@@ -76,66 +109,144 @@ reduce_dim_cta_kernel(T *out, const T *in, SliceView sv, uint64_t K, int64_t str
   sv.decode(blockIdx.x, in_off, out_off);
   const T *p = in + in_off;
   AccT acc = init;
-  // kLoadsInFlight elements are loaded before the first is folded (the functors take values, so the
-  // loads do not depend on one another); they are folded in the order a one-at-a-time walk would take
-  for (uint64_t k0 = threadIdx.x; k0 < K; k0 += (uint64_t)blockDim.x * kLoadsInFlight) {
-    T x[kLoadsInFlight];
+  // kLoadsInFlight loads are issued before the first value is folded (the functors take values, so
+  // the loads do not depend on one another); a thread folds its values in the order it loaded them
+  if (V > 1) {
+    const uint64_t packs = K / V;
+    const ValuePack<T, V> *pp = reinterpret_cast<const ValuePack<T, V> *>(p);
+    for (uint64_t k0 = threadIdx.x; k0 < packs; k0 += (uint64_t)blockDim.x * kLoadsInFlight) {
+      ValuePack<T, V> x[kLoadsInFlight];
 #pragma unroll
-    for (int u = 0; u < kLoadsInFlight; ++u) {
-      const uint64_t k = k0 + (uint64_t)u * blockDim.x;
-      if (k < K) x[u] = p[(int64_t)k * strideK];
+      for (int u = 0; u < kLoadsInFlight; ++u) {
+        const uint64_t k = k0 + (uint64_t)u * blockDim.x;
+        if (k < packs) x[u] = pp[k];
+      }
+#pragma unroll
+      for (int u = 0; u < kLoadsInFlight; ++u)
+        if (k0 + (uint64_t)u * blockDim.x < packs) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc = reduceOp(acc, modifyOp(x[u].v[j]));
+        }
     }
+    for (uint64_t k = packs * V + threadIdx.x; k < K; k += blockDim.x) acc = reduceOp(acc, modifyOp(p[k]));
+  } else {
+    for (uint64_t k0 = threadIdx.x; k0 < K; k0 += (uint64_t)blockDim.x * kLoadsInFlight) {
+      T x[kLoadsInFlight];
 #pragma unroll
-    for (int u = 0; u < kLoadsInFlight; ++u)
-      if (k0 + (uint64_t)u * blockDim.x < K) acc = reduceOp(acc, modifyOp(x[u]));
+      for (int u = 0; u < kLoadsInFlight; ++u) {
+        const uint64_t k = k0 + (uint64_t)u * blockDim.x;
+        if (k < K) x[u] = p[(int64_t)k * strideK];
+      }
+#pragma unroll
+      for (int u = 0; u < kLoadsInFlight; ++u)
+        if (k0 + (uint64_t)u * blockDim.x < K) acc = reduceOp(acc, modifyOp(x[u]));
+    }
   }
   acc = block_fold(acc, buf, accOp);
   if (threadIdx.x == 0) out[out_off] = (T)acc;
 }
 
+// A warp per slice (many slices): no shared memory and no barrier, the lanes' accumulators are folded
+// by shuffles in lane order.  CTAs stride over groups of blockDim.x / 32 slices.
+template <typename T, int V, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_dim_warp_kernel(T *out, const T *in, SliceView sv, uint64_t nslices, uint64_t K, int64_t strideK, AccT init,
+                       ModifyOp modifyOp, ReduceOp reduceOp, ReduceAccOp accOp) {
+  const unsigned lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (uint64_t slice = (uint64_t)blockIdx.x * warps + (threadIdx.x >> 5); slice < nslices; slice += (uint64_t)gridDim.x * warps) {
+    int64_t in_off, out_off;
+    sv.decode(slice, in_off, out_off);
+    const T *p = in + in_off;
+    AccT acc = init;
+    if (V > 1) {
+      const uint64_t packs = K / V;
+      const ValuePack<T, V> *pp = reinterpret_cast<const ValuePack<T, V> *>(p);
+      for (uint64_t k0 = lane; k0 < packs; k0 += 32 * kLoadsInFlight) {
+        ValuePack<T, V> x[kLoadsInFlight];
+#pragma unroll
+        for (int u = 0; u < kLoadsInFlight; ++u)
+          if (k0 + 32 * u < packs) x[u] = pp[k0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < kLoadsInFlight; ++u)
+          if (k0 + 32 * u < packs) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) acc = reduceOp(acc, modifyOp(x[u].v[j]));
+          }
+      }
+      for (uint64_t k = packs * V + lane; k < K; k += 32) acc = reduceOp(acc, modifyOp(p[k]));
+    } else {
+      for (uint64_t k0 = lane; k0 < K; k0 += 32 * kLoadsInFlight) {
+        T x[kLoadsInFlight];
+#pragma unroll
+        for (int u = 0; u < kLoadsInFlight; ++u)
+          if (k0 + 32 * u < K) x[u] = p[(int64_t)(k0 + 32 * u) * strideK];
+#pragma unroll
+        for (int u = 0; u < kLoadsInFlight; ++u)
+          if (k0 + 32 * u < K) acc = reduceOp(acc, modifyOp(x[u]));
+      }
+    }
+#pragma unroll
+    for (unsigned s = 1; s < 32; s <<= 1) {
+      const AccT other = shfl_down_any(acc, s);
+      if ((lane & (2 * s - 1)) == 0) acc = accOp(acc, other);
+    }
+    if (lane == 0) out[out_off] = (T)acc;
+  }
+}
+
 // The reduced dim is strided and some other dim (`inner` elements, stride 1 in the input) is dense:
-// the 32 lanes of a warp sit on 32 neighbouring slices, so every load of a warp is one 128-byte
-// line, the CTA's warps take the reduced positions round-robin with kLoadsInFlight of them in
-// flight per thread, and the warps' accumulators are merged in warp order through shared memory.
-template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+// a lane sits on V neighbouring slices (V * sizeof(T) = 16 bytes when alignment allows, else V = 1),
+// so every load of a warp is whole lines; the CTA's warps take the reduced positions round-robin
+// with kLoadsInFlight of them in flight per thread, and the warps' accumulators are merged in warp
+// order through shared memory.
+template <typename T, int V, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
 __global__ void __launch_bounds__(kReduceThreads)
 reduce_dim_col_kernel(T *out, const T *in, SliceView sv /* the dims other than the reduced and the inner one */, uint64_t inner,
                       int64_t out_inner_stride, uint32_t tiles_i, uint64_t K, int64_t strideK, AccT init, ModifyOp modifyOp,
                       ReduceOp reduceOp, ReduceAccOp accOp, uint32_t nsplit, uint64_t split_len, AccT *partials) {
   extern __shared__ __align__(16) unsigned char thcb_user_smem[];
-  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);     // [warp][lane]
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);     // [warp][lane][V]
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  // blockIdx.x -> (outer slice, split of the reduced dim, tile of 32 inner positions)
+  // blockIdx.x -> (outer slice, split of the reduced dim, tile of 32 * V inner positions)
   uint32_t b = blockIdx.x;
   const uint32_t ti = b % tiles_i; b /= tiles_i;
   const uint32_t split = b % nsplit;
   const uint64_t outer = b / nsplit;
-  const uint64_t i = (uint64_t)ti * 32 + lane;
+  const uint64_t i = ((uint64_t)ti * 32 + lane) * V;
   int64_t in_off, out_off;
   sv.decode(outer, in_off, out_off);
   const T *p = in + in_off + (int64_t)i;
   const uint64_t kbeg = (uint64_t)split * split_len, kend = kbeg + split_len < K ? kbeg + split_len : K;
-  AccT acc = init;
+  AccT acc[V];
+#pragma unroll
+  for (int j = 0; j < V; ++j) acc[j] = init;
   if (i < inner) {
     for (uint64_t k0 = kbeg + warp; k0 < kend; k0 += (uint64_t)nwarps * kLoadsInFlight) {
-      T x[kLoadsInFlight];
+      ValuePack<T, V> x[kLoadsInFlight];
 #pragma unroll
       for (int u = 0; u < kLoadsInFlight; ++u) {
         const uint64_t k = k0 + (uint64_t)u * nwarps;
-        if (k < kend) x[u] = p[(int64_t)k * strideK];
+        if (k < kend) x[u] = *reinterpret_cast<const ValuePack<T, V> *>(p + (int64_t)k * strideK);
       }
 #pragma unroll
       for (int u = 0; u < kLoadsInFlight; ++u)
-        if (k0 + (uint64_t)u * nwarps < kend) acc = reduceOp(acc, modifyOp(x[u]));
+        if (k0 + (uint64_t)u * nwarps < kend) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] = reduceOp(acc[j], modifyOp(x[u].v[j]));
+        }
     }
   }
-  buf[warp * 32 + lane] = acc;
+#pragma unroll
+  for (int j = 0; j < V; ++j) buf[(warp * 32 + lane) * V + j] = acc[j];
   __syncthreads();
   if (warp == 0 && i < inner) {
-    AccT r = buf[lane];
-    for (unsigned w = 1; w < nwarps; ++w) r = accOp(r, buf[w * 32 + lane]);
-    if (nsplit > 1) partials[(outer * nsplit + split) * inner + i] = r;   // [outer][split][inner]
-    else out[out_off + (int64_t)i * out_inner_stride] = (T)r;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      AccT r = buf[lane * V + j];
+      for (unsigned w = 1; w < nwarps; ++w) r = accOp(r, buf[(w * 32 + lane) * V + j]);
+      if (nsplit > 1) partials[(outer * nsplit + split) * inner + i + j] = r;   // [outer][split][inner]
+      else out[out_off + (int64_t)(i + j) * out_inner_stride] = (T)r;
+    }
   }
 }
 
@@ -198,6 +309,36 @@ reduce_all_partial_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, 
     for (int u = 0; u < kLoadsInFlight; ++u)
       if (i0 + (uint64_t)u * step < n) acc = reduceOp(acc, modifyOp(x[u]));
   }
+  acc = block_fold(acc, buf, accOp);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
+// the same for one dense run starting on a 16-byte boundary: 16-byte packs, the n % V elements left go to CTA 0
+template <typename T, int V, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
+__global__ void __launch_bounds__(kReduceThreads)
+reduce_all_partial_dense_kernel(const T *in, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp, ReduceAccOp accOp,
+                                AccT *partials) {
+  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
+  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
+  AccT acc = init;
+  const uint64_t packs = n / V, step = (uint64_t)gridDim.x * kReduceThreads;
+  const ValuePack<T, V> *pp = reinterpret_cast<const ValuePack<T, V> *>(in);
+  for (uint64_t i0 = (uint64_t)blockIdx.x * kReduceThreads + threadIdx.x; i0 < packs; i0 += step * kLoadsInFlight) {
+    ValuePack<T, V> x[kLoadsInFlight];
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u) {
+      const uint64_t i = i0 + (uint64_t)u * step;
+      if (i < packs) x[u] = pp[i];
+    }
+#pragma unroll
+    for (int u = 0; u < kLoadsInFlight; ++u)
+      if (i0 + (uint64_t)u * step < packs) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) acc = reduceOp(acc, modifyOp(x[u].v[j]));
+      }
+  }
+  if (blockIdx.x == 0)
+    for (uint64_t i = packs * V + threadIdx.x; i < n; i += kReduceThreads) acc = reduceOp(acc, modifyOp(in[i]));
   acc = block_fold(acc, buf, accOp);
   if (threadIdx.x == 0) partials[blockIdx.x] = acc;
 }
@@ -280,7 +421,13 @@ bool THC_reduceDim(THCState *state, TensorType *out, TensorType *in, const Modif
       ++so.n;
     }
     const uint64_t inner = (uint64_t)in->size[inner_dim];
-    const uint64_t tiles_i = (inner + 31) / 32;
+    // 16 bytes of neighbouring slices per lane when every row of the walk starts on a 16-byte boundary
+    constexpr int VEC = sizeof(T) < 16 ? 16 / (int)sizeof(T) : 1;
+    bool vec = VEC > 1 && ((uintptr_t)din.data & 15) == 0 && inner % VEC == 0 && strideK % VEC == 0 &&
+               sizeof(AccT) * kReduceThreads * VEC <= 48 * 1024;
+    for (int d = 0; d < so.n; ++d)
+      if (so.in_stride[d] % VEC != 0) vec = false;
+    const uint64_t tiles_i = (inner + 32 * (vec ? VEC : 1) - 1) / (32 * (vec ? VEC : 1));
     // few tiles: the reduced dim is cut into splits (one CTA each) whose partials a second small kernel
     // folds in split order; about eight CTAs per SM in all
     uint64_t nsplit = 1, split_len = K;
@@ -299,10 +446,16 @@ bool THC_reduceDim(THCState *state, TensorType *out, TensorType *in, const Modif
       ok = false;
     }
     if (ok) {
-      reduce_dim_col_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)(ctas * nsplit), kReduceThreads,
-                                                                      sizeof(AccT) * kReduceThreads, st>>>(
-          (T *)dout.data, (const T *)din.data, so, inner, out->stride[inner_dim], (uint32_t)tiles_i, K, strideK, init, modifyOp,
-          reduceOp, reduceAccOp, (uint32_t)nsplit, split_len, partials);
+      if (vec)
+        reduce_dim_col_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)(ctas * nsplit), kReduceThreads,
+                                                                             sizeof(AccT) * kReduceThreads * VEC, st>>>(
+            (T *)dout.data, (const T *)din.data, so, inner, out->stride[inner_dim], (uint32_t)tiles_i, K, strideK, init, modifyOp,
+            reduceOp, reduceAccOp, (uint32_t)nsplit, split_len, partials);
+      else
+        reduce_dim_col_kernel<T, 1, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)(ctas * nsplit), kReduceThreads,
+                                                                           sizeof(AccT) * kReduceThreads, st>>>(
+            (T *)dout.data, (const T *)din.data, so, inner, out->stride[inner_dim], (uint32_t)tiles_i, K, strideK, init, modifyOp,
+            reduceOp, reduceAccOp, (uint32_t)nsplit, split_len, partials);
       if (nsplit > 1) {
         const uint64_t outs = nouter * inner;
         reduce_dim_col_finish_kernel<T, ReduceAccOp, AccT><<<(unsigned)((outs + kReduceThreads - 1) / kReduceThreads), kReduceThreads, 0, st>>>(
@@ -315,12 +468,29 @@ bool THC_reduceDim(THCState *state, TensorType *out, TensorType *in, const Modif
     // fill the GPU with a thread each; otherwise a thread per slice
     const bool cta_per_slice = strideK == 1 || nslices < 148ull * 8 * kReduceThreads / 32;
     if (cta_per_slice && nslices < (1ull << 31)) {
+      constexpr int VEC = sizeof(T) < 16 ? 16 / (int)sizeof(T) : 1;
+      bool vec = VEC > 1 && strideK == 1 && ((uintptr_t)din.data & 15) == 0 && K >= (uint64_t)VEC * 32;
+      for (int d = 0; d < sv.n; ++d)
+        if (sv.in_stride[d] % VEC != 0) vec = false;
       int threads = 32;
-      while (threads < kReduceThreads && (uint64_t)threads * 4 < K) threads <<= 1;
+      while (threads < kReduceThreads && (uint64_t)threads * 4 * (vec ? VEC : 1) < K) threads <<= 1;
       const size_t smem = (size_t)threads * sizeof(AccT);
-      if (smem > 48 * 1024) ok = false;
+      // many slices: a warp each, CTAs striding over them; few: a CTA each
+      const uint64_t warps_per_cta = kReduceThreads / 32, groups = (nslices + warps_per_cta - 1) / warps_per_cta;
+      if (strideK == 1 && nslices >= 148ull * 4 * warps_per_cta) {
+        const unsigned grid = (unsigned)(groups < 148ull * 8 ? groups : 148ull * 8);
+        if (vec)
+          reduce_dim_warp_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<grid, kReduceThreads, 0, st>>>(
+              (T *)dout.data, (const T *)din.data, sv, nslices, K, strideK, init, modifyOp, reduceOp, reduceAccOp);
+        else
+          reduce_dim_warp_kernel<T, 1, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<grid, kReduceThreads, 0, st>>>(
+              (T *)dout.data, (const T *)din.data, sv, nslices, K, strideK, init, modifyOp, reduceOp, reduceAccOp);
+      } else if (smem > 48 * 1024) ok = false;
+      else if (vec)
+        reduce_dim_cta_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)nslices, threads, smem, st>>>(
+            (T *)dout.data, (const T *)din.data, sv, K, strideK, init, modifyOp, reduceOp, reduceAccOp);
       else
-        reduce_dim_cta_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)nslices, threads, smem, st>>>(
+        reduce_dim_cta_kernel<T, 1, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)nslices, threads, smem, st>>>(
             (T *)dout.data, (const T *)din.data, sv, K, strideK, init, modifyOp, reduceOp, reduceAccOp);
     } else {
       const uint64_t blocks = (nslices + kReduceThreads - 1) / kReduceThreads;
@@ -358,8 +528,14 @@ bool THC_reduceAll(THCState *state, TensorType *in, const ModifyOp &modifyOp, co
   if (cudaMallocAsync((void **)&scratch, sizeof(AccT) * (blocks + 1), st) != cudaSuccess) { cudaGetLastError(); return false; }
   AccT *result = outOnDevice ? out : scratch + blocks;
   const size_t smem = sizeof(AccT) * kReduceThreads;
-  reduce_all_partial_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
-      (const T *)din.data, collapse<uint64_t>(din), (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
+  const View<uint64_t> vin = collapse<uint64_t>(din);
+  constexpr int VEC = sizeof(T) < 16 ? 16 / (int)sizeof(T) : 1;
+  if (VEC > 1 && dense_aligned(vin, din.data))
+    reduce_all_partial_dense_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
+        (const T *)din.data, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
+  else
+    reduce_all_partial_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
+        (const T *)din.data, vin, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
   reduce_all_final_kernel<ReduceAccOp, AccT><<<1, kReduceThreads, smem, st>>>(scratch, (unsigned)blocks, init, reduceAccOp, result);
   bool ok = cudaGetLastError() == cudaSuccess;
   if (ok && !outOnDevice) ok = cudaMemcpyAsync(out, result, sizeof(AccT), cudaMemcpyDeviceToHost, st) == cudaSuccess;

@@ -38,6 +38,36 @@ def test_apply2_user_functor_on_strided_views(state, user):
         assert_bit_equal(ddst.numpy(), want, f"user functor {la}/{lb}")
 
 
+def test_apply2_patch_walk_and_dense_runs(state, user):
+    """Transposed matrices (walked in 32 x 32 patches, ragged at both edges), dense operands taken in
+    16-byte runs with a tail, and a dense operand that starts off a 16-byte boundary."""
+    r = rng("user2-patch")
+    for shape, la, lb in (((100, 70), "transposed", "contiguous"), ((257, 33), "contiguous", "transposed"),
+                          ((31, 16), "transposed", "transposed"), ((5, 40, 50), "permuted", "contiguous"),
+                          ((1, 100003), "contiguous", "contiguous"), ((640, 512), "transposed", "contiguous")):
+        src = make_view(r, "Float", shape, la)
+        dst = make_view(r, "Float", shape, lb)
+        dsrc, ddst = to_device(state, src), to_device(state, dst)
+        assert user.usertest_scale(state.ptr, ddst.ptr, dsrc.ptr, 0.5) == 1
+        want = (np.ascontiguousarray(src) * np.float32(0.5)).astype(np.float32) + np.float32(1)
+        assert_bit_equal(ddst.numpy(), want, f"user functor {shape} {la}/{lb}")
+    # same storage for both operands: a shifted dense window (not 16-byte aligned, may alias)
+    base = r.standard_normal(5000).astype(np.float32)
+    dbase = to_device(state, base)
+    a = thc.Tensor.wrap(state, "Float", dbase.data_ptr + 4, (4000,), (1,), storage_elems=4999)
+    out = thc.Tensor.new(state, "Float", 4000)
+    assert user.usertest_scale(state.ptr, out.ptr, a.ptr, 3.0) == 1
+    assert_bit_equal(out.numpy(), base[1:4001] * np.float32(3.0) + np.float32(1), "dense but unaligned source")
+    big = r.standard_normal(10007).astype(np.float32)
+    dbig = to_device(state, big)
+    assert user.usertest_add_one(state.ptr, dbig.ptr) == 1
+    assert_bit_equal(dbig.numpy(), big + np.float32(1), "apply1 on a dense tensor with a tail")
+    da, db = r.standard_normal(10003), r.standard_normal(10003)
+    mask = thc.Tensor.new(state, "Byte", 10003)
+    assert user.usertest_less_than(state.ptr, mask.ptr, to_device(state, da).ptr, to_device(state, db).ptr) == 1
+    assert_bit_equal(mask.numpy(), (da < db).astype(np.uint8), "dense byte mask from dense double operands")
+
+
 def test_apply2_different_shapes_same_count(state, user):
     r = rng("user2b")
     src = make_view(r, "Float", (4, 30), "transposed")
@@ -92,7 +122,10 @@ def test_reduce_dim_user_functors(state, user):
     r = rng("user-reduce-dim")
     for shape, layout in [((40, 1000), "contiguous"), ((1000, 40), "transposed"), ((6, 7, 50), "permuted"),
                           ((3000, 5), "contiguous"), ((9, 2000, 3), "holes"), ((300, 70), "contiguous"), ((17, 33, 65), "offset"),
-                          ((5, 700, 33), "contiguous"), ((3000, 40), "contiguous")]:
+                          ((5, 700, 33), "contiguous"), ((3000, 40), "contiguous"), ((1003,), "contiguous"), ((100003,), "contiguous"),
+                          ((8, 4100), "contiguous"), ((37, 1028), "contiguous"), ((2100, 256), "contiguous"), ((64, 36, 128), "contiguous"),
+                          ((513, 132), "holes"), ((700, 260), "offset"), ((5000, 64), "contiguous"), ((4800, 50), "contiguous"),
+                          ((4801, 36), "holes"), ((4800, 133), "holes"), ((4750, 132), "contiguous"), ((9, 133), "holes")]:
         # multiples of 1/4 so that float sums of squares are exact in any order
         x = make_view(r, "Float", shape, layout)
         x[...] = (r.integers(-8, 9, size=shape) / 4).astype(np.float32)
@@ -102,8 +135,9 @@ def test_reduce_dim_user_functors(state, user):
                 out = thc.Tensor.new(state, "Float")
                 assert user.usertest_sumsq_dim(state.ptr, out.ptr, dx.ptr, dim, keepdim) == 1
                 want = (np.asarray(x, dtype=np.float64) ** 2).sum(axis=dim, keepdims=bool(keepdim)).astype(np.float32)
-                assert out.sizes == list(want.shape), (shape, dim, keepdim)
-                assert_bit_equal(out.numpy(), want, f"user sum of squares {shape} {layout} dim {dim}")
+                # a 1-D tensor keeps its only dim when squeezed (TH tensors have no 0-dim form)
+                assert out.sizes == (list(want.shape) or [1]), (shape, dim, keepdim)
+                assert_bit_equal(out.numpy(), want.reshape(out.sizes), f"user sum of squares {shape} {layout} dim {dim}")
     out = thc.Tensor.new(state, "Float")
     assert user.usertest_sumsq_dim(state.ptr, out.ptr, dx.ptr, 7, 1) == 0   # bad dim -> false
 
