@@ -166,21 +166,23 @@ struct Walk {
   IndexT n, nblk;
   IndexT N, rows;
   Divisor<IndexT> patches_per_row;
+  template <int PT>
   __device__ __forceinline__ bool slot(IndexT blk, int u, IndexT &i, IndexT &row, IndexT &col) const {
     if (N == 0) {
-      i = blk * (IndexT)kSlotsPerBlock + (IndexT)(u * kThreads) + threadIdx.x;
+      i = blk * (IndexT)(kThreads * PT) + (IndexT)(u * kThreads) + threadIdx.x;
       row = 0;
       col = i;
       return i < n;
     }
     const IndexT pr = patches_per_row.quotient(blk), pc = blk - pr * patches_per_row.d;
     row = pr * 32 + (threadIdx.x >> 3);                        // warp w: rows 4w .. 4w+3 of the patch
-    col = pc * 32 + (IndexT)(u * 8) + (threadIdx.x & 7);
+    col = pc * (IndexT)(8 * PT) + (IndexT)(u * 8) + (threadIdx.x & 7);
     i = row * N + col;
     return row < rows && col < N;
   }
 };
-static_assert(kThreads == 256 && kPerThread == 4, "a block of the patch walk is 32 rows x (4 x 8) columns");
+static_assert(kThreads == 256, "a block of the patch walk is 32 rows (8 warps x 4) x 8 columns per element of a thread");
+constexpr int kPerThreadPatch = 4;   // elements per thread in the patch walk: patches of 32 rows x 32 columns (8 per thread: 215 -> 268 us)
 
 // N of the patch walk this operand asks for, or 0
 template <typename IndexT>
@@ -188,6 +190,8 @@ inline uint64_t wants_patches(const View<IndexT> &v) {
   if (v.dims < 2 || v.strides[v.dims - 1] == 1 || v.strides[v.dims - 2] != 1) return 0;
   return v.sizes[v.dims - 1].d >= 16 ? (uint64_t)v.sizes[v.dims - 1].d : 0;
 }
+// A patch walk (w.N != 0) is for the kernels with kPerThreadPatch elements per thread, a plain one
+// for those with kPerThread.
 template <typename IndexT>
 inline Walk<IndexT> make_walk(uint64_t n, uint64_t patchN) {
   Walk<IndexT> w;
@@ -195,9 +199,10 @@ inline Walk<IndexT> make_walk(uint64_t n, uint64_t patchN) {
   w.N = 0;
   w.rows = 0;
   w.patches_per_row.set(1);
+  const uint64_t width = 8ull * kPerThreadPatch;
   w.nblk = (IndexT)((n + kSlotsPerBlock - 1) / kSlotsPerBlock);
   if (patchN && n / patchN >= 16) {
-    const uint64_t rows = n / patchN, ppr = (patchN + 31) / 32, blocks = (rows + 31) / 32 * ppr;
+    const uint64_t rows = n / patchN, ppr = (patchN + width - 1) / width, blocks = (rows + 31) / 32 * ppr;
     if (blocks < (1ull << 31)) {
       w.N = (IndexT)patchN;
       w.rows = (IndexT)rows;
@@ -237,57 +242,57 @@ inline bool slots_fit_32bit(int64_t n) { return (uint64_t)n + kSlotsPerBlock < (
 template <typename T, bool NOALIAS> struct PtrOf { typedef T *type; };
 template <typename T> struct PtrOf<T, true> { typedef T *__restrict__ type; };
 
-template <typename Op, typename Ta, typename IndexT, typename ViewT>
+template <typename Op, typename Ta, typename IndexT, typename ViewT, int PT>
 __global__ void __launch_bounds__(kThreads) apply1_kernel(Ta *a, ViewT va, Walk<IndexT> w, Op op) {
   for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
-    IndexT oa[kPerThread];
-    bool ok[kPerThread];
+    IndexT oa[PT];
+    bool ok[PT];
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
+    for (int u = 0; u < PT; ++u) {
       IndexT i, row, col;
-      ok[u] = w.slot(blk, u, i, row, col);
+      ok[u] = w.template slot<PT>(blk, u, i, row, col);
       oa[u] = va.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u)
+    for (int u = 0; u < PT; ++u)
       if (ok[u]) op(&a[oa[u]]);
   }
 }
-template <typename Op, typename Ta, typename Tb, typename IndexT, bool NOALIAS, typename ViewT>
+template <typename Op, typename Ta, typename Tb, typename IndexT, bool NOALIAS, typename ViewT, int PT>
 __global__ void __launch_bounds__(kThreads)
 apply2_kernel(THCB_USER_PTR(Ta, NOALIAS) a, ViewT va, THCB_USER_PTR(Tb, NOALIAS) b, ViewT vb, Walk<IndexT> w, Op op) {
   for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
-    IndexT oa[kPerThread], ob[kPerThread];
-    bool ok[kPerThread];
+    IndexT oa[PT], ob[PT];
+    bool ok[PT];
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
+    for (int u = 0; u < PT; ++u) {
       IndexT i, row, col;
-      ok[u] = w.slot(blk, u, i, row, col);
+      ok[u] = w.template slot<PT>(blk, u, i, row, col);
       oa[u] = va.offset(i, row, col);
       ob[u] = vb.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u)
+    for (int u = 0; u < PT; ++u)
       if (ok[u]) op(&a[oa[u]], &b[ob[u]]);
   }
 }
-template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT, bool NOALIAS, typename ViewT>
+template <typename Op, typename Ta, typename Tb, typename Tc, typename IndexT, bool NOALIAS, typename ViewT, int PT>
 __global__ void __launch_bounds__(kThreads)
 apply3_kernel(THCB_USER_PTR(Ta, NOALIAS) a, ViewT va, THCB_USER_PTR(Tb, NOALIAS) b, ViewT vb,
               THCB_USER_PTR(Tc, NOALIAS) c, ViewT vc, Walk<IndexT> w, Op op) {
   for (IndexT blk = blockIdx.x; blk < w.nblk; blk += gridDim.x) {
-    IndexT oa[kPerThread], ob[kPerThread], oc[kPerThread];
-    bool ok[kPerThread];
+    IndexT oa[PT], ob[PT], oc[PT];
+    bool ok[PT];
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
+    for (int u = 0; u < PT; ++u) {
       IndexT i, row, col;
-      ok[u] = w.slot(blk, u, i, row, col);
+      ok[u] = w.template slot<PT>(blk, u, i, row, col);
       oa[u] = va.offset(i, row, col);
       ob[u] = vb.offset(i, row, col);
       oc[u] = vc.offset(i, row, col);
     }
 #pragma unroll
-    for (int u = 0; u < kPerThread; ++u)
+    for (int u = 0; u < PT; ++u)
       if (ok[u]) op(&a[oa[u]], &b[ob[u]], &c[oc[u]]);
   }
 }
@@ -401,14 +406,17 @@ bool THC_pointwiseApply1(THCState *state, TensorTypeA *a, const Op &op, TensorAr
     if (dense_aligned(va, da.data)) {
       apply1_dense_kernel<Op, Ta, RUN><<<grid_for_blocks(((uint64_t)n + RUN * kThreads - 1) / (RUN * kThreads)), kThreads, 0, st>>>((Ta *)da.data, (uint64_t)n, op);
     } else if (thcb200_can_use_32bit(&da) && slots_fit_32bit(n)) {
-      const Walk<uint32_t> w = make_walk<uint32_t>((uint64_t)n, wants_patches(va));
-      if (va.dims <= 2)
-        apply1_kernel<Op, Ta, uint32_t, View2<uint32_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, two_dims(va, w, (uint64_t)n), w, op);
+      const uint64_t patchN = va.dims <= 2 ? wants_patches(va) : 0;
+      const Walk<uint32_t> w = make_walk<uint32_t>((uint64_t)n, patchN);
+      if (w.N)
+        apply1_kernel<Op, Ta, uint32_t, View2<uint32_t>, kPerThreadPatch><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, two_dims(va, w, (uint64_t)n), w, op);
+      else if (va.dims <= 2)
+        apply1_kernel<Op, Ta, uint32_t, View2<uint32_t>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, two_dims(va, w, (uint64_t)n), w, op);
       else
-        apply1_kernel<Op, Ta, uint32_t, View<uint32_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, collapse<uint32_t>(da), w, op);
+        apply1_kernel<Op, Ta, uint32_t, View<uint32_t>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, collapse<uint32_t>(da), w, op);
     } else {
-      const Walk<uint64_t> w = make_walk<uint64_t>((uint64_t)n, wants_patches(va));
-      apply1_kernel<Op, Ta, uint64_t, View<uint64_t> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, va, w, op);
+      const Walk<uint64_t> w = make_walk<uint64_t>((uint64_t)n, 0);
+      apply1_kernel<Op, Ta, uint64_t, View<uint64_t>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>((Ta *)da.data, va, w, op);
     }
   }
   restore_overlap(state, a, oa);
@@ -441,12 +449,16 @@ bool THC_pointwiseApply2(THCState *state, TensorTypeA *a, TensorTypeB *b, const 
     constexpr int RUN = 16 / MinSize<(int)sizeof(Ta), (int)sizeof(Tb), 16>::value;
 #define THCB_USER_LAUNCH2(IDX, NA)                                                                                   \
   do {                                                                                                               \
-    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                         \
-    if (sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2)                                                            \
-      apply2_kernel<Op, Ta, Tb, IDX, NA, View2<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                 \
+    const bool two = sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2;                                               \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, two ? patchN : 0);                                           \
+    if (two && w.N)                                                                                                  \
+      apply2_kernel<Op, Ta, Tb, IDX, NA, View2<IDX>, kPerThreadPatch><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>( \
+          (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), w, op);         \
+    else if (two)                                                                                                    \
+      apply2_kernel<Op, Ta, Tb, IDX, NA, View2<IDX>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(      \
           (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), w, op);         \
     else                                                                                                             \
-      apply2_kernel<Op, Ta, Tb, IDX, NA, View<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                  \
+      apply2_kernel<Op, Ta, Tb, IDX, NA, View<IDX>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(       \
           (Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, collapse<IDX>(db), w, op);                               \
   } while (0)
     if (apart && dense_aligned(va, da.data) && dense_aligned(vb, db.data))
@@ -491,13 +503,18 @@ bool THC_pointwiseApply3(THCState *state, TensorTypeA *a, TensorTypeB *b, Tensor
     constexpr int RUN = 16 / MinSize<(int)sizeof(Ta), (int)sizeof(Tb), (int)sizeof(Tc)>::value;
 #define THCB_USER_LAUNCH3(IDX, NA)                                                                                       \
   do {                                                                                                                   \
-    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                             \
-    if (sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2 && vc.dims <= 2)                                                \
-      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View2<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                 \
+    const bool two = sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2 && vc.dims <= 2;                                   \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, two ? patchN : 0);                                               \
+    if (two && w.N)                                                                                                      \
+      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View2<IDX>, kPerThreadPatch><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>( \
+          (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), (Tc *)dc.data,      \
+          two_dims(vc, w, (uint64_t)n), w, op);                                                                          \
+    else if (two)                                                                                                        \
+      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View2<IDX>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(      \
           (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), (Tc *)dc.data,      \
           two_dims(vc, w, (uint64_t)n), w, op);                                                                          \
     else                                                                                                                 \
-      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View<IDX> ><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(                  \
+      apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View<IDX>, kPerThread><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>(       \
           (Ta *)da.data, collapse<IDX>(da), (Tb *)db.data, collapse<IDX>(db), (Tc *)dc.data, collapse<IDX>(dc), w, op);  \
   } while (0)
     if (apart && dense_aligned(va, da.data) && dense_aligned(vb, db.data) && dense_aligned(vc, dc.data))
