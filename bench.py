@@ -409,7 +409,8 @@ def ours_main(args):
                             ("b_template_apply2_scale_f32_contiguous_128M", "template_apply_contiguous"),
                             ("b_template_apply2_scale_f32_transposed_source_16384x8192", "template_apply_transposed"),
                             ("b_template_reduceDim_sumsq_f32_16384x8192_dim1", "template_reduce_dim1"),
-                            ("b_template_reduceDim_sumsq_f32_16384x8192_dim0", "template_reduce_dim0")):
+                            ("b_template_reduceDim_sumsq_f32_16384x8192_dim0", "template_reduce_dim0"),
+                            ("b_template_reduceAll_absmax_f32_128M_to_host", "template_reduce_all_to_host")):
             if name in per_config and "frac" in per_config[name]:
                 roofline[short + "_frac"] = per_config[name]["frac"]
         for name, r in per_config.items():
