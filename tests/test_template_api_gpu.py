@@ -174,3 +174,57 @@ def test_host_threads_share_a_state_with_a_stream_each(state, user):
     user.usertest_threads.argtypes = [C.c_void_p, C.c_int, C.c_int]
     assert user.usertest_threads(state.ptr, 4, 25) == 0
     state.check()
+
+
+# ---- seeded random layouts through the template headers ----
+
+def _fuzz_shape(r):
+    nd = int(r.integers(1, 4))
+    while True:
+        shape = tuple(int(r.choice([1, 2, 3, 5, 16, 31, 33, 40, 64, 100, 129, 257])) for _ in range(nd))
+        if 0 < int(np.prod(shape)) <= 200000:
+            return shape
+
+
+def _shifted(state, view, shift):
+    """The view on the device, its first element `shift` elements past a 256-byte boundary."""
+    if shift == 0:
+        return to_device(state, view)
+    item = view.dtype.itemsize
+    strides = [s // item for s in view.strides]
+    extent = 1 + sum((n - 1) * s for n, s in zip(view.shape, strides))
+    flat = np.zeros(extent + shift, view.dtype)
+    np.lib.stride_tricks.as_strided(flat[shift:], shape=view.shape, strides=view.strides)[...] = view
+    base = to_device(state, flat)
+    t = thc.Tensor.wrap(state, thc.KIND_OF_DTYPE[view.dtype], base.data_ptr + shift * item, view.shape, strides)
+    t._owner = base
+    return t
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_apply_and_reduce_random_layouts(state, user, seed):
+    """Every layout of common.make_view on either operand, bases on and off the 16-byte grid: the dense runs, the
+    patch walk, the two-dim and the dim-by-dim decode, the warp / CTA / column reductions with and without vector loads."""
+    from common import LAYOUTS
+    user.usertest_sumsq_dim.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+    r = rng("user-fuzz", seed)
+    for _ in range(10):
+        shape = _fuzz_shape(r)
+        la, lb = (LAYOUTS[int(r.integers(0, len(LAYOUTS)))] for _ in range(2))
+        sa, sb = (int(r.integers(0, 4)) for _ in range(2))
+        src, dst = make_view(r, "Float", shape, la), make_view(r, "Float", shape, lb)
+        dsrc, ddst = _shifted(state, src, sa), _shifted(state, dst, sb)
+        assert user.usertest_scale(state.ptr, ddst.ptr, dsrc.ptr, 0.75) == 1
+        want = (np.ascontiguousarray(src) * np.float32(0.75)).astype(np.float32) + np.float32(1)
+        assert_bit_equal(ddst.numpy(), want, f"seed {seed}: scale {shape} {la}->{lb} shifts {sa},{sb}")
+        assert user.usertest_add_one(state.ptr, ddst.ptr) == 1
+        assert_bit_equal(ddst.numpy(), want + np.float32(1), f"seed {seed}: add one in place {shape} {lb} shift {sb}")
+        # sums of squares of multiples of 1/4 are exact in any order
+        x = make_view(r, "Float", shape, la)
+        x[...] = (r.integers(-8, 9, size=shape) / 4).astype(np.float32)
+        dx = _shifted(state, x, sa)
+        dim = int(r.integers(0, len(shape)))
+        out = thc.Tensor.new(state, "Float")
+        assert user.usertest_sumsq_dim(state.ptr, out.ptr, dx.ptr, dim, 1) == 1
+        wantr = (np.asarray(x, dtype=np.float64) ** 2).sum(axis=dim, keepdims=True).astype(np.float32)
+        assert_bit_equal(out.numpy(), wantr, f"seed {seed}: sum of squares {shape} {la} shift {sa} dim {dim}")
