@@ -12,8 +12,11 @@
  * partial accumulators are merged with reduceAccOp.  `init` must be an identity of the fold: as in
  * the reference every thread starts from it.  THC_reduceDim resizes `out` to in's sizes with
  * size[dim] = 1 and squeezes that dim unless keepdim (lib/THC/THCReduce.cuh:328-332, 449-451).
- * THC_reduceAll writes *out on the host after a synchronous copy, or on the device when
- * outOnDevice (lib/THC/THCReduceAll.cuh:259-270, 333-335); a tensor without dimensions yields init.
+ * THC_reduceAll writes *out on the host, returning once the stream has finished as the reference's
+ * synchronous copy does, or on the device when outOnDevice (lib/THC/THCReduceAll.cuh:259-270,
+ * 333-335); a tensor without dimensions yields init.  It is one launch: the CTA that finishes last
+ * folds the CTAs' partials in index order and writes the result (for a host result into a pinned
+ * slot of the calling thread, so no copy follows the kernel).
  * Both return false for more than 25 dims.
  *
  * The built-in reductions (sum, prod, min, max, norm ...) do not come through here: they use the
@@ -289,11 +292,49 @@ reduce_dim_thread_kernel(T *out, const T *in, SliceView sv, uint64_t nslices, ui
   out[out_off] = (T)acc;
 }
 
-// full reduction, pass 1: every CTA strides over the logical index space and leaves one partial
+// Tail of the full reduction, run by every CTA after its own fold: the CTA's partial goes to
+// `partials`, and the CTA that draws the last ticket folds all partials in index order (thread t takes
+// t, t + 256, ..., then the fixed tree of block_fold) and writes the result -- to device memory or to a
+// pinned host slot the device can see.  One launch; the result does not depend on which CTA was last.
+template <typename ReduceAccOp, typename AccT>
+__device__ __forceinline__ void reduce_all_finish(AccT acc, AccT *buf, AccT *partials, unsigned int *ticket, AccT init,
+                                                  const ReduceAccOp &accOp, AccT *result) {
+  __shared__ bool thcb_user_last;
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = acc;
+    __threadfence();
+    thcb_user_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!thcb_user_last) return;
+  __threadfence();
+  AccT f = init;
+  const volatile AccT *vp = partials;
+  for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) {
+    AccT p;
+    // other CTAs wrote these: read them past the L1
+    const volatile unsigned char *src = reinterpret_cast<const volatile unsigned char *>(vp + i);
+    unsigned char *dst = reinterpret_cast<unsigned char *>(&p);
+    if (sizeof(AccT) % 4 == 0) {
+      for (unsigned w = 0; w < sizeof(AccT) / 4; ++w)
+        reinterpret_cast<uint32_t *>(dst)[w] = reinterpret_cast<const volatile uint32_t *>(src)[w];
+    } else {
+      for (unsigned w = 0; w < sizeof(AccT); ++w) dst[w] = src[w];
+    }
+    f = accOp(f, p);
+  }
+  f = block_fold(f, buf, accOp);
+  if (threadIdx.x == 0) {
+    *result = f;
+    __threadfence_system();
+  }
+}
+
+// full reduction: every CTA strides over the logical index space, then reduce_all_finish
 template <typename T, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
 __global__ void __launch_bounds__(kReduceThreads)
-reduce_all_partial_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp,
-                          ReduceAccOp accOp, AccT *partials) {
+reduce_all_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp,
+                  ReduceAccOp accOp, AccT *partials, unsigned int *ticket, AccT *result) {
   extern __shared__ __align__(16) unsigned char thcb_user_smem[];
   AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
   AccT acc = init;
@@ -310,14 +351,15 @@ reduce_all_partial_kernel(const T *in, View<uint64_t> v, uint64_t n, AccT init, 
       if (i0 + (uint64_t)u * step < n) acc = reduceOp(acc, modifyOp(x[u]));
   }
   acc = block_fold(acc, buf, accOp);
-  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+  __syncthreads();     // buf is used again by the finishing CTA
+  reduce_all_finish(acc, buf, partials, ticket, init, accOp, result);
 }
 
 // the same for one dense run starting on a 16-byte boundary: 16-byte packs, the n % V elements left go to CTA 0
 template <typename T, int V, typename ModifyOp, typename ReduceOp, typename ReduceAccOp, typename AccT>
 __global__ void __launch_bounds__(kReduceThreads)
-reduce_all_partial_dense_kernel(const T *in, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp, ReduceAccOp accOp,
-                                AccT *partials) {
+reduce_all_dense_kernel(const T *in, uint64_t n, AccT init, ModifyOp modifyOp, ReduceOp reduceOp, ReduceAccOp accOp,
+                        AccT *partials, unsigned int *ticket, AccT *result) {
   extern __shared__ __align__(16) unsigned char thcb_user_smem[];
   AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
   AccT acc = init;
@@ -340,19 +382,19 @@ reduce_all_partial_dense_kernel(const T *in, uint64_t n, AccT init, ModifyOp mod
   if (blockIdx.x == 0)
     for (uint64_t i = packs * V + threadIdx.x; i < n; i += kReduceThreads) acc = reduceOp(acc, modifyOp(in[i]));
   acc = block_fold(acc, buf, accOp);
-  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+  __syncthreads();
+  reduce_all_finish(acc, buf, partials, ticket, init, accOp, result);
 }
 
-// pass 2: one CTA folds the partials in index order
-template <typename ReduceAccOp, typename AccT>
-__global__ void __launch_bounds__(kReduceThreads)
-reduce_all_final_kernel(const AccT *partials, unsigned count, AccT init, ReduceAccOp accOp, AccT *result) {
-  extern __shared__ __align__(16) unsigned char thcb_user_smem[];
-  AccT *buf = reinterpret_cast<AccT *>(thcb_user_smem);
-  AccT acc = init;
-  for (unsigned i = threadIdx.x; i < count; i += blockDim.x) acc = accOp(acc, partials[i]);
-  acc = block_fold(acc, buf, accOp);
-  if (threadIdx.x == 0) *result = acc;
+// One pinned slot per host thread that the device can write (for results that go to the host): 256
+// bytes, allocated on first use and kept.  Null when pinned memory cannot be had.
+inline void *host_result_slot() {
+  static thread_local void *slot = 0;
+  if (!slot && cudaHostAlloc(&slot, 256, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+    cudaGetLastError();
+    slot = 0;
+  }
+  return slot;
 }
 
 template <typename TensorType> struct TensorShape;
@@ -523,25 +565,35 @@ bool THC_reduceAll(THCState *state, TensorType *in, const ModifyOp &modifyOp, co
   const uint64_t cap = 148 * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  // scratch: `blocks` partials and, for a host result, one slot for the total
-  AccT *scratch = 0;
-  if (cudaMallocAsync((void **)&scratch, sizeof(AccT) * (blocks + 1), st) != cudaSuccess) { cudaGetLastError(); return false; }
-  AccT *result = outOnDevice ? out : scratch + blocks;
+  // scratch: a ticket, `blocks` partials and one slot for a host result that cannot use the pinned slot
+  unsigned char *scratch = 0;
+  if (cudaMallocAsync((void **)&scratch, 16 + sizeof(AccT) * (blocks + 1), st) != cudaSuccess) { cudaGetLastError(); return false; }
+  unsigned int *ticket = reinterpret_cast<unsigned int *>(scratch);
+  AccT *partials = reinterpret_cast<AccT *>(scratch + 16);
+  // a host result is written by the finishing CTA straight into pinned host memory when the
+  // accumulator fits the thread's slot; otherwise it is copied back from the scratch
+  void *slot = (!outOnDevice && sizeof(AccT) <= 256) ? host_result_slot() : 0;
+  void *slot_dev = 0;
+  if (slot && cudaHostGetDevicePointer(&slot_dev, slot, 0) != cudaSuccess) { cudaGetLastError(); slot = 0; }
+  AccT *result = outOnDevice ? out : (slot ? reinterpret_cast<AccT *>(slot_dev) : partials + blocks);
+  bool ok = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st) == cudaSuccess;
   const size_t smem = sizeof(AccT) * kReduceThreads;
   const View<uint64_t> vin = collapse<uint64_t>(din);
   constexpr int VEC = sizeof(T) < 16 ? 16 / (int)sizeof(T) : 1;
   if (VEC > 1 && dense_aligned(vin, din.data))
-    reduce_all_partial_dense_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
-        (const T *)din.data, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
+    reduce_all_dense_kernel<T, VEC, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
+        (const T *)din.data, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, partials, ticket, result);
   else
-    reduce_all_partial_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
-        (const T *)din.data, vin, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, scratch);
-  reduce_all_final_kernel<ReduceAccOp, AccT><<<1, kReduceThreads, smem, st>>>(scratch, (unsigned)blocks, init, reduceAccOp, result);
-  bool ok = cudaGetLastError() == cudaSuccess;
-  if (ok && !outOnDevice) ok = cudaMemcpyAsync(out, result, sizeof(AccT), cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    reduce_all_kernel<T, ModifyOp, ReduceOp, ReduceAccOp, AccT><<<(unsigned)blocks, kReduceThreads, smem, st>>>(
+        (const T *)din.data, vin, (uint64_t)n, init, modifyOp, reduceOp, reduceAccOp, partials, ticket, result);
+  ok = (cudaGetLastError() == cudaSuccess) && ok;
+  if (ok && !outOnDevice && !slot) ok = cudaMemcpyAsync(out, result, sizeof(AccT), cudaMemcpyDeviceToHost, st) == cudaSuccess;
   // the scratch is released in stream order; only a host result waits for the stream
   cudaFreeAsync(scratch, st);
-  if (!outOnDevice) ok = (cudaStreamSynchronize(st) == cudaSuccess) && ok;
+  if (!outOnDevice) {
+    ok = (cudaStreamSynchronize(st) == cudaSuccess) && ok;
+    if (ok && slot) memcpy(out, slot, sizeof(AccT));
+  }
   return ok;
 }
 
