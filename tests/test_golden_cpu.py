@@ -49,7 +49,7 @@ def test_index_to_offset_matches_reference_fixtures():
             assert lib.thcb200_index_to_offset(C.byref(dc), linear) == off, case
 
 
-def test_baseline_config_views_collapse_as_surveyed():
+def test_baseline_config_views_collapse_to_the_golden_views():
     lib = _lib.load_library()
     assert product_collapse(lib, [64, 256, 56, 56], [802816, 3136, 56, 1], -1) == ([51380224], [1], -1)
     assert product_collapse(lib, [64, 256, 56, 56], [1605632, 6272, 112, 2], -1) == ([51380224], [2], -1)
