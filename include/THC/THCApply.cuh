@@ -183,6 +183,7 @@ struct Walk {
 };
 static_assert(kThreads == 256, "a block of the patch walk is 32 rows (8 warps x 4) x 8 columns per element of a thread");
 constexpr int kPerThreadPatch = 4;   // elements per thread in the patch walk: patches of 32 rows x 32 columns (8 per thread: 215 -> 268 us)
+static_assert(kPerThreadPatch == kPerThread, "views of more than two dims take the patch walk in the kernels built for kPerThread");
 
 // N of the patch walk this operand asks for, or 0
 template <typename IndexT>
@@ -450,7 +451,7 @@ bool THC_pointwiseApply2(THCState *state, TensorTypeA *a, TensorTypeB *b, const 
 #define THCB_USER_LAUNCH2(IDX, NA)                                                                                   \
   do {                                                                                                               \
     const bool two = sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2;                                               \
-    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, two ? patchN : 0);                                           \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                     \
     if (two && w.N)                                                                                                  \
       apply2_kernel<Op, Ta, Tb, IDX, NA, View2<IDX>, kPerThreadPatch><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>( \
           (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), w, op);         \
@@ -504,7 +505,7 @@ bool THC_pointwiseApply3(THCState *state, TensorTypeA *a, TensorTypeB *b, Tensor
 #define THCB_USER_LAUNCH3(IDX, NA)                                                                                       \
   do {                                                                                                                   \
     const bool two = sizeof(IDX) == 4 && va.dims <= 2 && vb.dims <= 2 && vc.dims <= 2;                                   \
-    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, two ? patchN : 0);                                               \
+    const Walk<IDX> w = make_walk<IDX>((uint64_t)n, patchN);                                                         \
     if (two && w.N)                                                                                                      \
       apply3_kernel<Op, Ta, Tb, Tc, IDX, NA, View2<IDX>, kPerThreadPatch><<<grid_for_blocks(w.nblk), kThreads, 0, st>>>( \
           (Ta *)da.data, two_dims(va, w, (uint64_t)n), (Tb *)db.data, two_dims(vb, w, (uint64_t)n), (Tc *)dc.data,      \

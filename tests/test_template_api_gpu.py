@@ -51,6 +51,13 @@ def test_apply2_patch_walk_and_dense_runs(state, user):
         assert user.usertest_scale(state.ptr, ddst.ptr, dsrc.ptr, 0.5) == 1
         want = (np.ascontiguousarray(src) * np.float32(0.5)).astype(np.float32) + np.float32(1)
         assert_bit_equal(ddst.numpy(), want, f"user functor {shape} {la}/{lb}")
+    # three collapsed dims whose last two are transposed (padded rows keep the outer dim from merging): the patch walk
+    # with the dim-by-dim decode
+    base3 = r.standard_normal((5, 50, 43)).astype(np.float32)
+    src3 = base3[:, :, :40].transpose(0, 2, 1)
+    dst3 = thc.Tensor.new(state, "Float", 5, 40, 50)
+    assert user.usertest_scale(state.ptr, dst3.ptr, to_device(state, src3).ptr, 2.0) == 1
+    assert_bit_equal(dst3.numpy(), np.ascontiguousarray(src3) * np.float32(2.0) + np.float32(1), "3-D source, last two dims transposed")
     # same storage for both operands: a shifted dense window (not 16-byte aligned, may alias)
     base = r.standard_normal(5000).astype(np.float32)
     dbase = to_device(state, base)
