@@ -158,9 +158,10 @@ constexpr int kSlotsPerBlock = kThreads * kPerThread;
 // warp four rows of it and a warp instruction a piece of 4 rows x 8 columns, so that every operand
 // is touched in runs of 16 or 32 bytes and the rest of each line is used by the same CTA out of the
 // L1.  Only the assignment of elements to threads changes: the functor still gets the element's
-// own pointers.  (Measured on a 16384 x 8192 fp32 transposed source: pieces of 8 x 4 instead of
-// 4 x 8, or patches numbered in 8 x 8 clusters instead of row by row, were slower; the kernel is
-// bound by instruction issue, so the index arithmetic is kept as short as it can be.)
+// own pointers.  (Measured on a 16384 x 8192 fp32 transposed source: pieces of 8 x 4 or 2 x 16
+// instead of 4 x 8, patches numbered in 8 x 8 clusters instead of row by row, and eight elements per
+// thread were each slower.  With a dim-by-dim offset decode the kernel was bound by instruction
+// issue, hence the short index arithmetic here and in View2.)
 template <typename IndexT>
 struct Walk {
   IndexT n, nblk;
