@@ -124,7 +124,8 @@ __attribute__((visibility("default"))) int usertest_minmax_all(THCState *state, 
 // Lua threads).  Thread 0 stays on the default stream; every other thread makes a stream of its own
 // current (thread-local, lib/THC/THCGeneral.c:516-561) and checks that it alone sees it.  Each then
 // runs, `iters` times on its own tensors, the calls that keep partial results in per-stream scratch:
-// a full sum, a sum over the outer dim split over many CTAs, a chunked cumulative sum.  All values are
+// a full sum, a sum over the outer dim split over many CTAs, a chunked cumulative sum, and a full
+// reduction through the template header (result in a per-thread pinned slot).  All values are
 // small integers, so every expected result is exact.  Returns the number of wrong results.
 __attribute__((visibility("default"))) int usertest_threads(THCState *state, int nthreads, int iters) {
   std::vector<int> bad((size_t)nthreads, 0);
@@ -156,6 +157,9 @@ __attribute__((visibility("default"))) int usertest_threads(THCState *state, int
         THCudaTensor_sum(state, colsum, m, 0, 1);
         if (THCudaTensor_sumall(state, colsum) != v * (float)(rows * cols)) ++wrong;
         if (THCudaTensor_maxall(state, colsum) != v * (float)rows) ++wrong;
+        // the template full reduction writes its host result into a pinned slot of the calling thread
+        float biggest = -1.0f;
+        if (!THC_reduceAll(state, m, AbsF(), MaxF(), MaxF(), 0.0f, &biggest, 0) || biggest != v) ++wrong;
         THCudaTensor_cumsum(state, scan, line, 0);
         if (THCudaTensor_maxall(state, scan) != (float)n1) ++wrong;
         if (THCudaTensor_sumall(state, scan) != (float)((double)n1 * (double)(n1 + 1) / 2.0)) ++wrong;
